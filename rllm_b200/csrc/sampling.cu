@@ -1,0 +1,198 @@
+// Token selection from float logits [R, V]: greedy argmax (lowest index wins a
+// tie) and the reference's sampling pipeline
+//   x/T -> top-k mask -> softmax -> min-p -> top-p -> inverse CDF in vocabulary order
+// (src/model/sampler.rs:361-499), one block per row, no scratch memory: the
+// probabilities are recomputed from the logits in every pass (V floats stay in L2).
+//
+// Instead of sorting, top-k and top-p find their thresholds by bisection on
+// the bit pattern of a float: "the k-th largest logit" and "the largest
+// probability tau such that the mass of {p >= tau} reaches top_p". Ties at a
+// threshold are all kept, as in sampler.rs:397-403.
+#include "common.cuh"
+using namespace rllm;
+
+namespace {
+
+constexpr int THREADS = 1024;
+
+// monotone map float -> uint32 (order-preserving)
+__device__ __forceinline__ unsigned f2key(float f) {
+  unsigned u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key2f(unsigned k) {
+  unsigned u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+  return __uint_as_float(u);
+}
+
+__global__ void __launch_bounds__(THREADS)
+argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const float* x = logits + (size_t)blockIdx.x * V;
+  float best = -INFINITY; int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = x[i];
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }   // NaN never wins
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    best = lane < nw ? sv[lane] : -INFINITY;
+    bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+  }
+}
+
+__device__ __forceinline__ float block_sum_f(float v, float* red) { return block_sum(v, red); }
+
+__device__ __forceinline__ int block_sum_i(int v, int* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  int r = (lane < (int)(blockDim.x >> 5)) ? red[lane] : 0;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+  return r;
+}
+
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const float* __restrict__ min_p, const float* __restrict__ uniform,
+              int* __restrict__ out) {
+  __shared__ float redf[32];
+  __shared__ int redi[32];
+  __shared__ float seg[THREADS];
+  __shared__ int pick_thread;
+  const int row = blockIdx.x;
+  const float* x = logits + (size_t)row * V;
+  const float T = temperature[row];
+  const float invT = 1.f / T;
+  const int tid = threadIdx.x;
+
+  // 1. top-k threshold on the scaled logits (k-th largest; ties kept)
+  float thr = -INFINITY;
+  const int k = top_k ? top_k[row] : 0;
+  if (k > 0 && k < V) {
+    unsigned lo = 0u, hi = 0xffffffffu;      // largest key with count(key' >= key) >= k
+    while (lo < hi) {
+      const unsigned mid = lo + ((hi - lo) >> 1) + 1u;
+      int c = 0;
+      for (int i = tid; i < V; i += THREADS) c += (f2key(x[i] * invT) >= mid);
+      c = block_sum_i(c, redi);
+      if (c >= k) lo = mid; else hi = mid - 1u;
+    }
+    thr = key2f(lo);
+  }
+  // 2. softmax over the kept logits
+  float mx = -INFINITY;
+  for (int i = tid; i < V; i += THREADS) { const float v = x[i] * invT; if (v >= thr) mx = fmaxf(mx, v); }
+  mx = block_max(mx, redf);
+  float sum = 0.f;
+  for (int i = tid; i < V; i += THREADS) { const float v = x[i] * invT; if (v >= thr) sum += expf(v - mx); }
+  sum = block_sum_f(sum, redf);
+  // 3. min-p: drop p < min_p * max p. With e = exp(v - max) the largest e is 1, so the
+  //    rule is e < min_p, exact in the e domain; renormalise over what is kept.
+  const float emin = min_p ? fmaxf(min_p[row], 0.f) : 0.f;
+#define EXPV(i) ((x[i] * invT >= thr) ? expf(x[i] * invT - mx) : 0.f)
+  if (emin > 0.f) {
+    float kept = 0.f;
+    for (int i = tid; i < V; i += THREADS) { const float e = EXPV(i); if (e >= emin) kept += e; }
+    sum = block_sum_f(kept, redf);
+  }
+  const float inv_sum = 1.f / sum;
+#define PROB(i) ([&]() { const float e_ = EXPV(i); return e_ >= emin ? e_ * inv_sum : 0.f; }())
+  // 4. top-p: largest tau with mass{p >= tau} >= top_p
+  const float tp = top_p ? top_p[row] : 1.f;
+  float tau = 0.f;
+  float mass = 1.f;
+  if (tp < 1.f) {
+    unsigned lo = 0u, hi = __float_as_uint(1.0f);
+    while (lo < hi) {
+      const unsigned mid = lo + ((hi - lo) >> 1) + 1u;
+      const float cand = __uint_as_float(mid);
+      float ms = 0.f;
+      for (int i = tid; i < V; i += THREADS) { const float p = PROB(i); if (p >= cand) ms += p; }
+      ms = block_sum_f(ms, redf);
+      if (ms >= tp) lo = mid; else hi = mid - 1u;
+    }
+    tau = __uint_as_float(lo);
+    float ms = 0.f;
+    for (int i = tid; i < V; i += THREADS) { const float p = PROB(i); if (p >= tau) ms += p; }
+    mass = block_sum_f(ms, redf);
+  }
+  // 5. inverse CDF in vocabulary order: first i with cumulative > u * mass
+  const int per = (V + THREADS - 1) / THREADS;
+  const int b = tid * per, e = min(V, b + per);
+  float local = 0.f;
+  for (int i = b; i < e; ++i) { const float p = PROB(i); if (p >= tau && p > 0.f) local += p; }
+  seg[tid] = local;
+  if (tid == 0) pick_thread = -1;
+  __syncthreads();
+  if (tid == 0) {
+    const float target = uniform[row] * mass;
+    float cum = 0.f; int last = -1;
+    for (int i = 0; i < THREADS; ++i) {
+      if (seg[i] > 0.f) last = i;
+      if (cum + seg[i] > target) { pick_thread = i; redf[0] = cum; break; }
+      cum += seg[i];
+    }
+    redf[1] = target;
+    // rounding left none above the target: the last entry with mass is taken
+    if (pick_thread < 0) { pick_thread = last < 0 ? 0 : last; redf[0] = 0.f; redf[1] = INFINITY; }
+  }
+  __syncthreads();
+  if (tid == pick_thread) {
+    float cum = redf[0]; const float target = redf[1];
+    int chosen = -1, last = -1;
+    for (int i = b; i < e; ++i) {
+      const float p = PROB(i);
+      if (!(p >= tau && p > 0.f)) continue;
+      last = i;
+      cum += p;
+      if (cum > target) { chosen = i; break; }
+    }
+    out[row] = chosen >= 0 ? chosen : (last >= 0 ? last : 0);
+  }
+#undef PROB
+#undef EXPV
+}
+
+}  // namespace
+
+RLLM_API int rllm_argmax(const float* logits, int R, int V, int* out, void* stream) {
+  if (R <= 0) return 0;
+  if (V <= 0) return ERR_BAD_SIZE;
+  argmax_kernel<<<R, THREADS, 0, (cudaStream_t)stream>>>(logits, V, out);
+  return launch_status();
+}
+
+// Per-row parameter arrays of length R; top_k / top_p / min_p may be null (off).
+// temperature must be > 0 (the caller sends temperature 0 to rllm_argmax).
+RLLM_API int rllm_sample(const float* logits, int R, int V, const float* temperature,
+                         const int* top_k, const float* top_p, const float* min_p,
+                         const float* uniform, int* out, void* stream) {
+  if (R <= 0) return 0;
+  if (V <= 0) return ERR_BAD_SIZE;
+  sample_kernel<<<R, THREADS, 0, (cudaStream_t)stream>>>(logits, V, temperature, top_k, top_p,
+                                                         min_p, uniform, out);
+  return launch_status();
+}

@@ -1,0 +1,189 @@
+// Generic element-wise and row-wise kernels, both precisions: embedding gather,
+// RMSNorm, rotary position encoding fused with the write of K and V into the
+// paged cache, row gather, residual add, SiLU-gate. All arithmetic in float;
+// one rounding on store.
+#include "common.cuh"
+using namespace rllm;
+
+// ---------------------------------------------------------------- embedding
+// out[t, :] = table[ids[t], :]  (reference: src/gpu/cuda/shaders/embed.cu:24-59)
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
+                             float* __restrict__ out, int H, int V, int* __restrict__ err) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= V) {           // never read outside the table: flag and emit zeros
+    if (threadIdx.x == 0 && err) atomicExch(err, 1);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)t * H + i] = 0.f;
+    return;
+  }
+  const TW* row = table + (size_t)id * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)t * H + i] = to_f32(row[i]);
+}
+
+RLLM_API int rllm_embed(const int* ids, const void* table, int table_dt, float* out, int T, int H,
+                        int V, int* err, void* stream) {
+  if (T <= 0) return 0;
+  const int threads = H >= 256 ? 256 : (H >= 128 ? 128 : 64);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (table_dt == DT_F32) embed_kernel<float><<<T, threads, 0, s>>>(ids, (const float*)table, out, H, V, err);
+  else if (table_dt == DT_BF16) embed_kernel<bf16><<<T, threads, 0, s>>>(ids, (const bf16*)table, out, H, V, err);
+  else return ERR_BAD_DTYPE;
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// y = x * rsqrt(mean(x^2) + eps) * w   (reference: src/gpu/cuda/shaders/rms_norm.cu:78-115)
+// x is the float residual stream; w float or bf16; y float or bf16.
+// The sum of squares is taken in a fixed order that depends on H only.
+template <typename TW, typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w,
+                               TO* __restrict__ y, int H, float eps) {
+  __shared__ float red[32];
+  const float* xr = x + (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = xr[i]; ss = fmaf(v, v, ss); }
+  ss = block_sum(ss, red);
+  const float r = rsqrtf(ss / (float)H + eps);
+  TO* yr = y + (size_t)blockIdx.x * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = from_f32<TO>(xr[i] * r * to_f32(w[i]));
+}
+
+RLLM_API int rllm_rmsnorm(const float* x, const void* w, int w_dt, void* y, int y_dt, int T, int H,
+                          float eps, void* stream) {
+  if (T <= 0) return 0;
+  const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+  cudaStream_t s = (cudaStream_t)stream;
+#define GO(TW, TO) rmsnorm_kernel<TW, TO><<<T, threads, 0, s>>>(x, (const TW*)w, (TO*)y, H, eps)
+  if (w_dt == DT_F32 && y_dt == DT_F32) GO(float, float);
+  else if (w_dt == DT_F32 && y_dt == DT_BF16) GO(float, bf16);
+  else if (w_dt == DT_BF16 && y_dt == DT_F32) GO(bf16, float);
+  else if (w_dt == DT_BF16 && y_dt == DT_BF16) GO(bf16, bf16);
+  else return ERR_BAD_DTYPE;
+#undef GO
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- RoPE + cache write
+// qkv: [T, (nh + 2 nkv) * hd], q heads first, then k heads, then v heads.
+// Pair (i, i + rot_dim/2), i < rot_dim/2, of every q and k head is rotated by angle
+// pos * inv_freq[i] (float; rot_dim = hd for Llama), q in place; rotated k and plain v go to the paged cache at `slots[t]`
+// (= page * page_size + offset, or < 0 to skip the write).
+// Cache layout: [page][kv head][offset in page][hd].
+// Reference: src/gpu/cuda/shaders/rope.cu:62-77 and attention.cu:295-300.
+template <typename T>
+__global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                  const float* __restrict__ inv_freq, const int* __restrict__ slots,
+                                  T* __restrict__ kcache, T* __restrict__ vcache, int nh, int nkv,
+                                  int hd, int page_size, int rot_dim) {
+  const int t = blockIdx.x;
+  const int half = hd / 2;
+  const int width = (nh + 2 * nkv) * hd;
+  T* row = qkv + (size_t)t * width;
+  const float pos = (float)positions[t];
+  const int slot = slots ? slots[t] : -1;
+  const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+  const int rh = rot_dim / 2;                 // rotated pairs are (i, i + rh), i < rh
+  const int n_rot = (nh + nkv) * half;
+  for (int idx = threadIdx.x; idx < n_rot; idx += blockDim.x) {
+    const int head = idx / half, i = idx % half;
+    T* hp = row + (size_t)head * hd;
+    int ia, ib;
+    if (i < rh) { ia = i; ib = i + rh; } else { ia = rot_dim + 2 * (i - rh); ib = ia + 1; }
+    float a = to_f32(hp[ia]), b = to_f32(hp[ib]);
+    float ra = a, rb = b;
+    if (i < rh) {
+      float sn, cs;
+      sincosf(pos * inv_freq[i], &sn, &cs);
+      ra = a * cs - b * sn;
+      rb = a * sn + b * cs;
+    }
+    if (head < nh) {
+      if (i < rh) { hp[ia] = from_f32<T>(ra); hp[ib] = from_f32<T>(rb); }
+    } else if (slot >= 0) {
+      const int kvh = head - nh;
+      T* dst = kcache + (((size_t)page * nkv + kvh) * page_size + off) * hd;
+      dst[ia] = from_f32<T>(ra);
+      dst[ib] = from_f32<T>(rb);
+    }
+  }
+  if (slot >= 0) {
+    const T* vrow = row + (size_t)(nh + nkv) * hd;
+    for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
+      const int kvh = idx / hd, d = idx % hd;
+      vcache[(((size_t)page * nkv + kvh) * page_size + off) * hd + d] = vrow[idx];
+    }
+  }
+}
+
+RLLM_API int rllm_rope_cache_write(void* qkv, int dt, const int* positions, const float* inv_freq,
+                                   const int* slots, void* kcache, void* vcache, int T, int nh,
+                                   int nkv, int hd, int page_size, int rot_dim, void* stream) {
+  if (T <= 0) return 0;
+  if (hd % 2 || rot_dim % 2 || rot_dim > hd || rot_dim < 0) return ERR_BAD_SIZE;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int work = (nh + nkv) * hd / 2;
+  const int threads = work >= 512 ? 256 : (work >= 128 ? 128 : 64);
+  if (dt == DT_F32)
+    rope_cache_kernel<float><<<T, threads, 0, s>>>((float*)qkv, positions, inv_freq, slots,
+                                                   (float*)kcache, (float*)vcache, nh, nkv, hd,
+                                                   page_size, rot_dim);
+  else if (dt == DT_BF16)
+    rope_cache_kernel<bf16><<<T, threads, 0, s>>>((bf16*)qkv, positions, inv_freq, slots,
+                                                  (bf16*)kcache, (bf16*)vcache, nh, nkv, hd,
+                                                  page_size, rot_dim);
+  else return ERR_BAD_DTYPE;
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- small helpers
+// out[r, :] = x[rows[r], :]   (float rows of the residual stream)
+__global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                   float* __restrict__ out, int H) {
+  const float* src = x + (size_t)rows[blockIdx.x] * H;
+  float* dst = out + (size_t)blockIdx.x * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+}
+RLLM_API int rllm_gather_rows(const float* x, const int* rows, float* out, int R, int H, void* stream) {
+  if (R <= 0) return 0;
+  gather_rows_kernel<<<R, H >= 256 ? 256 : 64, 0, (cudaStream_t)stream>>>(x, rows, out, H);
+  return launch_status();
+}
+
+// residual[i] += delta[i]   (float accumulate; delta float or bf16)
+template <typename T>
+__global__ void add_into_kernel(float* __restrict__ res, const T* __restrict__ delta, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) res[i] += to_f32(delta[i]);
+}
+RLLM_API int rllm_add_into(float* res, const void* delta, int dt, long long n, void* stream) {
+  if (n <= 0) return 0;
+  const int threads = 256;
+  const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dt == DT_F32) add_into_kernel<float><<<blocks, threads, 0, s>>>(res, (const float*)delta, (size_t)n);
+  else if (dt == DT_BF16) add_into_kernel<bf16><<<blocks, threads, 0, s>>>(res, (const bf16*)delta, (size_t)n);
+  else return ERR_BAD_DTYPE;
+  return launch_status();
+}
+
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i]   (reference: elementwise.cu:36-49)
+template <typename T>
+__global__ void silu_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t n) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n) return;
+  size_t t = idx / I; int i = (int)(idx % I);
+  float g = to_f32(gu[t * 2 * I + i]), u = to_f32(gu[t * 2 * I + I + i]);
+  out[idx] = from_f32<T>(g / (1.f + expf(-g)) * u);
+}
+RLLM_API int rllm_silu_gate(const void* gu, void* out, int dt, int T, int I, void* stream) {
+  size_t n = (size_t)T * I;
+  if (n == 0) return 0;
+  const int threads = 256;
+  const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dt == DT_F32) silu_gate_kernel<float><<<blocks, threads, 0, s>>>((const float*)gu, (float*)out, I, n);
+  else if (dt == DT_BF16) silu_gate_kernel<bf16><<<blocks, threads, 0, s>>>((const bf16*)gu, (bf16*)out, I, n);
+  else return ERR_BAD_DTYPE;
+  return launch_status();
+}

@@ -1,0 +1,93 @@
+"""Chooses the kernel for each operation of a run.
+
+`Backend(torch.float32)` is the true 32-bit path: float storage everywhere and
+FMA kernels only. `Backend(torch.bfloat16)` is the serving path: bfloat16
+weights, activations and cache, float residual stream and logits; it sends
+matrix products to the tcgen05 kernel and attention to the tiled kernels when
+those take the sizes at hand, and to the generic CUDA-core kernels otherwise.
+Both are hand-written CUDA; there is nothing else to fall back to.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from . import ops
+
+
+class Backend:
+    def __init__(self, dtype: torch.dtype, device: torch.device | str = "cuda:0"):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"run dtype must be float32 or bfloat16, got {dtype}")
+        self.dtype = dtype
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise ops.KernelError("the engine runs on a CUDA device only (there is no CPU path)")
+        self.fast = dtype == torch.bfloat16 and os.environ.get("RLLM_B200_GENERIC_ONLY") != "1"
+        self._sm100 = None
+        if self.fast:
+            from . import sm100          # builds/loads the tcgen05 library, or raises
+            self._sm100 = sm100
+            sm100.init(self.device)
+
+    # ---- element-wise / row-wise
+    def embed(self, ids, table, err=None):
+        return ops.embed(ids, table, err=err)
+
+    def rmsnorm(self, x, w, eps, out_dtype=None):
+        return ops.rmsnorm(x, w, eps, out_dtype or self.dtype)
+
+    def gather_rows(self, x, rows):
+        return ops.gather_rows(x, rows)
+
+    def add_into(self, residual, delta):
+        return ops.add_into(residual, delta)
+
+    # ---- matrix products: y = x W^T
+    def _tc(self, x, w):
+        return self._sm100 is not None and self._sm100.gemm_supported(x, w)
+
+    def linear(self, x, w, bias=None):
+        if bias is None and self._tc(x, w):
+            return self._sm100.gemm(x, w, ops.EPI_STORE)
+        return ops.gemm_simt(x, w, ops.EPI_STORE, bias=bias)
+
+    def linear_f32(self, x, w):
+        if self._tc(x, w):
+            return self._sm100.gemm(x, w, ops.EPI_STORE_F32)
+        return ops.gemm_simt(x, w, ops.EPI_STORE_F32)
+
+    def linear_residual(self, x, w, residual):
+        """residual (float32, in place) += x W^T"""
+        if self._tc(x, w):
+            return self._sm100.gemm(x, w, ops.EPI_ACCUM_F32, out=residual)
+        return ops.gemm_simt(x, w, ops.EPI_ACCUM_F32, out=residual)
+
+    def linear_swiglu(self, x, w_gate_up):
+        """silu(x Wg^T) * (x Wu^T) with w_gate_up = [Wg; Wu]"""
+        if self._tc(x, w_gate_up):
+            return self._sm100.gemm(x, w_gate_up, ops.EPI_SWIGLU)
+        return ops.gemm_simt(x, w_gate_up, ops.EPI_SWIGLU)
+
+    # ---- position encoding + cache write, attention
+    def rope_cache_write(self, qkv, positions, inv_freq, cache, nh, nkv, hd, rot_dim=None):
+        writes = cache.writes
+        ops.rope_cache_write(qkv, positions, inv_freq, cache.slots if writes else None,
+                             cache.k if writes else None, cache.v if writes else None,
+                             nh, nkv, hd, cache.page_size, rot_dim)
+
+    def attention(self, q, cache, ctx, nh, scale, window):
+        if self._sm100 is not None:
+            out = self._sm100.attention(q, cache, ctx, nh, scale, window)
+            if out is not None:
+                return out
+        return ops.paged_attention_simt(q, cache.k, cache.v, ctx.token_seq, ctx.positions,
+                                        cache.block_table, nh, scale, window)
+
+    # ---- selection
+    def argmax(self, logits):
+        return ops.argmax(logits)
+
+    def sample(self, logits, temperature, uniform, top_k=None, top_p=None, min_p=None):
+        return ops.sample(logits, temperature, uniform, top_k, top_p, min_p)

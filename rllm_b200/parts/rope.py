@@ -1,0 +1,63 @@
+"""Rotary position encoding as a part: a table of inverse frequencies, made once on the
+host in float64 and kept as float32; the rotation itself runs inside the kernel that
+also writes K and V to the cache.
+
+Plain rule f_i = theta^(-2i/d): src/gpu/cuda/shaders/rope.cu:62-66 of the reference.
+llama3 rule: the three bands of the reference's "yarn" kernel
+(src/gpu/cuda/shaders/rope.cu:233-251) with beta_fast = high_freq_factor and
+beta_slow = low_freq_factor. The reference parses `rope_scaling` for Llama
+(src/model/config.rs:724-746) but never applies it; here it is applied.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .base import Part, register_part
+
+
+def inverse_frequencies(rot_dim: int, theta: float, scaling=None) -> list[float]:
+    """The rot_dim/2 inverse frequencies in float64, scaling rule applied."""
+    out = []
+    for i in range(rot_dim // 2):
+        f = float(theta) ** (-2.0 * i / rot_dim)
+        if scaling is not None and scaling.rope_type == "llama3":
+            orig = float(scaling.original_max_position_embeddings)
+            wavelen = 2.0 * math.pi / f
+            if wavelen < orig / scaling.high_freq_factor:
+                pass
+            elif wavelen > orig / scaling.low_freq_factor:
+                f = f / scaling.factor
+            else:
+                s = (orig / wavelen - scaling.low_freq_factor) / \
+                    (scaling.high_freq_factor - scaling.low_freq_factor)
+                f = (1.0 - s) * f / scaling.factor + s * f
+        elif scaling is not None and scaling.rope_type == "linear":
+            f = f / scaling.factor
+        out.append(f)
+    return out
+
+
+class RotaryEmbedding(Part):
+    """Rotates pairs (i, i + rot_dim/2) of each head by position * f_i."""
+
+    def __init__(self, head_dim: int, theta: float, scaling=None, rot_dim: int | None = None):
+        self.head_dim = head_dim
+        self.rot_dim = head_dim if rot_dim is None else rot_dim
+        if self.rot_dim % 2 or self.rot_dim > head_dim:
+            raise ValueError(f"rotary width {self.rot_dim} must be even and <= head_dim {head_dim}")
+        self.theta, self.scaling = float(theta), scaling
+        self.inv_freq = None
+
+    def finalize(self, device, dtype):
+        f = inverse_frequencies(self.rot_dim, self.theta, self.scaling)
+        self.inv_freq = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(device)
+
+    def rotate_and_store(self, qkv, ctx, cache, nh, nkv):
+        """Rotate q (in place) and k of `qkv`, and write k, v into the layer's pages."""
+        ctx.backend.rope_cache_write(qkv, ctx.positions, self.inv_freq, cache, nh, nkv,
+                                     self.head_dim, self.rot_dim)
+
+
+register_part("position", "rope", RotaryEmbedding)

@@ -1,0 +1,64 @@
+"""Chooses tokens from a step's logits on the device: argmax rows and sampled rows in one
+pass each, parameters per row. Pipeline of the reference's `sample_from_logits`
+(src/model/sampler.rs:328-547): penalties -> temperature -> top-k -> softmax -> min-p ->
+top-p -> inverse CDF."""
+from __future__ import annotations
+
+import torch
+
+from .params import SamplingParams
+from .rng import uniform
+
+
+class Sampler:
+    def __init__(self, backend):
+        self.backend = backend
+        self.device = backend.device
+
+    def __call__(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int],
+                 indices: list[int], histories: list[list[int]] | None = None) -> list[int]:
+        """logits float32 [R, V]; row r is drawn with params[r] and the uniform number of
+        (seeds[r], indices[r]). `histories[r]`: the tokens generated so far (for penalties)."""
+        R = logits.shape[0]
+        assert R == len(params) == len(seeds) == len(indices)
+        if any(p.has_penalties for p in params):
+            logits = self._penalise(logits, params, histories)
+        be = self.backend
+        if all(p.greedy for p in params):
+            return be.argmax(logits).tolist()
+        f32 = dict(dtype=torch.float32, device=self.device)
+        temp = torch.tensor([p.temperature if not p.greedy else 1.0 for p in params], **f32)
+        u = torch.tensor([uniform(s, i) for s, i in zip(seeds, indices)], **f32)
+        top_k = top_p = min_p = None
+        if any(p.top_k > 0 for p in params):
+            top_k = torch.tensor([p.top_k for p in params], dtype=torch.int32, device=self.device)
+        if any(p.top_p < 1.0 for p in params):
+            top_p = torch.tensor([p.top_p for p in params], **f32)
+        if any(p.min_p > 0.0 for p in params):
+            min_p = torch.tensor([p.min_p for p in params], **f32)
+        drawn = be.sample(logits, temp, u, top_k, top_p, min_p).tolist()
+        if any(p.greedy for p in params):
+            best = be.argmax(logits).tolist()
+            drawn = [b if p.greedy else d for p, b, d in zip(params, best, drawn)]
+        return drawn
+
+    def _penalise(self, logits, params, histories):
+        """logit[token] -= frequency_penalty * count + presence_penalty for tokens already
+        generated (src/model/sampler.rs:341-350). A handful of entries per row: a scatter of
+        host-computed values into a copy of the logits."""
+        rows, cols, vals = [], [], []
+        for r, (p, hist) in enumerate(zip(params, histories or [[]] * len(params))):
+            if not p.has_penalties or not hist:
+                continue
+            counts: dict[int, int] = {}
+            for t in hist:
+                counts[t] = counts.get(t, 0) + 1
+            for t, c in counts.items():
+                rows.append(r); cols.append(t)
+                vals.append(-(p.frequency_penalty * c + p.presence_penalty))
+        if not rows:
+            return logits
+        out = logits.clone()
+        out.index_put_((torch.tensor(rows, device=self.device), torch.tensor(cols, device=self.device)),
+                       torch.tensor(vals, dtype=torch.float32, device=self.device), accumulate=True)
+        return out

@@ -1,0 +1,95 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16, for every way of
+cutting the same requests into steps. A difference that shows in one family only is a fault
+of the cache or the batch; the failure names the first wrong (request, position)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import replay
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+# Largest error relative to the largest logit. 32-bit: only summation order differs
+# (measured 2e-6 or less on these models). bfloat16: weights are the same bfloat16
+# values in both, activations and cache are rounded to 8 bits of mantissa at every
+# layer boundary (measured up to 1.2e-2 on these models).
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+
+LENGTHS = {"A": [5, 11, 17, 40, 70], "B": [3, 9, 24, 40, 97], "C": [6, 33, 58, 90, 121]}
+
+
+def requests_for(name):
+    vocab = tiny.TINY[name][0]["vocab_size"]
+    return {f"r{i}": tiny.random_prompt(n, vocab, 100 + i) for i, n in enumerate(LENGTHS[name])}
+
+
+@pytest.fixture(scope="module")
+def model_dirs(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    return {n: tiny.make_model_dir(root, n) for n in tiny.TINY}
+
+
+@pytest.fixture(scope="module")
+def plain(model_dirs):
+    return {n: replay.plain_logits(model_dirs[n], requests_for(n)) for n in tiny.TINY}
+
+
+def engine_for(model_dir, name, dtype, max_tokens):
+    from rllm_b200.engine import load_engine
+    return load_engine(model_dir, dtype=dtype, page_size=tiny.TINY[name][4], max_tokens=max_tokens,
+                       max_requests=8)
+
+
+FAMILIES = {
+    "whole": replay.whole,
+    "prefill_then_decode": replay.prefill_then_decode,
+    "portions": replay.portions,
+    "mixed": replay.mixed,
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(tiny.TINY))
+@pytest.mark.parametrize("family", list(FAMILIES))
+def test_family_matches_plain(model_dirs, plain, name, dtype, family):
+    reqs = requests_for(name)
+    steps = FAMILIES[family](reqs)
+    # a pool just large enough, so pages of finished requests are used again
+    eng = engine_for(model_dirs[name], name, dtype, replay.max_live_tokens(steps, reqs))
+    got = replay.run_in_process(eng, steps)
+    worst = replay.compare(got, plain[name], TOL[dtype], f"tiny-{name} {dtype} {family}")
+    assert all(n == eng.cache.groups[0].pool.num_pages for n in eng.cache.free_pages())
+    print(f"tiny-{name} {dtype} {family}: worst relative error {worst:.2e}")
+
+
+@pytest.mark.parametrize("name", list(tiny.TINY))
+def test_float32_is_the_same_however_it_is_cut(model_dirs, name):
+    """In 32-bit every family gives bit-identical logits: each output element is summed in
+    an order that depends on its position only."""
+    reqs = requests_for(name)
+    base = None
+    for family, make in FAMILIES.items():
+        steps = make(reqs)
+        eng = engine_for(model_dirs[name], name, "float32", replay.max_live_tokens(steps, reqs))
+        got = replay.run_in_process(eng, steps)
+        if base is None:
+            base = got
+        else:
+            for key in base:
+                assert np.array_equal(base[key], got[key]), f"{family}: {key} differs from whole"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(model_dirs, plain, tmp_path, dtype):
+    """The same through bin/trace_run (a process of its own, JSON in, .f32 files out)."""
+    name = "B"
+    reqs = requests_for(name)
+    steps = replay.mixed(reqs)
+    vocab = tiny.TINY[name][0]["vocab_size"]
+    got = replay.run_program(model_dirs[name], dtype, steps, str(tmp_path / "out"),
+                             replay.max_live_tokens(steps, reqs), vocab,
+                             extra_args=["--page-size", str(tiny.TINY[name][4])])
+    replay.compare(got, plain[name], TOL[dtype], f"trace_run {dtype}")

@@ -1,0 +1,53 @@
+"""The tests' own small configurations. They differ in every size and option: head counts
+and groups, head size, widths that are no power of two, layers, vocabulary, eps, rope rule,
+tied or separate output matrix, window, page size, weight scale."""
+import os
+
+import torch
+
+TINY_A = {  # 2 layers, 4 heads in 2 groups, head 16, tied, plain rope
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 64, "num_hidden_layers": 2, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 16, "intermediate_size": 128, "vocab_size": 256,
+    "max_position_embeddings": 128, "rope_theta": 10000.0, "rope_scaling": None,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+}
+TINY_B = {  # 3 layers, 3 heads on 1 kv head, head 32, hidden 96, untied, llama3 rope
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 96, "num_hidden_layers": 3, "num_attention_heads": 3,
+    "num_key_value_heads": 1, "head_dim": 32, "intermediate_size": 224, "vocab_size": 384,
+    "max_position_embeddings": 256, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 32},
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+}
+TINY_C = {  # 4 layers, 6 heads in 3 groups, head 48 (hidden 80 != heads*head), windows on 2 layers
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 80, "num_hidden_layers": 4, "num_attention_heads": 6,
+    "num_key_value_heads": 3, "head_dim": 48, "intermediate_size": 176, "vocab_size": 200,
+    "max_position_embeddings": 512, "rope_theta": 20000.0,
+    "rope_scaling": {"rope_type": "linear", "factor": 2.0},
+    "rms_norm_eps": 3e-6, "tie_word_embeddings": True, "sliding_window": 24,
+    "layer_types": ["sliding_attention", "full_attention", "sliding_attention", "full_attention"],
+}
+
+# name -> (config, seed, weight std, norm std, page size)
+TINY = {
+    "A": (TINY_A, 0, 0.02, 0.0, 16),
+    "B": (TINY_B, 1, 0.05, 0.1, 8),
+    "C": (TINY_C, 2, 0.08, 0.2, 4),
+}
+
+
+def make_model_dir(root, name, dtype=torch.bfloat16):
+    from rllm_b200.weights import write_random_model
+    cfg, seed, std, norm_std, _ = TINY[name]
+    d = os.path.join(str(root), f"tiny_{name}_{str(dtype).split('.')[-1]}")
+    if not os.path.isdir(d):
+        write_random_model(cfg, seed, d, std=std, norm_std=norm_std, dtype=dtype)
+    return d
+
+
+def random_prompt(n, vocab, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
