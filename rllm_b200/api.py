@@ -1,0 +1,101 @@
+"""The Python entry point: `LLM` and `generate()`.
+
+Shaped like the reference's commands (src/commands/run.rs, batch.rs): a model folder, a
+prompt (token ids; text when the folder has a tokenizer.json and the `tokenizers` package
+is importable), `max_tokens` 128, `temperature` 1.0 (0 = greedy), `top_p`. `LLM.step()`
+mirrors the reference's `InferenceEngine::step` loop (src/engine/mod.rs:82-117):
+`add_request`, `step`, `abort`, `has_work`.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import replace
+
+from .engine.factory import load_engine, parse_dtype, random_engine
+from .engine.scheduler import Scheduler, StepOutput
+from .sampling import Sampler, SamplingParams
+
+
+class LLM:
+    """A loaded model with its cache, scheduler and sampler on one GPU."""
+
+    def __init__(self, model: str | dict, dtype="bfloat16", device="cuda:0", seed: int = 0,
+                 page_size: int = 16, num_pages: int | None = None, max_active: int = 64,
+                 max_tokens_per_step: int = 2048, max_chunk: int | None = None,
+                 weight_std: float = 0.02, norm_std: float = 0.0):
+        """`model`: a folder with config.json + model.safetensors, or a raw config dict, which
+        gets random weights from `seed`."""
+        kw = dict(dtype=parse_dtype(dtype), device=device, page_size=page_size, num_pages=num_pages,
+                  max_requests=max_active)
+        if isinstance(model, dict):
+            self.engine = random_engine(model, seed, std=weight_std, norm_std=norm_std, **kw)
+            self.model_dir = None
+        else:
+            self.engine = load_engine(model, **kw)
+            self.model_dir = model
+        self.scheduler = Scheduler(self.engine.cache, max_active, max_tokens_per_step, max_chunk)
+        self.sampler = Sampler(self.engine.backend)
+        self._tokenizer = None
+
+    # ---- the reference's engine loop
+    def add_request(self, prompt_token_ids: list[int], params: SamplingParams | None = None) -> int:
+        return self.scheduler.add_request(prompt_token_ids, params)
+
+    def abort(self, request_id: int) -> bool:
+        return self.scheduler.abort(request_id, self.engine)
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def step(self) -> list[StepOutput]:
+        """One scheduler step: plan, run the batch, sample, finish and free."""
+        plan, failed = self.scheduler.schedule(self.engine)
+        if not plan:
+            return failed
+        logits = self.engine.step(self.scheduler.entries(plan))
+        sampled = [p.request for p in plan if p.samples]
+        tokens = []
+        if sampled:
+            tokens = self.sampler(logits, [r.params for r in sampled], [r.seed for r in sampled],
+                                  [len(r.output) for r in sampled], [r.output for r in sampled])
+        return failed + self.scheduler.advance(plan, tokens, self.engine)
+
+    # ---- whole generations
+    def generate(self, prompts, params: SamplingParams | list[SamplingParams] | None = None,
+                 **overrides) -> list[list[int]]:
+        """Token ids in, generated token ids out, one list per prompt (all prompts run
+        concurrently, as `rllm batch` does)."""
+        if prompts and isinstance(prompts[0], int):
+            prompts = [prompts]
+        base = params or SamplingParams()
+        plist = base if isinstance(base, list) else [base] * len(prompts)
+        if overrides:
+            plist = [replace(p, **overrides) for p in plist]
+        ids = [self.add_request(list(p), sp) for p, sp in zip(prompts, plist)]
+        while self.has_work():
+            self.step()
+        reqs = [self.scheduler.requests.pop(i) for i in ids]
+        return [r.output for r in reqs]
+
+    # ---- optional text I/O
+    def tokenizer(self):
+        if self._tokenizer is None:
+            path = os.path.join(self.model_dir or "", "tokenizer.json")
+            if not self.model_dir or not os.path.isfile(path):
+                raise RuntimeError("no tokenizer.json in the model folder: pass token ids")
+            try:
+                from tokenizers import Tokenizer
+            except ImportError as e:
+                raise RuntimeError("text prompts need the `tokenizers` package") from e
+            self._tokenizer = Tokenizer.from_file(path)
+        return self._tokenizer
+
+
+def generate(model: str | dict, prompts, max_tokens: int = 128, temperature: float = 1.0,
+             top_p: float = 1.0, top_k: int = 0, min_p: float = 0.0, seed: int | None = None,
+             dtype="bfloat16", **engine_opts) -> list[list[int]]:
+    """Load `model`, generate for every prompt (lists of token ids), return the new ids."""
+    llm = LLM(model, dtype=dtype, **engine_opts)
+    sp = SamplingParams(temperature=temperature, top_p=top_p, top_k=top_k, min_p=min_p,
+                        max_tokens=max_tokens, seed=seed)
+    return llm.generate(prompts, sp)

@@ -1,0 +1,88 @@
+"""The plain implementation itself: closed-form cases in the manner of the reference's CPU
+kernel tests (src/gpu/cpu/mod.rs:2344-2631), and that no cache or batching hides in it."""
+import math
+
+import torch
+
+import plain_llama as P
+import tiny
+
+
+def test_rms_norm_of_a_uniform_vector_is_the_weight():
+    x = torch.full((2, 8), 3.0)
+    w = torch.arange(8, dtype=torch.float32)
+    assert torch.allclose(P.rms_norm(x, w, 0.0), w.expand(2, 8), atol=1e-6)
+    y = P.rms_norm(torch.tensor([[3.0, 4.0]]), torch.ones(2), 0.0)
+    assert torch.allclose(y, torch.tensor([[3.0, 4.0]]) / math.sqrt(12.5))
+
+
+def test_linear_is_row_times_column():
+    w = torch.tensor([[1.0, 2.0], [3.0, 4.0], [5.0, 6.0]])
+    assert torch.equal(P.linear(torch.tensor([[1.0, 1.0]]), w), torch.tensor([[3.0, 7.0, 11.0]]))
+    assert torch.equal(P.linear(torch.eye(2), w), w.t())
+
+
+def test_rope_at_position_zero_is_identity_and_keeps_length():
+    f = P.rope_inv_freq(8, 10000.0, None)
+    x = torch.randn(3, 2, 8)
+    y = P.rope(x, torch.tensor([0, 5, 9]), f)
+    assert torch.equal(y[0], x[0]) and not torch.allclose(y[1], x[1])
+    assert torch.allclose(y.norm(dim=-1), x.norm(dim=-1), atol=1e-5)
+    # pair (0, 4) turns by the position itself (f_0 = 1)
+    e = torch.zeros(1, 1, 8); e[0, 0, 0] = 1.0
+    r = P.rope(e, torch.tensor([2]), f)[0, 0]
+    assert abs(float(r[0]) - math.cos(2.0)) < 1e-6 and abs(float(r[4]) - math.sin(2.0)) < 1e-6
+
+
+def test_llama3_bands():
+    sc = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+          "original_max_position_embeddings": 32}
+    base, f = P.rope_inv_freq(32, 500000.0, None), P.rope_inv_freq(32, 500000.0, sc)
+    wl = 2 * math.pi / base
+    hi, lo = wl < 32 / 4.0, wl > 32 / 1.0
+    assert hi.any() and lo.any() and (~hi & ~lo).any()         # all three bands occur
+    assert torch.equal(f[hi], base[hi]) and torch.allclose(f[lo], base[lo] / 8.0)
+    mid = ~hi & ~lo
+    assert ((f[mid] < base[mid]) & (f[mid] > base[mid] / 8.0)).all()
+
+
+def test_attention_single_key_returns_v_and_is_causal_and_windowed():
+    q, k, v = torch.randn(1, 4, 8), torch.randn(1, 2, 8), torch.randn(1, 2, 8)
+    o = P.attention(q, k, v, 8 ** -0.5)
+    assert torch.allclose(o[0, 0], v[0, 0]) and torch.allclose(o[0, 3], v[0, 1])   # heads 0,1 -> kv 0
+    q, k, v = torch.randn(6, 2, 8), torch.randn(6, 1, 8), torch.randn(6, 1, 8)
+    o = P.attention(q, k, v, 1.0)
+    k2, v2 = k.clone(), v.clone(); k2[4:] += 1.0; v2[4:] -= 2.0                    # later keys changed
+    assert torch.allclose(P.attention(q, k2, v2, 1.0)[:4], o[:4])
+    ow = P.attention(q, k, v, 1.0, window=2)
+    assert torch.allclose(ow[:2], o[:2]) and not torch.allclose(ow[5], o[5])
+    assert torch.allclose(ow[5], P.attention(q[4:], k[4:], v[4:], 1.0)[1], atol=1e-6)
+
+
+def test_swiglu_formula():
+    x = torch.tensor([[1.0, -2.0]])
+    wg, wu, wd = torch.tensor([[1.0, 0.0]]), torch.tensor([[0.0, 1.0]]), torch.tensor([[2.0]])
+    g, u = 1.0, -2.0
+    assert torch.allclose(P.swiglu(x, wg, wu, wd), torch.tensor([[2.0 * (g / (1 + math.exp(-g))) * u]]))
+
+
+def test_forward_is_causal_and_greedy_takes_the_lowest_index(tmp_path):
+    d = tiny.make_model_dir(tmp_path, "B")
+    cfg, w = P.read_model_dir(d)
+    ids = tiny.random_prompt(20, cfg["vocab_size"], 3)
+    full = P.forward(cfg, w, ids)
+    assert torch.allclose(P.forward(cfg, w, ids[:11]), full[:11], atol=1e-5)
+    out = P.greedy(cfg, w, ids[:5], 3)
+    assert out[0] == int(torch.argmax(P.forward(cfg, w, ids[:5])[-1]))
+    assert int(torch.argmax(torch.tensor([1.0, 3.0, 3.0]))) == 1
+
+
+def test_sampling_distribution_rules():
+    lg = torch.log(torch.tensor([0.5, 0.25, 0.125, 0.125]))
+    assert torch.allclose(P.sample_probs(lg, 1.0), torch.tensor([0.5, 0.25, 0.125, 0.125]))
+    assert torch.allclose(P.sample_probs(lg, 1.0, top_k=2), torch.tensor([2 / 3, 1 / 3, 0, 0]))
+    assert torch.allclose(P.sample_probs(lg, 1.0, top_p=0.7), torch.tensor([2 / 3, 1 / 3, 0, 0]))
+    assert torch.allclose(P.sample_probs(lg, 1.0, min_p=0.3), torch.tensor([2 / 3, 1 / 3, 0, 0]))
+    assert torch.allclose(P.sample_probs(lg, 0.5), torch.tensor([16 / 22, 4 / 22, 1 / 22, 1 / 22]))
+    p = torch.tensor([0.5, 0.25, 0.25])
+    assert [P.sample_from_probs(p, u) for u in (0.0, 0.49, 0.5, 0.76, 0.9999999)] == [0, 0, 1, 2, 2]

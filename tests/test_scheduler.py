@@ -1,0 +1,177 @@
+"""The scheduler's decisions, on the CPU with a fake executor (in the manner of the
+reference's MockDispatch tests, src/engine/mod.rs:1231-1310)."""
+import pytest
+import torch
+
+from rllm_b200.cache import CacheManager
+from rllm_b200.engine.scheduler import Scheduler
+from rllm_b200.parts.base import KVCacheSpec
+from rllm_b200.sampling import SamplingParams
+
+
+class FakeExecutor:
+    """Reserves and commits pages like the real step function; 'samples' a counter."""
+
+    def __init__(self, cache):
+        self.cache, self.batches = cache, []
+
+    def step(self, entries):
+        rcs = []
+        for e in entries:
+            rc = self.cache.live.get(e.request_id) or self.cache.open(e.request_id)
+            self.cache.reserve(rc, rc.num_tokens + len(e.tokens))
+            rcs.append(rc)
+        for e, rc in zip(entries, rcs):
+            self.cache.commit(rc, rc.num_tokens + len(e.tokens))
+        self.batches.append([(e.request_id, list(e.tokens), list(e.want)) for e in entries])
+        self.cache.check()
+
+    def end(self, ids):
+        for i in ids:
+            self.cache.close(i)
+
+
+def make(pages=64, page=4, **kw):
+    cache = CacheManager([KVCacheSpec(1, 16)], page, pages, 16, torch.float32, "cpu", allocate=False)
+    return Scheduler(cache, **kw), FakeExecutor(cache)
+
+
+def run_step(s, ex, token_of=lambda req: 1000 + len(req.output)):
+    plan, failed = s.schedule(ex)
+    if plan:
+        ex.step(s.entries(plan))
+    toks = [token_of(p.request) for p in plan if p.samples]
+    return plan, failed + s.advance(plan, toks, ex)
+
+
+def test_fcfs_admission_and_max_active():
+    s, ex = make(max_active=2, max_tokens_per_step=100)
+    ids = [s.add_request([1, 2, 3], SamplingParams(max_tokens=2)) for _ in range(3)]
+    plan, _ = run_step(s, ex)
+    assert [p.request.request_id for p in plan] == ids[:2]
+    assert len(s.waiting) == 1
+    plan, outs = run_step(s, ex)       # both decode one token and finish (max_tokens 2)
+    assert all(o.finished and o.finish_reason == "max_tokens" for o in outs)
+    plan, _ = run_step(s, ex)
+    assert [p.request.request_id for p in plan] == [ids[2]]
+
+
+def test_budget_cuts_prompts_into_portions_and_decodes_first():
+    s, ex = make(max_tokens_per_step=8)
+    a = s.add_request(list(range(5)), SamplingParams(max_tokens=4))
+    run_step(s, ex)                                   # a's prompt, first token
+    b = s.add_request(list(range(20)), SamplingParams(max_tokens=4))
+    plan, _ = run_step(s, ex)
+    assert [(p.request.request_id, len(p.tokens), p.samples) for p in plan] == [(a, 1, True), (b, 7, False)]
+    plan, _ = run_step(s, ex)
+    assert [(p.request.request_id, len(p.tokens), p.samples) for p in plan] == [(a, 1, True), (b, 7, False)]
+    plan, outs = run_step(s, ex)                      # a samples its 4th token and finishes
+    assert [(p.request.request_id, len(p.tokens), p.samples) for p in plan] == [(a, 1, True), (b, 6, True)]
+    assert [o.request_id for o in outs if o.finished] == [a]
+    # only the last portion of a prompt asks for logits
+    assert ex.batches[-1][1][2] == [5] and ex.batches[-2][1][2] == []
+    plan, _ = run_step(s, ex)
+    assert [(p.request.request_id, len(p.tokens)) for p in plan] == [(b, 1)]
+
+
+def test_max_chunk_limits_a_portion():
+    s, ex = make(max_tokens_per_step=64, max_chunk=5)
+    s.add_request(list(range(12)), SamplingParams(max_tokens=1))
+    sizes = []
+    while s.has_work():
+        plan, _ = run_step(s, ex)
+        sizes += [len(p.tokens) for p in plan]
+    assert sizes == [5, 5, 2]
+
+
+def test_head_of_line_blocks_when_pages_lack():
+    s, ex = make(pages=6, page=4, max_tokens_per_step=100)
+    a = s.add_request(list(range(14)), SamplingParams(max_tokens=3))   # 4 pages
+    b = s.add_request(list(range(12)), SamplingParams(max_tokens=3))   # 3 pages: does not fit beside a
+    c = s.add_request([1], SamplingParams(max_tokens=3))               # would fit, but must not overtake
+    plan, _ = run_step(s, ex)
+    assert [p.request.request_id for p in plan] == [a]
+    assert [r.request_id for r in s.waiting] == [b, c]
+    while s.requests[a].finished is False:
+        run_step(s, ex)
+    plan, _ = run_step(s, ex)
+    assert [p.request.request_id for p in plan] == [b, c]
+
+
+def test_finish_frees_pages_and_eos_stops():
+    s, ex = make(pages=8)
+    a = s.add_request([1, 2, 3], SamplingParams(max_tokens=50, eos_token_ids=(7,)))
+    run_step(s, ex, token_of=lambda r: 5)
+    assert ex.cache.free_pages() == [7]
+    _, outs = run_step(s, ex, token_of=lambda r: 7)
+    assert outs[0].finished and outs[0].finish_reason == "eos"
+    assert ex.cache.free_pages() == [8] and not s.has_work()
+    b = s.add_request([1, 2, 3], SamplingParams(max_tokens=3, eos_token_ids=(7,), ignore_eos=True))
+    outs = []
+    while s.has_work():
+        outs += run_step(s, ex, token_of=lambda r: 7)[1]
+    assert [o.finish_reason for o in outs] == [None, None, "max_tokens"]
+
+
+def test_abort_waiting_and_running():
+    s, ex = make(pages=8, max_active=1)
+    a = s.add_request([1, 2, 3, 4, 5])
+    b = s.add_request([1, 2, 3])
+    run_step(s, ex)
+    assert s.abort(b, ex) and not s.waiting
+    assert s.abort(a, ex) and ex.cache.free_pages() == [8]
+    assert not s.has_work() and not s.abort(a, ex)
+
+
+def test_preemption_when_pages_run_out_recomputes_and_keeps_tokens():
+    # 6 pages of 4: two requests of 8 prompt tokens take 2+2 pages (+1 each for the
+    # first decoded tokens = 6); the next page either needs preempts the later one
+    s, ex = make(pages=6, page=4, max_tokens_per_step=100)
+    a = s.add_request(list(range(8)), SamplingParams(max_tokens=12))
+    b = s.add_request(list(range(8)), SamplingParams(max_tokens=12))
+    seen_preempt = False
+    for _ in range(200):
+        if not s.has_work():
+            break
+        run_step(s, ex)
+        if s.preempted_total and not seen_preempt:
+            seen_preempt = True
+            # b (the later admission) went back to the FRONT of the line with prompt+output
+            assert s.waiting[0].request_id == b
+            assert s.waiting[0].pending == s.requests[b].prompt + s.requests[b].output
+    assert seen_preempt and not s.has_work()
+    for r in (a, b):
+        # the counter 'sampler' depends on len(output) only: recompute changes nothing
+        assert s.requests[r].output == [1000 + i for i in range(12)]
+        assert s.requests[r].finish_reason == "max_tokens"
+    assert ex.cache.free_pages() == [6]
+    # after the preemption b's whole history ran again as one prompt portion
+    assert any(rid == b and len(toks) > 8 for batch in ex.batches for rid, toks, _ in batch)
+
+
+def test_request_too_large_for_the_pool_fails_with_a_status():
+    s, ex = make(pages=3, page=4)
+    a = s.add_request(list(range(40)))            # can never fit: 10 pages
+    b = s.add_request([1, 2])
+    plan, outs = run_step(s, ex)
+    assert [(o.request_id, o.finish_reason) for o in outs if o.token is None] == [(a, "out_of_pages")]
+    assert [p.request.request_id for p in plan] == [b]
+
+
+def test_single_request_outgrowing_the_pool_fails_not_hangs():
+    s, ex = make(pages=2, page=4)
+    a = s.add_request(list(range(6)), SamplingParams(max_tokens=100))
+    reasons = []
+    for _ in range(50):
+        if not s.has_work():
+            break
+        reasons += [o.finish_reason for o in run_step(s, ex)[1] if o.finished]
+    assert reasons == ["out_of_pages"] and ex.cache.free_pages() == [2]
+    assert len(s.requests[a].output) >= 2        # it produced what fitted
+
+
+def test_seed_is_fixed_per_request():
+    s, _ = make()
+    a = s.add_request([1], SamplingParams(seed=42))
+    b = s.add_request([1], SamplingParams())
+    assert s.requests[a].seed == 42 and isinstance(s.requests[b].seed, int)
