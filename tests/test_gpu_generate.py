@@ -1,0 +1,159 @@
+"""Generation through the entry point: greedy tokens equal the plain implementation's,
+sampling follows the counter-based draws however the work is batched, long decoding stays
+on the plain logits, the first tokens of a sequence are right, and pages that run out
+preempt and recompute without changing the output."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+import replay
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dirs(tmp_path_factory):
+    root = tmp_path_factory.mktemp("gen")
+    return {n: tiny.make_model_dir(root, n) for n in tiny.TINY}
+
+
+def llm(d, name, dtype, **kw):
+    from rllm_b200.api import LLM
+    kw.setdefault("page_size", tiny.TINY[name][4])
+    return LLM(d, dtype=dtype, **kw)
+
+
+@pytest.mark.parametrize("name,lens,steps", [("A", [5, 11, 17], 8), ("B", [3, 9, 24, 40], 12)])
+def test_greedy_generation_equals_plain_float32(dirs, name, lens, steps):
+    from rllm_b200.sampling import SamplingParams
+    cfg, w = P.read_model_dir(dirs[name])
+    prompts = [tiny.random_prompt(n, cfg["vocab_size"], 7 + n) for n in lens]
+    want = [P.greedy(cfg, w, p, steps) for p in prompts]
+    sp = SamplingParams(temperature=0.0, max_tokens=steps)
+    # all together; in portions of 7 mixed with decodes; one at a time
+    assert llm(dirs[name], name, "float32", num_pages=64).generate(prompts, sp) == want
+    assert llm(dirs[name], name, "float32", num_pages=64, max_tokens_per_step=9, max_chunk=7).generate(prompts, sp) == want
+    one = llm(dirs[name], name, "float32", num_pages=64, max_active=1)
+    assert one.generate(prompts, sp) == want
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_bfloat16_stays_on_the_plain_path(dirs, name):
+    """In bfloat16 a near tie may flip a token, after which the texts differ; so each chosen
+    token is checked against the plain logits for the engine's own history: it must be the
+    plain argmax or within the bfloat16 tolerance of it."""
+    from rllm_b200.sampling import SamplingParams
+    cfg, w = P.read_model_dir(dirs[name])
+    prompts = [tiny.random_prompt(n, cfg["vocab_size"], 70 + n) for n in (6, 21)]
+    outs = llm(dirs[name], name, "bfloat16", num_pages=64).generate(prompts, SamplingParams(temperature=0.0, max_tokens=10))
+    for p, o in zip(prompts, outs):
+        assert len(o) == 10
+        lg = P.forward(cfg, w, p + o[:-1])[len(p) - 1:]
+        for i, tok in enumerate(o):
+            assert float(lg[i].max() - lg[i, tok]) <= 3e-2 * float(lg.abs().max()), (i, tok)
+
+
+def test_temperature_sampling_is_the_same_however_it_is_batched(dirs):
+    from rllm_b200.sampling import SamplingParams, uniform
+    name = "B"
+    cfg, w = P.read_model_dir(dirs[name])
+    prompts = [tiny.random_prompt(n, cfg["vocab_size"], 5 + n) for n in (3, 9, 24, 40)]
+    sps = [SamplingParams(temperature=0.8, max_tokens=12, seed=100 + i) for i in range(4)]
+    a = llm(dirs[name], name, "float32", num_pages=64).generate(prompts, sps)
+    b = llm(dirs[name], name, "float32", num_pages=64, max_tokens_per_step=9, max_chunk=7).generate(prompts, sps)
+    c = llm(dirs[name], name, "float32", num_pages=64, max_active=2).generate(prompts, sps)
+    assert a == b == c
+    # and each token is the one the plain pipeline picks for the same uniform number
+    for p, o, sp in zip(prompts, a, sps):
+        for i, tok in enumerate(o):
+            probs = P.sample_probs(P.forward(cfg, w, p + o[:i])[-1], 0.8).double()
+            cdf = torch.cumsum(probs, 0)
+            u = uniform(sp.seed, i)
+            lo = float(cdf[tok - 1]) if tok else 0.0
+            assert lo - 1e-4 <= u <= float(cdf[tok]) + 1e-4, (i, tok, u)
+    d = llm(dirs[name], name, "float32", num_pages=64).generate(
+        prompts, [SamplingParams(temperature=0.8, max_tokens=12, seed=999)] * 4)
+    assert d != a                                           # another seed, other draws
+
+
+def test_pages_running_out_preempts_and_output_is_unchanged(dirs):
+    from rllm_b200.sampling import SamplingParams
+    name = "B"                                              # pages of 8
+    cfg, _ = P.read_model_dir(dirs[name])
+    prompts = [tiny.random_prompt(n, cfg["vocab_size"], 31 + n) for n in (20, 22, 18)]
+    sp = SamplingParams(temperature=0.0, max_tokens=30)
+    roomy = llm(dirs[name], name, "float32", num_pages=64)
+    want = roomy.generate(prompts, sp)
+    tight = llm(dirs[name], name, "float32", num_pages=12)  # 96 positions for 3 x ~50
+    got = tight.generate(prompts, sp)
+    assert tight.scheduler.preempted_total > 0 and roomy.scheduler.preempted_total == 0
+    assert got == want
+    tight.engine.cache.check()
+    assert tight.engine.cache.free_pages() == [12]
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 3e-2)])
+def test_long_decoding_and_first_tokens(dirs, dtype, tol):
+    """250 tokens decoded one by one after a 3-token prompt (the window of model C passes
+    many pages meanwhile), logits compared at every position; the first positions include
+    position 0, where a key sees only itself."""
+    from rllm_b200.engine import Entry, load_engine
+    name = "C"
+    cfg, w = P.read_model_dir(dirs[name])
+    toks = tiny.random_prompt(253, cfg["vocab_size"], 77)
+    eng = load_engine(dirs[name], dtype=dtype, page_size=4, max_tokens=256, max_requests=2)
+    got = {}
+    lg = eng.step([Entry("a", toks[:3], [0, 1, 2])]).float().cpu().numpy()
+    got.update({("a", i): lg[i] for i in range(3)})
+    for i in range(3, 253):
+        got[("a", i)] = eng.step([Entry("a", [toks[i]], [0])]).float().cpu().numpy()[0]
+    held = [sum(p >= 0 for p in pages) for pages in eng.cache.live["a"].pages]
+    windowed = [g.spec.window is not None for g in eng.cache.groups]
+    assert any(windowed) and all((h <= 8) == wnd for h, wnd in zip(held, windowed))
+    replay.compare(got, replay.plain_logits(dirs[name], {"a": toks}), tol, f"long decode {dtype}")
+
+
+def test_sampling_params_defaults_follow_the_reference():
+    from rllm_b200.sampling import SamplingParams
+    sp = SamplingParams()
+    assert (sp.temperature, sp.top_p, sp.top_k, sp.min_p, sp.max_tokens) == (1.0, 1.0, 0, 0.0, 128)
+    with pytest.raises(ValueError):
+        SamplingParams(top_p=0.0)
+
+
+def test_penalties_change_the_choice(dirs):
+    from rllm_b200.sampling import SamplingParams
+    name = "A"
+    cfg, _ = P.read_model_dir(dirs[name])
+    prompt = tiny.random_prompt(8, cfg["vocab_size"], 3)
+    m = llm(dirs[name], name, "float32", num_pages=32)
+    plain = m.generate([prompt], SamplingParams(temperature=0.0, max_tokens=24))[0]
+    pen = m.generate([prompt], SamplingParams(temperature=0.0, max_tokens=24, presence_penalty=50.0))[0]
+    assert len(set(pen)) == len(pen)                        # a used token is never chosen again
+    assert plain[0] == pen[0]
+
+
+def test_cli_run_and_batch(dirs, tmp_path):
+    import os, subprocess, sys
+    rllm = os.path.join(replay.ROOT, "bin", "rllm")
+    cfg, w = P.read_model_dir(dirs["A"])
+    prompt = tiny.random_prompt(9, cfg["vocab_size"], 12)
+    want = P.greedy(cfg, w, prompt, 6)
+    r = subprocess.run([sys.executable, rllm, "run", "--model", dirs["A"], "--prompt-ids",
+                        " ".join(map(str, prompt)), "--max-tokens", "6", "--temperature", "0",
+                        "--dtype", "float32", "--kv-pages", "32"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    assert [int(x) for x in r.stdout.split()] == want and "tok/s" in r.stderr
+    f = tmp_path / "prompts.txt"
+    f.write_text(" ".join(map(str, prompt)) + "\n" + " ".join(map(str, prompt[:4])) + "\n")
+    r = subprocess.run([sys.executable, rllm, "batch", "--model", dirs["A"], "--batch-file", str(f), "--ids",
+                        "--max-tokens", "6", "--temperature", "0", "--dtype", "float32", "--kv-pages", "32"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    lines = [l for l in r.stdout.splitlines() if l.startswith("[")]
+    assert [int(x) for x in lines[0].split("]")[1].split()] == want
+    r = subprocess.run([sys.executable, rllm, "run", "--model", dirs["A"], "--prompt-ids", "1 2",
+                        "--kv-quant", "turbo4"], capture_output=True, text=True, timeout=600)
+    assert r.returncode != 0 and "not built" in r.stderr

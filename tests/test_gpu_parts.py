@@ -1,0 +1,289 @@
+"""Each part alone against the plain implementation's function for it, and a toy mixer with
+state of its own, defined here, that is registered, built into a model and stepped without
+a change to the package."""
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import plain_llama as P
+import replay
+import tiny
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 5e-6, "bfloat16": 2e-2}
+
+
+def rel(a, b):
+    return float((a.float().cpu() - b.float().cpu()).abs().max()) / max(float(b.abs().max()), 1e-30)
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale
+
+
+class Harness:
+    """A cache and a step context for one part: what the step function would hand it."""
+
+    def __init__(self, dtype, specs, page_size=4, pages=64):
+        from rllm_b200.cache import CacheManager
+        from rllm_b200.engine.step import Engine
+        from rllm_b200.kernels.backend import Backend
+
+        class NoModel:
+            vocab_size = 1 << 30
+        self.backend = Backend(DT[dtype], DEV)
+        self.cache = CacheManager(specs, page_size, pages, 8, DT[dtype], DEV)
+        self.engine = Engine(NoModel(), self.backend, self.cache)
+
+    def context(self, entries):
+        from rllm_b200.engine import Entry
+        entries = [Entry(r, [0] * n, []) for r, n in entries]
+        rcs = self.engine.prepare(entries)
+        ctx, _ = self.engine.build_context(entries, rcs)
+        return ctx, lambda: [self.cache.commit(rc, rc.num_tokens + len(e.tokens))
+                             for e, rc in zip(entries, rcs)]
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_rmsnorm_part(dtype):
+    from rllm_b200.parts import RMSNorm
+    part = RMSNorm(200, 3e-6)
+    part.weight = (1 + rnd(200, seed=1, scale=0.2)).to(DT[dtype]).to(DEV)
+    h = Harness(dtype, [])
+    ctx, _ = h.context([("a", 5)])
+    x = rnd(5, 200, seed=2, scale=4.0)
+    assert rel(part.forward(x.to(DEV), ctx), P.rms_norm(x, part.weight.float().cpu(), 3e-6)) <= TOL[dtype]
+
+
+def test_rotary_part_tables_follow_the_scaling_rule():
+    from rllm_b200.config.llama import RopeScaling
+    from rllm_b200.parts import RotaryEmbedding
+    for scaling, raw in [(None, None),
+                         (RopeScaling("llama3", 8.0, 1.0, 4.0, 32), tiny.TINY_B["rope_scaling"]),
+                         (RopeScaling("llama3", 32.0, 1.0, 4.0, 8192),
+                          {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                           "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}),
+                         (RopeScaling("linear", 2.0), {"rope_type": "linear", "factor": 2.0})]:
+        part = RotaryEmbedding(64, 500000.0, scaling)
+        part.finalize(torch.device(DEV), torch.float32)
+        assert torch.equal(part.inv_freq.cpu(), P.rope_inv_freq(64, 500000.0, raw))
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("heads,kv,hd,hidden,window", [(4, 2, 16, 72, None), (6, 3, 48, 80, 7)])
+def test_attention_part_over_steps(dtype, heads, kv, hd, hidden, window):
+    """The mixer alone: a 19-token sequence in portions of 8, 2, 1, 8 equals the plain
+    q/k/v -> rope -> attention -> o formula on the whole sequence."""
+    from rllm_b200.parts import GQAttention, RotaryEmbedding
+    rope = RotaryEmbedding(hd, 10000.0)
+    part = GQAttention(hidden, heads, kv, hd, rope, window=window)
+    Q, KV = heads * hd, kv * hd
+    wq, wk, wv = (rnd(n, hidden, seed=s, scale=hidden ** -0.5).to(DT[dtype]) for n, s in ((Q, 1), (KV, 2), (KV, 3)))
+    wo = rnd(hidden, Q, seed=4, scale=Q ** -0.5).to(DT[dtype])
+    part.w_qkv, part.w_o = torch.cat([wq, wk, wv]).to(DEV), wo.to(DEV)
+    rope.finalize(torch.device(DEV), DT[dtype])
+    h = Harness(dtype, [part.cache_spec()])
+    T = 19
+    x = rnd(T, hidden, seed=5).to(DT[dtype])
+    res0 = rnd(T, hidden, seed=6)
+    got = res0.clone().to(DEV)
+    i = 0
+    for n in (8, 2, 1, 8):
+        ctx, commit = h.context([("a", n)])
+        part.forward(x[i:i + n].to(DEV), ctx, h.cache.layer_view(0, ctx), got[i:i + n])
+        commit()
+        i += n
+    pos = torch.arange(T)
+    f = P.rope_inv_freq(hd, 10000.0, None)
+    q = P.rope(P.linear(x.float(), wq.float()).view(T, heads, hd), pos, f)
+    k = P.rope(P.linear(x.float(), wk.float()).view(T, kv, hd), pos, f)
+    v = P.linear(x.float(), wv.float()).view(T, kv, hd)
+    want = res0 + P.linear(P.attention(q, k, v, hd ** -0.5, window).reshape(T, Q), wo.float())
+    assert rel(got, want) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_swiglu_part(dtype):
+    from rllm_b200.parts import SwiGLU
+    part = SwiGLU(72, 200)
+    wg, wu = (rnd(200, 72, seed=s, scale=72 ** -0.5).to(DT[dtype]) for s in (1, 2))
+    wd = rnd(72, 200, seed=3, scale=200 ** -0.5).to(DT[dtype])
+    part.w_gate_up, part.w_down = torch.cat([wg, wu]).to(DEV), wd.to(DEV)
+    h = Harness(dtype, [])
+    ctx, _ = h.context([("a", 9)])
+    x = rnd(9, 72, seed=4).to(DT[dtype])
+    res = rnd(9, 72, seed=5)
+    got = res.clone().to(DEV)
+    part.forward(x.to(DEV), ctx, got)
+    assert rel(got, res + P.swiglu(x.float(), wg.float(), wu.float(), wd.float())) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("tied", [True, False])
+def test_embedding_and_output_head(dtype, tied):
+    from rllm_b200.parts import Embedding, OutputHead, RMSNorm
+    emb = Embedding(300, 72)
+    emb.table = rnd(300, 72, seed=1).to(DT[dtype]).to(DEV)
+    norm = RMSNorm(72, 1e-5)
+    norm.weight = (1 + rnd(72, seed=2, scale=0.1)).to(DT[dtype]).to(DEV)
+    head = OutputHead(300, 72, norm, emb if tied else None)
+    if not tied:
+        head.weight = rnd(300, 72, seed=3).to(DT[dtype]).to(DEV)
+    h = Harness(dtype, [])
+    ctx, _ = h.context([("a", 4)])
+    ctx.token_ids.copy_(torch.tensor([5, 299, 0, 5], dtype=torch.int32))
+    x = emb.forward(ctx)
+    assert torch.equal(x.cpu(), emb.table.float().cpu()[[5, 299, 0, 5]])
+    hid = rnd(4, 72, seed=4, scale=2.0)
+    rows = torch.tensor([3, 1], dtype=torch.int32, device=DEV)
+    lg = head.forward(hid.to(DEV), rows, ctx)
+    w = (emb.table if tied else head.weight).float().cpu()
+    want = P.linear(P.rms_norm(hid[[3, 1]], norm.weight.float().cpu(), 1e-5), w)
+    assert lg.dtype == torch.float32 and lg.shape == (2, 300) and rel(lg, want) <= TOL[dtype]
+
+
+# ------------------------------------------------------------------------------------------
+# a toy mixer with state of its own, and a toy architecture that uses it on some layers
+# ------------------------------------------------------------------------------------------
+
+def toy_recurrence(x, s0, decay):
+    """s_t = decay * s_{t-1} + x_t; out_t = s_t.  x: [n, H]."""
+    out, s = [], s0
+    for t in range(x.shape[0]):
+        s = decay * s + x[t]
+        out.append(s)
+    return torch.stack(out), s
+
+
+def make_toy():
+    from rllm_b200.config import ModelConfig, register_architecture
+    from rllm_b200.models import LayerCall, Model
+    from rllm_b200.parts import (Embedding, GQAttention, OutputHead, Param, Part, PreNormBlock,
+                                 RMSNorm, RotaryEmbedding, Source, StateSpec, SwiGLU, make_part,
+                                 register_part)
+
+    class DecayMixer(Part):
+        """Keeps one float vector per request in a state slot; no pages."""
+
+        def __init__(self, hidden, decay):
+            self.hidden, self.decay, self.w = hidden, decay, None
+
+        def params(self):
+            return [Param("w", (Source("mix.weight", (self.hidden, self.hidden)),))]
+
+        def cache_spec(self):
+            return StateSpec((("s", (self.hidden,), torch.float32),))
+
+        def forward(self, x, ctx, cache, residual):
+            y = ctx.backend.linear(x, self.w).float()
+            row = 0
+            for n, slot in zip(ctx.q_lens_host, ctx.state_slots_host):
+                out, s = toy_recurrence(y[row: row + n], cache.state["s"][slot], self.decay)
+                cache.state["s"][slot] = s
+                ctx.backend.add_into(residual[row: row + n], out.contiguous())
+                row += n
+
+    register_part("mixer", "decay", DecayMixer)
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        hidden: int
+        vocab: int
+        mixers: tuple
+        decay: float
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["toy_hidden"], raw["toy_vocab"], tuple(raw["toy_mixers"]), raw["toy_decay"])
+
+    def build(cfg):
+        emb = Embedding(cfg.vocab, cfg.hidden); emb.prefix = "model."
+        blocks = []
+        for i, kind in enumerate(cfg.mixers):
+            if kind == "decay":
+                mixer = make_part("mixer", "decay", hidden=cfg.hidden, decay=cfg.decay)
+            else:
+                mixer = GQAttention(cfg.hidden, 2, 1, 16, RotaryEmbedding(16, 10000.0))
+            b = PreNormBlock(RMSNorm(cfg.hidden, 1e-5), mixer, RMSNorm(cfg.hidden, 1e-5),
+                             SwiGLU(cfg.hidden, 2 * cfg.hidden))
+            b.set_prefix(f"model.layers.{i}.")
+            blocks.append(b)
+        norm = RMSNorm(cfg.hidden, 1e-5); norm.prefix = "model.norm."
+        head = OutputHead(cfg.vocab, cfg.hidden, norm, emb); head.prefix = "lm_head."
+        # the order is data: block 0 runs twice (its second run reads the first run's keys
+        # and writes none), then the other layers
+        schedule = [LayerCall(0, 0, True), LayerCall(0, 0, False)] + \
+                   [LayerCall(i, i, True) for i in range(1, len(blocks))]
+        return Model(cfg, emb, blocks, schedule, head)
+
+    register_architecture("ToyDecayForCausalLM", ToyConfig, build, model_types=("toy_decay",))
+
+
+TOY = {"architectures": ["ToyDecayForCausalLM"], "toy_hidden": 48, "toy_vocab": 120,
+       "toy_mixers": ["attention", "decay", "attention", "decay"], "toy_decay": 0.75}
+
+
+def toy_plain(w, ids, cfg=TOY):
+    ids = torch.as_tensor(ids)
+    T, H = ids.numel(), cfg["toy_hidden"]
+    pos = torch.arange(T)
+    f = P.rope_inv_freq(16, 10000.0, None)
+    h = P.embedding(w["model.embed_tokens.weight"], ids)
+
+    def run(i, h):
+        p = f"model.layers.{i}."
+        n = P.rms_norm(h, w[p + "input_layernorm.weight"], 1e-5)
+        if cfg["toy_mixers"][i] == "decay":
+            out, _ = toy_recurrence(P.linear(n, w[p + "self_attn.mix.weight"]), torch.zeros(H), cfg["toy_decay"])
+            h = h + out
+        else:
+            q = P.rope(P.linear(n, w[p + "self_attn.q_proj.weight"]).view(T, 2, 16), pos, f)
+            k = P.rope(P.linear(n, w[p + "self_attn.k_proj.weight"]).view(T, 1, 16), pos, f)
+            v = P.linear(n, w[p + "self_attn.v_proj.weight"]).view(T, 1, 16)
+            kv = (k, v)
+            h = h + P.linear(P.attention(q, k, v, 0.25).reshape(T, 32), w[p + "self_attn.o_proj.weight"])
+        n = P.rms_norm(h, w[p + "post_attention_layernorm.weight"], 1e-5)
+        return h + P.swiglu(n, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                            w[p + "mlp.down_proj.weight"]), (kv if cfg["toy_mixers"][i] != "decay" else None)
+
+    h, kv0 = run(0, h)
+    # second run of block 0: its own queries against the keys/values the first run stored
+    p = "model.layers.0."
+    n = P.rms_norm(h, w[p + "input_layernorm.weight"], 1e-5)
+    q = P.rope(P.linear(n, w[p + "self_attn.q_proj.weight"]).view(T, 2, 16), pos, f)
+    h = h + P.linear(P.attention(q, kv0[0], kv0[1], 0.25).reshape(T, 32), w[p + "self_attn.o_proj.weight"])
+    n = P.rms_norm(h, w[p + "post_attention_layernorm.weight"], 1e-5)
+    h = h + P.swiglu(n, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    for i in range(1, 4):
+        h, _ = run(i, h)
+    return P.linear(P.rms_norm(h, w["model.norm.weight"], 1e-5), w["model.embed_tokens.weight"])
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype):
+    from rllm_b200.config import registered_architectures
+    from rllm_b200.engine import load_engine
+    from rllm_b200.parts import registered_parts
+    from rllm_b200.weights import write_random_model
+    if "ToyDecayForCausalLM" not in registered_architectures():
+        make_toy()
+    assert "decay" in registered_parts("mixer")
+    d = write_random_model(TOY, 5, str(tmp_path / "toy"), std=0.1, norm_std=0.1)
+    _, w = P.read_model_dir(d)
+    reqs = {f"r{i}": tiny.random_prompt(n, 120, 40 + i) for i, n in enumerate([9, 30, 17, 50, 23])}
+    want = {}
+    for rid, toks in reqs.items():
+        lg = toy_plain(w, toks).numpy()
+        want.update({(rid, i): lg[i] for i in range(len(toks))})
+    for family in (replay.whole, replay.portions, replay.mixed):
+        steps = family(reqs)
+        eng = load_engine(d, dtype=dtype, page_size=4, max_tokens=replay.max_live_tokens(steps, reqs),
+                          max_requests=4)
+        # two kinds of cache in one model: a page group for layers 0 and 2, state for 1 and 3
+        assert len(eng.cache.groups) == 1 and eng.cache.groups[0].layers == [0, 2]
+        assert sorted(eng.cache.state_layers) == [1, 3]
+        got = replay.run_in_process(eng, steps)
+        replay.compare(got, want, {"float32": 2e-5, "bfloat16": 3e-2}[dtype], f"toy {dtype} {family.__name__}")
