@@ -1,0 +1,269 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of Llama 3.2 1B (random weights) on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+Prints ONE JSON line. `value`: decoded tokens per second at batch 8 with the context at
+4,096 tokens when the timed steps end, timed on the device with CUDA events around K decode
+steps (a "step" is one decode step of the whole batch). `e2e`: the same through the Python
+entry point (`LLM.add_request` / `LLM.step`), host token ids in, host token ids out, every
+step copying its inputs from pinned host memory and reading its tokens back. `prefill`: one
+2,048-token prompt in one step. `roofline`: bytes the decode step has to read (every weight
+once, and the cache of the live requests) over its time, against the measured copy
+bandwidth. `points`: decode at batch 1 and 64. Between timed steps nothing is flushed: one
+step reads 2.47 GB of weights, twenty times the 126 MB L2.
+This engine runs on one GPU: for --gpus N > 1 it says so and exits with 2.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA_1B = {   # BASELINE.json configs[2]
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": 2048,
+    "num_hidden_layers": 16, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64,
+    "intermediate_size": 8192, "vocab_size": 128256, "max_position_embeddings": 131072,
+    "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+}
+FULL_LAYERS = 16
+CONTEXT = 4096
+PROMPT = 2048
+PAGE = 16
+
+
+def peaks():
+    p = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            m = json.load(f)
+        p.update({k: m[k] for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained") if k in m})
+        p["source"] = "measured"
+    return p
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed regions run."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
+
+    def stop(self, windows):
+        if self.proc is not None:
+            self.proc.terminate()
+        rows = [r for t, r in self.rows if any(a <= t <= b for a, b in windows)] or [r for _, r in self.rows]
+        sm = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
+        reasons = set()
+        for r in rows:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        mx = [float(r[1]) for r in rows if r[1].replace(".", "").isdigit()]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(rows)}
+
+
+def weight_bytes(model):
+    seen, total = set(), 0
+    for part in model.parts():
+        for p in part.params():
+            t = getattr(part, p.attr)
+            if t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+    return total
+
+
+def prefill_flops(cfg, T):
+    H, L, Q = cfg["hidden_size"], cfg["num_hidden_layers"], cfg["num_attention_heads"] * cfg["head_dim"]
+    KV, I, V = cfg["num_key_value_heads"] * cfg["head_dim"], cfg["intermediate_size"], cfg["vocab_size"]
+    linear = 2 * T * L * (H * (Q + 2 * KV) + Q * H + 3 * H * I)
+    attn = L * 4 * Q * T * (T + 1) // 2          # QK^T and PV over the causal half
+    return linear + attn + 2 * H * V             # logits for the last row only
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers where memory or time needs it")
+    ap.add_argument("--no-points", action="store_true")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust crate (Cargo.toml); no cargo/rustc in this image and no "
+                          "network, so pip cannot build or install it"}))
+        return 0
+    if a.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
+        return 2
+    W, K = max(a.warmup, 3), a.steps
+
+    import torch
+    from rllm_b200.api import LLM
+    from rllm_b200.engine import Entry
+    from rllm_b200.kernels import ops
+    from rllm_b200.sampling import SamplingParams
+
+    pk = peaks()
+    cfg = dict(LLAMA_1B, num_hidden_layers=a.layers)
+    batches = [a.batch] if a.no_points else sorted({1, a.batch, 64})
+    pages = max(batches) * (CONTEXT // PAGE + 1) + 64
+    llm = LLM(cfg, dtype="bfloat16", seed=0, page_size=PAGE, num_pages=pages, max_active=max(batches),
+              max_tokens_per_step=8192)
+    eng = llm.engine
+    wbytes = weight_bytes(eng.model)
+    kv_bytes_per_token = sum(2 * s.kv_heads * s.head_dim * 2 for s in eng.model.cache_specs())
+    g = torch.Generator().manual_seed(0)
+    rand_ids = lambda n: torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist()
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler()
+    sampler.start()
+    windows = []
+
+    # ---------------------------------------------------------------- prefill, 2,048 tokens
+    prompt = rand_ids(PROMPT)
+    times = []
+    for i in range(W + 5):
+        torch.cuda.synchronize()
+        t0, t1 = ev(), ev()
+        w0 = time.time()
+        t0.record()
+        eng.step([Entry(f"p{i}", prompt, [PROMPT - 1])])
+        t1.record()
+        torch.cuda.synchronize()
+        if i >= W:
+            times.append(t0.elapsed_time(t1))
+            windows.append((w0, time.time()))
+        eng.end([f"p{i}"])
+    pre_ms = statistics.median(times)
+    pre_flops = prefill_flops(cfg, PROMPT)
+    prefill = {"value": round(PROMPT / pre_ms * 1e3, 1), "tokens": PROMPT, "ms": round(pre_ms, 4),
+               "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               "tflops": round(pre_flops / (pre_ms * 1e-3) / 1e12, 1)}
+
+    # ---------------------------------------------------------------- decode on the device
+    def fill(B, start_ctx):
+        ids = [f"d{B}_{i}" for i in range(B)]
+        for rid in ids:
+            left = start_ctx
+            while left:
+                n = min(left, 2048)
+                eng.step([Entry(rid, rand_ids(n), [])])
+                left -= n
+        return ids
+
+    def decode_device(B):
+        start_ctx = CONTEXT - (W + K)
+        ids = fill(B, start_ctx)
+        toks = rand_ids(B)
+        launches0 = None
+
+        def one(toks):
+            logits = eng.step([Entry(r, [t], [0]) for r, t in zip(ids, toks)])
+            return eng.backend.argmax(logits)
+        for _ in range(W):
+            toks = one(toks).tolist()
+        torch.cuda.synchronize()
+        launches0 = ops.LAUNCHES
+        t0, t1 = ev(), ev()
+        w0 = time.time()
+        t0.record()
+        for _ in range(K):
+            toks = one(toks).tolist()
+        t1.record()
+        torch.cuda.synchronize()
+        windows.append((w0, time.time()))
+        ms = t0.elapsed_time(t1) / K
+        launches = ops.LAUNCHES - launches0
+        ctx_mean = start_ctx + W + (K + 1) / 2
+        eng.end(ids)
+        return ms, launches, ctx_mean
+
+    results = {B: decode_device(B) for B in batches}
+    ms, launches, ctx_mean = results[a.batch]
+    step_bytes = wbytes + a.batch * ctx_mean * kv_bytes_per_token
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+
+    # ---------------------------------------------------------------- end to end, host in/out
+    def decode_e2e(B):
+        start_ctx = CONTEXT - (W + K) - 1
+        sp = SamplingParams(temperature=0.0, max_tokens=W + K + 1, ignore_eos=True)
+        for _ in range(B):
+            llm.add_request(rand_ids(start_ctx), sp)
+        produced = 0
+        while produced < B * (W + 1):             # prompts and warm-up decode steps
+            produced += sum(o.token is not None for o in llm.step())
+        torch.cuda.synchronize()
+        w0 = time.time()
+        n = 0
+        for _ in range(K):
+            n += sum(o.token is not None for o in llm.step())
+        torch.cuda.synchronize()
+        dt = time.time() - w0
+        windows.append((w0, time.time()))
+        while llm.has_work():
+            llm.step()
+        return n / dt
+    e2e_value = decode_e2e(a.batch)
+    meta_ints = 3 * a.batch + 3 * a.batch + 2 + a.batch * (1 + CONTEXT // PAGE + 1)
+    clocks = sampler.stop(windows)
+
+    out = {
+        "metric": "decode tok/s at batch 8 (Llama 3.2 1B, bf16, context 4096)" if a.batch == 8
+        else f"decode tok/s at batch {a.batch} (Llama 3.2 1B, bf16, context 4096)",
+        "value": round(a.batch / ms * 1e3, 1), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (random token ids, random weights N(0,0.02))",
+        "impl": "ours",
+        "config": {"model": "llama-3.2-1b-shape", "layers": a.layers, "layers_full": FULL_LAYERS,
+                   "hidden": 2048, "heads": 32, "kv_heads": 8, "head_dim": 64, "intermediate": 8192,
+                   "vocab": 128256, "global_batch": a.batch, "seq_len": CONTEXT, "prompt_len": PROMPT,
+                   "kv_page": PAGE, "parallelism": "single-gpu", "l2": "step reads 2.5 GB > 126 MB L2, no flush",
+                   "peaks": pk["source"]},
+        "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": 4 * meta_ints,
+                "d2h_bytes_per_step": 4 * a.batch},
+        "gpu_launches": launches,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
+        "points": {f"decode_b{B}": round(B / results[B][0] * 1e3, 1) for B in batches if B != a.batch},
+        "published": {"h100_nvl_b1_tok_s": 326, "note": "reference README, other hardware, batch 1"},
+        "clocks": clocks,
+    }
+    if 1 in results:
+        out["points"]["decode_b1"] = round(1 / results[1][0] * 1e3, 1)
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -64,8 +64,13 @@ def register_signatures(lib: str, sigs: dict) -> None:
     _SIGS.setdefault(lib, {}).update(sigs)
 
 
-def _check(rc: int, what: str) -> None:
+LAUNCHES = 0          # kernel launches issued through this module (bench.py reports it)
+
+
+def _check(rc: int, what: str, launches: int = 1) -> None:
+    global LAUNCHES
     if rc == 0:
+        LAUNCHES += launches
         return
     if rc < 0:
         raise KernelError(f"{what}: {_ERR.get(rc, 'refused')} (code {rc})")
