@@ -74,6 +74,7 @@ class LLM:
         ids = [self.add_request(list(p), sp) for p, sp in zip(prompts, plist)]
         while self.has_work():
             self.step()
+        self.engine.check()
         reqs = [self.scheduler.requests.pop(i) for i in ids]
         return [r.output for r in reqs]
 

@@ -1,0 +1,387 @@
+// bfloat16 matrix product on the 5th-generation tensor cores (tcgen05), operands staged by
+// TMA, accumulators in TMEM:
+//     C[T, N] = X[T, K] * W[N, K]^T          (X activations, W weights as stored, both K-major)
+//
+// The weight tile is the MMA's A operand (M = 128 weight rows) and the token tile is its B
+// operand (N = BN tokens, 16..256), so a decode step with a handful of tokens still fills the
+// 128-row MMA and streams every weight byte exactly once; a prefill uses BN = 256 (128 with the
+// gate/up pair). The accumulator D[weight row (TMEM lane), token (TMEM column)] is read back
+// with tcgen05.ld by four epilogue warps, thread = weight row, and written as C[token][row].
+//
+// One CTA = one 128 x BN output tile over a range of K (split-K): warp 0 issues TMA loads into
+// a ring of shared-memory stages, warp 1 issues the MMAs (one thread) and owns the TMEM
+// allocation, warps 2-5 run the epilogue. With split-K every CTA writes its float partial tile
+// to scratch memory; the CTA that arrives last at the tile's counter sums the partials in split
+// order (so the result does not depend on arrival order) and runs the epilogue.
+//
+// Epilogues: store bf16 | store float (logits) | add into the float residual stream |
+// SwiGLU over a gate/up pair of weight tiles (two accumulators): out = silu(g) * u.
+// Reference counterparts: gemm_bf16_tc (src/gpu/cuda/shaders/matmul_tc.cu:224-413, wmma),
+// matvec_bf16 (matmul.cu:49-77) and fused_gate_up_swiglu_bf16 (moe.cu:86-147).
+//
+// Every mbarrier wait is bounded; on a time-out the CTA records an error word, drains what it
+// has in flight, frees its TMEM and returns.
+#include "common.cuh"
+#include "sm100.cuh"
+#include <mutex>
+#include <unordered_map>
+
+using namespace rllm;
+using namespace sm100;
+
+namespace {
+
+enum : int { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ACCUM_F32 = 2, EPI_SWIGLU = 3 };
+
+constexpr int BM = 128;        // weight rows per tile (MMA M)
+constexpr int BK = 64;         // K per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;   // warp 0 TMA, warp 1 MMA + TMEM, warps 2..5 epilogue
+
+template <int BN, bool DUAL> struct Cfg {
+  static constexpr int A_TILES = DUAL ? 2 : 1;
+  static constexpr int A_BYTES = BM * BK * 2;                  // 16 KB per weight tile
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
+  // enough stages to keep ~100 KB in flight, at most 8, within 200 KB
+  static constexpr int STAGES_RAW = 200 * 1024 / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? (BN <= 32 ? 6 : 8) : (STAGES_RAW < 2 ? 2 : STAGES_RAW);
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + alignment slack
+  static constexpr int ACC_COLS = A_TILES * BN;
+  static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128
+                                   : ACC_COLS <= 256 ? 256 : 512;
+};
+
+struct Params {
+  void* C;            // output, type by epilogue
+  int ldc;            // row stride of C in elements
+  int T, N, K;        // tokens, output features, inner size
+  int up_row0;        // DUAL: first weight row of the "up" half
+  int splits;
+  float* ws;          // split-K scratch: [tile][split][acc][BN][128] floats
+  int* counters;      // one per output tile, zero between launches
+  int* err;           // device error word (0 = fine)
+};
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + __expf(-g)) * u; }
+
+template <int EPI>
+__device__ __forceinline__ void emit(const Params& p, int t, int n, float v, float u) {
+  const size_t o = (size_t)t * p.ldc + n;
+  if (EPI == EPI_STORE) ((bf16*)p.C)[o] = __float2bfloat16_rn(v);
+  else if (EPI == EPI_STORE_F32) ((float*)p.C)[o] = v;
+  else if (EPI == EPI_ACCUM_F32) ((float*)p.C)[o] += v;
+  else ((bf16*)p.C)[o] = __float2bfloat16_rn(v / (1.f + expf(-v)) * u);
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+               const Params p) {
+  constexpr bool DUAL = (EPI == EPI_SWIGLU);
+  typedef Cfg<BN, DUAL> C;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[C::STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[C::STAGES];
+  __shared__ __align__(8) uint64_t acc_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ int last_flag;
+  __shared__ int never_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+
+  const int n0 = blockIdx.x * BM;          // first weight row / output feature of the tile
+  const int t0 = blockIdx.y * BN;          // first token of the tile
+  const int kb_total = (p.K + BK - 1) / BK;
+  const int kb_begin = (int)((long long)blockIdx.z * kb_total / p.splits);
+  const int kb_end = (int)((long long)(blockIdx.z + 1) * kb_total / p.splits);
+  const int n_kb = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&acc_bar, 1);
+    abort_flag = 0;
+    last_flag = 0;
+    never_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) { prefetch_tensormap(&tmap_w); prefetch_tensormap(&tmap_x); }
+  if (warp == 1) { tmem_alloc(&tmem_base_slot, C::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const uint64_t pol_w = policy_evict_first();   // weights are read once per step
+      const uint64_t pol_x = policy_evict_last();    // the token tile is shared by every weight tile
+      int issued = 0;
+      for (int i = 0; i < n_kb; ++i) {
+        const int s = i % C::STAGES;
+        const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 1); break; }
+        uint8_t* st = smem + (size_t)s * C::STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
+        const int k = (kb_begin + i) * BK;
+        tma_load_2d_hint(st, &tmap_w, &full_bar[s], k, n0, pol_w);
+        if (DUAL) tma_load_2d_hint(st + C::A_BYTES, &tmap_w, &full_bar[s], k, p.up_row0 + n0, pol_w);
+        tma_load_2d_hint(st + C::A_TILES * C::A_BYTES, &tmap_x, &full_bar[s], k, t0, pol_x);
+        issued = i + 1;
+      }
+      if (abort_flag) {
+        // let copies already issued land before the CTA's shared memory is given back
+        for (int i = max(0, issued - C::STAGES); i < issued; ++i)
+          mbar_wait(&full_bar[i % C::STAGES], (uint32_t)(i / C::STAGES) & 1u, &never_flag, 200000000LL);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      bool ok = true;
+      for (int i = 0; i < n_kb && ok; ++i) {
+        const int s = i % C::STAGES;
+        const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], ph, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 2); ok = false; break; }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
+        const uint32_t b_addr = a_addr + C::A_TILES * C::A_BYTES;
+        const uint64_t da = umma_desc_sw128(a_addr);
+        const uint64_t db = umma_desc_sw128(b_addr);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+          const uint64_t koff = (uint64_t)(k * UMMA_K * 2 / 16);
+          umma_bf16(tmem_base, da + koff, db + koff, idesc, acc);
+          if (DUAL) {
+            const uint64_t du = umma_desc_sw128(a_addr + C::A_BYTES);
+            umma_bf16(tmem_base + BN, du + koff, db + koff, idesc, acc);
+          }
+        }
+        umma_commit(&empty_bar[s]);      // the stage is free once these MMAs have read it
+      }
+      if (ok) umma_commit(&acc_bar);      // accumulators complete
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                       // TMEM lanes [32q, 32q + 32) belong to this warp
+    const int row = q * 32 + lane;                // weight row within the tile
+    const int n = n0 + row;
+    bool ok = mbar_wait(&acc_bar, 0, &abort_flag);
+    if (!ok) { abort_flag = 1; atomicExch(p.err, 3); }
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+    if (ok && p.splits == 1) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (t0 + c0 >= p.T) break;
+        uint32_t g[16], u[16];
+        tmem_ld16(taddr + c0, g);
+        if (DUAL) tmem_ld16(taddr + BN + c0, u);
+        tmem_ld_wait();
+        if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = t0 + c0 + j;
+            if (t < p.T) emit<EPI>(p, t, n, __uint_as_float(g[j]), DUAL ? __uint_as_float(u[j]) : 0.f);
+          }
+        }
+      }
+    } else if (ok) {
+      // split-K: park the partial tile, then the last CTA of the tile reduces in split order
+      const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+      constexpr int ACCS = DUAL ? 2 : 1;
+      float* mine = p.ws + ((size_t)tile * p.splits + blockIdx.z) * (ACCS * BN * BM);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (t0 + c0 >= p.T) break;
+        uint32_t g[16], u[16];
+        tmem_ld16(taddr + c0, g);
+        if (DUAL) tmem_ld16(taddr + BN + c0, u);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          __stcg(mine + (size_t)(c0 + j) * BM + row, __uint_as_float(g[j]));
+          if (DUAL) __stcg(mine + (size_t)(BN + c0 + j) * BM + row, __uint_as_float(u[j]));
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        const int old = atomicAdd(&p.counters[tile], 1);
+        last_flag = (old == p.splits - 1);
+        if (old == p.splits - 1) p.counters[tile] = 0;      // ready for the next launch
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (last_flag) {
+        __threadfence();
+        const float* base = p.ws + (size_t)tile * p.splits * (ACCS * BN * BM);
+        if (n < p.N) {
+#pragma unroll 1
+          for (int c = 0; c < BN; ++c) {
+            const int t = t0 + c;
+            if (t >= p.T) break;
+            float g = 0.f, u = 0.f;
+            for (int s = 0; s < p.splits; ++s) {
+              const float* part = base + (size_t)s * (ACCS * BN * BM);
+              g += __ldcg(part + (size_t)c * BM + row);
+              if (DUAL) u += __ldcg(part + (size_t)(BN + c) * BM + row);
+            }
+            emit<EPI>(p, t, n, g, u);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, C::TMEM_COLS); }
+}
+
+// ------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+std::mutex g_mu;
+
+int get_encoder() {
+  if (g_encode) return 0;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess || !fn) {
+    cudaGetLastError();
+    return -5;
+  }
+  g_encode = (EncodeTiledFn)fn;
+  return 0;
+}
+
+// bf16 matrix [rows, cols] with row stride ld (elements); box = 64 columns x box_rows rows
+int make_map(CUtensorMap* m, const void* ptr, long long rows, long long cols, long long ld, int box_rows) {
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -5;
+}
+
+struct MapKey {
+  const void* p; long long rows, cols, ld; int box;
+  bool operator==(const MapKey& o) const { return p == o.p && rows == o.rows && cols == o.cols && ld == o.ld && box == o.box; }
+};
+struct MapHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.p) ^ (std::hash<long long>()(k.rows * 1315423911LL + k.cols * 2654435761LL + k.ld) << 1) ^ k.box;
+  }
+};
+std::unordered_map<MapKey, CUtensorMap, MapHash> g_maps;   // weight maps live as long as the process
+
+int cached_map(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long ld, int box) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  MapKey key{ptr, rows, cols, ld, box};
+  auto it = g_maps.find(key);
+  if (it == g_maps.end()) {
+    CUtensorMap m;
+    int rc = make_map(&m, ptr, rows, cols, ld, box);
+    if (rc) return rc;
+    if (g_maps.size() > 4096) g_maps.clear();
+    it = g_maps.emplace(key, m).first;
+  }
+  *out = it->second;
+  return 0;
+}
+
+template <int BN, int EPI>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t s) {
+  typedef Cfg<BN, EPI == EPI_SWIGLU> C;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(tc_gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             C::SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return -5; }
+    configured = true;
+  }
+  tc_gemm_kernel<BN, EPI><<<grid, THREADS, C::SMEM_BYTES, s>>>(mw, mx, p);
+  return launch_status();
+}
+
+template <int EPI>
+int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t s) {
+  switch (bn) {
+    case 16: return launch<16, EPI>(mw, mx, p, grid, s);
+    case 32: return launch<32, EPI>(mw, mx, p, grid, s);
+    case 64: return launch<64, EPI>(mw, mx, p, grid, s);
+    case 128: return launch<128, EPI>(mw, mx, p, grid, s);
+    case 256:
+      if constexpr (EPI != EPI_SWIGLU) return launch<256, EPI>(mw, mx, p, grid, s);
+      break;
+  }
+  return ERR_BAD_SIZE;
+}
+
+}  // namespace
+
+// Token tile and split count the launcher would choose (exposed for tests and sizing scratch).
+RLLM_API int rllm_tc_gemm_plan(int epi, int T, int N, int K, int sm_count, long long ws_bytes,
+                               int max_counters, int* bn_out, int* splits_out) {
+  const bool dual = epi == EPI_SWIGLU;
+  int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : (T <= 128 || dual) ? 128 : 256;
+  const int tiles = ((N + BM - 1) / BM) * ((T + bn - 1) / bn);
+  const int kb = (K + BK - 1) / BK;
+  int splits = 1;
+  if (tiles < sm_count) {
+    splits = (2 * sm_count + tiles - 1) / tiles;            // aim at two CTAs' worth of tiles per SM
+    if (splits > kb / 2) splits = kb / 2;                   // at least two K blocks per split
+    if (splits > 32) splits = 32;
+    const long long per_split = (long long)tiles * (dual ? 2 : 1) * bn * BM * 4;
+    if (per_split > 0 && splits * per_split > ws_bytes) splits = (int)(ws_bytes / per_split);
+    if (tiles > max_counters) splits = 1;
+    if (splits < 1) splits = 1;
+  }
+  *bn_out = bn;
+  *splits_out = splits;
+  return 0;
+}
+
+// X: [T, K] bf16, row stride ldx; W: [N, K] bf16 contiguous ([2N, K] for SwiGLU: gate rows then up
+// rows); C: [T, N] with row stride ldc, bf16 (store, SwiGLU) or float (store-float, accumulate).
+// ws / counters: split-K scratch (may be null: then no split). Returns 0, or a negative refusal.
+RLLM_API int rllm_tc_gemm(int epi, const void* X, long long ldx, const void* W, void* Cout, long long ldc,
+                          int T, int N, int K, float* ws, long long ws_bytes, int* counters,
+                          int max_counters, int* err, int sm_count, void* stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || ldx % 8) return ERR_BAD_SIZE;              // TMA: strides multiple of 16 bytes
+  if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return ERR_BAD_ALIGN;
+  if (epi < 0 || epi > 3) return ERR_BAD_SIZE;
+  int rc = get_encoder();
+  if (rc) return rc;
+  int bn, splits;
+  rllm_tc_gemm_plan(epi, T, N, K, sm_count, ws ? ws_bytes : 0, counters ? max_counters : 0, &bn, &splits);
+  if (!ws || !counters) splits = 1;
+  const bool dual = epi == EPI_SWIGLU;
+  CUtensorMap mw, mx;
+  if ((rc = cached_map(&mw, W, dual ? 2LL * N : N, K, K, BM))) return rc;
+  if ((rc = make_map(&mx, X, T, K, ldx, bn))) return rc;
+  Params p;
+  p.C = Cout; p.ldc = (int)ldc; p.T = T; p.N = N; p.K = K; p.up_row0 = N; p.splits = splits;
+  p.ws = ws; p.counters = counters; p.err = err;
+  dim3 grid((N + BM - 1) / BM, (T + bn - 1) / bn, splits);
+  if (grid.y > 65535) return ERR_TOO_LARGE;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (epi) {
+    case EPI_STORE: return launch_bn<EPI_STORE>(bn, mw, mx, p, grid, s);
+    case EPI_STORE_F32: return launch_bn<EPI_STORE_F32>(bn, mw, mx, p, grid, s);
+    case EPI_ACCUM_F32: return launch_bn<EPI_ACCUM_F32>(bn, mw, mx, p, grid, s);
+    default: return launch_bn<EPI_SWIGLU>(bn, mw, mx, p, grid, s);
+  }
+}

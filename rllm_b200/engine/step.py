@@ -55,6 +55,17 @@ class Engine:
             if rid in self.cache.live:
                 self.cache.close(rid)
 
+    def check(self) -> None:
+        """Read the device error words (one small copy): a token id outside the table, or a
+        kernel whose bounded wait ran out. Callers that read results back anyway call this at
+        the same time."""
+        if int(self._err_flag.item()):
+            self._err_flag.zero_()
+            raise StepError("a token id outside the embedding table reached the device")
+        if self.backend.fast:
+            from ..kernels import sm100
+            sm100.check_error(self.device)
+
     # ------------------------------------------------------------------ the step
     def _validate(self, entries: list[Entry]) -> None:
         if not entries:
