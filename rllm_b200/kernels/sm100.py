@@ -3,7 +3,7 @@ calls. Holds the scratch memory of the split-K product (partial tiles and tile c
 the device error word that a bounded wait sets when it runs out."""
 from __future__ import annotations
 
-from ctypes import c_int, c_longlong, c_void_p, POINTER, byref
+from ctypes import c_float, c_int, c_longlong, c_void_p, POINTER, byref
 
 import torch
 
@@ -14,6 +14,8 @@ ops.register_signatures("sm100", {
     "rllm_tc_gemm": [c_int, _P, c_longlong, _P, _P, c_longlong, c_int, c_int, c_int, _P, c_longlong, _P,
                      c_int, _P, c_int, _P],
     "rllm_tc_gemm_plan": [c_int, c_int, c_int, c_int, c_int, c_longlong, c_int, POINTER(c_int), POINTER(c_int)],
+    "rllm_attention_fa": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
+                          c_int, c_int, c_float, c_int, c_int, _P, _P, _P],
 })
 
 WS_BYTES = 64 << 20
@@ -93,5 +95,50 @@ def gemm(x: torch.Tensor, w: torch.Tensor, epilogue: int, out: torch.Tensor | No
     return out
 
 
+def attention_supported(q: torch.Tensor, kcache: torch.Tensor) -> bool:
+    return q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and kcache.shape[3] in (64, 128)
+
+
+def attention_splits(num_seqs: int, nkv: int, max_rows: int, max_kv_len: int, sm_count: int) -> int:
+    """How many ranges the keys of a sequence are cut into. Prefill-sized tiles fill the GPU
+    by themselves; decode-sized batches are cut until about four CTAs per SM exist, each with
+    at least two 64-key tiles."""
+    if max_rows > 16:
+        return 1
+    base = max(1, num_seqs * nkv)
+    want = (4 * sm_count + base - 1) // base
+    return max(1, min(want, max_kv_len // 128, 64))
+
+
+def attention_fa(q, kcache, vcache, cu_q, kv_lens, block_table, num_tokens, max_q_len, max_kv_len, nh,
+                 scale, window, splits=None, out=None):
+    """Tiled tensor-core attention over the paged cache (bf16, head size 64 or 128)."""
+    st = init(q.device)
+    _, nkv, page_size, hd = kcache.shape
+    S = kv_lens.numel()
+    G = nh // nkv
+    if splits is None:
+        splits = attention_splits(S, nkv, max_q_len * G, max_kv_len, st.sm_count)
+    if out is None:
+        out = torch.empty((q.shape[0], nh * hd), dtype=torch.bfloat16, device=q.device)
+    part_o = part_ml = None
+    if splits > 1:
+        need = num_tokens * nh * splits
+        part_o = torch.empty(need * hd, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(need * 2, dtype=torch.float32, device=q.device)
+    rc = ops._fn("sm100", "rllm_attention_fa")(
+        q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(), out.data_ptr(), out.stride(0),
+        cu_q.data_ptr(), kv_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0), S, num_tokens,
+        max_q_len, nh, nkv, hd, page_size, float(scale), int(window or 0), splits,
+        None if part_o is None else part_o.data_ptr(), None if part_ml is None else part_ml.data_ptr(),
+        ops._stream())
+    ops._check(rc, "attention_fa", 2 if splits > 1 else 1)
+    return out
+
+
 def attention(q, cache, ctx, nh, scale, window):
-    return None
+    """The backend's hook: None when this kernel does not take the sizes at hand."""
+    if not attention_supported(q, cache.k):
+        return None
+    return attention_fa(q, cache.k, cache.v, ctx.cu_q, ctx.kv_lens, cache.block_table, ctx.num_tokens,
+                        ctx.max_q_len, ctx.max_kv_len, nh, scale, window)

@@ -1,0 +1,84 @@
+"""The tiled tensor-core attention alone against the plain formula: head sizes 64 and 128,
+group sizes 1 to 8, pages of 16, 8, 5 and 32 positions scattered over the pool, windows,
+prompt portions beside decode tokens, and the keys of a sequence cut into 1 to 7 ranges."""
+import pytest
+import torch
+
+import plain_llama as P
+from test_gpu_kernels import scattered_cache
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = 8e-3      # bf16 probabilities and output; inputs are the same bf16 values on both sides
+
+
+def rel(a, b):
+    return float((a.float().cpu() - b.float().cpu()).abs().max()) / max(float(b.abs().max()), 1e-30)
+
+
+def run(nh, nkv, hd, page, window, lens, q_lens, splits, far=None):
+    from rllm_b200.kernels import sm100
+    S = len(lens)
+    kc, vc, bt, ks, vs = scattered_cache(S, lens, nkv, hd, page, torch.bfloat16, seed=hd + nh)
+    g = torch.Generator().manual_seed(5)
+    T = sum(q_lens)
+    q = torch.randn(T, nh, hd, generator=g).to(torch.bfloat16)
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    if far is not None:          # (sequence, key index): that key dominates the sequence's last query
+        s_, j = far
+        ks[s_][j] = 0
+        ks[s_][j, :, 0] = 30.0
+        q[cu[s_ + 1] - 1, :, 0] = 30.0
+        kc[int(bt[s_, j // page]), :, j % page] = ks[s_][j]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    # the q rows sit inside a wider buffer, as in the engine's qkv tensor
+    buf = torch.zeros(T, (nh + 2 * nkv) * hd, dtype=torch.bfloat16)
+    buf[:, : nh * hd] = q.reshape(T, nh * hd)
+    bufd = buf.to(DEV)
+    out = sm100.attention_fa(bufd[:, : nh * hd], kc.to(DEV), vc.to(DEV), i32(cu), i32(lens), bt.to(DEV), T,
+                             max(q_lens), max(lens), nh, hd ** -0.5, window, splits=splits)
+    row = 0
+    for s in range(S):
+        L, n = lens[s], q_lens[s]
+        qf = torch.zeros(L, nh, hd); qf[L - n:] = q[row: row + n].float()
+        ref = P.attention(qf, ks[s].float(), vs[s].float(), hd ** -0.5, window)[L - n:]
+        got = out[row: row + n].float().cpu().view(n, nh, hd)
+        assert torch.isfinite(got).all()
+        assert rel(got, ref) <= TOL, f"sequence {s} (len {L}, q {n})"
+        row += n
+    if far is not None:
+        s_, j = far
+        got = out[cu[s_ + 1] - 1].float().cpu().view(nh, hd)
+        assert rel(got, vs[s_][j].float().repeat_interleave(nh // nkv, 0)) <= TOL
+    return out
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page", [(32, 8, 64, 16), (4, 2, 64, 8), (3, 1, 64, 5), (8, 8, 128, 16),
+                                            (24, 8, 128, 32), (16, 2, 64, 16), (6, 2, 128, 8)])
+def test_mixed_batch(nh, nkv, hd, page):
+    run(nh, nkv, hd, page, None, lens=[37, 300, 1, 130, 64, 200], q_lens=[37, 9, 1, 1, 2, 200], splits=1,
+        far=(1, 11))
+
+
+@pytest.mark.parametrize("window", [24, 64, 100])
+@pytest.mark.parametrize("hd", [64, 128])
+def test_window(window, hd):
+    run(8, 2, hd, 8, window, lens=[150, 97, 23, 64], q_lens=[150, 1, 23, 5], splits=1)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 7])
+@pytest.mark.parametrize("nh,nkv,hd,page", [(32, 8, 64, 16), (8, 1, 128, 8), (3, 1, 64, 5)])
+def test_decode_with_split_keys(splits, nh, nkv, hd, page):
+    run(nh, nkv, hd, page, None, lens=[1, 63, 64, 65, 700, 129], q_lens=[1, 1, 1, 1, 1, 1], splits=splits,
+        far=(4, 5))
+    run(nh, nkv, hd, page, 50, lens=[1, 63, 64, 65, 700, 129], q_lens=[1, 1, 1, 1, 1, 1], splits=splits)
+
+
+def test_long_prompt_whole_and_chosen_splits():
+    from rllm_b200.kernels import sm100
+    run(8, 2, 64, 16, None, lens=[1500], q_lens=[1500], splits=1, far=(0, 3))
+    assert sm100.attention_splits(8, 8, 4, 4096, 148) >= 8       # decode: cut until the GPU is full
+    assert sm100.attention_splits(8, 8, 2048 * 4, 4096, 148) == 1  # prefill: tiles fill it already
+    assert sm100.attention_splits(1, 8, 4, 100, 148) == 1          # too short to cut
