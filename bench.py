@@ -116,6 +116,10 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers where memory or time needs it")
     ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--phase", default="all", choices=["all", "prefill", "decode"],
+                    help="run one part only (for profiling; the JSON line then lacks the other parts)")
+    ap.add_argument("--profile-range", action="store_true",
+                    help="bracket one timed step with cudaProfilerStart/Stop (ncu --profile-from-start off)")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -152,19 +156,24 @@ def main():
     # ---------------------------------------------------------------- prefill, 2,048 tokens
     prompt = rand_ids(PROMPT)
     times = []
-    for i in range(W + 5):
+    for i in range(W + 5 if a.phase != "decode" else 0):
         torch.cuda.synchronize()
         t0, t1 = ev(), ev()
         w0 = time.time()
         t0.record()
+        prof = a.profile_range and i == W
+        if prof:
+            torch.cuda.profiler.start()
         eng.step([Entry(f"p{i}", prompt, [PROMPT - 1])])
+        if prof:
+            torch.cuda.profiler.stop()
         t1.record()
         torch.cuda.synchronize()
         if i >= W:
             times.append(t0.elapsed_time(t1))
             windows.append((w0, time.time()))
         eng.end([f"p{i}"])
-    pre_ms = statistics.median(times)
+    pre_ms = statistics.median(times) if times else float("nan")
     pre_flops = prefill_flops(cfg, PROMPT)
     prefill = {"value": round(PROMPT / pre_ms * 1e3, 1), "tokens": PROMPT, "ms": round(pre_ms, 4),
                "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
@@ -188,7 +197,7 @@ def main():
         launches0 = None
 
         def one(toks):
-            logits = eng.step([Entry(r, [t], [0]) for r, t in zip(ids, toks)])
+            logits = eng.step([Entry(r, [t], [0]) for r, t in zip(ids, toks)], keep=False)
             return eng.backend.argmax(logits)
         for _ in range(W):
             toks = one(toks).tolist()
@@ -197,8 +206,13 @@ def main():
         t0, t1 = ev(), ev()
         w0 = time.time()
         t0.record()
-        for _ in range(K):
+        for k in range(K):
+            prof = a.profile_range and k == 0 and B == a.batch
+            if prof:
+                torch.cuda.profiler.start()
             toks = one(toks).tolist()
+            if prof:
+                torch.cuda.profiler.stop()
         t1.record()
         torch.cuda.synchronize()
         windows.append((w0, time.time()))
@@ -208,6 +222,10 @@ def main():
         eng.end(ids)
         return ms, launches, ctx_mean
 
+    if a.phase == "prefill":
+        print(json.dumps({"impl": "ours", "phase": "prefill", "prefill": prefill}))
+        sampler.stop(windows)
+        return 0
     results = {B: decode_device(B) for B in batches}
     ms, launches, ctx_mean = results[a.batch]
     step_bytes = wbytes + a.batch * ctx_mean * kv_bytes_per_token
@@ -233,7 +251,7 @@ def main():
         while llm.has_work():
             llm.step()
         return n / dt
-    e2e_value = decode_e2e(a.batch)
+    e2e_value = decode_e2e(a.batch) if a.phase == "all" else float("nan")
     meta_ints = 3 * a.batch + 3 * a.batch + 2 + a.batch * (1 + CONTEXT // PAGE + 1)
     clocks = sampler.stop(windows)
 
@@ -251,7 +269,7 @@ def main():
                    "peaks": pk["source"]},
         "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": 4 * meta_ints,
                 "d2h_bytes_per_step": 4 * a.batch},
-        "gpu_launches": launches,
+        "gpu_launches": launches, "graph_replays": eng.graph_steps,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},

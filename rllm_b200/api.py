@@ -52,7 +52,7 @@ class LLM:
         plan, failed = self.scheduler.schedule(self.engine)
         if not plan:
             return failed
-        logits = self.engine.step(self.scheduler.entries(plan))
+        logits = self.engine.step(self.scheduler.entries(plan), keep=False)
         sampled = [p.request for p in plan if p.samples]
         tokens = []
         if sampled:

@@ -1,0 +1,124 @@
+"""CUDA graphs for decode steps.
+
+A step that brings one token per request launches some nine kernels per layer, each a few
+microseconds long; issued one by one from the host they cost more than they run. Such a
+step is therefore captured once per shape and replayed: the same kernels, on the same cache,
+reading the step's metadata (token ids, positions, slots, block tables, key counts) from a
+device buffer at a fixed address that is refilled before every replay.
+
+A graph is keyed by (number of requests, block-table width). The width is the pages of the
+longest request rounded up to a power of two, so that a request growing by a token a step
+meets a new graph only when its length doubles. Everything a kernel's launch shape depends
+on (grid sizes, how many ranges the keys are cut into) follows from the key; what differs
+from step to step is read on the device.
+
+Only models whose parts all declare `graph_safe` (they read nothing of the step on the
+host) are captured; any other model runs launch by launch.
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+
+MAX_GRAPH_BATCH = 256
+MAX_GRAPHS = 48
+
+
+class _Slot:
+    __slots__ = ("lay", "host", "dev", "ctx", "rows", "graph", "logits", "copied", "launches")
+
+
+class DecodeGraphs:
+    def __init__(self, engine):
+        self.engine = engine
+        self.slots: OrderedDict[tuple[int, int], _Slot] = OrderedDict()
+        self.pool = None
+        self.captures = 0
+
+    def _width(self, rcs) -> int:
+        G = len(self.engine.cache.groups)
+        need = max((len(rc.pages[g]) for rc in rcs for g in range(G)), default=1)
+        p = 8
+        while p < need:
+            p *= 2
+        return p
+
+    def takes(self, entries, rcs) -> bool:
+        return len(entries) <= MAX_GRAPH_BATCH and all(len(e.tokens) == 1 and len(e.want) <= 1
+                                                       for e in entries)
+
+    def _forward(self, slot: _Slot) -> torch.Tensor:
+        eng = self.engine
+        h = eng.model.forward(slot.ctx, eng.cache)
+        return eng.model.logits(h, slot.rows, slot.ctx)
+
+    def _new_slot(self, S: int, P: int) -> _Slot:
+        from .step import MetaLayout
+        eng = self.engine
+        slot = _Slot()
+        slot.lay = lay = MetaLayout(S, S, P, S, len(eng.cache.groups))
+        slot.host = torch.full((lay.total,), -1, dtype=torch.int32).pin_memory()
+        slot.dev = torch.full((lay.total,), -1, dtype=torch.int32, device=eng.device)
+        cap = P * eng.cache.page_size           # upper bound of every request's key count
+        slot.ctx, slot.rows = eng.make_context(slot.dev, lay, [1] * S, [cap] * S, [cap - 1] * S, [-1] * S)
+        slot.ctx.graph_safe = True
+        slot.ctx.kv_lens_host = slot.ctx.state_slots_host = None     # not known when replayed
+        slot.ctx.extras.pop("starts_host", None)
+        slot.graph = slot.logits = None
+        slot.copied = torch.cuda.Event()
+        return slot
+
+    def _capture(self, slot: _Slot) -> None:
+        # once launch by launch (this also sets every kernel's attributes), then captured
+        cur = torch.cuda.current_stream(self.engine.device)
+        side = torch.cuda.Stream(self.engine.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            self._forward(slot)
+        cur.wait_stream(side)
+        torch.cuda.synchronize(self.engine.device)
+        if self.pool is None:
+            self.pool = torch.cuda.graph_pool_handle()
+        graph = torch.cuda.CUDAGraph()
+        before = ops.LAUNCHES
+        with torch.cuda.graph(graph, pool=self.pool):
+            slot.logits = self._forward(slot)
+        slot.launches = ops.LAUNCHES - before    # kernels one replay launches
+        ops.LAUNCHES = before                    # a capture launches nothing
+        slot.graph = graph
+        self.captures += 1
+
+    def run(self, entries, rcs, keep: bool = True) -> torch.Tensor | None:
+        eng = self.engine
+        S = len(entries)
+        key = (S, self._width(rcs))
+        slot = self.slots.get(key)
+        if slot is None:
+            slot = self._new_slot(*key)
+            self.slots[key] = slot
+            while len(self.slots) > MAX_GRAPHS:
+                self.slots.popitem(last=False)
+        else:
+            self.slots.move_to_end(key)
+        slot.copied.synchronize()               # the last copy out of the host buffer is over
+        host = slot.host.numpy()
+        host.fill(-1)
+        eng.fill_meta(host, slot.lay, entries, rcs)
+        slot.lay.view(host, 6, S)[:] = np.arange(S, dtype=np.int32)   # logits of every row
+        slot.dev.copy_(slot.host, non_blocking=True)
+        slot.copied.record()
+        if slot.graph is None:
+            self._capture(slot)
+        slot.graph.replay()
+        ops.LAUNCHES += slot.launches
+        wanted = [s for s, e in enumerate(entries) if e.want]
+        if not wanted:
+            return None
+        if len(wanted) == S:
+            return slot.logits.clone() if keep else slot.logits
+        idx = torch.tensor(wanted, dtype=torch.int32).to(eng.device)
+        return ops.gather_rows(slot.logits, idx)

@@ -9,9 +9,14 @@ one function.
 The reference runs one forward per prefilling sequence and a separate batched decode
 (src/engine/mod.rs:485-714); here they are one call, and a later portion of a prompt
 attends the keys of the earlier ones through the block table.
+
+Steps that bring exactly one token per request (decoding) replay a CUDA graph of the
+same launches (see `graphs.py`) when every part of the model allows it; the kernels and
+the cache are the same either way.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -34,13 +39,38 @@ class StepError(ValueError):
     pass
 
 
+class MetaLayout:
+    """Where each vector of a step's metadata lies in the one int32 buffer that is copied
+    to the device: ids | positions | token_seq | cu_q | kv_lens | state_slots | rows |
+    per cache group: slots[T], block_table[S * P]. Every vector starts on a 16-byte
+    boundary."""
+
+    def __init__(self, T: int, S: int, P: int, n_rows: int, G: int):
+        self.T, self.S, self.P, self.n_rows, self.G = T, S, P, n_rows, G
+        sizes = [T, T, T, S + 1, S, S, max(n_rows, 1)] + [T, S * P] * G
+        self.offs = np.concatenate([[0], np.cumsum([(n + 3) // 4 * 4 for n in sizes])]).astype(np.int64)
+        self.total = int(self.offs[-1])
+
+    def view(self, buf, i: int, n: int):
+        o = int(self.offs[i])
+        return buf[o: o + n]
+
+
 class Engine:
-    def __init__(self, model, backend, cache: CacheManager):
+    def __init__(self, model, backend, cache: CacheManager, use_graphs: bool | None = None):
         self.model, self.backend, self.cache = model, backend, cache
         self.device = backend.device
         self.vocab = model.vocab_size
         self._err_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.steps_run = 0
+        self.graph_steps = 0
+        if use_graphs is None:
+            use_graphs = os.environ.get("RLLM_B200_NO_GRAPHS") != "1"
+        self.graphs = None
+        if use_graphs and hasattr(model, "parts") and all(getattr(p, "graph_safe", False)
+                                                          for p in model.parts()):
+            from .graphs import DecodeGraphs
+            self.graphs = DecodeGraphs(self)
 
     # ------------------------------------------------------------------ requests
     def has(self, request_id) -> bool:
@@ -108,77 +138,83 @@ class Engine:
             raise
         return rcs
 
-    def build_context(self, entries: list[Entry], rcs) -> tuple[StepContext, torch.Tensor]:
-        cache, ps = self.cache, self.cache.page_size
-        S = len(entries)
-        q_lens = [len(e.tokens) for e in entries]
-        T = sum(q_lens)
-        starts = [rc.num_tokens for rc in rcs]
-        kv_lens = [s + q for s, q in zip(starts, q_lens)]
-        G = len(cache.groups)
-        P = max(1, max((len(rc.pages[g]) for rc in rcs for g in range(G)), default=1))
-        n_rows = sum(len(e.want) for e in entries)
-
-        # one int32 buffer: ids | positions | token_seq | cu_q | kv_lens | state_slots | rows |
-        #                   per group: slots[T], block_table[S*P]
-        sizes = [T, T, T, S + 1, S, S, max(n_rows, 1)] + [T, S * P] * G
-        offs = np.concatenate([[0], np.cumsum([(n + 3) // 4 * 4 for n in sizes])]).astype(np.int64)
-        host = np.full(int(offs[-1]), -1, dtype=np.int32)
-        ids = host[offs[0]:offs[0] + T]
-        pos = host[offs[1]:offs[1] + T]
-        tseq = host[offs[2]:offs[2] + T]
-        cu = host[offs[3]:offs[3] + S + 1]
-        kvl = host[offs[4]:offs[4] + S]
-        sslot = host[offs[5]:offs[5] + S]
-        rows = host[offs[6]:offs[6] + max(n_rows, 1)]
-        r = 0
-        q0 = 0
+    def fill_meta(self, host: np.ndarray, lay: MetaLayout, entries: list[Entry], rcs) -> None:
+        """Write the step's metadata into `host` (int32, `lay.total` long, preset to -1)."""
+        ps = self.cache.page_size
+        T, S, P, G = lay.T, lay.S, lay.P, lay.G
+        ids, pos, tseq = lay.view(host, 0, T), lay.view(host, 1, T), lay.view(host, 2, T)
+        cu, kvl, sslot = lay.view(host, 3, S + 1), lay.view(host, 4, S), lay.view(host, 5, S)
+        rows = lay.view(host, 6, max(lay.n_rows, 1))
+        r = q0 = 0
         cu[0] = 0
         for s, (e, rc) in enumerate(zip(entries, rcs)):
-            q = q_lens[s]
+            q = len(e.tokens)
+            start = rc.num_tokens
             ids[q0:q0 + q] = e.tokens
-            pos[q0:q0 + q] = np.arange(starts[s], starts[s] + q, dtype=np.int32)
+            pos[q0:q0 + q] = np.arange(start, start + q, dtype=np.int32)
             tseq[q0:q0 + q] = s
             cu[s + 1] = q0 + q
-            kvl[s] = kv_lens[s]
+            kvl[s] = start + q
             sslot[s] = rc.state_slot
             for w in e.want:
                 rows[r] = q0 + w
                 r += 1
             for g in range(G):
                 pages = np.asarray(rc.pages[g], dtype=np.int32)
-                bt = host[offs[8 + 2 * g] + s * P: offs[8 + 2 * g] + s * P + len(pages)]
-                bt[:] = pages
+                o = int(lay.offs[8 + 2 * g]) + s * P
+                host[o: o + len(pages)] = pages
                 p = pos[q0:q0 + q]
-                host[offs[7 + 2 * g] + q0: offs[7 + 2 * g] + q0 + q] = pages[p // ps] * ps + p % ps
+                o = int(lay.offs[7 + 2 * g]) + q0
+                host[o: o + q] = pages[p // ps] * ps + p % ps
             q0 += q
-        if n_rows == 0:
+        if lay.n_rows == 0:
             rows[0] = 0
-        dev = torch.from_numpy(host).pin_memory().to(self.device, non_blocking=True)
 
-        def view(i, n):
-            return dev[int(offs[i]): int(offs[i]) + n]
-
-        groups = {g: GroupView(view(7 + 2 * g, T), view(8 + 2 * g, S * P).view(S, P), ps)
-                  for g in range(G)}
+    def make_context(self, dev: torch.Tensor, lay: MetaLayout, q_lens, kv_lens, starts,
+                     state_slots) -> tuple[StepContext, torch.Tensor]:
+        """The step context over the device copy `dev` of a metadata buffer."""
+        T, S, P = lay.T, lay.S, lay.P
+        ps = self.cache.page_size
+        groups = {g: GroupView(lay.view(dev, 7 + 2 * g, T), lay.view(dev, 8 + 2 * g, S * P).view(S, P), ps)
+                  for g in range(lay.G)}
         ctx = StepContext(
-            backend=self.backend, num_tokens=T, num_seqs=S, token_ids=view(0, T),
-            positions=view(1, T), token_seq=view(2, T), cu_q=view(3, S + 1), kv_lens=view(4, S),
-            state_slots=view(5, S), q_lens_host=q_lens, kv_lens_host=kv_lens,
-            state_slots_host=[rc.state_slot for rc in rcs], groups=groups,
+            backend=self.backend, num_tokens=T, num_seqs=S, token_ids=lay.view(dev, 0, T),
+            positions=lay.view(dev, 1, T), token_seq=lay.view(dev, 2, T), cu_q=lay.view(dev, 3, S + 1),
+            kv_lens=lay.view(dev, 4, S), state_slots=lay.view(dev, 5, S), q_lens_host=list(q_lens),
+            kv_lens_host=list(kv_lens), state_slots_host=list(state_slots), groups=groups,
             max_q_len=max(q_lens), max_kv_len=max(kv_lens))
         ctx.extras["err_flag"] = self._err_flag
-        ctx.extras["starts_host"] = starts
-        return ctx, view(6, n_rows)
+        ctx.extras["starts_host"] = list(starts)
+        return ctx, lay.view(dev, 6, lay.n_rows)
 
-    def step(self, entries: list[Entry]) -> torch.Tensor | None:
+    def build_context(self, entries: list[Entry], rcs) -> tuple[StepContext, torch.Tensor]:
+        G = len(self.cache.groups)
+        q_lens = [len(e.tokens) for e in entries]
+        starts = [rc.num_tokens for rc in rcs]
+        kv_lens = [s + q for s, q in zip(starts, q_lens)]
+        P = max(1, max((len(rc.pages[g]) for rc in rcs for g in range(G)), default=1))
+        lay = MetaLayout(sum(q_lens), len(entries), P, sum(len(e.want) for e in entries), G)
+        host = torch.full((lay.total,), -1, dtype=torch.int32).pin_memory()
+        self.fill_meta(host.numpy(), lay, entries, rcs)
+        dev = host.to(self.device, non_blocking=True)
+        return self.make_context(dev, lay, q_lens, kv_lens, starts, [rc.state_slot for rc in rcs])
+
+    def step(self, entries: list[Entry], keep: bool = True) -> torch.Tensor | None:
         """Run one batch; returns float32 logits [wanted places, vocab] on the device, in
         the order of the entries and of each `want` (None if nothing is wanted).
-        Raises OutOfPages, leaving every request as it was, if the pages do not suffice."""
+        Raises OutOfPages, leaving every request as it was, if the pages do not suffice.
+        `keep=False`: the caller reads the logits before the next step, so they may live
+        in a buffer that the next step overwrites (saves a copy)."""
         rcs = self.prepare(entries)
-        ctx, rows = self.build_context(entries, rcs)
-        h = self.model.forward(ctx, self.cache)
-        logits = self.model.logits(h, rows, ctx) if rows.numel() else None
+        logits = None
+        if self.graphs is not None and self.graphs.takes(entries, rcs):
+            logits = self.graphs.run(entries, rcs, keep)
+            self.graph_steps += 1
+        else:
+            ctx, rows = self.build_context(entries, rcs)
+            h = self.model.forward(ctx, self.cache)
+            if rows.numel():
+                logits = self.model.logits(h, rows, ctx)
         for e, rc in zip(entries, rcs):
             self.cache.commit(rc, rc.num_tokens + len(e.tokens))
         self.steps_run += 1

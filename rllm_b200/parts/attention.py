@@ -13,6 +13,8 @@ from .base import KVCacheSpec, Param, Part, Source, register_part
 
 
 class GQAttention(Part):
+    graph_safe = True
+
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, position: Part,
                  window: int | None = None, bias: bool = False, scale: float | None = None):
         if heads % kv_heads:

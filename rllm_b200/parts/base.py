@@ -65,6 +65,9 @@ class Part:
     """Base of all parts. `prefix` (checkpoint name prefix, ending in '.') is set by
     whoever assembles the model."""
     prefix: str = ""
+    # True when `forward` reads nothing of the step on the host (no `*_host` mirror of the
+    # context, no device-to-host copy): only then can a decode step be captured in a CUDA graph
+    graph_safe: bool = False
 
     def params(self) -> list[Param]:
         return []

@@ -7,6 +7,7 @@ from .base import Part, register_part
 
 class PreNormBlock(Part):
     """`names` maps the four parts to their checkpoint sub-prefixes."""
+    graph_safe = True
 
     def __init__(self, mixer_norm: Part, mixer: Part, ffn_norm: Part, ffn: Part,
                  names=("input_layernorm.", "self_attn.", "post_attention_layernorm.", "mlp.")):

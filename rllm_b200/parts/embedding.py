@@ -9,6 +9,8 @@ from .base import Param, Part, Source
 
 
 class Embedding(Part):
+    graph_safe = True
+
     def __init__(self, vocab: int, hidden: int, name: str = "embed_tokens.weight"):
         self.vocab, self.hidden, self.name = vocab, hidden, name
         self.table = None
@@ -22,6 +24,7 @@ class Embedding(Part):
 
 class OutputHead(Part):
     """`tied_to`: the Embedding whose table doubles as the output matrix, or None."""
+    graph_safe = True
 
     def __init__(self, vocab: int, hidden: int, norm: Part, tied_to: Embedding | None,
                  name: str = "weight"):

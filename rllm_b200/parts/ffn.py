@@ -7,6 +7,8 @@ from .base import Param, Part, Source, register_part
 
 
 class SwiGLU(Part):
+    graph_safe = True
+
     def __init__(self, hidden: int, intermediate: int):
         self.hidden, self.intermediate = hidden, intermediate
         self.w_gate_up = self.w_down = None

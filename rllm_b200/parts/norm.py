@@ -6,6 +6,8 @@ from .base import Param, Part, Source, register_part
 
 
 class RMSNorm(Part):
+    graph_safe = True
+
     def __init__(self, size: int, eps: float, weight_name: str = "weight"):
         self.size, self.eps, self.weight_name = size, float(eps), weight_name
         self.weight = None

@@ -41,6 +41,7 @@ def inverse_frequencies(rot_dim: int, theta: float, scaling=None) -> list[float]
 
 class RotaryEmbedding(Part):
     """Rotates pairs (i, i + rot_dim/2) of each head by position * f_i."""
+    graph_safe = True
 
     def __init__(self, head_dim: int, theta: float, scaling=None, rot_dim: int | None = None):
         self.head_dim = head_dim
