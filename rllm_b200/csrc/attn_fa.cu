@@ -336,3 +336,69 @@ RLLM_API int rllm_attention_fa(const void* q, int q_stride, const void* kcache, 
   else fa_combine_kernel<128><<<blocks, 128, 0, s>>>(part_o, part_ml, (bf16*)out, out_stride, nh, splits);
   return launch_status();
 }
+
+// ------------------------------------------------------------------------------------------
+// Split-key attention for callers that cannot allocate device memory (see attn_fa_noalloc.h).
+// Same kernels as rllm_attention_fa; the partial sums of the key ranges go to a fixed array
+// inside this library instead of buffers the caller would have to allocate.
+// ------------------------------------------------------------------------------------------
+#include "attn_fa_noalloc.h"
+#include <mutex>
+
+// One copy per GPU that loads this library, held until the process exits:
+// partial outputs first, then the (maximum, sum) pairs.
+static __device__ __align__(256) float g_noalloc_scratch[RLLM_NOALLOC_PART_O_FLOATS + RLLM_NOALLOC_PART_ML_FLOATS];
+
+namespace {
+
+constexpr size_t NOALLOC_O_FLOATS = RLLM_NOALLOC_PART_O_FLOATS;
+constexpr size_t NOALLOC_ML_FLOATS = RLLM_NOALLOC_PART_ML_FLOATS;
+constexpr int NOALLOC_MAX_DEVICES = 64;
+
+// In host code `g_noalloc_scratch` is only a handle; the address a kernel can use is asked
+// for once per device, with that device current, and kept here.
+float* g_noalloc_addr[NOALLOC_MAX_DEVICES] = {nullptr};
+std::mutex g_noalloc_mu;
+
+int noalloc_scratch_address(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
+    cudaGetLastError();
+    return -5;
+  }
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (!g_noalloc_addr[dev]) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || !p) {
+      cudaGetLastError();
+      return -5;
+    }
+    g_noalloc_addr[dev] = static_cast<float*>(p);
+  }
+  *out = g_noalloc_addr[dev];
+  return 0;
+}
+
+}  // namespace
+
+RLLM_API int rllm_attention_fa_noalloc(const void* q, int q_stride, const void* kcache, const void* vcache,
+                                       void* out, int out_stride, const int* cu_q, const int* kv_lens,
+                                       const int* block_table, int bt_stride, int num_seqs, int num_tokens,
+                                       int max_q_len, int nh, int nkv, int hd, int page_size, float scale,
+                                       int window, int splits, void* stream) {
+  if (num_seqs <= 0 || num_tokens <= 0) return 0;
+  if (splits < 1) splits = 1;
+  if (nh <= 0 || hd <= 0) return ERR_BAD_SIZE;
+  const size_t rows = (size_t)num_tokens * (size_t)nh * (size_t)splits;
+  if (splits > 1 && (rows * (size_t)hd > NOALLOC_O_FLOATS || rows * 2 > NOALLOC_ML_FLOATS))
+    return ERR_TOO_LARGE;                       // beyond the fixed scratch: refuse, never overrun
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch_address(&scratch);
+  if (rc) return rc;
+  // Every (token, head, range) slot that the merge reads is written by the first kernel of the
+  // same call, so nothing of an earlier call's contents is ever read and nothing needs clearing.
+  return rllm_attention_fa(q, q_stride, kcache, vcache, out, out_stride, cu_q, kv_lens, block_table,
+                           bt_stride, num_seqs, num_tokens, max_q_len, nh, nkv, hd, page_size, scale, window,
+                           splits, scratch, scratch + NOALLOC_O_FLOATS, stream);
+}
