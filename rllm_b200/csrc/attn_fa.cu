@@ -70,6 +70,8 @@ struct FaParams {
 template <int HD, int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32)
 fa_paged_kernel(const FaParams p) {
+  pdl_launch();
+  pdl_wait();
   constexpr int BM = 16 * NWARPS;
   constexpr int CH = HD / 8;            // 16-byte chunks per key row
   constexpr int NT = NWARPS * 32;
@@ -268,6 +270,8 @@ fa_paged_kernel(const FaParams p) {
 template <int HD>
 __global__ void fa_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   bf16* __restrict__ out, int out_stride, int nh, int splits) {
+  pdl_launch();
+  pdl_wait();
   const int th = blockIdx.x;                 // token * nh + head
   const int token = th / nh, head = th % nh;
   const float* ml = part_ml + (size_t)th * splits * 2;
@@ -298,8 +302,7 @@ int launch_fa(const FaParams& p, int num_seqs, int max_rows, cudaStream_t s) {
   }
   dim3 grid((max_rows + BM - 1) / BM, p.nkv * p.splits, num_seqs);
   if (grid.y > 65535 || grid.z > 65535) return ERR_TOO_LARGE;
-  fa_paged_kernel<HD, NWARPS><<<grid, NWARPS * 32, SMEM, s>>>(p);
-  return launch_status();
+  return launch_ex(fa_paged_kernel<HD, NWARPS>, grid, dim3(NWARPS * 32), SMEM, s, 1, p);
 }
 
 }  // namespace
@@ -332,9 +335,11 @@ RLLM_API int rllm_attention_fa(const void* q, int q_stride, const void* kcache, 
   else rc = hd == 64 ? launch_fa<64, 4>(p, num_seqs, max_rows, s) : launch_fa<128, 4>(p, num_seqs, max_rows, s);
   if (rc || splits == 1) return rc;
   const int blocks = num_tokens * nh;
-  if (hd == 64) fa_combine_kernel<64><<<blocks, 64, 0, s>>>(part_o, part_ml, (bf16*)out, out_stride, nh, splits);
-  else fa_combine_kernel<128><<<blocks, 128, 0, s>>>(part_o, part_ml, (bf16*)out, out_stride, nh, splits);
-  return launch_status();
+  if (hd == 64)
+    return launch_ex(fa_combine_kernel<64>, dim3(blocks), dim3(64), 0, s, 1, (const float*)part_o,
+                     (const float*)part_ml, (bf16*)out, out_stride, nh, splits);
+  return launch_ex(fa_combine_kernel<128>, dim3(blocks), dim3(128), 0, s, 1, (const float*)part_o,
+                   (const float*)part_ml, (bf16*)out, out_stride, nh, splits);
 }
 
 // ------------------------------------------------------------------------------------------

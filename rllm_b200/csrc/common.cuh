@@ -9,6 +9,8 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <utility>
 
 #define RLLM_API extern "C" __attribute__((visibility("default")))
 
@@ -63,6 +65,54 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 
 static inline int launch_status() {
   cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+  return 0;
+}
+
+// ---- programmatic dependent launch
+// Every kernel of this library starts with pdl_launch() (its successor in the stream may begin
+// its own prologue) and calls pdl_wait() before it reads what its predecessor wrote or writes
+// anything. Launched without the attribute both are no-ops. RLLM_B200_NO_PDL=1 turns the
+// attribute off (plain stream order).
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+static inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("RLLM_B200_NO_PDL");
+    v = (e && e[0] == '1') ? 0 : 1;
+  }
+  return v != 0;
+}
+
+// Launch with the attributes this library uses: programmatic stream serialization, and a
+// thread-block cluster of (1, 1, cluster_z) when cluster_z > 1.
+template <typename... KArgs, typename... Args>
+static inline int launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                            int cluster_z, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attrs[2];
+  int n = 0;
+  if (pdl_enabled()) {
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_z > 1) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = 1;
+    attrs[n].val.clusterDim.y = 1;
+    attrs[n].val.clusterDim.z = (unsigned)cluster_z;
+    ++n;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
   if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
   return 0;
 }

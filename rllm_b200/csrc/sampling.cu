@@ -27,6 +27,8 @@ __device__ __forceinline__ float key2f(unsigned k) {
 
 __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
   const float* x = logits + (size_t)blockIdx.x * V;
@@ -78,6 +80,8 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const float* __restrict__ min_p, const float* __restrict__ uniform,
               int* __restrict__ out) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float redf[32];
   __shared__ int redi[32];
   __shared__ float seg[THREADS];
@@ -181,8 +185,8 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
 RLLM_API int rllm_argmax(const float* logits, int R, int V, int* out, void* stream) {
   if (R <= 0) return 0;
   if (V <= 0) return ERR_BAD_SIZE;
-  argmax_kernel<<<R, THREADS, 0, (cudaStream_t)stream>>>(logits, V, out);
-  return launch_status();
+  int rc = launch_ex(argmax_kernel, dim3(R), dim3(THREADS), 0, (cudaStream_t)stream, 1, logits, V, out);
+  return rc;
 }
 
 // Per-row parameter arrays of length R; top_k / top_p / min_p may be null (off).
@@ -192,7 +196,7 @@ RLLM_API int rllm_sample(const float* logits, int R, int V, const float* tempera
                          const float* uniform, int* out, void* stream) {
   if (R <= 0) return 0;
   if (V <= 0) return ERR_BAD_SIZE;
-  sample_kernel<<<R, THREADS, 0, (cudaStream_t)stream>>>(logits, V, temperature, top_k, top_p,
+  int rc = launch_ex(sample_kernel, dim3(R), dim3(THREADS), 0, (cudaStream_t)stream, 1, logits, V, temperature, top_k, top_p,
                                                          min_p, uniform, out);
-  return launch_status();
+  return rc;
 }

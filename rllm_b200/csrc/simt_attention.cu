@@ -47,6 +47,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, const T* __re
                             const int* __restrict__ token_seq, const int* __restrict__ positions,
                             const int* __restrict__ block_table, int bt_stride, int n_tokens,
                             int nh, int nkv, int hd, int page_size, float scale, int window) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float qs[WARPS][MAX_HD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long gw = (long long)blockIdx.x * WARPS + warp;
@@ -129,16 +131,17 @@ RLLM_API int rllm_paged_attention_simt(int dt, const void* q, int q_stride, cons
   const long long blocks = (warps + WARPS - 1) / WARPS;
   if (blocks > 2147483647LL) return ERR_TOO_LARGE;
   cudaStream_t s = (cudaStream_t)stream;
+  int rc = 0;
   if (dt == DT_F32)
-    paged_attention_simt_kernel<float><<<(unsigned)blocks, WARPS * 32, 0, s>>>(
+    rc = launch_ex(paged_attention_simt_kernel<float>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, s, 1, 
         (const float*)q, q_stride, (const float*)kcache, (const float*)vcache, (float*)out,
         out_stride, token_seq, positions, block_table, bt_stride, n_tokens, nh, nkv, hd, page_size,
         scale, window);
   else if (dt == DT_BF16)
-    paged_attention_simt_kernel<bf16><<<(unsigned)blocks, WARPS * 32, 0, s>>>(
+    rc = launch_ex(paged_attention_simt_kernel<bf16>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, s, 1, 
         (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, (bf16*)out, out_stride,
         token_seq, positions, block_table, bt_stride, n_tokens, nh, nkv, hd, page_size, scale,
         window);
   else return ERR_BAD_DTYPE;
-  return launch_status();
+  return rc;
 }

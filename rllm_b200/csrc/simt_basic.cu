@@ -10,6 +10,8 @@ using namespace rllm;
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                              float* __restrict__ out, int H, int V, int* __restrict__ err) {
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= V) {           // never read outside the table: flag and emit zeros
@@ -26,10 +28,11 @@ RLLM_API int rllm_embed(const int* ids, const void* table, int table_dt, float* 
   if (T <= 0) return 0;
   const int threads = H >= 256 ? 256 : (H >= 128 ? 128 : 64);
   cudaStream_t s = (cudaStream_t)stream;
-  if (table_dt == DT_F32) embed_kernel<float><<<T, threads, 0, s>>>(ids, (const float*)table, out, H, V, err);
-  else if (table_dt == DT_BF16) embed_kernel<bf16><<<T, threads, 0, s>>>(ids, (const bf16*)table, out, H, V, err);
+  int rc = 0;
+  if (table_dt == DT_F32) rc = launch_ex(embed_kernel<float>, dim3(T), dim3(threads), 0, s, 1, ids, (const float*)table, out, H, V, err);
+  else if (table_dt == DT_BF16) rc = launch_ex(embed_kernel<bf16>, dim3(T), dim3(threads), 0, s, 1, ids, (const bf16*)table, out, H, V, err);
   else return ERR_BAD_DTYPE;
-  return launch_status();
+  return rc;
 }
 
 // ---------------------------------------------------------------- RMSNorm
@@ -39,6 +42,8 @@ RLLM_API int rllm_embed(const int* ids, const void* table, int table_dt, float* 
 template <typename TW, typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w,
                                TO* __restrict__ y, int H, float eps) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float red[32];
   const float* xr = x + (size_t)blockIdx.x * H;
   float ss = 0.f;
@@ -54,14 +59,15 @@ RLLM_API int rllm_rmsnorm(const float* x, const void* w, int w_dt, void* y, int 
   if (T <= 0) return 0;
   const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
   cudaStream_t s = (cudaStream_t)stream;
-#define GO(TW, TO) rmsnorm_kernel<TW, TO><<<T, threads, 0, s>>>(x, (const TW*)w, (TO*)y, H, eps)
+  int rc = 0;
+#define GO(TW, TO) rc = launch_ex(rmsnorm_kernel<TW, TO>, dim3(T), dim3(threads), 0, s, 1, x, (const TW*)w, (TO*)y, H, eps)
   if (w_dt == DT_F32 && y_dt == DT_F32) GO(float, float);
   else if (w_dt == DT_F32 && y_dt == DT_BF16) GO(float, bf16);
   else if (w_dt == DT_BF16 && y_dt == DT_F32) GO(bf16, float);
   else if (w_dt == DT_BF16 && y_dt == DT_BF16) GO(bf16, bf16);
   else return ERR_BAD_DTYPE;
 #undef GO
-  return launch_status();
+  return rc;
 }
 
 // ---------------------------------------------------------------- RoPE + cache write
@@ -76,6 +82,8 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   const float* __restrict__ inv_freq, const int* __restrict__ slots,
                                   T* __restrict__ kcache, T* __restrict__ vcache, int nh, int nkv,
                                   int hd, int page_size, int rot_dim) {
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.x;
   const int half = hd / 2;
   const int width = (nh + 2 * nkv) * hd;
@@ -122,37 +130,42 @@ RLLM_API int rllm_rope_cache_write(void* qkv, int dt, const int* positions, cons
   if (T <= 0) return 0;
   if (hd % 2 || rot_dim % 2 || rot_dim > hd || rot_dim < 0) return ERR_BAD_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
+  int rc = 0;
   const int work = (nh + nkv) * hd / 2;
   const int threads = work >= 512 ? 256 : (work >= 128 ? 128 : 64);
   if (dt == DT_F32)
-    rope_cache_kernel<float><<<T, threads, 0, s>>>((float*)qkv, positions, inv_freq, slots,
+    rc = launch_ex(rope_cache_kernel<float>, dim3(T), dim3(threads), 0, s, 1, (float*)qkv, positions, inv_freq, slots,
                                                    (float*)kcache, (float*)vcache, nh, nkv, hd,
                                                    page_size, rot_dim);
   else if (dt == DT_BF16)
-    rope_cache_kernel<bf16><<<T, threads, 0, s>>>((bf16*)qkv, positions, inv_freq, slots,
+    rc = launch_ex(rope_cache_kernel<bf16>, dim3(T), dim3(threads), 0, s, 1, (bf16*)qkv, positions, inv_freq, slots,
                                                   (bf16*)kcache, (bf16*)vcache, nh, nkv, hd,
                                                   page_size, rot_dim);
   else return ERR_BAD_DTYPE;
-  return launch_status();
+  return rc;
 }
 
 // ---------------------------------------------------------------- small helpers
 // out[r, :] = x[rows[r], :]   (float rows of the residual stream)
 __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                    float* __restrict__ out, int H) {
+  pdl_launch();
+  pdl_wait();
   const float* src = x + (size_t)rows[blockIdx.x] * H;
   float* dst = out + (size_t)blockIdx.x * H;
   for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
 }
 RLLM_API int rllm_gather_rows(const float* x, const int* rows, float* out, int R, int H, void* stream) {
   if (R <= 0) return 0;
-  gather_rows_kernel<<<R, H >= 256 ? 256 : 64, 0, (cudaStream_t)stream>>>(x, rows, out, H);
-  return launch_status();
+  int rc = launch_ex(gather_rows_kernel, dim3(R), dim3(H >= 256 ? 256 : 64), 0, (cudaStream_t)stream, 1, x, rows, out, H);
+  return rc;
 }
 
 // residual[i] += delta[i]   (float accumulate; delta float or bf16)
 template <typename T>
 __global__ void add_into_kernel(float* __restrict__ res, const T* __restrict__ delta, size_t n) {
+  pdl_launch();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) res[i] += to_f32(delta[i]);
 }
@@ -161,15 +174,18 @@ RLLM_API int rllm_add_into(float* res, const void* delta, int dt, long long n, v
   const int threads = 256;
   const unsigned blocks = (unsigned)((n + threads - 1) / threads);
   cudaStream_t s = (cudaStream_t)stream;
-  if (dt == DT_F32) add_into_kernel<float><<<blocks, threads, 0, s>>>(res, (const float*)delta, (size_t)n);
-  else if (dt == DT_BF16) add_into_kernel<bf16><<<blocks, threads, 0, s>>>(res, (const bf16*)delta, (size_t)n);
+  int rc = 0;
+  if (dt == DT_F32) rc = launch_ex(add_into_kernel<float>, dim3(blocks), dim3(threads), 0, s, 1, res, (const float*)delta, (size_t)n);
+  else if (dt == DT_BF16) rc = launch_ex(add_into_kernel<bf16>, dim3(blocks), dim3(threads), 0, s, 1, res, (const bf16*)delta, (size_t)n);
   else return ERR_BAD_DTYPE;
-  return launch_status();
+  return rc;
 }
 
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i]   (reference: elementwise.cu:36-49)
 template <typename T>
 __global__ void silu_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t n) {
+  pdl_launch();
+  pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n) return;
   size_t t = idx / I; int i = (int)(idx % I);
@@ -182,8 +198,9 @@ RLLM_API int rllm_silu_gate(const void* gu, void* out, int dt, int T, int I, voi
   const int threads = 256;
   const unsigned blocks = (unsigned)((n + threads - 1) / threads);
   cudaStream_t s = (cudaStream_t)stream;
-  if (dt == DT_F32) silu_gate_kernel<float><<<blocks, threads, 0, s>>>((const float*)gu, (float*)out, I, n);
-  else if (dt == DT_BF16) silu_gate_kernel<bf16><<<blocks, threads, 0, s>>>((const bf16*)gu, (bf16*)out, I, n);
+  int rc = 0;
+  if (dt == DT_F32) rc = launch_ex(silu_gate_kernel<float>, dim3(blocks), dim3(threads), 0, s, 1, (const float*)gu, (float*)out, I, n);
+  else if (dt == DT_BF16) rc = launch_ex(silu_gate_kernel<bf16>, dim3(blocks), dim3(threads), 0, s, 1, (const bf16*)gu, (bf16*)out, I, n);
   else return ERR_BAD_DTYPE;
-  return launch_status();
+  return rc;
 }

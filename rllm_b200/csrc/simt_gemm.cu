@@ -24,6 +24,8 @@ template <typename TI, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ W, void* __restrict__ Cv,
                  const TI* __restrict__ bias, int T, int N, int K, int lda, int ldc) {
+  pdl_launch();
+  pdl_wait();
   constexpr bool DUAL = (EPI == EPI_SWIGLU);
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
@@ -93,7 +95,8 @@ template <typename TI>
 int launch(int epi, const void* A, const void* W, void* C, const void* bias, int T, int N, int K,
            int lda, int ldc, cudaStream_t s) {
   dim3 grid((N + BN - 1) / BN, (T + BM - 1) / BM), block(256);
-#define GO(E) gemm_simt_kernel<TI, E><<<grid, block, 0, s>>>((const TI*)A, (const TI*)W, C, (const TI*)bias, T, N, K, lda, ldc)
+  int rc = 0;
+#define GO(E) rc = launch_ex(gemm_simt_kernel<TI, E>, dim3(grid), dim3(block), 0, s, 1, (const TI*)A, (const TI*)W, C, (const TI*)bias, T, N, K, lda, ldc)
   switch (epi) {
     case EPI_STORE: GO(EPI_STORE); break;
     case EPI_STORE_F32: GO(EPI_STORE_F32); break;
@@ -102,7 +105,7 @@ int launch(int epi, const void* A, const void* W, void* C, const void* bias, int
     default: return ERR_BAD_SIZE;
   }
 #undef GO
-  return launch_status();
+  return rc;
 }
 
 }  // namespace

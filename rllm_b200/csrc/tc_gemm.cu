@@ -8,19 +8,29 @@
 // gate/up pair). The accumulator D[weight row (TMEM lane), token (TMEM column)] is read back
 // with tcgen05.ld by four epilogue warps, thread = weight row, and written as C[token][row].
 //
-// One CTA = one 128 x BN output tile over a range of K (split-K): warp 0 issues TMA loads into
-// a ring of shared-memory stages, warp 1 issues the MMAs (one thread) and owns the TMEM
-// allocation, warps 2-5 run the epilogue. With split-K every CTA writes its float partial tile
-// to scratch memory; the CTA that arrives last at the tile's counter sums the partials in split
-// order (so the result does not depend on arrival order) and runs the epilogue.
+// One CTA = one 128 x BN output tile over a range of K: warp 0 issues TMA loads into a ring of
+// shared-memory stages, warp 1 issues the MMAs (one thread) and owns the TMEM allocation,
+// warps 2-5 run the epilogue.
+//
+// Split-K for small batches (few output tiles, long K) runs inside a thread-block cluster:
+// the CTAs of a cluster share one output tile and take consecutive ranges of K. Each parks its
+// float partial tile in its own shared memory; after a cluster barrier CTA r sums columns
+// r, r + C, ... over all ranks, in rank order, through distributed shared memory and runs the
+// epilogue for them. Nothing goes through global memory and the sum does not depend on timing.
+//
+// Programmatic dependent launch: the kernel lets its successor start at once, and itself
+// fetches its first weight tiles (which no earlier kernel writes) before it waits for its
+// predecessor; activations are read and outputs written only after that wait.
 //
 // Epilogues: store bf16 | store float (logits) | add into the float residual stream |
-// SwiGLU over a gate/up pair of weight tiles (two accumulators): out = silu(g) * u.
+// SwiGLU over a gate/up pair of weight tiles (two accumulators): out = silu(g) * u |
+// rotary position encoding of q and k heads with the write of k and v into the paged cache.
 // Reference counterparts: gemm_bf16_tc (src/gpu/cuda/shaders/matmul_tc.cu:224-413, wmma),
-// matvec_bf16 (matmul.cu:49-77) and fused_gate_up_swiglu_bf16 (moe.cu:86-147).
+// matvec_bf16 (matmul.cu:49-77), fused_gate_up_swiglu_bf16 (moe.cu:86-147), rotary_embedding
+// (rope.cu:62-77) and copy_to_paged_kv_cache (attention.cu:295-300).
 //
 // Every mbarrier wait is bounded; on a time-out the CTA records an error word, drains what it
-// has in flight, frees its TMEM and returns.
+// has in flight, still meets its cluster's barriers, frees its TMEM and returns.
 #include "common.cuh"
 #include "sm100.cuh"
 #include <mutex>
@@ -31,12 +41,13 @@ using namespace sm100;
 
 namespace {
 
-enum : int { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ACCUM_F32 = 2, EPI_SWIGLU = 3 };
+enum : int { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ACCUM_F32 = 2, EPI_SWIGLU = 3, EPI_QKV_ROPE = 4 };
 
 constexpr int BM = 128;        // weight rows per tile (MMA M)
 constexpr int BK = 64;         // K per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;   // warp 0 TMA, warp 1 MMA + TMEM, warps 2..5 epilogue
+constexpr int MAX_CLUSTER = 8;
 
 template <int BN, bool DUAL> struct Cfg {
   static constexpr int A_TILES = DUAL ? 2 : 1;
@@ -50,6 +61,18 @@ template <int BN, bool DUAL> struct Cfg {
   static constexpr int ACC_COLS = A_TILES * BN;
   static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128
                                    : ACC_COLS <= 256 ? 256 : 512;
+  // the partial tile of a split is parked over the (by then idle) stages
+  static_assert(A_TILES * BN * BM * 4 <= STAGES * STAGE_BYTES, "partial tile must fit in the stage ring");
+};
+
+// What the rotary epilogue needs besides the product (see rllm_tc_gemm_qkv_rope).
+struct RopeArgs {
+  const int* positions;     // [T] absolute position of each token
+  const float* inv_freq;    // [rot_dim / 2]
+  const int* slots;         // [T] page * page_size + offset, < 0: do not write; may be null
+  bf16* kcache;             // [pages][nkv][page_size][hd]
+  bf16* vcache;
+  int nh, nkv, hd, page_size, rot_dim;
 };
 
 struct Params {
@@ -57,13 +80,10 @@ struct Params {
   int ldc;            // row stride of C in elements
   int T, N, K;        // tokens, output features, inner size
   int up_row0;        // DUAL: first weight row of the "up" half
-  int splits;
-  float* ws;          // split-K scratch: [tile][split][acc][BN][128] floats
-  int* counters;      // one per output tile, zero between launches
+  int splits;         // CTAs per cluster = ranges of K
   int* err;           // device error word (0 = fine)
+  RopeArgs rope;
 };
-
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + __expf(-g)) * u; }
 
 template <int EPI>
 __device__ __forceinline__ void emit(const Params& p, int t, int n, float v, float u) {
@@ -71,7 +91,55 @@ __device__ __forceinline__ void emit(const Params& p, int t, int n, float v, flo
   if (EPI == EPI_STORE) ((bf16*)p.C)[o] = __float2bfloat16_rn(v);
   else if (EPI == EPI_STORE_F32) ((float*)p.C)[o] = v;
   else if (EPI == EPI_ACCUM_F32) ((float*)p.C)[o] += v;
-  else ((bf16*)p.C)[o] = __float2bfloat16_rn(v / (1.f + expf(-v)) * u);
+  else if (EPI == EPI_SWIGLU) ((bf16*)p.C)[o] = __float2bfloat16_rn(v / (1.f + expf(-v)) * u);
+}
+
+// Rotary epilogue for one (token, output row n) whose pre-rotation value is v and whose pair
+// partner's value is w (partner = n +- rot_dim/2 inside the same head). Rows are laid out
+// [q heads | k heads | v heads] x hd. q is stored rotated into C; k rotated and v as is go to
+// C as well (so the buffer stays complete) and into the paged cache.
+__device__ __forceinline__ void emit_rope(const Params& p, int t, int n, float v, float w) {
+  const RopeArgs& r = p.rope;
+  const int head = n / r.hd, d = n % r.hd;
+  float out = v;
+  if (head < r.nh + r.nkv && d < r.rot_dim) {
+    const int half = r.rot_dim >> 1;
+    const int i = d < half ? d : d - half;
+    float sn, cs;
+    sincosf((float)r.positions[t] * r.inv_freq[i], &sn, &cs);
+    out = d < half ? v * cs - w * sn : w * sn + v * cs;
+  }
+  const bf16 ob = __float2bfloat16_rn(out);
+  ((bf16*)p.C)[(size_t)t * p.ldc + n] = ob;
+  if (head >= r.nh && r.slots) {
+    const int slot = r.slots[t];
+    if (slot >= 0) {
+      const int page = slot / r.page_size, off = slot % r.page_size;
+      const bool is_k = head < r.nh + r.nkv;
+      const int kvh = is_k ? head - r.nh : head - r.nh - r.nkv;
+      bf16* dst = (is_k ? r.kcache : r.vcache) + (((size_t)page * r.nkv + kvh) * r.page_size + off) * r.hd;
+      dst[d] = ob;
+    }
+  }
+}
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
 }
 
 template <int BN, int EPI>
@@ -79,6 +147,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const Params p) {
   constexpr bool DUAL = (EPI == EPI_SWIGLU);
+  constexpr bool ROPE = (EPI == EPI_QKV_ROPE);
   typedef Cfg<BN, DUAL> C;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[C::STAGES];
@@ -86,7 +155,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   __shared__ __align__(8) uint64_t acc_bar;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ int last_flag;
   __shared__ int never_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -94,16 +162,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 
   const int n0 = blockIdx.x * BM;          // first weight row / output feature of the tile
   const int t0 = blockIdx.y * BN;          // first token of the tile
+  const int rank = p.splits > 1 ? (int)cluster_rank() : 0;
   const int kb_total = (p.K + BK - 1) / BK;
-  const int kb_begin = (int)((long long)blockIdx.z * kb_total / p.splits);
-  const int kb_end = (int)((long long)(blockIdx.z + 1) * kb_total / p.splits);
+  const int kb_begin = (int)((long long)rank * kb_total / p.splits);
+  const int kb_end = (int)((long long)(rank + 1) * kb_total / p.splits);
   const int n_kb = kb_end - kb_begin;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     mbar_init(&acc_bar, 1);
     abort_flag = 0;
-    last_flag = 0;
     never_flag = 0;
     fence_barrier_init();
   }
@@ -112,15 +180,31 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_launch();        // the next kernel may start its prologue: every CTA of this one holds its TMEM by now
   const uint32_t tmem_base = tmem_base_slot;
+  float* red = reinterpret_cast<float*>(smem);          // [ACCS * BN][BM] partial tile of this rank
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       const uint64_t pol_w = policy_evict_first();   // weights are read once per step
       const uint64_t pol_x = policy_evict_last();    // the token tile is shared by every weight tile
-      int issued = 0;
-      for (int i = 0; i < n_kb; ++i) {
+      // weights of the first stages do not depend on the kernel before this one
+      const int pre = n_kb < C::STAGES ? n_kb : C::STAGES;
+      for (int i = 0; i < pre; ++i) {
+        uint8_t* st = smem + (size_t)i * C::STAGE_BYTES;
+        mbar_expect_tx(&full_bar[i], C::STAGE_BYTES);
+        const int k = (kb_begin + i) * BK;
+        tma_load_2d_hint(st, &tmap_w, &full_bar[i], k, n0, pol_w);
+        if (DUAL) tma_load_2d_hint(st + C::A_BYTES, &tmap_w, &full_bar[i], k, p.up_row0 + n0, pol_w);
+      }
+      pdl_wait();                                    // activations come from the kernel before
+      for (int i = 0; i < pre; ++i) {
+        uint8_t* st = smem + (size_t)i * C::STAGE_BYTES;
+        tma_load_2d_hint(st + C::A_TILES * C::A_BYTES, &tmap_x, &full_bar[i], (kb_begin + i) * BK, t0, pol_x);
+      }
+      int issued = pre;
+      for (int i = pre; i < n_kb; ++i) {
         const int s = i % C::STAGES;
         const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
         if (!mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 1); break; }
@@ -171,12 +255,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     const int q = warp & 3;                       // TMEM lanes [32q, 32q + 32) belong to this warp
     const int row = q * 32 + lane;                // weight row within the tile
     const int n = n0 + row;
+    pdl_wait();                                   // nothing is written before the predecessor is done
     bool ok = mbar_wait(&acc_bar, 0, &abort_flag);
     if (!ok) { abort_flag = 1; atomicExch(p.err, 3); }
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-    if (ok && p.splits == 1) {
+    if (ok && p.splits == 1 && !ROPE) {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         if (t0 + c0 >= p.T) break;
@@ -193,10 +278,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         }
       }
     } else if (ok) {
-      // split-K: park the partial tile, then the last CTA of the tile reduces in split order
-      const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-      constexpr int ACCS = DUAL ? 2 : 1;
-      float* mine = p.ws + ((size_t)tile * p.splits + blockIdx.z) * (ACCS * BN * BM);
+      // park the partial tile in shared memory (the stages are idle: every load was consumed)
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         if (t0 + c0 >= p.T) break;
@@ -206,37 +288,55 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          __stcg(mine + (size_t)(c0 + j) * BM + row, __uint_as_float(g[j]));
-          if (DUAL) __stcg(mine + (size_t)(BN + c0 + j) * BM + row, __uint_as_float(u[j]));
-        }
-      }
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) {
-        const int old = atomicAdd(&p.counters[tile], 1);
-        last_flag = (old == p.splits - 1);
-        if (old == p.splits - 1) p.counters[tile] = 0;      // ready for the next launch
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (last_flag) {
-        __threadfence();
-        const float* base = p.ws + (size_t)tile * p.splits * (ACCS * BN * BM);
-        if (n < p.N) {
-#pragma unroll 1
-          for (int c = 0; c < BN; ++c) {
-            const int t = t0 + c;
-            if (t >= p.T) break;
-            float g = 0.f, u = 0.f;
-            for (int s = 0; s < p.splits; ++s) {
-              const float* part = base + (size_t)s * (ACCS * BN * BM);
-              g += __ldcg(part + (size_t)c * BM + row);
-              if (DUAL) u += __ldcg(part + (size_t)(BN + c) * BM + row);
-            }
-            emit<EPI>(p, t, n, g, u);
-          }
+          red[(size_t)(c0 + j) * BM + row] = __uint_as_float(g[j]);
+          if (DUAL) red[(size_t)(BN + c0 + j) * BM + row] = __uint_as_float(u[j]);
         }
       }
     }
+  }
+
+  if (p.splits > 1 || ROPE) {
+    // ---------------------------------------------------------- sum over the ranks of the cluster
+    __syncwarp();
+    tc_fence_before();
+    if (p.splits > 1) cluster_sync_all(); else __syncthreads();      // every partial tile is parked
+    if (warp >= 2 && !abort_flag) {
+      const int row = (warp & 3) * 32 + lane;
+      const int n = n0 + row;
+      uint32_t base[MAX_CLUSTER];
+      const uint32_t mine = smem_u32(red);
+#pragma unroll
+      for (int s = 0; s < MAX_CLUSTER; ++s) base[s] = (p.splits > 1 && s < p.splits) ? map_to_rank(mine, (uint32_t)s) : mine;
+      // the pair partner of this row under the rotary epilogue (same tile: heads do not straddle tiles)
+      int prow = row;
+      if (ROPE) {
+        const int d = n % p.rope.hd, half = p.rope.rot_dim >> 1;
+        if (d < p.rope.rot_dim) prow = d < half ? row + half : row - half;
+      }
+#pragma unroll 1
+      for (int c = rank; c < BN; c += p.splits) {
+        const int t = t0 + c;
+        if (t >= p.T) break;
+        float g = 0.f, u = 0.f, w = 0.f;
+        float pg[MAX_CLUSTER], pu[MAX_CLUSTER], pw[MAX_CLUSTER];
+#pragma unroll
+        for (int s = 0; s < MAX_CLUSTER; ++s) {
+          pg[s] = pu[s] = pw[s] = 0.f;
+          if (s < p.splits) {
+            pg[s] = ld_cluster_f32(base[s] + (uint32_t)((c * BM + row) * 4));
+            if (DUAL) pu[s] = ld_cluster_f32(base[s] + (uint32_t)(((BN + c) * BM + row) * 4));
+            if (ROPE) pw[s] = ld_cluster_f32(base[s] + (uint32_t)((c * BM + prow) * 4));
+          }
+        }
+#pragma unroll
+        for (int s = 0; s < MAX_CLUSTER; ++s) { g += pg[s]; u += pu[s]; w += pw[s]; }   // rank order
+        if (n < p.N) {
+          if (ROPE) emit_rope(p, t, n, g, w);
+          else emit<EPI>(p, t, n, g, u);
+        }
+      }
+    }
+    if (p.splits > 1) cluster_sync_all();       // nobody leaves while its shared memory is still read
   }
   tc_fence_before();
   __syncthreads();
@@ -311,8 +411,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 g
                              C::SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return -5; }
     configured = true;
   }
-  tc_gemm_kernel<BN, EPI><<<grid, THREADS, C::SMEM_BYTES, s>>>(mw, mx, p);
-  return launch_status();
+  return launch_ex(tc_gemm_kernel<BN, EPI>, grid, dim3(THREADS), C::SMEM_BYTES, s, p.splits, mw, mx, p);
 }
 
 template <int EPI>
@@ -329,52 +428,38 @@ int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const Params
   return ERR_BAD_SIZE;
 }
 
-}  // namespace
-
-// Token tile and split count the launcher would choose (exposed for tests and sizing scratch).
-RLLM_API int rllm_tc_gemm_plan(int epi, int T, int N, int K, int sm_count, long long ws_bytes,
-                               int max_counters, int* bn_out, int* splits_out) {
+void plan(int epi, int T, int N, int K, int sm_count, bool allow_split, int* bn_out, int* splits_out) {
   const bool dual = epi == EPI_SWIGLU;
   int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : (T <= 128 || dual) ? 128 : 256;
   const int tiles = ((N + BM - 1) / BM) * ((T + bn - 1) / bn);
   const int kb = (K + BK - 1) / BK;
   int splits = 1;
-  if (tiles < sm_count) {
-    splits = (2 * sm_count + tiles - 1) / tiles;            // aim at two CTAs' worth of tiles per SM
-    if (splits > kb / 2) splits = kb / 2;                   // at least two K blocks per split
-    if (splits > 32) splits = 32;
-    const long long per_split = (long long)tiles * (dual ? 2 : 1) * bn * BM * 4;
-    if (per_split > 0 && splits * per_split > ws_bytes) splits = (int)(ws_bytes / per_split);
-    if (tiles > max_counters) splits = 1;
+  if (allow_split && tiles * 2 <= sm_count) {
+    splits = sm_count / tiles;                              // one CTA per SM, as far as it goes
+    if (splits > kb / 2) splits = kb / 2;                   // at least two K blocks per range
+    if (splits > MAX_CLUSTER) splits = MAX_CLUSTER;
     if (splits < 1) splits = 1;
   }
   *bn_out = bn;
   *splits_out = splits;
-  return 0;
 }
 
-// X: [T, K] bf16, row stride ldx; W: [N, K] bf16 contiguous ([2N, K] for SwiGLU: gate rows then up
-// rows); C: [T, N] with row stride ldc, bf16 (store, SwiGLU) or float (store-float, accumulate).
-// ws / counters: split-K scratch (may be null: then no split). Returns 0, or a negative refusal.
-RLLM_API int rllm_tc_gemm(int epi, const void* X, long long ldx, const void* W, void* Cout, long long ldc,
-                          int T, int N, int K, float* ws, long long ws_bytes, int* counters,
-                          int max_counters, int* err, int sm_count, void* stream) {
+int run(int epi, const void* X, long long ldx, const void* W, void* Cout, long long ldc, int T, int N, int K,
+        int allow_split, int* err, int sm_count, const RopeArgs* rope, void* stream) {
   if (T <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8) return ERR_BAD_SIZE;              // TMA: strides multiple of 16 bytes
   if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return ERR_BAD_ALIGN;
-  if (epi < 0 || epi > 3) return ERR_BAD_SIZE;
   int rc = get_encoder();
   if (rc) return rc;
   int bn, splits;
-  rllm_tc_gemm_plan(epi, T, N, K, sm_count, ws ? ws_bytes : 0, counters ? max_counters : 0, &bn, &splits);
-  if (!ws || !counters) splits = 1;
+  plan(epi, T, N, K, sm_count, allow_split != 0, &bn, &splits);
   const bool dual = epi == EPI_SWIGLU;
   CUtensorMap mw, mx;
   if ((rc = cached_map(&mw, W, dual ? 2LL * N : N, K, K, BM))) return rc;
   if ((rc = make_map(&mx, X, T, K, ldx, bn))) return rc;
   Params p;
-  p.C = Cout; p.ldc = (int)ldc; p.T = T; p.N = N; p.K = K; p.up_row0 = N; p.splits = splits;
-  p.ws = ws; p.counters = counters; p.err = err;
+  p.C = Cout; p.ldc = (int)ldc; p.T = T; p.N = N; p.K = K; p.up_row0 = N; p.splits = splits; p.err = err;
+  p.rope = rope ? *rope : RopeArgs{};
   dim3 grid((N + BM - 1) / BM, (T + bn - 1) / bn, splits);
   if (grid.y > 65535) return ERR_TOO_LARGE;
   cudaStream_t s = (cudaStream_t)stream;
@@ -382,6 +467,42 @@ RLLM_API int rllm_tc_gemm(int epi, const void* X, long long ldx, const void* W, 
     case EPI_STORE: return launch_bn<EPI_STORE>(bn, mw, mx, p, grid, s);
     case EPI_STORE_F32: return launch_bn<EPI_STORE_F32>(bn, mw, mx, p, grid, s);
     case EPI_ACCUM_F32: return launch_bn<EPI_ACCUM_F32>(bn, mw, mx, p, grid, s);
-    default: return launch_bn<EPI_SWIGLU>(bn, mw, mx, p, grid, s);
+    case EPI_SWIGLU: return launch_bn<EPI_SWIGLU>(bn, mw, mx, p, grid, s);
+    case EPI_QKV_ROPE: return launch_bn<EPI_QKV_ROPE>(bn, mw, mx, p, grid, s);
   }
+  return ERR_BAD_SIZE;
+}
+
+}  // namespace
+
+// Token tile and ranges of K (= CTAs per cluster) the launcher would choose.
+RLLM_API int rllm_tc_gemm_plan(int epi, int T, int N, int K, int sm_count, int allow_split, int* bn_out,
+                               int* splits_out) {
+  plan(epi, T, N, K, sm_count, allow_split != 0, bn_out, splits_out);
+  return 0;
+}
+
+// X: [T, K] bf16, row stride ldx; W: [N, K] bf16 contiguous ([2N, K] for SwiGLU: gate rows then up
+// rows); C: [T, N] with row stride ldc, bf16 (store, SwiGLU) or float (store-float, accumulate).
+// allow_split 0: one CTA per output tile whatever the size. Returns 0, or a negative refusal.
+RLLM_API int rllm_tc_gemm(int epi, const void* X, long long ldx, const void* W, void* Cout, long long ldc,
+                          int T, int N, int K, int allow_split, int* err, int sm_count, void* stream) {
+  if (epi < 0 || epi > 3) return ERR_BAD_SIZE;
+  return run(epi, X, ldx, W, Cout, ldc, T, N, K, allow_split, err, sm_count, nullptr, stream);
+}
+
+// The q/k/v projection with the rotary position encoding and the cache write in its epilogue:
+// QKV[T, (nh + 2 nkv) * hd] = X W^T; pair (i, i + rot_dim/2) of every q and k head is rotated by
+// positions[t] * inv_freq[i]; rotated k and plain v also go to the paged cache at slots[t]
+// (slots null or < 0: no write). Head size must divide 128 so that no head straddles two tiles.
+RLLM_API int rllm_tc_gemm_qkv_rope(const void* X, long long ldx, const void* W, void* QKV, long long ldc, int T,
+                                   int K, const int* positions, const float* inv_freq, const int* slots,
+                                   void* kcache, void* vcache, int nh, int nkv, int hd, int page_size,
+                                   int rot_dim, int allow_split, int* err, int sm_count, void* stream) {
+  if (hd <= 0 || BM % hd || rot_dim % 2 || rot_dim > hd || rot_dim < 0 || nh <= 0 || nkv <= 0 || page_size <= 0)
+    return ERR_BAD_SIZE;
+  RopeArgs r;
+  r.positions = positions; r.inv_freq = inv_freq; r.slots = slots; r.kcache = (bf16*)kcache;
+  r.vcache = (bf16*)vcache; r.nh = nh; r.nkv = nkv; r.hd = hd; r.page_size = page_size; r.rot_dim = rot_dim;
+  return run(EPI_QKV_ROPE, X, ldx, W, QKV, ldc, T, (nh + 2 * nkv) * hd, K, allow_split, err, sm_count, &r, stream);
 }

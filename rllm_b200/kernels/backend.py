@@ -71,6 +71,20 @@ class Backend:
         return ops.gemm_simt(x, w_gate_up, ops.EPI_SWIGLU)
 
     # ---- position encoding + cache write, attention
+    def qkv_rope_cache_write(self, x, w_qkv, bias, positions, inv_freq, cache, nh, nkv, hd, rot_dim=None):
+        """qkv = x w_qkv^T (+ bias), q and k rotated, k and v written to the cache. One kernel when
+        the tensor-core product takes the sizes, else the product followed by the rotation kernel."""
+        rot_dim = hd if rot_dim is None else rot_dim
+        if bias is None and self._sm100 is not None and \
+                self._sm100.qkv_rope_supported(x, w_qkv, cache.k if cache.writes else None, hd):
+            writes = cache.writes
+            return self._sm100.gemm_qkv_rope(x, w_qkv, positions, inv_freq, cache.slots if writes else None,
+                                             cache.k if writes else None, cache.v if writes else None,
+                                             nh, nkv, hd, cache.page_size, rot_dim)
+        qkv = self.linear(x, w_qkv, bias=bias)
+        self.rope_cache_write(qkv, positions, inv_freq, cache, nh, nkv, hd, rot_dim)
+        return qkv
+
     def rope_cache_write(self, qkv, positions, inv_freq, cache, nh, nkv, hd, rot_dim=None):
         writes = cache.writes
         ops.rope_cache_write(qkv, positions, inv_freq, cache.slots if writes else None,

@@ -1,6 +1,5 @@
 """Python face of the tcgen05 / TMA kernels (library "sm100"), which only the bfloat16 path
-calls. Holds the scratch memory of the split-K product (partial tiles and tile counters) and
-the device error word that a bounded wait sets when it runs out."""
+calls. Holds the device error word that a bounded wait sets when it runs out."""
 from __future__ import annotations
 
 from ctypes import c_float, c_int, c_longlong, c_void_p, POINTER, byref
@@ -11,22 +10,18 @@ from . import ops
 
 _P = c_void_p
 ops.register_signatures("sm100", {
-    "rllm_tc_gemm": [c_int, _P, c_longlong, _P, _P, c_longlong, c_int, c_int, c_int, _P, c_longlong, _P,
-                     c_int, _P, c_int, _P],
-    "rllm_tc_gemm_plan": [c_int, c_int, c_int, c_int, c_int, c_longlong, c_int, POINTER(c_int), POINTER(c_int)],
+    "rllm_tc_gemm": [c_int, _P, c_longlong, _P, _P, c_longlong, c_int, c_int, c_int, c_int, _P, c_int, _P],
+    "rllm_tc_gemm_plan": [c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)],
+    "rllm_tc_gemm_qkv_rope": [_P, c_longlong, _P, _P, c_longlong, c_int, c_int, _P, _P, _P, _P, _P, c_int, c_int,
+                              c_int, c_int, c_int, c_int, _P, c_int, _P],
     "rllm_attention_fa": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_float, c_int, c_int, _P, _P, _P],
 })
-
-WS_BYTES = 64 << 20
-MAX_COUNTERS = 8192
 
 
 class _State:
     def __init__(self, device):
         self.device = device
-        self.ws = torch.empty(WS_BYTES // 4, dtype=torch.float32, device=device)
-        self.counters = torch.zeros(MAX_COUNTERS, dtype=torch.int32, device=device)
         self.err = torch.zeros(1, dtype=torch.int32, device=device)
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
 
@@ -63,11 +58,11 @@ def gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and x.shape[0] > 0)
 
 
-def plan(epilogue: int, T: int, N: int, K: int, device="cuda:0") -> tuple[int, int]:
+def plan(epilogue: int, T: int, N: int, K: int, device="cuda:0", split: bool = True) -> tuple[int, int]:
+    """(token tile, ranges of K = CTAs per cluster) the launcher chooses for a problem."""
     st = init(device)
     bn, sp = c_int(), c_int()
-    ops._fn("sm100", "rllm_tc_gemm_plan")(epilogue, T, N, K, st.sm_count, WS_BYTES, MAX_COUNTERS,
-                                          byref(bn), byref(sp))
+    ops._fn("sm100", "rllm_tc_gemm_plan")(epilogue, T, N, K, st.sm_count, int(split), byref(bn), byref(sp))
     return bn.value, sp.value
 
 
@@ -89,9 +84,44 @@ def gemm(x: torch.Tensor, w: torch.Tensor, epilogue: int, out: torch.Tensor | No
         raise ops.KernelError(f"tc gemm out must be [{T}, {N}] of {out_dtype}")
     rc = ops._fn("sm100", "rllm_tc_gemm")(
         epilogue, x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), T, N, K,
-        st.ws.data_ptr() if split else None, WS_BYTES, st.counters.data_ptr() if split else None,
-        MAX_COUNTERS, st.err.data_ptr(), st.sm_count, ops._stream())
+        int(split), st.err.data_ptr(), st.sm_count, ops._stream())
     ops._check(rc, "tc_gemm")
+    return out
+
+
+def qkv_rope_supported(x: torch.Tensor, w: torch.Tensor, kcache, hd: int) -> bool:
+    return gemm_supported(x, w) and 128 % hd == 0 and (kcache is None or kcache.dtype == torch.bfloat16)
+
+
+def gemm_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
+                  slots: torch.Tensor | None, kcache: torch.Tensor | None, vcache: torch.Tensor | None,
+                  nh: int, nkv: int, hd: int, page_size: int, rot_dim: int, split: bool = True) -> torch.Tensor:
+    """qkv = x w_qkv^T with q and k rotated by position and k, v written to the paged cache at
+    `slots` (None: no write), all in the product's epilogue. Returns qkv [T, (nh + 2 nkv) * hd]."""
+    if not qkv_rope_supported(x, w_qkv, kcache, hd):
+        raise ops.KernelError("tc gemm with rotary epilogue: bfloat16 operands and a head size dividing 128")
+    st = init(x.device)
+    T, K = x.shape
+    N = (nh + 2 * nkv) * hd
+    if w_qkv.shape[0] != N:
+        raise ops.KernelError(f"w_qkv must have {N} rows, got {w_qkv.shape[0]}")
+    if positions.dtype != torch.int32 or positions.numel() < T or inv_freq.dtype != torch.float32 \
+            or inv_freq.numel() < rot_dim // 2:
+        raise ops.KernelError("positions must be int32 [T] and inv_freq float32 [rot_dim/2]")
+    if slots is not None:
+        if slots.dtype != torch.int32 or slots.numel() < T:
+            raise ops.KernelError("slots must be int32 [T]")
+        for c in (kcache, vcache):
+            if c is None or c.dtype != torch.bfloat16 or c.dim() != 4 or tuple(c.shape[1:]) != (nkv, page_size, hd) \
+                    or not c.is_contiguous():
+                raise ops.KernelError(f"caches must be contiguous bfloat16 [pages, {nkv}, {page_size}, {hd}]")
+    out = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
+    rc = ops._fn("sm100", "rllm_tc_gemm_qkv_rope")(
+        x.data_ptr(), x.stride(0), w_qkv.data_ptr(), out.data_ptr(), out.stride(0), T, K, positions.data_ptr(),
+        inv_freq.data_ptr(), ops._ptr(slots), ops._ptr(kcache) if slots is not None else None,
+        ops._ptr(vcache) if slots is not None else None, nh, nkv, hd, page_size, rot_dim, int(split),
+        st.err.data_ptr(), st.sm_count, ops._stream())
+    ops._check(rc, "tc_gemm_qkv_rope")
     return out
 
 

@@ -54,8 +54,12 @@ class GQAttention(Part):
     def forward(self, x, ctx, cache, residual):
         """x: normalised activations [T, hidden]; adds the mixer's output into `residual`."""
         be = ctx.backend
-        qkv = be.linear(x, self.w_qkv, bias=self.b_qkv)
-        self.position.rotate_and_store(qkv, ctx, cache, self.heads, self.kv_heads)
+        if hasattr(self.position, "project_rotate_store"):
+            qkv = self.position.project_rotate_store(x, self.w_qkv, self.b_qkv, ctx, cache, self.heads,
+                                                     self.kv_heads)
+        else:
+            qkv = be.linear(x, self.w_qkv, bias=self.b_qkv)
+            self.position.rotate_and_store(qkv, ctx, cache, self.heads, self.kv_heads)
         q = qkv[:, : self.q_size]
         attn = be.attention(q, cache, ctx, self.heads, self.scale, self.window)
         be.linear_residual(attn, self.w_o, residual)

@@ -55,6 +55,12 @@ class RotaryEmbedding(Part):
         f = inverse_frequencies(self.rot_dim, self.theta, self.scaling)
         self.inv_freq = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(device)
 
+    def project_rotate_store(self, x, w_qkv, bias, ctx, cache, nh, nkv):
+        """qkv = x w_qkv^T (+ bias) with q and k rotated and k, v written into the layer's pages:
+        the projection and this part's work in one kernel where the backend can."""
+        return ctx.backend.qkv_rope_cache_write(x, w_qkv, bias, ctx.positions, self.inv_freq, cache, nh, nkv,
+                                                self.head_dim, self.rot_dim)
+
     def rotate_and_store(self, qkv, ctx, cache, nh, nkv):
         """Rotate q (in place) and k of `qkv`, and write k, v into the layer's pages."""
         ctx.backend.rope_cache_write(qkv, ctx.positions, self.inv_freq, cache, nh, nkv,

@@ -38,7 +38,7 @@ def test_tc_gemm_epilogues(T, N, K, split):
     want = ref / (1 + torch.exp(-ref)) * up
     assert rel(sm100.gemm(xd, wd, ops.EPI_SWIGLU, split=split), want) <= 6e-3
     sm100.check_error(DEV)
-    # the same call again gives the same bits (split-K sums in split order, counters reset)
+    # the same call again gives the same bits (the ranges of K are summed in rank order)
     again = sm100.gemm(xd, w1, ops.EPI_STORE_F32, split=split)
     assert torch.equal(again, out32)
 
@@ -57,6 +57,69 @@ def test_tc_gemm_takes_a_strided_view_and_refuses_misfits():
 
 def test_plan_splits_small_batches_only():
     from rllm_b200.kernels import ops, sm100
-    assert sm100.plan(ops.EPI_STORE, 8, 3072, 2048) == (16, 13) or sm100.plan(ops.EPI_STORE, 8, 3072, 2048)[1] > 1
+    bn, splits = sm100.plan(ops.EPI_STORE, 8, 3072, 2048)
+    assert bn == 16 and 2 <= splits <= 8                 # 24 tiles: a cluster of ranges of K per tile
+    assert sm100.plan(ops.EPI_ACCUM_F32, 64, 2048, 8192) == (64, 8)
+    assert sm100.plan(ops.EPI_STORE, 8, 3072, 2048, split=False) == (16, 1)
     assert sm100.plan(ops.EPI_STORE, 2048, 3072, 2048) == (256, 1)
     assert sm100.plan(ops.EPI_SWIGLU, 2048, 8192, 2048) == (128, 1)
+    assert sm100.plan(ops.EPI_STORE_F32, 8, 128256, 2048) == (16, 1)
+
+
+@pytest.mark.parametrize("split", [True, False])
+@pytest.mark.parametrize("T,K,nh,nkv,hd,page,rot", [
+    (1, 64, 4, 2, 16, 16, None), (9, 96, 3, 1, 32, 8, None), (8, 2048, 32, 8, 64, 16, None),
+    (70, 256, 5, 5, 64, 4, 32), (300, 128, 2, 1, 128, 16, None), (17, 512, 6, 2, 128, 32, 64)])
+def test_qkv_product_with_rotary_epilogue(T, K, nh, nkv, hd, page, rot, split):
+    """q/k/v projection, rotation of q and k, and the cache write in one kernel, against the
+    plain formulas: widths that are no multiple of the tile, head sizes 16 to 128, partial
+    rotation, scattered slots, one token that must not be written."""
+    import plain_llama as P
+    from rllm_b200.kernels import sm100
+    rot_dim = rot or hd
+    N = (nh + 2 * nkv) * hd
+    x, w = rnd(T, K, seed=1), rnd(N, K, seed=2, scale=K ** -0.5)
+    g = torch.Generator().manual_seed(7)
+    positions = torch.randint(0, 5000, (T,), generator=g, dtype=torch.int32)
+    positions[0] = 0
+    inv_freq = P.rope_inv_freq(rot_dim, 500000.0, {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                               "high_freq_factor": 4.0, "original_max_position_embeddings": 32})
+    pages = (T + page - 1) // page + 3
+    slots = torch.randperm(pages * page, generator=g)[:T].to(torch.int32)
+    if T > 2:
+        slots[T // 2] = -1
+    kc = torch.zeros(pages, nkv, page, hd, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    out = sm100.gemm_qkv_rope(x.to(DEV), w.to(DEV), positions.to(DEV), inv_freq.to(DEV), slots.to(DEV), kc, vc,
+                              nh, nkv, hd, page, rot_dim, split=split)
+    sm100.check_error(DEV)
+    ref = x.float() @ w.float().t()
+    q = ref[:, : nh * hd].view(T, nh, hd)
+    k = ref[:, nh * hd: (nh + nkv) * hd].view(T, nkv, hd)
+    v = ref[:, (nh + nkv) * hd:].view(T, nkv, hd)
+
+    def rope(t):
+        r = P.rope(t[..., :rot_dim], positions, inv_freq)
+        return torch.cat([r, t[..., rot_dim:]], -1)
+
+    qr, kr = rope(q), rope(k)
+    scale = float(ref.abs().max())
+    got = out.float().cpu()
+    assert float((got[:, : nh * hd].view(T, nh, hd) - qr).abs().max()) <= 6e-3 * scale
+    assert float((got[:, nh * hd: (nh + nkv) * hd].view(T, nkv, hd) - kr).abs().max()) <= 6e-3 * scale
+    assert float((got[:, (nh + nkv) * hd:].view(T, nkv, hd) - v).abs().max()) <= 6e-3 * scale
+    written = torch.zeros(pages, page, dtype=torch.bool)
+    kcc, vcc = kc.float().cpu(), vc.float().cpu()
+    for t in range(T):
+        if slots[t] < 0:
+            continue
+        pg, off = int(slots[t]) // page, int(slots[t]) % page
+        written[pg, off] = True
+        assert float((kcc[pg, :, off] - kr[t]).abs().max()) <= 6e-3 * scale
+        assert float((vcc[pg, :, off] - v[t]).abs().max()) <= 6e-3 * scale
+    mask = ~written[:, None, :].expand(-1, nkv, -1)
+    assert float(kcc[mask].abs().sum()) == 0.0 and float(vcc[mask].abs().sum()) == 0.0   # nothing else touched
+    # no cache write at all when no slots are given (a layer that reads another layer's cache)
+    out2 = sm100.gemm_qkv_rope(x.to(DEV), w.to(DEV), positions.to(DEV), inv_freq.to(DEV), None, None, None,
+                               nh, nkv, hd, page, rot_dim, split=split)
+    assert torch.equal(out2, out)
