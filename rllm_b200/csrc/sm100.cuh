@@ -57,6 +57,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return true;
 }
 
+// The first failure of a launch is the one recorded: low byte = the role that gave up, the rest
+// = a detail the kernel chooses (which tile, which sequence). Later failures of the same launch
+// are consequences (they saw the abort flag) and do not overwrite it.
+__device__ __forceinline__ void record_failure(int* err, int role, int detail = 0) {
+  atomicCAS(err, 0, (role & 0xff) | (detail << 8));
+}
+
 // ------------------------------------------------------------------ TMA
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");

@@ -207,7 +207,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       for (int i = pre; i < n_kb; ++i) {
         const int s = i % C::STAGES;
         const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
-        if (!mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 1); break; }
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag)) { abort_flag = 1; record_failure(p.err, 1); break; }
         uint8_t* st = smem + (size_t)s * C::STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
         const int k = (kb_begin + i) * BK;
@@ -230,7 +230,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       for (int i = 0; i < n_kb && ok; ++i) {
         const int s = i % C::STAGES;
         const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
-        if (!mbar_wait(&full_bar[s], ph, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 2); ok = false; break; }
+        if (!mbar_wait(&full_bar[s], ph, &abort_flag)) { abort_flag = 1; record_failure(p.err, 2); ok = false; break; }
         tc_fence_after();
         const uint32_t a_addr = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
         const uint32_t b_addr = a_addr + C::A_TILES * C::A_BYTES;
@@ -257,7 +257,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     const int n = n0 + row;
     pdl_wait();                                   // nothing is written before the predecessor is done
     bool ok = mbar_wait(&acc_bar, 0, &abort_flag);
-    if (!ok) { abort_flag = 1; atomicExch(p.err, 3); }
+    if (!ok) { abort_flag = 1; record_failure(p.err, 3); }
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
@@ -270,10 +270,21 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         if (DUAL) tmem_ld16(taddr + BN + c0, u);
         tmem_ld_wait();
         if (n < p.N) {
+          if (EPI == EPI_ACCUM_F32) {
+            // all sixteen residual values are fetched before the first store, so the loads overlap
+            float* cp = (float*)p.C + (size_t)(t0 + c0) * p.ldc + n;
+            float r[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int t = t0 + c0 + j;
-            if (t < p.T) emit<EPI>(p, t, n, __uint_as_float(g[j]), DUAL ? __uint_as_float(u[j]) : 0.f);
+            for (int j = 0; j < 16; ++j) r[j] = (t0 + c0 + j < p.T) ? __ldcg(cp + (size_t)j * p.ldc) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (t0 + c0 + j < p.T) cp[(size_t)j * p.ldc] = r[j] + __uint_as_float(g[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int t = t0 + c0 + j;
+              if (t < p.T) emit<EPI>(p, t, n, __uint_as_float(g[j]), DUAL ? __uint_as_float(u[j]) : 0.f);
+            }
           }
         }
       }
@@ -318,6 +329,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const int t = t0 + c;
         if (t >= p.T) break;
         float g = 0.f, u = 0.f, w = 0.f;
+        if (EPI == EPI_ACCUM_F32 && n < p.N) g = __ldcg((const float*)p.C + (size_t)t * p.ldc + n);   // residual
         float pg[MAX_CLUSTER], pu[MAX_CLUSTER], pw[MAX_CLUSTER];
 #pragma unroll
         for (int s = 0; s < MAX_CLUSTER; ++s) {
@@ -332,6 +344,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         for (int s = 0; s < MAX_CLUSTER; ++s) { g += pg[s]; u += pu[s]; w += pw[s]; }   // rank order
         if (n < p.N) {
           if (ROPE) emit_rope(p, t, n, g, w);
+          else if (EPI == EPI_ACCUM_F32) ((float*)p.C)[(size_t)t * p.ldc + n] = g;   // residual + ranks in order
           else emit<EPI>(p, t, n, g, u);
         }
       }

@@ -75,7 +75,9 @@ class Backend:
         """qkv = x w_qkv^T (+ bias), q and k rotated, k and v written to the cache. One kernel when
         the tensor-core product takes the sizes, else the product followed by the rotation kernel."""
         rot_dim = hd if rot_dim is None else rot_dim
-        if bias is None and self._sm100 is not None and \
+        # the fused epilogue pays for decode and small mixed steps; a long prompt portion
+        # rotates faster in the row-parallel kernel
+        if bias is None and self._sm100 is not None and x.shape[0] <= 128 and \
                 self._sm100.qkv_rope_supported(x, w_qkv, cache.k if cache.writes else None, hd):
             writes = cache.writes
             return self._sm100.gemm_qkv_rope(x, w_qkv, positions, inv_freq, cache.slots if writes else None,

@@ -16,6 +16,8 @@ ops.register_signatures("sm100", {
                               c_int, c_int, c_int, c_int, _P, c_int, _P],
     "rllm_attention_fa": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_float, c_int, c_int, _P, _P, _P],
+    "rllm_attention_decode": [_P, c_int, _P, _P, c_longlong, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int,
+                              c_int, c_float, c_int, c_int, _P, _P],
 })
 
 
@@ -48,7 +50,8 @@ def check_error(device) -> None:
     code = int(st.err.item())
     if code:
         st.err.zero_()
-        raise ops.KernelError(f"a tcgen05 kernel gave up waiting (role {code}); its output is not valid")
+        raise ops.KernelError(f"a kernel's bounded wait ran out (role {code & 0xff}, detail {code >> 8}); "
+                              f"its output is not valid")
 
 
 def gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -166,9 +169,52 @@ def attention_fa(q, kcache, vcache, cu_q, kv_lens, block_table, num_tokens, max_
     return out
 
 
+def decode_supported(q: torch.Tensor, kcache: torch.Tensor, nh: int) -> bool:
+    _, nkv, page_size, hd = kcache.shape
+    return (attention_supported(q, kcache) and page_size in (8, 16, 32, 64) and page_size * hd <= 4096
+            and nh // nkv <= 16
+            and kcache.data_ptr() % 128 == 0)
+
+
+def decode_splits(num_seqs: int, nkv: int, max_kv_len: int, sm_count: int) -> int:
+    """Ranges the keys of a sequence are cut into (= CTAs per cluster, at most 8): enough for
+    about two CTAs per SM, each with at least four 64-key tiles."""
+    base = max(1, num_seqs * nkv)
+    want = (2 * sm_count + base // 2) // base
+    return max(1, min(want, max_kv_len // 256, 8))
+
+
+def attention_decode(q, kcache, vcache, kv_lens, block_table, nh, scale, window, max_kv_len, splits=None,
+                     out=None):
+    """Attention for a step in which every sequence brings one token: TMA-fed, merged inside a
+    thread-block cluster (bf16, head size 64 or 128, pages of 8/16/32/64 positions)."""
+    st = init(q.device)
+    num_pages, nkv, page_size, hd = kcache.shape
+    S = kv_lens.numel()
+    if not decode_supported(q, kcache, nh) or q.shape[0] != S:
+        raise ops.KernelError("attention_decode: one bfloat16 query row per sequence, head size 64 or 128, "
+                              "pages of 8, 16, 32 or 64 positions, at most 16 heads per kv head")
+    if vcache.shape != kcache.shape or vcache.dtype != kcache.dtype or not kcache.is_contiguous() \
+            or not vcache.is_contiguous() or block_table.dtype != torch.int32 or kv_lens.dtype != torch.int32:
+        raise ops.KernelError("attention_decode: caches must be contiguous and alike, tables int32")
+    if splits is None:
+        splits = decode_splits(S, nkv, max_kv_len, st.sm_count)
+    if out is None:
+        out = torch.empty((S, nh * hd), dtype=torch.bfloat16, device=q.device)
+    rc = ops._fn("sm100", "rllm_attention_decode")(
+        q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(), num_pages, out.data_ptr(),
+        out.stride(0), kv_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0), S, nh, nkv, hd,
+        page_size, float(scale), int(window or 0), int(splits), st.err.data_ptr(), ops._stream())
+    ops._check(rc, "attention_decode")
+    return out
+
+
 def attention(q, cache, ctx, nh, scale, window):
     """The backend's hook: None when this kernel does not take the sizes at hand."""
     if not attention_supported(q, cache.k):
         return None
+    if ctx.max_q_len == 1 and decode_supported(q, cache.k, nh):
+        return attention_decode(q, cache.k, cache.v, ctx.kv_lens, cache.block_table, nh, scale, window,
+                                ctx.max_kv_len)
     return attention_fa(q, cache.k, cache.v, ctx.cu_q, ctx.kv_lens, cache.block_table, ctx.num_tokens,
                         ctx.max_q_len, ctx.max_kv_len, nh, scale, window)

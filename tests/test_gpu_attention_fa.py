@@ -76,6 +76,50 @@ def test_decode_with_split_keys(splits, nh, nkv, hd, page):
     run(nh, nkv, hd, page, 50, lens=[1, 63, 64, 65, 700, 129], q_lens=[1, 1, 1, 1, 1, 1], splits=splits)
 
 
+@pytest.mark.parametrize("splits", [1, 2, 3, 8])
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [
+    (32, 8, 64, 16, None), (8, 1, 128, 8, None), (3, 1, 64, 32, None), (16, 1, 64, 64, 100),
+    (4, 4, 128, 16, 70), (12, 4, 64, 8, None), (6, 2, 128, 32, None)])
+def test_decode_kernel_with_cluster_merge(splits, nh, nkv, hd, page, window):
+    """The TMA-fed decode kernel against the plain formula: lengths on both sides of a tile and
+    of a page, one sequence of a single key, scattered pages, windows, and a far key that must
+    dominate (it lies in another range than the query's own position)."""
+    from rllm_b200.kernels import sm100
+    lens = [1, 63, 64, 65, 700, 129, 1000, 17]
+    S = len(lens)
+    kc, vc, bt, ks, vs = scattered_cache(S, lens, nkv, hd, page, torch.bfloat16, seed=hd + nh + page)
+    g = torch.Generator().manual_seed(6)
+    q = torch.randn(S, nh, hd, generator=g).to(torch.bfloat16)
+    far = None
+    if window is None:
+        far = (4, 5)
+        ks[4][5] = 0
+        ks[4][5, :, 0] = 30.0
+        q[4, :, 0] = 30.0
+        kc[int(bt[4, 5 // page]), :, 5 % page] = ks[4][5]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    buf = torch.zeros(S, (nh + 2 * nkv) * hd, dtype=torch.bfloat16)
+    buf[:, : nh * hd] = q.reshape(S, nh * hd)
+    bufd = buf.to(DEV)
+    out = sm100.attention_decode(bufd[:, : nh * hd], kc.to(DEV), vc.to(DEV), i32(lens), bt.to(DEV), nh,
+                                 hd ** -0.5, window, max(lens), splits=splits)
+    sm100.check_error(DEV)
+    for s in range(S):
+        L = lens[s]
+        qf = torch.zeros(L, nh, hd); qf[L - 1] = q[s].float()
+        ref = P.attention(qf, ks[s].float(), vs[s].float(), hd ** -0.5, window)[L - 1]
+        got = out[s].float().cpu().view(nh, hd)
+        assert torch.isfinite(got).all()
+        assert rel(got, ref) <= TOL, f"sequence {s} (len {L})"
+    if far is not None:
+        got = out[4].float().cpu().view(nh, hd)
+        assert rel(got, vs[4][5].float().repeat_interleave(nh // nkv, 0)) <= TOL
+    # the same call again: same bits (the merge order is fixed)
+    again = sm100.attention_decode(bufd[:, : nh * hd], kc.to(DEV), vc.to(DEV), i32(lens), bt.to(DEV), nh,
+                                   hd ** -0.5, window, max(lens), splits=splits)
+    assert torch.equal(out, again)
+
+
 def test_long_prompt_whole_and_chosen_splits():
     from rllm_b200.kernels import sm100
     run(8, 2, 64, 16, None, lens=[1500], q_lens=[1500], splits=1, far=(0, 3))
