@@ -9,6 +9,7 @@
 // probability tau such that the mass of {p >= tau} reaches top_p". Ties at a
 // threshold are all kept, as in sampler.rs:397-403.
 #include "common.cuh"
+#include "sm100.cuh"
 using namespace rllm;
 
 namespace {
@@ -25,23 +26,47 @@ __device__ __forceinline__ float key2f(unsigned k) {
   return __uint_as_float(u);
 }
 
+// One row of the logits is shared by the CTAs of a thread-block cluster along z (ARGMAX_SPLIT
+// of them for a large vocabulary, one otherwise); each takes a contiguous range, and rank 0
+// picks among the ranks' candidates through distributed shared memory. The rule "largest value,
+// lowest index among equals, NaN never wins" holds at every level, so the result does not
+// depend on how the row is cut.
+constexpr int ARGMAX_SPLIT = 8;
+
+__device__ __forceinline__ void argmax_take(float& best, int& bi, float v, int i) {
+  if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+}
+
 __global__ void __launch_bounds__(THREADS)
-argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
+argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out, int splits) {
   pdl_launch();
   pdl_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
+  __shared__ float cand_v;
+  __shared__ int cand_i;
+  const int rank = splits > 1 ? (int)sm100::cluster_rank() : 0;
   const float* x = logits + (size_t)blockIdx.x * V;
+  // ranges start on multiples of 4 so that the vector loads stay aligned
+  const int per = ((V + splits - 1) / splits + 3) & ~3;
+  const int b = min(V, rank * per), e = min(V, b + per);
   float best = -INFINITY; int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = x[i];
-    if (v > best || (v == best && i < bi)) { best = v; bi = i; }   // NaN never wins
+  if ((V & 3) == 0 && ((uintptr_t)logits & 15) == 0) {
+    const int e4 = b + ((e - b) & ~3);
+    for (int i = b + threadIdx.x * 4; i < e4; i += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(x + i);
+      argmax_take(best, bi, v.x, i); argmax_take(best, bi, v.y, i + 1);
+      argmax_take(best, bi, v.z, i + 2); argmax_take(best, bi, v.w, i + 3);
+    }
+    for (int i = e4 + threadIdx.x; i < e; i += blockDim.x) argmax_take(best, bi, x[i], i);
+  } else {
+    for (int i = b + threadIdx.x; i < e; i += blockDim.x) argmax_take(best, bi, x[i], i);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
     const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    argmax_take(best, bi, ov, oi);
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (lane == 0) { sv[warp] = best; si[warp] = bi; }
@@ -54,9 +79,24 @@ argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, best, o);
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+      argmax_take(best, bi, ov, oi);
     }
-    if (lane == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+    if (lane == 0) { cand_v = best; cand_i = bi; }
+  }
+  if (splits > 1) {
+    sm100::cluster_sync_all();                 // every rank's candidate is in its shared memory
+    if (rank == 0 && threadIdx.x == 0) {
+      best = cand_v; bi = cand_i;
+      for (int r = 1; r < splits; ++r) {
+        const float ov = sm100::ld_cluster_f32(sm100::map_to_rank(sm100::smem_u32(&cand_v), (uint32_t)r));
+        const int oi = (int)sm100::ld_cluster_u32(sm100::map_to_rank(sm100::smem_u32(&cand_i), (uint32_t)r));
+        argmax_take(best, bi, ov, oi);
+      }
+      out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+    }
+    sm100::cluster_sync_all();                 // nobody leaves while rank 0 still reads
+  } else if (threadIdx.x == 0) {
+    out[blockIdx.x] = (cand_i == 0x7fffffff) ? 0 : cand_i;
   }
 }
 
@@ -185,8 +225,9 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
 RLLM_API int rllm_argmax(const float* logits, int R, int V, int* out, void* stream) {
   if (R <= 0) return 0;
   if (V <= 0) return ERR_BAD_SIZE;
-  int rc = launch_ex(argmax_kernel, dim3(R), dim3(THREADS), 0, (cudaStream_t)stream, 1, logits, V, out);
-  return rc;
+  const int splits = V >= 16384 ? ARGMAX_SPLIT : 1;
+  return launch_ex(argmax_kernel, dim3(R, 1, splits), dim3(THREADS), 0, (cudaStream_t)stream, splits, logits, V,
+                   out, splits);
 }
 
 // Per-row parameter arrays of length R; top_k / top_p / min_p may be null (off).

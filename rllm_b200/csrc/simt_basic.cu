@@ -39,28 +39,93 @@ RLLM_API int rllm_embed(const int* ids, const void* table, int table_dt, float* 
 // y = x * rsqrt(mean(x^2) + eps) * w   (reference: src/gpu/cuda/shaders/rms_norm.cu:78-115)
 // x is the float residual stream; w float or bf16; y float or bf16.
 // The sum of squares is taken in a fixed order that depends on H only.
-template <typename TW, typename TO>
+// Rows of up to RMS_VEC * 4 * blockDim floats whose length is a multiple of 4 are held in
+// registers between the two passes (one read of x); other rows are read twice. Either way the
+// order of the sum is the same: thread i takes elements i*4..i*4+3, then (i + blockDim)*4.., a
+// tree over the warp, then over the warps.
+constexpr int RMS_VEC = 4;
+
+template <typename TW> __device__ __forceinline__ void load4(const TW* p, float (&w)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&w)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+}
+template <> __device__ __forceinline__ void load4<bf16>(const bf16* p, float (&w)[4]) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+  w[0] = __low2float(a); w[1] = __high2float(a); w[2] = __low2float(b); w[3] = __high2float(b);
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 o;
+  o.x = *reinterpret_cast<uint32_t*>(&a);
+  o.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = o;
+}
+
+template <typename TW, typename TO, bool VEC>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w,
                                TO* __restrict__ y, int H, float eps) {
   pdl_launch();
-  pdl_wait();
   __shared__ float red[32];
   const float* xr = x + (size_t)blockIdx.x * H;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = xr[i]; ss = fmaf(v, v, ss); }
-  ss = block_sum(ss, red);
-  const float r = rsqrtf(ss / (float)H + eps);
   TO* yr = y + (size_t)blockIdx.x * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = from_f32<TO>(xr[i] * r * to_f32(w[i]));
+  if (VEC) {
+    float wv[RMS_VEC][4];
+#pragma unroll
+    for (int j = 0; j < RMS_VEC; ++j) {                 // weights do not depend on the kernel before
+      const int i = (threadIdx.x + j * blockDim.x) * 4;
+      if (i < H) load4<TW>(w + i, wv[j]);
+    }
+    pdl_wait();
+    float v[RMS_VEC][4];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < RMS_VEC; ++j) {
+      const int i = (threadIdx.x + j * blockDim.x) * 4;
+      if (i < H) {
+        load4<float>(xr + i, v[j]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) ss = fmaf(v[j][q], v[j][q], ss);
+      }
+    }
+    ss = block_sum(ss, red);
+    const float r = rsqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int j = 0; j < RMS_VEC; ++j) {
+      const int i = (threadIdx.x + j * blockDim.x) * 4;
+      if (i < H) {
+        float o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) o[q] = v[j][q] * r * wv[j][q];
+        store4(yr + i, o);
+      }
+    }
+  } else {
+    pdl_wait();
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = xr[i]; ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, red);
+    const float r = rsqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = from_f32<TO>(xr[i] * r * to_f32(w[i]));
+  }
 }
 
 RLLM_API int rllm_rmsnorm(const float* x, const void* w, int w_dt, void* y, int y_dt, int T, int H,
                           float eps, void* stream) {
   if (T <= 0) return 0;
   const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+  const bool vec = H % 4 == 0 && H <= RMS_VEC * 4 * threads && ((uintptr_t)x & 15) == 0 &&
+                   ((uintptr_t)w & 15) == 0 && ((uintptr_t)y & 15) == 0;
   cudaStream_t s = (cudaStream_t)stream;
   int rc = 0;
-#define GO(TW, TO) rc = launch_ex(rmsnorm_kernel<TW, TO>, dim3(T), dim3(threads), 0, s, 1, x, (const TW*)w, (TO*)y, H, eps)
+#define GO(TW, TO)                                                                                              \
+  rc = vec ? launch_ex(rmsnorm_kernel<TW, TO, true>, dim3(T), dim3(threads), 0, s, 1, x, (const TW*)w, (TO*)y, H, eps) \
+           : launch_ex(rmsnorm_kernel<TW, TO, false>, dim3(T), dim3(threads), 0, s, 1, x, (const TW*)w, (TO*)y, H, eps)
   if (w_dt == DT_F32 && y_dt == DT_F32) GO(float, float);
   else if (w_dt == DT_F32 && y_dt == DT_BF16) GO(float, bf16);
   else if (w_dt == DT_BF16 && y_dt == DT_F32) GO(bf16, float);
