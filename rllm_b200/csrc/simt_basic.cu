@@ -68,11 +68,12 @@ __device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
 }
 
 template <typename TW, typename TO, bool VEC>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w,
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const TW* __restrict__ w,
                                TO* __restrict__ y, int H, float eps) {
   pdl_launch();
   __shared__ float red[32];
-  const float* xr = x + (size_t)blockIdx.x * H;
+  // rows (when given) come with the step's metadata, which no kernel of the step writes
+  const float* xr = x + (size_t)(rows ? rows[blockIdx.x] : blockIdx.x) * H;
   TO* yr = y + (size_t)blockIdx.x * H;
   if (VEC) {
     float wv[RMS_VEC][4];
@@ -115,8 +116,9 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
   }
 }
 
-RLLM_API int rllm_rmsnorm(const float* x, const void* w, int w_dt, void* y, int y_dt, int T, int H,
-                          float eps, void* stream) {
+// y[t] = norm(x[rows[t]]) when rows is given, else norm(x[t]).
+RLLM_API int rllm_rmsnorm(const float* x, const int* rows, const void* w, int w_dt, void* y, int y_dt, int T,
+                          int H, float eps, void* stream) {
   if (T <= 0) return 0;
   const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
   const bool vec = H % 4 == 0 && H <= RMS_VEC * 4 * threads && ((uintptr_t)x & 15) == 0 &&
@@ -124,8 +126,8 @@ RLLM_API int rllm_rmsnorm(const float* x, const void* w, int w_dt, void* y, int 
   cudaStream_t s = (cudaStream_t)stream;
   int rc = 0;
 #define GO(TW, TO)                                                                                              \
-  rc = vec ? launch_ex(rmsnorm_kernel<TW, TO, true>, dim3(T), dim3(threads), 0, s, 1, x, (const TW*)w, (TO*)y, H, eps) \
-           : launch_ex(rmsnorm_kernel<TW, TO, false>, dim3(T), dim3(threads), 0, s, 1, x, (const TW*)w, (TO*)y, H, eps)
+  rc = vec ? launch_ex(rmsnorm_kernel<TW, TO, true>, dim3(T), dim3(threads), 0, s, 1, x, rows, (const TW*)w, (TO*)y, H, eps) \
+           : launch_ex(rmsnorm_kernel<TW, TO, false>, dim3(T), dim3(threads), 0, s, 1, x, rows, (const TW*)w, (TO*)y, H, eps)
   if (w_dt == DT_F32 && y_dt == DT_F32) GO(float, float);
   else if (w_dt == DT_F32 && y_dt == DT_BF16) GO(float, bf16);
   else if (w_dt == DT_BF16 && y_dt == DT_F32) GO(bf16, float);
@@ -142,9 +144,31 @@ RLLM_API int rllm_rmsnorm(const float* x, const void* w, int w_dt, void* y, int 
 // (= page * page_size + offset, or < 0 to skip the write).
 // Cache layout: [page][kv head][offset in page][hd].
 // Reference: src/gpu/cuda/shaders/rope.cu:62-77 and attention.cu:295-300.
+// The rotation of a step, made once and read by every layer: cs[t][i] = (cos, sin)(positions[t] *
+// inv_freq[i]) in float, i < n_freq. The same sincosf the kernels below call when they get no table.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float2* __restrict__ cs, int T, int n_freq) {
+  pdl_launch();
+  pdl_wait();
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= T * n_freq) return;
+  const int t = idx / n_freq, i = idx % n_freq;
+  float sn, c;
+  sincosf((float)positions[t] * inv_freq[i], &sn, &c);
+  cs[idx] = make_float2(c, sn);
+}
+RLLM_API int rllm_rope_table(const int* positions, const float* inv_freq, void* cs, int T, int n_freq,
+                             void* stream) {
+  if (T <= 0 || n_freq <= 0) return 0;
+  const int n = T * n_freq;
+  return launch_ex(rope_table_kernel, dim3((n + 255) / 256), dim3(256), 0, (cudaStream_t)stream, 1, positions,
+                   inv_freq, (float2*)cs, T, n_freq);
+}
+
 template <typename T>
 __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
-                                  const float* __restrict__ inv_freq, const int* __restrict__ slots,
+                                  const float* __restrict__ inv_freq, const float2* __restrict__ cos_sin,
+                                  const int* __restrict__ slots,
                                   T* __restrict__ kcache, T* __restrict__ vcache, int nh, int nkv,
                                   int hd, int page_size, int rot_dim) {
   pdl_launch();
@@ -167,7 +191,8 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ p
     float ra = a, rb = b;
     if (i < rh) {
       float sn, cs;
-      sincosf(pos * inv_freq[i], &sn, &cs);
+      if (cos_sin) { const float2 v = cos_sin[(size_t)t * rh + i]; cs = v.x; sn = v.y; }
+      else sincosf(pos * inv_freq[i], &sn, &cs);
       ra = a * cs - b * sn;
       rb = a * sn + b * cs;
     }
@@ -189,8 +214,9 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ p
   }
 }
 
+// cos_sin: the table of rllm_rope_table for these positions ([T][rot_dim / 2] float2), or null.
 RLLM_API int rllm_rope_cache_write(void* qkv, int dt, const int* positions, const float* inv_freq,
-                                   const int* slots, void* kcache, void* vcache, int T, int nh,
+                                   const void* cos_sin, const int* slots, void* kcache, void* vcache, int T, int nh,
                                    int nkv, int hd, int page_size, int rot_dim, void* stream) {
   if (T <= 0) return 0;
   if (hd % 2 || rot_dim % 2 || rot_dim > hd || rot_dim < 0) return ERR_BAD_SIZE;
@@ -199,11 +225,11 @@ RLLM_API int rllm_rope_cache_write(void* qkv, int dt, const int* positions, cons
   const int work = (nh + nkv) * hd / 2;
   const int threads = work >= 512 ? 256 : (work >= 128 ? 128 : 64);
   if (dt == DT_F32)
-    rc = launch_ex(rope_cache_kernel<float>, dim3(T), dim3(threads), 0, s, 1, (float*)qkv, positions, inv_freq, slots,
+    rc = launch_ex(rope_cache_kernel<float>, dim3(T), dim3(threads), 0, s, 1, (float*)qkv, positions, inv_freq, (const float2*)cos_sin, slots,
                                                    (float*)kcache, (float*)vcache, nh, nkv, hd,
                                                    page_size, rot_dim);
   else if (dt == DT_BF16)
-    rc = launch_ex(rope_cache_kernel<bf16>, dim3(T), dim3(threads), 0, s, 1, (bf16*)qkv, positions, inv_freq, slots,
+    rc = launch_ex(rope_cache_kernel<bf16>, dim3(T), dim3(threads), 0, s, 1, (bf16*)qkv, positions, inv_freq, (const float2*)cos_sin, slots,
                                                   (bf16*)kcache, (bf16*)vcache, nh, nkv, hd,
                                                   page_size, rot_dim);
   else return ERR_BAD_DTYPE;

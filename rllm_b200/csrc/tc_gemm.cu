@@ -12,22 +12,36 @@
 // shared-memory stages, warp 1 issues the MMAs (one thread) and owns the TMEM allocation,
 // warps 2-5 run the epilogue.
 //
+// Fused RMSNorm (NORM variants, token tiles up to 64): X is not read by TMA. The input is the
+// float residual stream h and a norm weight g; warps 2-5 build the B operand themselves, stage
+// by stage: bf16(h[t,k] * g[k]) written in the 128-byte swizzled layout the MMA expects, while
+// they add up h[t,k]^2. Since rsqrt(mean(h^2) + eps) is one number per token it commutes with
+// the product and is applied in the epilogue: y[t,n] = rstd[t] * sum_k (h[t,k] g[k]) W[n,k].
+// A list of row indices lets the product read chosen rows of h only (the output head).
+//
 // Split-K for small batches (few output tiles, long K) runs inside a thread-block cluster:
-// the CTAs of a cluster share one output tile and take consecutive ranges of K. Each parks its
-// float partial tile in its own shared memory; after a cluster barrier CTA r sums columns
-// r, r + C, ... over all ranks, in rank order, through distributed shared memory and runs the
-// epilogue for them. Nothing goes through global memory and the sum does not depend on timing.
+// the CTAs of a cluster share one output tile and take consecutive ranges of K. Rank r owns
+// the token columns r, r + C, ...: every rank pushes its float partial column (and its part
+// of the sum of squares) into the owner's shared memory through distributed shared memory,
+// one cluster barrier later the owner adds the parts in rank order from its own shared memory
+// and runs the epilogue. Nothing goes through global memory and the sum does not depend on
+// timing. For token tiles up to 32 the landing area is a region of its own, so a rank pushes as
+// soon as its own products are done; larger tiles land in the (by then idle) stage ring after
+// one more cluster barrier.
 //
 // Programmatic dependent launch: the kernel lets its successor start at once, and itself
 // fetches its first weight tiles (which no earlier kernel writes) before it waits for its
-// predecessor; activations are read and outputs written only after that wait.
+// predecessor; activations are read and outputs written only after that wait. Small token
+// tiles keep their shared memory under half an SM's, so that the successor's CTAs find room
+// beside them and their weight tiles are already on the way when the predecessor ends.
 //
 // Epilogues: store bf16 | store float (logits) | add into the float residual stream |
 // SwiGLU over a gate/up pair of weight tiles (two accumulators): out = silu(g) * u |
 // rotary position encoding of q and k heads with the write of k and v into the paged cache.
 // Reference counterparts: gemm_bf16_tc (src/gpu/cuda/shaders/matmul_tc.cu:224-413, wmma),
-// matvec_bf16 (matmul.cu:49-77), fused_gate_up_swiglu_bf16 (moe.cu:86-147), rotary_embedding
-// (rope.cu:62-77) and copy_to_paged_kv_cache (attention.cu:295-300).
+// matvec_bf16 (matmul.cu:49-77), fused_gate_up_swiglu_bf16 (moe.cu:86-147), rms_norm
+// (rms_norm.cu:78-115), rotary_embedding (rope.cu:62-77) and copy_to_paged_kv_cache
+// (attention.cu:295-300).
 //
 // Every mbarrier wait is bounded; on a time-out the CTA records an error word, drains what it
 // has in flight, still meets its cluster's barriers, frees its TMEM and returns.
@@ -48,31 +62,66 @@ constexpr int BK = 64;         // K per stage: 64 bf16 = one 128-byte swizzle ro
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;   // warp 0 TMA, warp 1 MMA + TMEM, warps 2..5 epilogue
 constexpr int MAX_CLUSTER = 8;
+#ifndef SMALL_KB
+#define SMALL_KB 84
+#endif
+#ifndef SMALL_DUAL_KB
+#define SMALL_DUAL_KB 126
+#endif
+constexpr int NORM_MAX_T = 64;        // the fused-norm variants take steps of at most this many tokens
+
+// the most column slots a landing area needs: ranks * ceil(BN / ranks) over 1..8 ranks
+constexpr int max_slots(int bn) {
+  int m = 0;
+  for (int s = 1; s <= MAX_CLUSTER; ++s) {
+    const int v = s * ((bn + s - 1) / s);
+    if (v > m) m = v;
+  }
+  return m;
+}
 
 template <int BN, bool DUAL> struct Cfg {
   static constexpr int A_TILES = DUAL ? 2 : 1;
   static constexpr int A_BYTES = BM * BK * 2;                  // 16 KB per weight tile
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
-  // enough stages to keep ~100 KB in flight, at most 8, within 200 KB
-  static constexpr int STAGES_RAW = 200 * 1024 / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 8 ? (BN <= 32 ? 6 : 8) : (STAGES_RAW < 2 ? 2 : STAGES_RAW);
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + alignment slack
+  // token tiles up to 64 (decode, small mixed steps) stay under half an SM's shared memory so
+  // that two kernels' CTAs are resident side by side; large tiles take what one CTA can have
+  static constexpr bool SMALL = BN <= 64;
+  static constexpr bool DEDICATED = BN <= 32;                  // landing area of its own
+  static constexpr int SLOTS = max_slots(BN);
+  static constexpr int LAND_BYTES = SLOTS * A_TILES * BM * 4;
+  // 84 KB + 126 KB (gate/up pair) = 210 KB: any two small-tile kernels of a layer fit one SM together
+  static constexpr int BUDGET = (SMALL ? (DUAL ? SMALL_DUAL_KB : SMALL_KB) : 200) * 1024 - 1024 - (DEDICATED ? LAND_BYTES : 0);
+  static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : (STAGES_RAW < 2 ? 2 : STAGES_RAW);
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = 1024 + RING_BYTES + (DEDICATED ? LAND_BYTES : 0);   // + alignment slack
   static constexpr int ACC_COLS = A_TILES * BN;
   static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128
                                    : ACC_COLS <= 256 ? 256 : 512;
-  // the partial tile of a split is parked over the (by then idle) stages
-  static_assert(A_TILES * BN * BM * 4 <= STAGES * STAGE_BYTES, "partial tile must fit in the stage ring");
+  static_assert(DEDICATED || LAND_BYTES <= RING_BYTES, "the landing area must fit in the stage ring");
 };
 
 // What the rotary epilogue needs besides the product (see rllm_tc_gemm_qkv_rope).
 struct RopeArgs {
   const int* positions;     // [T] absolute position of each token
   const float* inv_freq;    // [rot_dim / 2]
+  const float2* cos_sin;    // [T][rot_dim / 2] (cos, sin) of positions[t] * inv_freq[i], or null: computed here
   const int* slots;         // [T] page * page_size + offset, < 0: do not write; may be null
   bf16* kcache;             // [pages][nkv][page_size][hd]
   bf16* vcache;
   int nh, nkv, hd, page_size, rot_dim;
+};
+
+// The input of the fused-RMSNorm variants: rows of the float residual stream and the norm weight.
+struct NormArgs {
+  const float* h;     // [*, K] float, row stride ldh
+  long long ldh;
+  const int* rows;    // null: token t reads row t; else row rows[t]
+  const void* g;      // norm weight [K]
+  int g_is_bf16;      // 1: bfloat16, 0: float
+  float eps;
 };
 
 struct Params {
@@ -83,6 +132,7 @@ struct Params {
   int splits;         // CTAs per cluster = ranges of K
   int* err;           // device error word (0 = fine)
   RopeArgs rope;
+  NormArgs norm;      // NORM variants only
 };
 
 template <int EPI>
@@ -106,7 +156,8 @@ __device__ __forceinline__ void emit_rope(const Params& p, int t, int n, float v
     const int half = r.rot_dim >> 1;
     const int i = d < half ? d : d - half;
     float sn, cs;
-    sincosf((float)r.positions[t] * r.inv_freq[i], &sn, &cs);
+    if (r.cos_sin) { const float2 v = r.cos_sin[(size_t)t * half + i]; cs = v.x; sn = v.y; }
+    else sincosf((float)r.positions[t] * r.inv_freq[i], &sn, &cs);
     out = d < half ? v * cs - w * sn : w * sn + v * cs;
   }
   const bf16 ob = __float2bfloat16_rn(out);
@@ -124,13 +175,24 @@ __device__ __forceinline__ void emit_rope(const Params& p, int t, int n, float v
 }
 
 
-template <int BN, int EPI>
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void epilogue_warps_sync() {       // warps 2..5 only
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+template <int BN, int EPI, bool NORM>
 __global__ void __launch_bounds__(THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const Params p) {
   constexpr bool DUAL = (EPI == EPI_SWIGLU);
   constexpr bool ROPE = (EPI == EPI_QKV_ROPE);
   typedef Cfg<BN, DUAL> C;
+  constexpr int ACCS = C::A_TILES;
+  constexpr int W_BYTES = C::A_TILES * C::A_BYTES;
+  static_assert(!NORM || BN <= 64, "the fused norm builds token tiles of at most 64 rows");
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[C::STAGES];
   __shared__ __align__(8) uint64_t empty_bar[C::STAGES];
@@ -138,33 +200,40 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ int never_flag;
+  __shared__ float ss_part[NORM ? BN : 1];                 // this rank's sum of h^2 per token of the tile
+  __shared__ float ss_land[NORM ? MAX_CLUSTER * BN : 1];   // [rank][slot]: the ranks' parts for the columns owned here
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
 
   const int n0 = blockIdx.x * BM;          // first weight row / output feature of the tile
   const int t0 = blockIdx.y * BN;          // first token of the tile
-  const int rank = p.splits > 1 ? (int)cluster_rank() : 0;
+  const bool clustered = p.splits > 1;
+  const bool landing = clustered || ROPE;  // the epilogue goes through the landing area
+  const int rank = clustered ? (int)cluster_rank() : 0;
   const int kb_total = (p.K + BK - 1) / BK;
   const int kb_begin = (int)((long long)rank * kb_total / p.splits);
   const int kb_end = (int)((long long)(rank + 1) * kb_total / p.splits);
   const int n_kb = kb_end - kb_begin;
+  // float [ranks][slots per rank][ACCS][BM]: partial columns pushed here by every rank
+  float* land = reinterpret_cast<float*>(C::DEDICATED ? smem + C::RING_BYTES : smem);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], NORM ? 5 : 1); mbar_init(&empty_bar[s], 1); }
     mbar_init(&acc_bar, 1);
     abort_flag = 0;
     never_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 0 && lane == 0) { prefetch_tensormap(&tmap_w); prefetch_tensormap(&tmap_x); }
+  if (warp == 0 && lane == 0) { prefetch_tensormap(&tmap_w); if (!NORM) prefetch_tensormap(&tmap_x); }
   if (warp == 1) { tmem_alloc(&tmem_base_slot, C::TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   pdl_launch();        // the next kernel may start its prologue: every CTA of this one holds its TMEM by now
+  // a landing area of its own may be written as soon as its CTA runs: this arrival says so
+  if (clustered && C::DEDICATED) cluster_arrive();
   const uint32_t tmem_base = tmem_base_slot;
-  float* red = reinterpret_cast<float*>(smem);          // [ACCS * BN][BM] partial tile of this rank
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -175,15 +244,17 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       const int pre = n_kb < C::STAGES ? n_kb : C::STAGES;
       for (int i = 0; i < pre; ++i) {
         uint8_t* st = smem + (size_t)i * C::STAGE_BYTES;
-        mbar_expect_tx(&full_bar[i], C::STAGE_BYTES);
+        mbar_expect_tx(&full_bar[i], NORM ? W_BYTES : C::STAGE_BYTES);
         const int k = (kb_begin + i) * BK;
         tma_load_2d_hint(st, &tmap_w, &full_bar[i], k, n0, pol_w);
         if (DUAL) tma_load_2d_hint(st + C::A_BYTES, &tmap_w, &full_bar[i], k, p.up_row0 + n0, pol_w);
       }
-      pdl_wait();                                    // activations come from the kernel before
-      for (int i = 0; i < pre; ++i) {
-        uint8_t* st = smem + (size_t)i * C::STAGE_BYTES;
-        tma_load_2d_hint(st + C::A_TILES * C::A_BYTES, &tmap_x, &full_bar[i], (kb_begin + i) * BK, t0, pol_x);
+      if (!NORM) {
+        pdl_wait();                                  // activations come from the kernel before
+        for (int i = 0; i < pre; ++i) {
+          uint8_t* st = smem + (size_t)i * C::STAGE_BYTES;
+          tma_load_2d_hint(st + W_BYTES, &tmap_x, &full_bar[i], (kb_begin + i) * BK, t0, pol_x);
+        }
       }
       int issued = pre;
       for (int i = pre; i < n_kb; ++i) {
@@ -191,11 +262,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
         if (!mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag)) { abort_flag = 1; record_failure(p.err, 1); break; }
         uint8_t* st = smem + (size_t)s * C::STAGE_BYTES;
-        mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
+        mbar_expect_tx(&full_bar[s], NORM ? W_BYTES : C::STAGE_BYTES);
         const int k = (kb_begin + i) * BK;
         tma_load_2d_hint(st, &tmap_w, &full_bar[s], k, n0, pol_w);
         if (DUAL) tma_load_2d_hint(st + C::A_BYTES, &tmap_w, &full_bar[s], k, p.up_row0 + n0, pol_w);
-        tma_load_2d_hint(st + C::A_TILES * C::A_BYTES, &tmap_x, &full_bar[s], k, t0, pol_x);
+        if (!NORM) tma_load_2d_hint(st + W_BYTES, &tmap_x, &full_bar[s], k, t0, pol_x);
         issued = i + 1;
       }
       if (abort_flag) {
@@ -215,7 +286,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         if (!mbar_wait(&full_bar[s], ph, &abort_flag)) { abort_flag = 1; record_failure(p.err, 2); ok = false; break; }
         tc_fence_after();
         const uint32_t a_addr = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
-        const uint32_t b_addr = a_addr + C::A_TILES * C::A_BYTES;
+        const uint32_t b_addr = a_addr + W_BYTES;
         const uint64_t da = umma_desc_sw128(a_addr);
         const uint64_t db = umma_desc_sw128(b_addr);
 #pragma unroll
@@ -232,18 +303,121 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       }
       if (ok) umma_commit(&acc_bar);      // accumulators complete
     }
-  } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
-    const int q = warp & 3;                       // TMEM lanes [32q, 32q + 32) belong to this warp
-    const int row = q * 32 + lane;                // weight row within the tile
-    const int n = n0 + row;
-    pdl_wait();                                   // nothing is written before the predecessor is done
+  }
+  bool epi_ok = false;
+  const int row = (warp & 3) * 32 + lane;         // TMEM lanes [32 (warp & 3), +32) belong to this warp
+  const int n = n0 + row;                         // output feature of this thread
+  const float inv_k = 1.f / (float)p.K;
+  if (warp >= 2) {
+    // ------------------------------------------------------------ epilogue warps (2..5)
+    pdl_wait();                                   // nothing is read or written before the predecessor is done
+    if (NORM) {
+      // ---- they first build the token operand: bf16(h * g), 128-byte swizzled, and add up h^2
+      constexpr int RPT = BN / 16;                // token rows per thread
+      const int pt = (warp - 2) * 32 + lane;      // 0..127
+      const int j = pt & 7;                       // which 16-byte chunk (8 values of K) of a 64-wide block
+      const float* hrow[RPT];
+      float ss[RPT];
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) {
+        const int tg = t0 + (pt >> 3) + 16 * r;
+        hrow[r] = tg < p.T ? p.norm.h + (size_t)(p.norm.rows ? p.norm.rows[tg] : tg) * p.norm.ldh : nullptr;
+        ss[r] = 0.f;
+      }
+      // The loads of h and g for the next PF stages are always in flight (registers), so that a
+      // stage costs a write to shared memory, not a trip to L2.
+      constexpr int PF = BN <= 16 ? 4 : 2;
+      float4 ha[PF][RPT], hb[PF][RPT];
+      uint4 ga[PF], gb[PF];
+      auto fetch = [&](int i, float4 (&a)[RPT], float4 (&b)[RPT], uint4& g0, uint4& g1) {
+        const int kk = (kb_begin + i) * BK + 8 * j;
+        g0 = g1 = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int r = 0; r < RPT; ++r) a[r] = b[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < n_kb && kk < p.K) {               // K is a multiple of 8: a chunk is inside or outside
+          if (p.norm.g_is_bf16) {
+            g0 = *reinterpret_cast<const uint4*>((const bf16*)p.norm.g + kk);
+          } else {
+            g0 = *reinterpret_cast<const uint4*>((const float*)p.norm.g + kk);
+            g1 = *reinterpret_cast<const uint4*>((const float*)p.norm.g + kk + 4);
+          }
+#pragma unroll
+          for (int r = 0; r < RPT; ++r) {
+            if (hrow[r]) {
+              a[r] = *reinterpret_cast<const float4*>(hrow[r] + kk);
+              b[r] = *reinterpret_cast<const float4*>(hrow[r] + kk + 4);
+            }
+          }
+        }
+      };
+#pragma unroll
+      for (int d = 0; d < PF; ++d) fetch(d, ha[d], hb[d], ga[d], gb[d]);
+      bool pok = true;
+      for (int i0 = 0; i0 < n_kb && pok; i0 += PF) {
+#pragma unroll
+        for (int d = 0; d < PF; ++d) {
+          const int i = i0 + d;
+          if (i >= n_kb || !pok) break;
+          const int s = i % C::STAGES;
+          const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
+          if (i >= C::STAGES) {
+            int w_ok = 1;
+            if (lane == 0 && !mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag)) {
+              abort_flag = 1; record_failure(p.err, 4); w_ok = 0;
+            }
+            pok = __shfl_sync(0xffffffffu, w_ok, 0) != 0;
+            if (!pok) break;
+          }
+          uint8_t* bt = smem + (size_t)s * C::STAGE_BYTES + W_BYTES;
+          float gv[8];
+          if (p.norm.g_is_bf16) {
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&ga[d]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { gv[2 * e] = __low2float(h2[e]); gv[2 * e + 1] = __high2float(h2[e]); }
+          } else {
+            gv[0] = __uint_as_float(ga[d].x); gv[1] = __uint_as_float(ga[d].y);
+            gv[2] = __uint_as_float(ga[d].z); gv[3] = __uint_as_float(ga[d].w);
+            gv[4] = __uint_as_float(gb[d].x); gv[5] = __uint_as_float(gb[d].y);
+            gv[6] = __uint_as_float(gb[d].z); gv[7] = __uint_as_float(gb[d].w);
+          }
+#pragma unroll
+          for (int r = 0; r < RPT; ++r) {
+            const int t = (pt >> 3) + 16 * r;
+            const float4 a = ha[d][r], b = hb[d][r];     // zeros outside the matrix
+            float acc = ss[r];
+            acc = fmaf(a.x, a.x, acc); acc = fmaf(a.y, a.y, acc); acc = fmaf(a.z, a.z, acc); acc = fmaf(a.w, a.w, acc);
+            acc = fmaf(b.x, b.x, acc); acc = fmaf(b.y, b.y, acc); acc = fmaf(b.z, b.z, acc); acc = fmaf(b.w, b.w, acc);
+            ss[r] = acc;
+            uint4 o;
+            o.x = pack_bf16x2(a.x * gv[0], a.y * gv[1]); o.y = pack_bf16x2(a.z * gv[2], a.w * gv[3]);
+            o.z = pack_bf16x2(b.x * gv[4], b.y * gv[5]); o.w = pack_bf16x2(b.z * gv[6], b.w * gv[7]);
+            *reinterpret_cast<uint4*>(bt + t * 128 + ((j ^ (t & 7)) << 4)) = o;
+          }
+          fetch(i + PF, ha[d], hb[d], ga[d], gb[d]);       // the stage PF ahead takes these registers
+          fence_proxy_async();                            // generic-proxy stores -> visible to the MMA's reads
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_bar[s]);
+        }
+      }
+      // the eight threads of a token row hold its parts: a fixed tree, then one of them parks the sum
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) {
+        float v = ss[r];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        if (j == 0) ss_part[(pt >> 3) + 16 * r] = v;
+      }
+      epilogue_warps_sync();
+    }
     bool ok = mbar_wait(&acc_bar, 0, &abort_flag);
     if (!ok) { abort_flag = 1; record_failure(p.err, 3); }
     ok = __all_sync(0xffffffffu, ok);
+    epi_ok = ok;
     tc_fence_after();
-    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-    if (ok && p.splits == 1 && !ROPE) {
+    const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    if (ok && !landing) {
+      // ---- one CTA holds the whole sum: straight from TMEM to the output
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         if (t0 + c0 >= p.T) break;
@@ -251,55 +425,83 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         tmem_ld16(taddr + c0, g);
         if (DUAL) tmem_ld16(taddr + BN + c0, u);
         tmem_ld_wait();
+        if (NORM) {
+#pragma unroll
+          for (int jj = 0; jj < 16; ++jj) {
+            const float rs = rsqrtf(ss_part[c0 + jj] * inv_k + p.norm.eps);
+            g[jj] = __float_as_uint(__uint_as_float(g[jj]) * rs);
+            if (DUAL) u[jj] = __float_as_uint(__uint_as_float(u[jj]) * rs);
+          }
+        }
         if (n < p.N) {
           if (EPI == EPI_ACCUM_F32) {
             // all sixteen residual values are fetched before the first store, so the loads overlap
             float* cp = (float*)p.C + (size_t)(t0 + c0) * p.ldc + n;
             float r[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) r[j] = (t0 + c0 + j < p.T) ? __ldcg(cp + (size_t)j * p.ldc) : 0.f;
+            for (int jj = 0; jj < 16; ++jj) r[jj] = (t0 + c0 + jj < p.T) ? __ldcg(cp + (size_t)jj * p.ldc) : 0.f;
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (t0 + c0 + j < p.T) cp[(size_t)j * p.ldc] = r[j] + __uint_as_float(g[j]);
+            for (int jj = 0; jj < 16; ++jj)
+              if (t0 + c0 + jj < p.T) cp[(size_t)jj * p.ldc] = r[jj] + __uint_as_float(g[jj]);
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int t = t0 + c0 + j;
-              if (t < p.T) emit<EPI>(p, t, n, __uint_as_float(g[j]), DUAL ? __uint_as_float(u[j]) : 0.f);
+            for (int jj = 0; jj < 16; ++jj) {
+              const int t = t0 + c0 + jj;
+              if (t < p.T) emit<EPI>(p, t, n, __uint_as_float(g[jj]), DUAL ? __uint_as_float(u[jj]) : 0.f);
             }
           }
-        }
-      }
-    } else if (ok) {
-      // park the partial tile in shared memory (the stages are idle: every load was consumed)
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        if (t0 + c0 >= p.T) break;
-        uint32_t g[16], u[16];
-        tmem_ld16(taddr + c0, g);
-        if (DUAL) tmem_ld16(taddr + BN + c0, u);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          red[(size_t)(c0 + j) * BM + row] = __uint_as_float(g[j]);
-          if (DUAL) red[(size_t)(BN + c0 + j) * BM + row] = __uint_as_float(u[j]);
         }
       }
     }
   }
 
-  if (p.splits > 1 || ROPE) {
-    // ---------------------------------------------------------- sum over the ranks of the cluster
+  if (landing) {
+    // ---------------------------------------------------------- the ranks' parts meet at the column's owner
+    const int ncols = min(BN, p.T - t0);                      // token columns that exist
+    const int cpr = (BN + p.splits - 1) / p.splits;           // column slots per rank in a landing area
     __syncwarp();
     tc_fence_before();
-    if (p.splits > 1) cluster_sync_all(); else __syncthreads();      // every partial tile is parked
-    if (warp >= 2 && !abort_flag) {
-      const int row = (warp & 3) * 32 + lane;
-      const int n = n0 + row;
-      uint32_t base[MAX_CLUSTER];
-      const uint32_t mine = smem_u32(red);
+    if (clustered) {
+      // every landing area may be written: its CTA runs (own area) / its products are done (ring)
+      if (!C::DEDICATED) cluster_arrive();
+      cluster_wait();
+    }
+    if (warp >= 2 && epi_ok) {
+      const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+      const uint32_t land_cta = smem_u32(land);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (c0 >= ncols) break;
+        uint32_t g[16], u[16];
+        tmem_ld16(taddr + c0, g);
+        if (DUAL) tmem_ld16(taddr + BN + c0, u);
+        tmem_ld_wait();
 #pragma unroll
-      for (int s = 0; s < MAX_CLUSTER; ++s) base[s] = (p.splits > 1 && s < p.splits) ? map_to_rank(mine, (uint32_t)s) : mine;
+        for (int jj = 0; jj < 16; ++jj) {
+          const int c = c0 + jj;
+          if (c < ncols) {
+            const int owner = c % p.splits, slot = c / p.splits;
+            const uint32_t off = (uint32_t)((((rank * cpr + slot) * ACCS) * BM + row) * 4);
+            if (clustered) {
+              const uint32_t dst = map_to_rank(land_cta, (uint32_t)owner) + off;
+              st_cluster_f32(dst, __uint_as_float(g[jj]));
+              if (DUAL) st_cluster_f32(dst + BM * 4, __uint_as_float(u[jj]));
+            } else {
+              land[off / 4] = __uint_as_float(g[jj]);
+              if (DUAL) land[off / 4 + BM] = __uint_as_float(u[jj]);
+            }
+          }
+        }
+      }
+      if (NORM && row < ncols) {
+        const int owner = row % p.splits, slot = row / p.splits;
+        if (clustered) st_cluster_f32(map_to_rank(smem_u32(&ss_land[rank * BN + slot]), (uint32_t)owner), ss_part[row]);
+        else ss_land[slot] = ss_part[row];
+      }
+    }
+    __syncwarp();
+    if (clustered) { cluster_arrive(); cluster_wait(); } else __syncthreads();     // every part has landed
+    if (warp >= 2 && !abort_flag) {
       // the pair partner of this row under the rotary epilogue (same tile: heads do not straddle tiles)
       int prow = row;
       if (ROPE) {
@@ -307,23 +509,28 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         if (d < p.rope.rot_dim) prow = d < half ? row + half : row - half;
       }
 #pragma unroll 1
-      for (int c = rank; c < BN; c += p.splits) {
-        const int t = t0 + c;
-        if (t >= p.T) break;
-        float g = 0.f, u = 0.f, w = 0.f;
+      for (int slot = 0; slot * p.splits + rank < ncols; ++slot) {
+        const int t = t0 + slot * p.splits + rank;
+        float g = 0.f, u = 0.f, w = 0.f, ssum = 0.f;
         if (EPI == EPI_ACCUM_F32 && n < p.N) g = __ldcg((const float*)p.C + (size_t)t * p.ldc + n);   // residual
-        float pg[MAX_CLUSTER], pu[MAX_CLUSTER], pw[MAX_CLUSTER];
+        float pg[MAX_CLUSTER], pu[MAX_CLUSTER], pw[MAX_CLUSTER], ps[MAX_CLUSTER];
 #pragma unroll
         for (int s = 0; s < MAX_CLUSTER; ++s) {
-          pg[s] = pu[s] = pw[s] = 0.f;
+          pg[s] = pu[s] = pw[s] = ps[s] = 0.f;
           if (s < p.splits) {
-            pg[s] = ld_cluster_f32(base[s] + (uint32_t)((c * BM + row) * 4));
-            if (DUAL) pu[s] = ld_cluster_f32(base[s] + (uint32_t)(((BN + c) * BM + row) * 4));
-            if (ROPE) pw[s] = ld_cluster_f32(base[s] + (uint32_t)((c * BM + prow) * 4));
+            const float* base = land + (size_t)((s * cpr + slot) * ACCS) * BM;
+            pg[s] = base[row];
+            if (DUAL) pu[s] = base[BM + row];
+            if (ROPE) pw[s] = base[prow];
+            if (NORM) ps[s] = ss_land[s * BN + slot];
           }
         }
 #pragma unroll
-        for (int s = 0; s < MAX_CLUSTER; ++s) { g += pg[s]; u += pu[s]; w += pw[s]; }   // rank order
+        for (int s = 0; s < MAX_CLUSTER; ++s) { g += pg[s]; u += pu[s]; w += pw[s]; ssum += ps[s]; }   // rank order
+        if (NORM) {
+          const float rs = rsqrtf(ssum * inv_k + p.norm.eps);
+          g *= rs; u *= rs; w *= rs;
+        }
         if (n < p.N) {
           if (ROPE) emit_rope(p, t, n, g, w);
           else if (EPI == EPI_ACCUM_F32) ((float*)p.C)[(size_t)t * p.ldc + n] = g;   // residual + ranks in order
@@ -331,7 +538,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         }
       }
     }
-    if (p.splits > 1) cluster_sync_all();       // nobody leaves while its shared memory is still read
   }
   tc_fence_before();
   __syncthreads();
@@ -397,27 +603,38 @@ int cached_map(CUtensorMap* out, const void* ptr, long long rows, long long cols
   return 0;
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool NORM>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t s) {
   typedef Cfg<BN, EPI == EPI_SWIGLU> C;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(tc_gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(tc_gemm_kernel<BN, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              C::SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return -5; }
     configured = true;
   }
-  return launch_ex(tc_gemm_kernel<BN, EPI>, grid, dim3(THREADS), C::SMEM_BYTES, s, p.splits, mw, mx, p);
+  return launch_ex(tc_gemm_kernel<BN, EPI, NORM>, grid, dim3(THREADS), C::SMEM_BYTES, s, p.splits, mw, mx, p);
 }
 
 template <int EPI>
-int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t s) {
+int launch_bn(int bn, bool norm, const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid,
+              cudaStream_t s) {
+  if (norm) {
+    if constexpr (EPI != EPI_ACCUM_F32) {
+      switch (bn) {
+        case 16: return launch<16, EPI, true>(mw, mx, p, grid, s);
+        case 32: return launch<32, EPI, true>(mw, mx, p, grid, s);
+        case 64: return launch<64, EPI, true>(mw, mx, p, grid, s);
+      }
+    }
+    return ERR_BAD_SIZE;
+  }
   switch (bn) {
-    case 16: return launch<16, EPI>(mw, mx, p, grid, s);
-    case 32: return launch<32, EPI>(mw, mx, p, grid, s);
-    case 64: return launch<64, EPI>(mw, mx, p, grid, s);
-    case 128: return launch<128, EPI>(mw, mx, p, grid, s);
+    case 16: return launch<16, EPI, false>(mw, mx, p, grid, s);
+    case 32: return launch<32, EPI, false>(mw, mx, p, grid, s);
+    case 64: return launch<64, EPI, false>(mw, mx, p, grid, s);
+    case 128: return launch<128, EPI, false>(mw, mx, p, grid, s);
     case 256:
-      if constexpr (EPI != EPI_SWIGLU) return launch<256, EPI>(mw, mx, p, grid, s);
+      if constexpr (EPI != EPI_SWIGLU) return launch<256, EPI, false>(mw, mx, p, grid, s);
       break;
   }
   return ERR_BAD_SIZE;
@@ -439,11 +656,19 @@ void plan(int epi, int T, int N, int K, int sm_count, bool allow_split, int* bn_
   *splits_out = splits;
 }
 
-int run(int epi, const void* X, long long ldx, const void* W, void* Cout, long long ldc, int T, int N, int K,
-        int allow_split, int* err, int sm_count, const RopeArgs* rope, void* stream) {
+// X null: the fused-norm variants (norm must be given, T <= NORM_MAX_T).
+int run(int epi, const void* X, long long ldx, const NormArgs* norm, const void* W, void* Cout, long long ldc,
+        int T, int N, int K, int allow_split, int* err, int sm_count, const RopeArgs* rope, void* stream) {
   if (T <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 || ldx % 8) return ERR_BAD_SIZE;              // TMA: strides multiple of 16 bytes
-  if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return ERR_BAD_ALIGN;
+  if (K <= 0 || K % 8) return ERR_BAD_SIZE;                          // TMA: strides multiple of 16 bytes
+  if ((uintptr_t)W & 15) return ERR_BAD_ALIGN;
+  if (norm) {
+    if (T > NORM_MAX_T || epi == EPI_ACCUM_F32) return ERR_BAD_SIZE;
+    if (norm->ldh % 4 || ((uintptr_t)norm->h & 15) || ((uintptr_t)norm->g & 15)) return ERR_BAD_ALIGN;
+  } else {
+    if (ldx % 8) return ERR_BAD_SIZE;
+    if ((uintptr_t)X & 15) return ERR_BAD_ALIGN;
+  }
   int rc = get_encoder();
   if (rc) return rc;
   int bn, splits;
@@ -451,19 +676,22 @@ int run(int epi, const void* X, long long ldx, const void* W, void* Cout, long l
   const bool dual = epi == EPI_SWIGLU;
   CUtensorMap mw, mx;
   if ((rc = cached_map(&mw, W, dual ? 2LL * N : N, K, K, BM))) return rc;
-  if ((rc = make_map(&mx, X, T, K, ldx, bn))) return rc;
+  if (norm) mx = mw;                                                 // not used by the kernel
+  else if ((rc = make_map(&mx, X, T, K, ldx, bn))) return rc;
   Params p;
   p.C = Cout; p.ldc = (int)ldc; p.T = T; p.N = N; p.K = K; p.up_row0 = N; p.splits = splits; p.err = err;
   p.rope = rope ? *rope : RopeArgs{};
+  p.norm = norm ? *norm : NormArgs{};
   dim3 grid((N + BM - 1) / BM, (T + bn - 1) / bn, splits);
   if (grid.y > 65535) return ERR_TOO_LARGE;
   cudaStream_t s = (cudaStream_t)stream;
+  const bool nm = norm != nullptr;
   switch (epi) {
-    case EPI_STORE: return launch_bn<EPI_STORE>(bn, mw, mx, p, grid, s);
-    case EPI_STORE_F32: return launch_bn<EPI_STORE_F32>(bn, mw, mx, p, grid, s);
-    case EPI_ACCUM_F32: return launch_bn<EPI_ACCUM_F32>(bn, mw, mx, p, grid, s);
-    case EPI_SWIGLU: return launch_bn<EPI_SWIGLU>(bn, mw, mx, p, grid, s);
-    case EPI_QKV_ROPE: return launch_bn<EPI_QKV_ROPE>(bn, mw, mx, p, grid, s);
+    case EPI_STORE: return launch_bn<EPI_STORE>(bn, nm, mw, mx, p, grid, s);
+    case EPI_STORE_F32: return launch_bn<EPI_STORE_F32>(bn, nm, mw, mx, p, grid, s);
+    case EPI_ACCUM_F32: return launch_bn<EPI_ACCUM_F32>(bn, nm, mw, mx, p, grid, s);
+    case EPI_SWIGLU: return launch_bn<EPI_SWIGLU>(bn, nm, mw, mx, p, grid, s);
+    case EPI_QKV_ROPE: return launch_bn<EPI_QKV_ROPE>(bn, nm, mw, mx, p, grid, s);
   }
   return ERR_BAD_SIZE;
 }
@@ -482,22 +710,46 @@ RLLM_API int rllm_tc_gemm_plan(int epi, int T, int N, int K, int sm_count, int a
 // allow_split 0: one CTA per output tile whatever the size. Returns 0, or a negative refusal.
 RLLM_API int rllm_tc_gemm(int epi, const void* X, long long ldx, const void* W, void* Cout, long long ldc,
                           int T, int N, int K, int allow_split, int* err, int sm_count, void* stream) {
-  if (epi < 0 || epi > 3) return ERR_BAD_SIZE;
-  return run(epi, X, ldx, W, Cout, ldc, T, N, K, allow_split, err, sm_count, nullptr, stream);
+  if (epi < 0 || epi > 3 || !X) return ERR_BAD_SIZE;
+  return run(epi, X, ldx, nullptr, W, Cout, ldc, T, N, K, allow_split, err, sm_count, nullptr, stream);
 }
+
+// The same product with RMSNorm in front, in one kernel: X[t, :] = h[row(t), :] * rsqrt(mean(h^2) + eps) * g,
+// row(t) = rows[t], or t when rows is null. h float [*, K] with row stride ldh (a multiple of 4); g the norm
+// weight [K], float (g_dt 0) or bfloat16 (g_dt 1). T at most 64 (rllm_tc_gemm_norm_max_tokens); epilogues
+// store, store-float and SwiGLU.
+RLLM_API int rllm_tc_gemm_norm(int epi, const float* h, long long ldh, const int* rows, const void* g, int g_dt,
+                               float eps, const void* W, void* Cout, long long ldc, int T, int N, int K,
+                               int allow_split, int* err, int sm_count, void* stream) {
+  if (epi < 0 || epi > 3 || epi == EPI_ACCUM_F32 || !h || !g || (g_dt != DT_F32 && g_dt != DT_BF16)) return ERR_BAD_SIZE;
+  NormArgs nm;
+  nm.h = h; nm.ldh = ldh; nm.rows = rows; nm.g = g; nm.g_is_bf16 = g_dt == DT_BF16; nm.eps = eps;
+  return run(epi, nullptr, 0, &nm, W, Cout, ldc, T, N, K, allow_split, err, sm_count, nullptr, stream);
+}
+RLLM_API int rllm_tc_gemm_norm_max_tokens() { return NORM_MAX_T; }
 
 // The q/k/v projection with the rotary position encoding and the cache write in its epilogue:
 // QKV[T, (nh + 2 nkv) * hd] = X W^T; pair (i, i + rot_dim/2) of every q and k head is rotated by
 // positions[t] * inv_freq[i]; rotated k and plain v also go to the paged cache at slots[t]
 // (slots null or < 0: no write). Head size must divide 128 so that no head straddles two tiles.
-RLLM_API int rllm_tc_gemm_qkv_rope(const void* X, long long ldx, const void* W, void* QKV, long long ldc, int T,
-                                   int K, const int* positions, const float* inv_freq, const int* slots,
-                                   void* kcache, void* vcache, int nh, int nkv, int hd, int page_size,
+// cos_sin: the step's table [T][rot_dim / 2] of (cos, sin), or null to compute them in the epilogue.
+// X null: RMSNorm in front as in rllm_tc_gemm_norm (h, ldh, g, g_dt, eps; T at most 64).
+RLLM_API int rllm_tc_gemm_qkv_rope(const void* X, long long ldx, const float* h, long long ldh, const void* g,
+                                   int g_dt, float eps, const void* W, void* QKV, long long ldc, int T,
+                                   int K, const int* positions, const float* inv_freq, const void* cos_sin,
+                                   const int* slots, void* kcache, void* vcache, int nh, int nkv, int hd, int page_size,
                                    int rot_dim, int allow_split, int* err, int sm_count, void* stream) {
   if (hd <= 0 || BM % hd || rot_dim % 2 || rot_dim > hd || rot_dim < 0 || nh <= 0 || nkv <= 0 || page_size <= 0)
     return ERR_BAD_SIZE;
   RopeArgs r;
-  r.positions = positions; r.inv_freq = inv_freq; r.slots = slots; r.kcache = (bf16*)kcache;
+  r.positions = positions; r.inv_freq = inv_freq; r.cos_sin = (const float2*)cos_sin; r.slots = slots; r.kcache = (bf16*)kcache;
   r.vcache = (bf16*)vcache; r.nh = nh; r.nkv = nkv; r.hd = hd; r.page_size = page_size; r.rot_dim = rot_dim;
-  return run(EPI_QKV_ROPE, X, ldx, W, QKV, ldc, T, (nh + 2 * nkv) * hd, K, allow_split, err, sm_count, &r, stream);
+  NormArgs nm;
+  const bool fused = X == nullptr;
+  if (fused) {
+    if (!h || !g || (g_dt != DT_F32 && g_dt != DT_BF16)) return ERR_BAD_SIZE;
+    nm.h = h; nm.ldh = ldh; nm.rows = nullptr; nm.g = g; nm.g_is_bf16 = g_dt == DT_BF16; nm.eps = eps;
+  }
+  return run(EPI_QKV_ROPE, X, ldx, fused ? &nm : nullptr, W, QKV, ldc, T, (nh + 2 * nkv) * hd, K, allow_split, err,
+             sm_count, &r, stream);
 }

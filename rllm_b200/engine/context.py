@@ -43,6 +43,9 @@ class StepContext:
     # decode-only steps captured in a CUDA graph read their sizes from device memory
     graph_safe: bool = False
     extras: dict[str, Any] = field(default_factory=dict)
+    # what one forward pass shares between its layers (tables made at first use); the model
+    # empties it when a pass begins, so nothing outlives the pass that made it
+    per_forward: dict[str, Any] = field(default_factory=dict)
 
     @property
     def all_decode(self) -> bool:

@@ -17,6 +17,8 @@ host) are captured; any other model runs launch by launch.
 """
 from __future__ import annotations
 
+import gc
+import weakref
 from collections import OrderedDict
 
 import numpy as np
@@ -34,10 +36,14 @@ class _Slot:
 
 class DecodeGraphs:
     def __init__(self, engine):
-        self.engine = engine
+        self._engine = weakref.ref(engine)      # the engine owns this object, not the reverse
         self.slots: OrderedDict[tuple[int, int], _Slot] = OrderedDict()
         self.pool = None
         self.captures = 0
+
+    @property
+    def engine(self):
+        return self._engine()
 
     def _width(self, rcs) -> int:
         G = len(self.engine.cache.groups)
@@ -85,8 +91,17 @@ class DecodeGraphs:
             self.pool = torch.cuda.graph_pool_handle()
         graph = torch.cuda.CUDAGraph()
         before = ops.LAUNCHES
-        with torch.cuda.graph(graph, pool=self.pool):
-            slot.logits = self._forward(slot)
+        # Nothing may be destroyed while the capture runs: a dead cycle that holds another
+        # engine's graphs or pinned buffers, collected in the middle of it, invalidates it.
+        gc.collect()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, pool=self.pool):
+                slot.logits = self._forward(slot)
+        finally:
+            if gc_was_on:
+                gc.enable()
         slot.launches = ops.LAUNCHES - before    # kernels one replay launches
         ops.LAUNCHES = before                    # a capture launches nothing
         slot.graph = graph

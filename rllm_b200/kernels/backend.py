@@ -16,6 +16,25 @@ import torch
 from . import ops
 
 
+class Normed:
+    """An RMSNorm that has not run yet: rows of the float residual stream, the norm's weight and
+    eps. A product that can take the norm in front of it in one kernel consumes it as it is;
+    everything else calls `tensor()`, which runs the norm kernel once and keeps the result."""
+
+    def __init__(self, backend, h, weight, eps, rows=None):
+        self.backend, self.h, self.weight, self.eps, self.rows = backend, h, weight, float(eps), rows
+        self._tensor = None
+
+    @property
+    def shape(self):
+        return (self.h.shape[0] if self.rows is None else self.rows.numel(), self.h.shape[1])
+
+    def tensor(self):
+        if self._tensor is None:
+            self._tensor = self.backend.rmsnorm(self.h, self.weight, self.eps, rows=self.rows)
+        return self._tensor
+
+
 class Backend:
     def __init__(self, dtype: torch.dtype, device: torch.device | str = "cuda:0"):
         if dtype not in (torch.float32, torch.bfloat16):
@@ -35,8 +54,23 @@ class Backend:
     def embed(self, ids, table, err=None):
         return ops.embed(ids, table, err=err)
 
-    def rmsnorm(self, x, w, eps, out_dtype=None):
-        return ops.rmsnorm(x, w, eps, out_dtype or self.dtype)
+    def rmsnorm(self, x, w, eps, out_dtype=None, rows=None):
+        return ops.rmsnorm(x, w, eps, out_dtype or self.dtype, rows=rows)
+
+    def normed(self, h, weight, eps, rows=None):
+        """rmsnorm(h[rows]) for a consumer that may fuse it: deferred on the serving path, computed
+        at once on the 32-bit path."""
+        n = Normed(self, h, weight, eps, rows)
+        return n if self._sm100 is not None else n.tensor()
+
+    def _fused_norm(self, x, w):
+        """Take the norm into the product? Every CTA of the product then normalises its own slice of
+        the rows, which pays while the weight has no more 128-row tiles than the GPU has SMs; a
+        wider weight (the output head) gets the norm from its own kernel, once."""
+        return (isinstance(x, Normed) and x._tensor is None and self._sm100 is not None
+                and os.environ.get("RLLM_B200_NO_NORM_FUSION") != "1"
+                and (w.shape[0] + 127) // 128 <= self._sm100.init(self.device).sm_count
+                and self._sm100.norm_supported(x.h, x.weight, w, x.rows))
 
     def gather_rows(self, x, rows):
         return ops.gather_rows(x, rows)
@@ -49,32 +83,64 @@ class Backend:
         return self._sm100 is not None and self._sm100.gemm_supported(x, w)
 
     def linear(self, x, w, bias=None):
+        if bias is None and self._fused_norm(x, w):
+            return self._sm100.gemm_norm(x.h, x.weight, x.eps, w, ops.EPI_STORE, rows=x.rows)
+        x = x.tensor() if isinstance(x, Normed) else x
         if bias is None and self._tc(x, w):
             return self._sm100.gemm(x, w, ops.EPI_STORE)
         return ops.gemm_simt(x, w, ops.EPI_STORE, bias=bias)
 
     def linear_f32(self, x, w):
+        if self._fused_norm(x, w):
+            return self._sm100.gemm_norm(x.h, x.weight, x.eps, w, ops.EPI_STORE_F32, rows=x.rows)
+        x = x.tensor() if isinstance(x, Normed) else x
         if self._tc(x, w):
             return self._sm100.gemm(x, w, ops.EPI_STORE_F32)
         return ops.gemm_simt(x, w, ops.EPI_STORE_F32)
 
     def linear_residual(self, x, w, residual):
         """residual (float32, in place) += x W^T"""
+        x = x.tensor() if isinstance(x, Normed) else x
         if self._tc(x, w):
             return self._sm100.gemm(x, w, ops.EPI_ACCUM_F32, out=residual)
         return ops.gemm_simt(x, w, ops.EPI_ACCUM_F32, out=residual)
 
     def linear_swiglu(self, x, w_gate_up):
         """silu(x Wg^T) * (x Wu^T) with w_gate_up = [Wg; Wu]"""
+        if self._fused_norm(x, w_gate_up):
+            return self._sm100.gemm_norm(x.h, x.weight, x.eps, w_gate_up, ops.EPI_SWIGLU, rows=x.rows)
+        x = x.tensor() if isinstance(x, Normed) else x
         if self._tc(x, w_gate_up):
             return self._sm100.gemm(x, w_gate_up, ops.EPI_SWIGLU)
         return ops.gemm_simt(x, w_gate_up, ops.EPI_SWIGLU)
 
     # ---- position encoding + cache write, attention
-    def qkv_rope_cache_write(self, x, w_qkv, bias, positions, inv_freq, cache, nh, nkv, hd, rot_dim=None):
+    def rope_table(self, ctx, positions, inv_freq, rot_dim, key=None):
+        """The step's (cos, sin) table for one rotation rule, made at its first use in a forward
+        pass and shared by the layers with the same rule (`key`)."""
+        if ctx is None:
+            return None
+        tables = ctx.per_forward.setdefault("rope_tables", {})
+        key = key if key is not None else (inv_freq.data_ptr(), rot_dim)
+        t = tables.get(key)
+        if t is None:
+            t = tables[key] = ops.rope_table(positions, inv_freq[: rot_dim // 2].contiguous(), ctx.num_tokens)
+        return t
+
+    def qkv_rope_cache_write(self, x, w_qkv, bias, positions, inv_freq, cache, nh, nkv, hd, rot_dim=None,
+                             ctx=None, key=None):
         """qkv = x w_qkv^T (+ bias), q and k rotated, k and v written to the cache. One kernel when
         the tensor-core product takes the sizes, else the product followed by the rotation kernel."""
         rot_dim = hd if rot_dim is None else rot_dim
+        table = self.rope_table(ctx, positions, inv_freq, rot_dim, key)
+        kc = cache.k if cache.writes else None
+        if bias is None and self._fused_norm(x, w_qkv) and x.rows is None and 128 % hd == 0 and \
+                (kc is None or kc.dtype == torch.bfloat16):
+            writes = cache.writes
+            return self._sm100.gemm_qkv_rope(None, w_qkv, positions, inv_freq, cache.slots if writes else None,
+                                             kc, cache.v if writes else None, nh, nkv, hd, cache.page_size,
+                                             rot_dim, norm=(x.h, x.weight, x.eps), table=table)
+        x = x.tensor() if isinstance(x, Normed) else x
         # the fused epilogue pays for decode and small mixed steps; a long prompt portion
         # rotates faster in the row-parallel kernel
         if bias is None and self._sm100 is not None and x.shape[0] <= 128 and \
@@ -82,16 +148,18 @@ class Backend:
             writes = cache.writes
             return self._sm100.gemm_qkv_rope(x, w_qkv, positions, inv_freq, cache.slots if writes else None,
                                              cache.k if writes else None, cache.v if writes else None,
-                                             nh, nkv, hd, cache.page_size, rot_dim)
+                                             nh, nkv, hd, cache.page_size, rot_dim, table=table)
         qkv = self.linear(x, w_qkv, bias=bias)
-        self.rope_cache_write(qkv, positions, inv_freq, cache, nh, nkv, hd, rot_dim)
+        self.rope_cache_write(qkv, positions, inv_freq, cache, nh, nkv, hd, rot_dim, ctx=ctx, key=key)
         return qkv
 
-    def rope_cache_write(self, qkv, positions, inv_freq, cache, nh, nkv, hd, rot_dim=None):
+    def rope_cache_write(self, qkv, positions, inv_freq, cache, nh, nkv, hd, rot_dim=None, ctx=None, key=None):
         writes = cache.writes
+        rot_dim = hd if rot_dim is None else rot_dim
+        table = self.rope_table(ctx, positions, inv_freq, rot_dim, key)
         ops.rope_cache_write(qkv, positions, inv_freq, cache.slots if writes else None,
                              cache.k if writes else None, cache.v if writes else None,
-                             nh, nkv, hd, cache.page_size, rot_dim)
+                             nh, nkv, hd, cache.page_size, rot_dim, table=table)
 
     def attention(self, q, cache, ctx, nh, scale, window):
         if self._sm100 is not None:

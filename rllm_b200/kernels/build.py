@@ -108,7 +108,9 @@ def build_library(name: str, verbose_ptxas: bool = False) -> str:
     if not srcs:
         raise BuildError(f"library {name!r} has no sources under {CSRC}")
     nvcc = _nvcc()
-    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if verbose_ptxas else [])
+    # RLLM_B200_NVCC_FLAGS: extra compiler flags (e.g. -DNAME=value to try a tuning constant)
+    flags = list(NVCC_FLAGS) + os.environ.get("RLLM_B200_NVCC_FLAGS", "").split() + \
+        (["-Xptxas", "-v"] if verbose_ptxas else [])
     libdir = _lib_dir()
     hdrs = _headers()
     objs, jobs = [], []
@@ -142,7 +144,22 @@ def build_library(name: str, verbose_ptxas: bool = False) -> str:
                         f"link {os.path.basename(so)}")
     os.replace(tmp, so)
     _say(f"built {os.path.basename(so)}")
+    _prune(libdir, name, srcs, objs, so)
     return so
+
+
+def _prune(libdir: str, name: str, srcs: list[str], objs: list[str], so: str) -> None:
+    """Delete what earlier versions of the sources left behind (a loaded library stays mapped)."""
+    keep = {os.path.basename(p) for p in objs} | {os.path.basename(so)}
+    stems = tuple(os.path.splitext(s)[0] + "." for s in srcs)
+    for f in os.listdir(libdir):
+        stale_obj = f.endswith(".o") and f.startswith(stems)
+        stale_so = f.endswith(".so") and f.startswith(f"librllm_b200_{name}.")
+        if (stale_obj or stale_so) and f not in keep:
+            try:
+                os.remove(os.path.join(libdir, f))
+            except OSError:
+                pass
 
 
 def load_library(name: str) -> ctypes.CDLL:

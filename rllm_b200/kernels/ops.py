@@ -30,8 +30,9 @@ _P = c_void_p
 _SIGS = {
     "simt": {
         "rllm_embed": [_P, _P, c_int, _P, c_int, c_int, c_int, _P, _P],
-        "rllm_rmsnorm": [_P, _P, c_int, _P, c_int, c_int, c_int, c_float, _P],
-        "rllm_rope_cache_write": [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
+        "rllm_rmsnorm": [_P, _P, _P, c_int, _P, c_int, c_int, c_int, c_float, _P],
+        "rllm_rope_table": [_P, _P, _P, c_int, c_int, _P],
+        "rllm_rope_cache_write": [_P, c_int, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
                                   c_int, _P],
         "rllm_gather_rows": [_P, _P, _P, c_int, c_int, _P],
         "rllm_add_into": [_P, _P, c_int, c_longlong, _P],
@@ -116,26 +117,45 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = Non
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype,
-            out: torch.Tensor | None = None) -> torch.Tensor:
-    """y = x * rsqrt(mean(x^2) + eps) * w. x float32 [T, H]; w [H]."""
+            out: torch.Tensor | None = None, rows: torch.Tensor | None = None) -> torch.Tensor:
+    """y = x * rsqrt(mean(x^2) + eps) * w. x float32 [T, H]; w [H]. With `rows` (int32 [R]) only
+    those rows of x are normalised: y [R, H]."""
     _cuda(x, "x"); _cuda(w, "w")
     if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
         raise KernelError("rmsnorm input must be a contiguous float32 [T, H]")
     T, H = x.shape
+    if rows is not None:
+        if rows.dtype != torch.int32 or rows.dim() != 1 or not rows.is_contiguous():
+            raise KernelError("rmsnorm rows must be a contiguous int32 vector")
+        T = rows.numel()
     if w.shape != (H,) or not w.is_contiguous():
         raise KernelError(f"rmsnorm weight must be [{H}], got {tuple(w.shape)}")
     if out is None:
         out = torch.empty((T, H), dtype=out_dtype, device=x.device)
-    _check(_fn("simt", "rllm_rmsnorm")(x.data_ptr(), w.data_ptr(), _dt(w, "w"), out.data_ptr(),
+    _check(_fn("simt", "rllm_rmsnorm")(x.data_ptr(), _ptr(rows), w.data_ptr(), _dt(w, "w"), out.data_ptr(),
                                        _dt(out, "out"), T, H, float(eps), _stream()), "rmsnorm")
+    return out
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, T: int) -> torch.Tensor:
+    """(cos, sin)(positions[t] * inv_freq[i]) as float32 [T, len(inv_freq), 2]: a step's rotations,
+    made once and read by every layer."""
+    _cuda(positions, "positions"); _cuda(inv_freq, "inv_freq")
+    if positions.dtype != torch.int32 or positions.numel() < T or inv_freq.dtype != torch.float32 \
+            or not inv_freq.is_contiguous():
+        raise KernelError("rope_table takes int32 positions [T] and float32 inverse frequencies")
+    out = torch.empty((T, inv_freq.numel(), 2), dtype=torch.float32, device=positions.device)
+    _check(_fn("simt", "rllm_rope_table")(positions.data_ptr(), inv_freq.data_ptr(), out.data_ptr(), T,
+                                          inv_freq.numel(), _stream()), "rope_table")
     return out
 
 
 def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
                      slots: torch.Tensor | None, kcache: torch.Tensor | None,
                      vcache: torch.Tensor | None, nh: int, nkv: int, hd: int, page_size: int,
-                     rot_dim: int | None = None) -> None:
-    """Rotate q and k of `qkv` [T, (nh+2nkv)*hd] (q in place) and write k, v to the cache."""
+                     rot_dim: int | None = None, table: torch.Tensor | None = None) -> None:
+    """Rotate q and k of `qkv` [T, (nh+2nkv)*hd] (q in place) and write k, v to the cache.
+    `table`: `rope_table(positions, inv_freq[:rot_dim // 2], T)`, else the angles are computed here."""
     _cuda(qkv, "qkv")
     T = qkv.shape[0]
     if qkv.dim() != 2 or qkv.shape[1] != (nh + 2 * nkv) * hd or not qkv.is_contiguous():
@@ -152,8 +172,11 @@ def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch
             if c is None or c.dtype != qkv.dtype or c.dim() != 4 or c.shape[1:] != (nkv, page_size, hd) \
                     or not c.is_contiguous():
                 raise KernelError(f"{n} must be contiguous [pages, {nkv}, {page_size}, {hd}] of {qkv.dtype}")
+    if table is not None and (table.dtype != torch.float32 or tuple(table.shape) != (T, rot_dim // 2, 2)
+                              or not table.is_contiguous()):
+        raise KernelError(f"rope table must be contiguous float32 [{T}, {rot_dim // 2}, 2]")
     _check(_fn("simt", "rllm_rope_cache_write")(
-        qkv.data_ptr(), _dt(qkv, "qkv"), positions.data_ptr(), inv_freq.data_ptr(), _ptr(slots),
+        qkv.data_ptr(), _dt(qkv, "qkv"), positions.data_ptr(), inv_freq.data_ptr(), _ptr(table), _ptr(slots),
         _ptr(kcache), _ptr(vcache), T, nh, nkv, hd, page_size, rot_dim, _stream()), "rope_cache_write")
 
 

@@ -12,8 +12,11 @@ _P = c_void_p
 ops.register_signatures("sm100", {
     "rllm_tc_gemm": [c_int, _P, c_longlong, _P, _P, c_longlong, c_int, c_int, c_int, c_int, _P, c_int, _P],
     "rllm_tc_gemm_plan": [c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)],
-    "rllm_tc_gemm_qkv_rope": [_P, c_longlong, _P, _P, c_longlong, c_int, c_int, _P, _P, _P, _P, _P, c_int, c_int,
-                              c_int, c_int, c_int, c_int, _P, c_int, _P],
+    "rllm_tc_gemm_norm": [c_int, _P, c_longlong, _P, _P, c_int, c_float, _P, _P, c_longlong, c_int, c_int, c_int,
+                          c_int, _P, c_int, _P],
+    "rllm_tc_gemm_norm_max_tokens": [],
+    "rllm_tc_gemm_qkv_rope": [_P, c_longlong, _P, c_longlong, _P, c_int, c_float, _P, _P, c_longlong, c_int, c_int,
+                              _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P],
     "rllm_attention_fa": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_float, c_int, c_int, _P, _P, _P],
     "rllm_attention_decode": [_P, c_int, _P, _P, c_longlong, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int,
@@ -92,19 +95,74 @@ def gemm(x: torch.Tensor, w: torch.Tensor, epilogue: int, out: torch.Tensor | No
     return out
 
 
+_norm_max = None
+
+
+def norm_max_tokens() -> int:
+    """The most tokens a step may bring for the products with RMSNorm in front."""
+    global _norm_max
+    if _norm_max is None:
+        _norm_max = int(ops._fn("sm100", "rllm_tc_gemm_norm_max_tokens")())
+    return _norm_max
+
+
+def norm_supported(h: torch.Tensor, g: torch.Tensor, w: torch.Tensor, rows: torch.Tensor | None = None) -> bool:
+    """Can `rmsnorm(h[rows]) W^T` run as one kernel? h float32 [*, K] rows, g the norm weight."""
+    T = h.shape[0] if rows is None else rows.numel()
+    return (h.dtype == torch.float32 and h.dim() == 2 and h.stride(1) == 1 and h.stride(0) % 4 == 0
+            and w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_contiguous() and h.shape[1] == w.shape[1]
+            and h.shape[1] % 8 == 0 and g.dtype in (torch.float32, torch.bfloat16) and g.is_contiguous()
+            and g.numel() == h.shape[1] and h.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and g.data_ptr() % 16 == 0 and 0 < T <= norm_max_tokens()
+            and (rows is None or (rows.dtype == torch.int32 and rows.is_contiguous())))
+
+
+def gemm_norm(h: torch.Tensor, g: torch.Tensor, eps: float, w: torch.Tensor, epilogue: int,
+              rows: torch.Tensor | None = None, split: bool = True) -> torch.Tensor:
+    """C = rmsnorm(h[rows]; g, eps) W^T in one kernel (store, store-float or SwiGLU epilogue)."""
+    if not norm_supported(h, g, w, rows):
+        raise ops.KernelError("tc gemm with norm: float32 rows of K % 8 == 0 values, at most "
+                              f"{norm_max_tokens()} tokens, bfloat16 weights, 16-byte aligned")
+    if epilogue not in (ops.EPI_STORE, ops.EPI_STORE_F32, ops.EPI_SWIGLU):
+        raise ops.KernelError("tc gemm with norm: epilogue must be store, store-float or SwiGLU")
+    st = init(h.device)
+    T = h.shape[0] if rows is None else rows.numel()
+    K = h.shape[1]
+    N = w.shape[0] // 2 if epilogue == ops.EPI_SWIGLU else w.shape[0]
+    out = torch.empty((T, N), dtype=torch.float32 if epilogue == ops.EPI_STORE_F32 else torch.bfloat16,
+                      device=h.device)
+    rc = ops._fn("sm100", "rllm_tc_gemm_norm")(
+        epilogue, h.data_ptr(), h.stride(0), ops._ptr(rows), g.data_ptr(), ops._dt(g, "norm weight"), float(eps),
+        w.data_ptr(), out.data_ptr(), out.stride(0), T, N, K, int(split), st.err.data_ptr(), st.sm_count,
+        ops._stream())
+    ops._check(rc, "tc_gemm_norm")
+    return out
+
+
 def qkv_rope_supported(x: torch.Tensor, w: torch.Tensor, kcache, hd: int) -> bool:
     return gemm_supported(x, w) and 128 % hd == 0 and (kcache is None or kcache.dtype == torch.bfloat16)
 
 
-def gemm_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
+def gemm_qkv_rope(x: torch.Tensor | None, w_qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
                   slots: torch.Tensor | None, kcache: torch.Tensor | None, vcache: torch.Tensor | None,
-                  nh: int, nkv: int, hd: int, page_size: int, rot_dim: int, split: bool = True) -> torch.Tensor:
+                  nh: int, nkv: int, hd: int, page_size: int, rot_dim: int, split: bool = True,
+                  norm: tuple | None = None, table: torch.Tensor | None = None) -> torch.Tensor:
     """qkv = x w_qkv^T with q and k rotated by position and k, v written to the paged cache at
-    `slots` (None: no write), all in the product's epilogue. Returns qkv [T, (nh + 2 nkv) * hd]."""
-    if not qkv_rope_supported(x, w_qkv, kcache, hd):
-        raise ops.KernelError("tc gemm with rotary epilogue: bfloat16 operands and a head size dividing 128")
-    st = init(x.device)
-    T, K = x.shape
+    `slots` (None: no write), all in the product's epilogue. Returns qkv [T, (nh + 2 nkv) * hd].
+    `norm` = (h, g, eps) instead of x: RMSNorm of the float rows h in front, in the same kernel.
+    `table`: `ops.rope_table` of these positions ([T, rot_dim / 2, 2]); else the angles are computed here."""
+    if norm is not None:
+        h, g, eps = norm
+        if not norm_supported(h, g, w_qkv) or 128 % hd or (kcache is not None and kcache.dtype != torch.bfloat16):
+            raise ops.KernelError("tc gemm with norm and rotary epilogue: sizes not supported")
+        T, K = h.shape
+        dev = h.device
+    else:
+        if not qkv_rope_supported(x, w_qkv, kcache, hd):
+            raise ops.KernelError("tc gemm with rotary epilogue: bfloat16 operands and a head size dividing 128")
+        T, K = x.shape
+        dev = x.device
+    st = init(dev)
     N = (nh + 2 * nkv) * hd
     if w_qkv.shape[0] != N:
         raise ops.KernelError(f"w_qkv must have {N} rows, got {w_qkv.shape[0]}")
@@ -118,10 +176,17 @@ def gemm_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, positions: torch.Tensor,
             if c is None or c.dtype != torch.bfloat16 or c.dim() != 4 or tuple(c.shape[1:]) != (nkv, page_size, hd) \
                     or not c.is_contiguous():
                 raise ops.KernelError(f"caches must be contiguous bfloat16 [pages, {nkv}, {page_size}, {hd}]")
-    out = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
+    if table is not None and (table.dtype != torch.float32 or tuple(table.shape) != (T, rot_dim // 2, 2)
+                              or not table.is_contiguous()):
+        raise ops.KernelError(f"rope table must be contiguous float32 [{T}, {rot_dim // 2}, 2]")
+    out = torch.empty((T, N), dtype=torch.bfloat16, device=dev)
+    if norm is not None:
+        xa = (None, 0, h.data_ptr(), h.stride(0), g.data_ptr(), ops._dt(g, "norm weight"), float(eps))
+    else:
+        xa = (x.data_ptr(), x.stride(0), None, 0, None, 0, 0.0)
     rc = ops._fn("sm100", "rllm_tc_gemm_qkv_rope")(
-        x.data_ptr(), x.stride(0), w_qkv.data_ptr(), out.data_ptr(), out.stride(0), T, K, positions.data_ptr(),
-        inv_freq.data_ptr(), ops._ptr(slots), ops._ptr(kcache) if slots is not None else None,
+        *xa, w_qkv.data_ptr(), out.data_ptr(), out.stride(0), T, K, positions.data_ptr(),
+        inv_freq.data_ptr(), ops._ptr(table), ops._ptr(slots), ops._ptr(kcache) if slots is not None else None,
         ops._ptr(vcache) if slots is not None else None, nh, nkv, hd, page_size, rot_dim, int(split),
         st.err.data_ptr(), st.sm_count, ops._stream())
     ops._check(rc, "tc_gemm_qkv_rope")

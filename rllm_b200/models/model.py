@@ -63,6 +63,8 @@ class Model:
     # -- running
     def forward(self, ctx, caches):
         """Run the step's tokens through every scheduled layer -> float32 [T, hidden]."""
+        if hasattr(ctx, "per_forward"):
+            ctx.per_forward.clear()
         h = self.embedding.forward(ctx)
         for call in self.schedule:
             cache = caches.layer_view(call.cache_layer, ctx, call.writes) if call.cache_layer >= 0 else None

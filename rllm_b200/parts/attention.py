@@ -14,6 +14,7 @@ from .base import KVCacheSpec, Param, Part, Source, register_part
 
 class GQAttention(Part):
     graph_safe = True
+    takes_deferred = True      # x goes to the backend's products as it comes
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, position: Part,
                  window: int | None = None, bias: bool = False, scale: float | None = None):

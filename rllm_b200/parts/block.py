@@ -30,9 +30,17 @@ class PreNormBlock(Part):
 
     def forward(self, h, ctx, cache):
         """h: float32 residual stream [T, hidden], updated in place."""
-        self.mixer.forward(self.mixer_norm.forward(h, ctx), ctx, cache, h)
-        self.ffn.forward(self.ffn_norm.forward(h, ctx), ctx, h)
+        self.mixer.forward(self._norm(self.mixer_norm, self.mixer, h, ctx), ctx, cache, h)
+        self.ffn.forward(self._norm(self.ffn_norm, self.ffn, h, ctx), ctx, h)
         return h
+
+    @staticmethod
+    def _norm(norm, consumer, h, ctx):
+        """A consumer that hands its input straight to the backend's products (`takes_deferred`)
+        gets the norm in deferred form, so that it can run inside the first product."""
+        if getattr(consumer, "takes_deferred", False) and hasattr(norm, "deferred"):
+            return norm.deferred(h, ctx)
+        return norm.forward(h, ctx)
 
 
 register_part("block", "prenorm", PreNormBlock)

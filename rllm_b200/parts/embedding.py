@@ -44,6 +44,8 @@ class OutputHead(Part):
 
     def forward(self, h, rows, ctx):
         """h: float32 [T, hidden]; rows: int32 device vector of the wanted rows -> [R, vocab]."""
-        sel = ctx.backend.gather_rows(h, rows)
-        n = self.norm.forward(sel, ctx)
+        if hasattr(self.norm, "deferred"):
+            n = self.norm.deferred(h, ctx, rows)      # gather, norm and product may be one kernel
+        else:
+            n = self.norm.forward(ctx.backend.gather_rows(h, rows), ctx)
         return ctx.backend.linear_f32(n, self.matrix())

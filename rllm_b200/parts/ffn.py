@@ -8,6 +8,7 @@ from .base import Param, Part, Source, register_part
 
 class SwiGLU(Part):
     graph_safe = True
+    takes_deferred = True      # x goes to the backend's products as it comes
 
     def __init__(self, hidden: int, intermediate: int):
         self.hidden, self.intermediate = hidden, intermediate

@@ -19,6 +19,11 @@ class RMSNorm(Part):
         """h: float32 residual stream [T, size] -> normalised activations in the run dtype."""
         return ctx.backend.rmsnorm(h, self.weight, self.eps)
 
+    def deferred(self, h, ctx, rows=None):
+        """The same norm (of rows `rows` of h when given) for a consumer that may run it inside its
+        own first product: a tensor, or the backend's deferred form that its products accept."""
+        return ctx.backend.normed(h, self.weight, self.eps, rows)
+
     def forward_f32(self, h, ctx):
         import torch
         return ctx.backend.rmsnorm(h, self.weight, self.eps, out_dtype=torch.float32)

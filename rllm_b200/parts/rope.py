@@ -50,6 +50,8 @@ class RotaryEmbedding(Part):
             raise ValueError(f"rotary width {self.rot_dim} must be even and <= head_dim {head_dim}")
         self.theta, self.scaling = float(theta), scaling
         self.inv_freq = None
+        # layers with the same rule share one table of angles per step
+        self.table_key = ("rope", self.rot_dim, self.theta, repr(scaling))
 
     def finalize(self, device, dtype):
         f = inverse_frequencies(self.rot_dim, self.theta, self.scaling)
@@ -59,12 +61,12 @@ class RotaryEmbedding(Part):
         """qkv = x w_qkv^T (+ bias) with q and k rotated and k, v written into the layer's pages:
         the projection and this part's work in one kernel where the backend can."""
         return ctx.backend.qkv_rope_cache_write(x, w_qkv, bias, ctx.positions, self.inv_freq, cache, nh, nkv,
-                                                self.head_dim, self.rot_dim)
+                                                self.head_dim, self.rot_dim, ctx=ctx, key=self.table_key)
 
     def rotate_and_store(self, qkv, ctx, cache, nh, nkv):
         """Rotate q (in place) and k of `qkv`, and write k, v into the layer's pages."""
         ctx.backend.rope_cache_write(qkv, ctx.positions, self.inv_freq, cache, nh, nkv,
-                                     self.head_dim, self.rot_dim)
+                                     self.head_dim, self.rot_dim, ctx=ctx, key=self.table_key)
 
 
 register_part("position", "rope", RotaryEmbedding)

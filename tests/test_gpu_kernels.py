@@ -52,6 +52,10 @@ def test_rmsnorm(dtype, T, H, eps):
     assert rel(out, P.rms_norm(x, w.float(), eps)) <= TOL[dtype]
     out32 = ops().rmsnorm(x.to(DEV), w.float().to(DEV), eps, torch.float32)   # weight kept in 32-bit
     assert rel(out32, P.rms_norm(x, w.float(), eps)) <= 2e-6
+    # chosen rows only (the output head normalises the wanted rows): the same values, row by row
+    rows = torch.tensor([T - 1, 0, T - 1], dtype=torch.int32)
+    picked = ops().rmsnorm(x.to(DEV), w.float().to(DEV), eps, torch.float32, rows=rows.to(DEV))
+    assert torch.equal(picked, out32[rows.long()])
 
 
 @pytest.mark.parametrize("dtype", list(DT))
@@ -180,6 +184,15 @@ def test_rope_and_cache_write(dtype, nh, nkv, hd, page, rot):
         assert rel(kc[pg, :, off], kr[t]) <= TOL[dtype]
         assert torch.equal(vc[pg, :, off].cpu(), v[t])
     assert float(kc.float().cpu()[~written[:, None, :].expand(-1, nkv, -1)].abs().sum()) == 0.0
+    # with the step's table of angles instead of angles computed in the kernel: the same bits
+    table = o.rope_table(positions.to(DEV), inv_freq[: rot_dim // 2].contiguous().to(DEV), T)
+    ang = positions.float()[:, None] * inv_freq[: rot_dim // 2].float()[None, :]
+    assert rel(table[..., 0], torch.cos(ang.double()).float()) <= 2e-6
+    assert rel(table[..., 1], torch.sin(ang.double()).float()) <= 2e-6
+    kc2, vc2, buf2 = torch.zeros_like(kc), torch.zeros_like(vc), qkv.to(DEV).clone()
+    o.rope_cache_write(buf2, positions.to(DEV), inv_freq.to(DEV), slots.to(DEV), kc2, vc2, nh, nkv, hd,
+                       page, rot_dim, table=table)
+    assert torch.equal(buf2, buf) and torch.equal(kc2, kc) and torch.equal(vc2, vc)
 
 
 def test_argmax_lowest_index_wins_and_large_vocab():

@@ -43,6 +43,61 @@ def test_tc_gemm_epilogues(T, N, K, split):
     assert torch.equal(again, out32)
 
 
+NORM_SHAPES = [(1, 128, 64), (8, 384, 200), (16, 100, 72), (17, 3072, 2048), (33, 640, 520), (64, 2048, 2048),
+               (5, 128256, 256), (8, 2048, 8192), (64, 256, 1000)]
+
+
+@pytest.mark.parametrize("T,N,K", NORM_SHAPES)
+@pytest.mark.parametrize("split,g_dtype", [(True, torch.float32), (False, torch.bfloat16)])
+def test_tc_gemm_with_rmsnorm_in_front(T, N, K, split, g_dtype):
+    """rmsnorm(h[rows]) W^T in one kernel, every epilogue it has, against (a) the same formula with
+    the kernel's one rounding (bf16 of h * g) and float elsewhere, tightly, and (b) the plain float
+    formula, within bfloat16 rounding. h has a few large columns, as a residual stream has; the rows
+    are picked out of a larger h through an index list in half of the cases."""
+    from rllm_b200.kernels import ops, sm100
+    g0 = torch.Generator().manual_seed(11)
+    R = T + 5
+    h = torch.randn(R, K, generator=g0)
+    h[:, :: max(1, K // 7)] *= 25.0
+    gw = (1.0 + 0.3 * torch.randn(K, generator=g0)).to(g_dtype)
+    eps = 1e-5 if split else 1e-6
+    w = rnd(2 * N, K, seed=2, scale=K ** -0.5)
+    rows = torch.randperm(R, generator=g0)[:T].to(torch.int32) if split else None
+    hs = h[rows.long()] if rows is not None else h[:T]
+    rstd = torch.rsqrt((hs.double() ** 2).mean(-1, keepdim=True) + eps).float()
+    xb = (hs * gw.float()).to(torch.bfloat16).float()                  # the kernel's rounding point
+    x_plain = hs * rstd * gw.float()
+    hd_, wd = (h if rows is not None else h[:T].contiguous()).to(DEV), w.to(DEV)
+    rd = rows.to(DEV) if rows is not None else None
+    gd = gw.to(DEV)
+    w1 = wd[:N].contiguous()
+    same = (xb @ w[:N].float().t()) * rstd
+    plain = x_plain @ w[:N].float().t()
+    out32 = sm100.gemm_norm(hd_, gd, eps, w1, ops.EPI_STORE_F32, rows=rd, split=split)
+    assert out32.dtype == torch.float32 and rel(out32, same) <= 3e-5
+    assert rel(out32, plain) <= 6e-3
+    assert rel(sm100.gemm_norm(hd_, gd, eps, w1, ops.EPI_STORE, rows=rd, split=split), plain) <= 8e-3
+    up = (xb @ w[N:].float().t()) * rstd
+    want = same / (1 + torch.exp(-same)) * up
+    assert rel(sm100.gemm_norm(hd_, gd, eps, wd, ops.EPI_SWIGLU, rows=rd, split=split), want) <= 8e-3
+    sm100.check_error(DEV)
+    again = sm100.gemm_norm(hd_, gd, eps, w1, ops.EPI_STORE_F32, rows=rd, split=split)
+    assert torch.equal(again, out32)
+
+
+def test_tc_gemm_with_norm_refuses_misfits():
+    from rllm_b200.kernels import ops, sm100
+    h = torch.randn(sm100.norm_max_tokens() + 1, 128, device=DEV)
+    g, w = torch.ones(128, device=DEV), rnd(64, 128).to(DEV)
+    assert not sm100.norm_supported(h, g, w)                                   # too many tokens
+    assert sm100.norm_supported(h[:4], g, w)
+    assert not sm100.norm_supported(h[:4, :100], g[:100], w[:, :100].contiguous())   # K % 8
+    with pytest.raises(ops.KernelError):
+        sm100.gemm_norm(h, g, 1e-5, w, ops.EPI_STORE)
+    with pytest.raises(ops.KernelError):
+        sm100.gemm_norm(h[:4], g, 1e-5, w, ops.EPI_ACCUM_F32)
+
+
 def test_tc_gemm_takes_a_strided_view_and_refuses_misfits():
     from rllm_b200.kernels import ops, sm100
     big = rnd(40, 3 * 128, seed=5).to(DEV)
@@ -123,3 +178,27 @@ def test_qkv_product_with_rotary_epilogue(T, K, nh, nkv, hd, page, rot, split):
     out2 = sm100.gemm_qkv_rope(x.to(DEV), w.to(DEV), positions.to(DEV), inv_freq.to(DEV), None, None, None,
                                nh, nkv, hd, page, rot_dim, split=split)
     assert torch.equal(out2, out)
+    if T <= sm100.norm_max_tokens():
+        # the same with RMSNorm in front, in the same kernel: h = x scaled per row, norm weight 1
+        hrows = x.float() * torch.linspace(0.5, 3.0, T)[:, None]
+        rstd = torch.rsqrt((hrows.double() ** 2).mean(-1, keepdim=True) + 1e-6).float()
+        refn = ((hrows.to(torch.bfloat16).float() @ w.float().t()) * rstd)
+        kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(vc)
+        out3 = sm100.gemm_qkv_rope(None, w.to(DEV), positions.to(DEV), inv_freq.to(DEV), slots.to(DEV), kc2, vc2,
+                                   nh, nkv, hd, page, rot_dim, split=split,
+                                   norm=(hrows.to(DEV), torch.ones(K, device=DEV), 1e-6))
+        sm100.check_error(DEV)
+        qn = rope(refn[:, : nh * hd].view(T, nh, hd))
+        kn = rope(refn[:, nh * hd: (nh + nkv) * hd].view(T, nkv, hd))
+        vn = refn[:, (nh + nkv) * hd:].view(T, nkv, hd)
+        sc = float(refn.abs().max())
+        g3 = out3.float().cpu()
+        assert float((g3[:, : nh * hd].view(T, nh, hd) - qn).abs().max()) <= 6e-3 * sc
+        assert float((g3[:, nh * hd: (nh + nkv) * hd].view(T, nkv, hd) - kn).abs().max()) <= 6e-3 * sc
+        assert float((g3[:, (nh + nkv) * hd:].view(T, nkv, hd) - vn).abs().max()) <= 6e-3 * sc
+        k2, v2 = kc2.float().cpu(), vc2.float().cpu()
+        for t in range(T):
+            if slots[t] >= 0:
+                pg, off = int(slots[t]) // page, int(slots[t]) % page
+                assert float((k2[pg, :, off] - kn[t]).abs().max()) <= 6e-3 * sc
+                assert float((v2[pg, :, off] - vn[t]).abs().max()) <= 6e-3 * sc
