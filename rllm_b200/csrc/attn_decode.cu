@@ -4,15 +4,17 @@
 // heads of its kv head), so the kernel is built around keeping bytes in flight:
 //   * a CTA serves one (sequence, kv head, range of keys); the ranges of a sequence form a
 //     thread-block cluster along z;
-//   * one producer warp walks the block table and issues TMA tensor copies, two per page
-//     (keys, values), 128-byte swizzled, into a ring of tiles of 64 keys (32 for head size 128); an mbarrier
-//     per stage counts the bytes;
-//   * four consumer warps take the tiles round-robin. Each holds the G query rows as the
-//     A operand of mma.sync m16n8k16 (rows beyond G are zero), computes scores, the running
-//     maximum/sum softmax in float with exp2, and the weighted sum of values, all from the
-//     swizzled tile with ldmatrix;
-//   * the four warps' partial results are merged in shared memory, then the ranges of the
-//     cluster are merged through distributed shared memory in rank order, and the output row is
+//   * every warp fetches its own tiles (tile i of the range goes to warp i % NW) with 16-byte
+//     asynchronous copies (cp.async), each lane looking up the page of its key row in the block
+//     table, into stages of its own, written in the 128-byte swizzled layout that ldmatrix reads
+//     without bank conflicts. D tiles per warp are on the way while it works on one. (Tensor
+//     copies by TMA, one per page, topped out at two thirds of the memory bandwidth here: a
+//     page of 16 positions is 2 KB per kv head, too small a box for the copy engine.)
+//   * the warp holds the G query rows as the A operand of mma.sync m16n8k16 (rows beyond G are
+//     zero), computes scores, the running maximum/sum softmax in float with exp2, and the
+//     weighted sum of values;
+//   * the warps' partial results are merged in shared memory, then the ranges of the cluster
+//     are merged through distributed shared memory in rank order, and the output row is
 //     written once. No scratch memory in global memory, no second kernel.
 // A key j is visible when j <= pos (pos = kv_len - 1) and j > pos - window if a window is set.
 // Pages the table does not hold (given back by a window, or beyond the sequence in the last
@@ -20,32 +22,39 @@
 //
 // Formulas: src/gpu/cuda/shaders/attention.cu:328-388 of the reference (scale, softmax with
 // the maximum subtracted, weighted V, head h -> kv head h / G, window start :337-338).
-// Cache layout: [page][kv head][offset in page][HD]; page_size 8, 16, 32 or 64 and at most a tile
-// (64 keys for HD 64, 32 keys for HD 128).
+// Cache layout: [page][kv head][offset in page][HD]; any page size.
 //
 // Programmatic dependent launch: tiles that cannot hold the token the previous kernel has just
 // written are fetched before the wait for that kernel.
 #include "common.cuh"
 #include "sm100.cuh"
-#include <mutex>
-#include <unordered_map>
 
 using namespace rllm;
 using namespace sm100;
 
 namespace {
 
-constexpr int NW = 4;                    // consumer warps
-constexpr int THREADS = (NW + 1) * 32;   // + one producer warp
+#ifndef ADEC_NW
+#define ADEC_NW 4
+#endif
+#ifndef ADEC_D
+#define ADEC_D 3                         // tiles in flight per warp
+#endif
+#ifndef ADEC_TILE_KB
+#define ADEC_TILE_KB 4                   // K (and V) bytes per tile, in KB
+#endif
+constexpr int NW = ADEC_NW;              // warps per CTA
+constexpr int D = ADEC_D;
+constexpr int THREADS = NW * 32;
 constexpr int MAX_CLUSTER = 8;
 
 struct DecParams {
   const bf16* q; int q_stride;
+  const bf16* kcache; const bf16* vcache;
   bf16* out; int out_stride;
   const int* kv_lens; const int* block_table; int bt_stride;
   int nh, nkv, page_size, window, splits;
   float scale_log2e;
-  int* err;
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -67,23 +76,32 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {          // exp2(-inf) = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 // Byte offset of 16-byte chunk `ch` of key row `r` inside a K or V tile: 64-column sub-tiles
-// of [TILE rows][128 bytes], chunk index XORed with the row (the TMA 128-byte swizzle).
+// of [TILE rows][128 bytes], chunk index XORed with the row (the 128-byte swizzle).
 template <int TILE>
 __device__ __forceinline__ uint32_t tile_off(int r, int ch) {
   return (uint32_t)((ch >> 3) * (TILE * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4));
 }
 
 template <int HD> struct DCfg {
-  static constexpr int TILE = 4096 / HD;                      // keys per stage: 64 (HD 64), 32 (HD 128)
-  static constexpr int KV_BYTES = TILE * HD * 2;              // one K (or V) tile: 8 KB
+  static constexpr int KV_BYTES = ADEC_TILE_KB * 1024;        // one K (or V) tile
+  static constexpr int TILE = KV_BYTES / (HD * 2);            // keys per tile: 32 (HD 64), 16 (HD 128)
   static constexpr int STAGE_BYTES = 2 * KV_BYTES;
-  // A stage is always consumed by the same warp (STAGES is a multiple of NW and tile i goes to
-  // warp i % NW, stage i % STAGES), so no warp can ask for a later use of a stage before it has
-  // itself consumed the earlier one.
-  static constexpr int STAGES = NW;                           // 64 KB in flight per CTA, 3 CTAs per SM
-  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int STAGES = NW * D;                       // warp w owns stages w * D .. w * D + D - 1
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;     // 96 KB in flight per CTA, 2 CTAs per SM
   // after the ring: per-warp partial results [NW][G][HD], their (max, sum) [NW][16] each, then the
   // CTA's merged partial [G][HD] and its (max, sum) [16] each, all float
   static constexpr int merge_floats(int G) { return NW * G * HD + 2 * NW * 16 + G * HD + 32; }
@@ -92,18 +110,14 @@ template <int HD> struct DCfg {
 
 template <int HD>
 __global__ void __launch_bounds__(THREADS)
-attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
-                   const DecParams p) {
+attn_decode_kernel(const DecParams p) {
   typedef DCfg<HD> C;
   constexpr int TILE = C::TILE;
   constexpr int KSTEPS = HD / 16;
   constexpr int DTILES = HD / 8;
-  static_assert(C::STAGES % NW == 0, "a stage must always belong to the same consumer warp");
+  constexpr int CPR = HD / 8;                              // 16-byte chunks per key row
+  constexpr int CHUNKS = TILE * CPR / 32;                  // chunks per lane per K (or V) tile
   extern __shared__ uint8_t dsmem_raw[];
-  __shared__ __align__(8) uint64_t full_bar[C::STAGES];
-  __shared__ __align__(8) uint64_t empty_bar[C::STAGES];
-  __shared__ int abort_flag;
-  __shared__ int never_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* smem = (uint8_t*)(((uintptr_t)dsmem_raw + 1023) & ~(uintptr_t)1023);
@@ -117,15 +131,6 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
   float* c_o = w_l + NW * 16;                                      // [G][HD]
   float* c_m = c_o + G * HD;                                       // [16]
   float* c_l = c_m + 16;                                           // [16]
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    abort_flag = 0;
-    never_flag = 0;
-    fence_barrier_init();
-  }
-  if (warp == NW && lane == 0) { prefetch_tensormap(&tmap_k); prefetch_tensormap(&tmap_v); }
-  __syncthreads();
   pdl_launch();
 
   // kv_lens and the block table come from the host copy that precedes the whole step, not from
@@ -140,60 +145,43 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
   const int te = min(tile_first + tiles_total, tb + per);
   const int n_tiles = te > tb ? te - tb : 0;
   const int last_tile = pos / TILE;                         // the tile the newest token lies in
+  const int* bt = p.block_table + (size_t)seq * p.bt_stride;
+  const int last_held = pos / p.page_size;
+  const int pos_page = bt[last_held];
+  const uint32_t ring = smem_u32(smem) + (uint32_t)(warp * D) * C::STAGE_BYTES;   // this warp's stages
+  bool waited = false;
 
-  if (warp == NW) {
-    // ------------------------------------------------------------ producer
-    const int ppt = TILE / p.page_size;                     // pages per tile
-    const int* bt = p.block_table + (size_t)seq * p.bt_stride;
-    const int pos_page = bt[pos / p.page_size];
-    const int last_held = pos / p.page_size;
-    bool waited = false, ok = true;
-    int issued = 0;
-    for (int i0 = 0; i0 < n_tiles && ok; i0 += 32 / ppt) {
-      // the page ids of up to 32 pages (32 / ppt tiles) in one load
-      const int pg_idx = (tb + i0) * ppt + lane;
-      int page = (pg_idx <= last_held) ? bt[pg_idx] : -1;
-      if (page < 0) page = pos_page;
-      const int n_here = min(32 / ppt, n_tiles - i0);
-      for (int ii = 0; ii < n_here && ok; ++ii) {
-        const int i = i0 + ii;
-        const int s = i % C::STAGES;
-        const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
-        if (tb + i == last_tile && !waited) { pdl_wait(); waited = true; }
-        if (lane == 0) {
-          if (i >= C::STAGES && !mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag)) {
-            abort_flag = 1; record_failure(p.err, 11, (i & 0xfff) | (seq << 12)); ok = false;
-          }
-          if (ok) mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
-        }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) break;
-        uint8_t* st = smem + (size_t)s * C::STAGE_BYTES;
-        for (int j = 0; j < ppt; ++j) {
-          const int pj = __shfl_sync(0xffffffffu, page, ii * ppt + j);
-          if (lane == 0) {
-            const int row = (pj * p.nkv + kvh) * p.page_size;
+  // Starts the copies of this warp's tile `i` (the (i / NW)-th of the warp) and closes a copy
+  // group, also when there is no such tile, so that the groups can be counted.
+  auto issue = [&](int i) {
+    if (i < n_tiles) {
+      if (tb + i == last_tile && !waited) { pdl_wait(); waited = true; }
+      const uint32_t st = ring + (uint32_t)((i / NW) % D) * C::STAGE_BYTES;
+      const int j0 = (tb + i) * TILE;
 #pragma unroll
-            for (int h = 0; h < HD / 64; ++h) {
-              tma_load_2d(st + h * (TILE * 128) + j * p.page_size * 128, &tmap_k, &full_bar[s], h * 64, row);
-              tma_load_2d(st + C::KV_BYTES + h * (TILE * 128) + j * p.page_size * 128, &tmap_v, &full_bar[s],
-                          h * 64, row);
-            }
-          }
-        }
-        issued = i + 1;
+      for (int c = 0; c < CHUNKS; ++c) {
+        const int id = lane + 32 * c;
+        const int r = id / CPR, ch = id % CPR;
+        const int j = j0 + r;
+        const int pg_idx = j / p.page_size;
+        int page = pg_idx <= last_held ? __ldg(bt + pg_idx) : -1;
+        if (page < 0) page = pos_page;
+        const size_t src = (((size_t)page * p.nkv + kvh) * p.page_size + j % p.page_size) * HD + ch * 8;
+        const uint32_t dst = st + tile_off<TILE>(r, ch);
+        cp_async16(dst, p.kcache + src);
+        cp_async16(dst + C::KV_BYTES, p.vcache + src);
       }
     }
-    if (!waited) pdl_wait();
-    if (lane == 0 && abort_flag) {
-      for (int i = max(0, issued - C::STAGES); i < issued; ++i)
-        mbar_wait(&full_bar[i % C::STAGES], (uint32_t)(i / C::STAGES) & 1u, &never_flag, 200000000LL);
-    }
-  } else {
-    // ------------------------------------------------------------ consumers
+    cp_async_commit();
+  };
+
+  {
+    // ------------------------------------------------------------ every warp: fetch, then work
     const int quad = lane >> 2, qi = lane & 3;
     const bool vA = quad < G, vB = quad + 8 < G;
-    pdl_wait();                                   // q comes from the kernel before this one
+#pragma unroll
+    for (int d = 0; d < D; ++d) issue(warp + d * NW);
+    if (!waited) { pdl_wait(); waited = true; }   // q comes from the kernel before this one
     uint32_t qf[KSTEPS][4];
     {
       const bf16* qa = p.q + (size_t)seq * p.q_stride + (size_t)(kvh * G + (vA ? quad : 0)) * HD;
@@ -212,80 +200,94 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     for (int i = 0; i < DTILES; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
     const int mat = lane >> 3, rr = lane & 7;
-    bool ok = true;
 
-    for (int i = warp; i < n_tiles && ok; i += NW) {
-      const int s = i % C::STAGES;
-      const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
-      bool got = true;
-      if (lane == 0) got = mbar_wait(&full_bar[s], ph, &abort_flag);
-      got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
-      if (!got) { if (lane == 0) { abort_flag = 1; record_failure(p.err, 12, (i & 0xfff) | (seq << 12)); } ok = false; break; }
-      const uint32_t kt = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
+    for (int i = warp; i < n_tiles; i += NW) {
+      cp_async_wait<D - 1>();                       // this warp's oldest group, tile i, has landed
+      __syncwarp();
+      const uint32_t kt = ring + (uint32_t)((i / NW) % D) * C::STAGE_BYTES;
       const uint32_t vt = kt + C::KV_BYTES;
       const int j0 = (tb + i) * TILE;
 
+      // ---- scores: every fragment of the K tile is fetched before the first product, so the
+      // shared-memory latencies overlap; rows beyond G hold zeros and are never stored
+      uint32_t kf[KSTEPS][TILE / 16][4];
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk)
+#pragma unroll
+        for (int np = 0; np < TILE / 16; ++np)
+          ldsm_x4(kf[kk][np], kt + tile_off<TILE>((2 * np + (mat >> 1)) * 8 + rr, 2 * kk + (mat & 1)));
       float sc[TILE / 8][4];
 #pragma unroll
       for (int x = 0; x < TILE / 8; ++x) { sc[x][0] = sc[x][1] = sc[x][2] = sc[x][3] = 0.f; }
 #pragma unroll
       for (int kk = 0; kk < KSTEPS; ++kk) {
 #pragma unroll
-        for (int nt = 0; nt < TILE / 8; nt += 2) {
-          uint32_t b[4];
-          ldsm_x4(b, kt + tile_off<TILE>((nt + (mat >> 1)) * 8 + rr, 2 * kk + (mat & 1)));
-          mma16816(sc[nt], qf[kk], b[0], b[1]);
-          mma16816(sc[nt + 1], qf[kk], b[2], b[3]);
+        for (int np = 0; np < TILE / 16; ++np) {
+          mma16816(sc[2 * np], qf[kk], kf[kk][np][0], kf[kk][np][1]);
+          mma16816(sc[2 * np + 1], qf[kk], kf[kk][np][2], kf[kk][np][3]);
+        }
+      }
+      // ---- the V fragments are asked for now and used after the softmax arithmetic
+      uint32_t vf[TILE / 16][DTILES / 2][4];
+#pragma unroll
+      for (int kb = 0; kb < TILE / 16; ++kb)
+#pragma unroll
+        for (int dp = 0; dp < DTILES / 2; ++dp)
+          ldsm_x4_t(vf[kb][dp], vt + tile_off<TILE>(kb * 16 + (mat & 1) * 8 + rr, 2 * dp + (mat >> 1)));
+      __syncwarp();                                    // everything is in registers: the stage may be refilled
+      issue(i + D * NW);
+      if (j0 < lo || j0 + TILE - 1 > pos) {        // only a tile at an edge has keys to hide
+#pragma unroll
+        for (int nt = 0; nt < TILE / 8; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int j = j0 + nt * 8 + qi * 2 + e;
+            if (j > pos || j < lo) { sc[nt][e] = -INFINITY; sc[nt][2 + e] = -INFINITY; }
+          }
         }
       }
       float mxA = -INFINITY, mxB = -INFINITY;
 #pragma unroll
       for (int nt = 0; nt < TILE / 8; ++nt) {
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int j = j0 + nt * 8 + qi * 2 + e;
-          const bool vis = j <= pos && j >= lo;
-          sc[nt][e] = (vis && vA) ? sc[nt][e] * p.scale_log2e : -INFINITY;
-          sc[nt][2 + e] = (vis && vB) ? sc[nt][2 + e] * p.scale_log2e : -INFINITY;
-          mxA = fmaxf(mxA, sc[nt][e]);
-          mxB = fmaxf(mxB, sc[nt][2 + e]);
-        }
+        mxA = fmaxf(mxA, fmaxf(sc[nt][0], sc[nt][1]));
+        mxB = fmaxf(mxB, fmaxf(sc[nt][2], sc[nt][3]));
       }
       mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
       mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
       mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
       mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
-      const float mnA = fmaxf(mA, mxA), mnB = fmaxf(mB, mxB);
+      // running maximum in the exp2 domain (the scale is positive, so it commutes with max)
+      const float mnA = fmaxf(mA, mxA * p.scale_log2e), mnB = fmaxf(mB, mxB * p.scale_log2e);
       const float useA = (mnA == -INFINITY) ? 0.f : mnA, useB = (mnB == -INFINITY) ? 0.f : mnB;
-      const float corrA = exp2f(mA - useA), corrB = exp2f(mB - useB);     // exp2(-inf) = 0
-      mA = mnA; mB = mnB;
-      lA *= corrA; lB *= corrB;
+      if (__any_sync(0xffffffffu, mnA != mA || mnB != mB)) {      // a new maximum somewhere: rescale
+        const float corrA = fast_exp2(mA - useA), corrB = fast_exp2(mB - useB);     // exp2(-inf) = 0
+        lA *= corrA; lB *= corrB;
 #pragma unroll
-      for (int x = 0; x < DTILES; ++x) { o[x][0] *= corrA; o[x][1] *= corrA; o[x][2] *= corrB; o[x][3] *= corrB; }
+        for (int x = 0; x < DTILES; ++x) { o[x][0] *= corrA; o[x][1] *= corrA; o[x][2] *= corrB; o[x][3] *= corrB; }
+        mA = mnA; mB = mnB;
+      }
 #pragma unroll
       for (int kb = 0; kb < TILE / 16; ++kb) {
         uint32_t a[4];
         {
-          const float p0 = exp2f(sc[2 * kb][0] - useA), p1 = exp2f(sc[2 * kb][1] - useA);
-          const float p2 = exp2f(sc[2 * kb][2] - useB), p3 = exp2f(sc[2 * kb][3] - useB);
-          const float p4 = exp2f(sc[2 * kb + 1][0] - useA), p5 = exp2f(sc[2 * kb + 1][1] - useA);
-          const float p6 = exp2f(sc[2 * kb + 1][2] - useB), p7 = exp2f(sc[2 * kb + 1][3] - useB);
+          const float sl = p.scale_log2e;
+          const float p0 = fast_exp2(fmaf(sc[2 * kb][0], sl, -useA)), p1 = fast_exp2(fmaf(sc[2 * kb][1], sl, -useA));
+          const float p2 = fast_exp2(fmaf(sc[2 * kb][2], sl, -useB)), p3 = fast_exp2(fmaf(sc[2 * kb][3], sl, -useB));
+          const float p4 = fast_exp2(fmaf(sc[2 * kb + 1][0], sl, -useA)), p5 = fast_exp2(fmaf(sc[2 * kb + 1][1], sl, -useA));
+          const float p6 = fast_exp2(fmaf(sc[2 * kb + 1][2], sl, -useB)), p7 = fast_exp2(fmaf(sc[2 * kb + 1][3], sl, -useB));
           lA += p0 + p1 + p4 + p5;
           lB += p2 + p3 + p6 + p7;
           a[0] = pack2(p0, p1); a[1] = pack2(p2, p3);
           a[2] = pack2(p4, p5); a[3] = pack2(p6, p7);
         }
 #pragma unroll
-        for (int dn = 0; dn < DTILES; dn += 2) {
-          uint32_t b[4];
-          ldsm_x4_t(b, vt + tile_off<TILE>(kb * 16 + (mat & 1) * 8 + rr, dn + (mat >> 1)));
-          mma16816(o[dn], a, b[0], b[1]);
-          mma16816(o[dn + 1], a, b[2], b[3]);
+        for (int dp = 0; dp < DTILES / 2; ++dp) {
+          mma16816(o[2 * dp], a, vf[kb][dp][0], vf[kb][dp][1]);
+          mma16816(o[2 * dp + 1], a, vf[kb][dp][2], vf[kb][dp][3]);
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty_bar[s]);       // the stage may be refilled
-    }
+        }
+    cp_async_wait<0>();
     lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
     lB += __shfl_xor_sync(0xffffffffu, lB, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
     // park this warp's partial result (rows beyond G hold zeros and -inf)
@@ -299,10 +301,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
       w_m[warp * 16 + quad] = mA; w_l[warp * 16 + quad] = lA;
       w_m[warp * 16 + quad + 8] = mB; w_l[warp * 16 + quad + 8] = lB;
     }
-  }
+    }
   __syncthreads();
 
-  // ---------------------------------------------------------------- merge the four warps
+  // ---------------------------------------------------------------- merge the warps
   for (int idx = threadIdx.x; idx < G * HD; idx += THREADS) {
     const int r = idx / HD, d = idx % HD;
     float M = -INFINITY;
@@ -327,7 +329,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     // ---------------------------------------------------------------- merge the ranges of the cluster
     __syncwarp();
     cluster_sync_all();
-    if (!abort_flag) {
+    {
       uint32_t bo[MAX_CLUSTER], bm[MAX_CLUSTER], bl[MAX_CLUSTER];
 #pragma unroll
       for (int s = 0; s < MAX_CLUSTER; ++s) {
@@ -366,61 +368,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
 }
 
 // ------------------------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-EncodeTiledFn g_enc = nullptr;
-std::mutex g_dmu;
-
-int get_enc() {
-  if (g_enc) return 0;
-  void* fn = nullptr;
-  cudaDriverEntryPointQueryResult qres;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
-      qres != cudaDriverEntryPointSuccess || !fn) {
-    cudaGetLastError();
-    return -5;
-  }
-  g_enc = (EncodeTiledFn)fn;
-  return 0;
-}
-
-struct CKey {
-  const void* p; long long rows; int hd, box;
-  bool operator==(const CKey& o) const { return p == o.p && rows == o.rows && hd == o.hd && box == o.box; }
-};
-struct CHash {
-  size_t operator()(const CKey& k) const {
-    return std::hash<const void*>()(k.p) ^ (std::hash<long long>()(k.rows * 31 + k.hd) << 1) ^ (size_t)k.box;
-  }
-};
-std::unordered_map<CKey, CUtensorMap, CHash> g_cache_maps;     // one per cache tensor, kept for the process
-
-// the cache as a matrix [pages * nkv * page_size, hd]; box = 64 columns x page_size rows
-int cache_map(CUtensorMap* out, const void* ptr, long long rows, int hd, int page_size) {
-  std::lock_guard<std::mutex> lk(g_dmu);
-  CKey key{ptr, rows, hd, page_size};
-  auto it = g_cache_maps.find(key);
-  if (it == g_cache_maps.end()) {
-    CUtensorMap m;
-    cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
-    cuuint32_t box[2] = {64u, (cuuint32_t)page_size};
-    cuuint32_t estr[2] = {1, 1};
-    if (g_enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      return -5;
-    if (g_cache_maps.size() > 1024) g_cache_maps.clear();
-    it = g_cache_maps.emplace(key, m).first;
-  }
-  *out = it->second;
-  return 0;
-}
-
 template <int HD>
-int launch_dec(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int num_seqs, cudaStream_t s) {
+int launch_dec(const DecParams& p, int num_seqs, cudaStream_t s) {
   typedef DCfg<HD> C;
   static bool configured = false;
   if (!configured) {
@@ -430,7 +379,7 @@ int launch_dec(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p,
   }
   dim3 grid(p.nkv, num_seqs, p.splits);
   if (grid.y > 65535) return ERR_TOO_LARGE;
-  return launch_ex(attn_decode_kernel<HD>, grid, dim3(THREADS), C::smem_bytes(p.nh / p.nkv), s, p.splits, mk, mv, p);
+  return launch_ex(attn_decode_kernel<HD>, grid, dim3(THREADS), C::smem_bytes(p.nh / p.nkv), s, p.splits, p);
 }
 
 }  // namespace
@@ -438,28 +387,22 @@ int launch_dec(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p,
 // q: [S, ...] bf16, one row per sequence, stride q_stride, head h at h*hd; out likewise.
 // kcache / vcache: [num_pages][nkv][page_size][hd] bf16. kv_lens [S]: keys visible to each
 // sequence's token (its own included). splits: ranges of keys per sequence (1..8, one cluster).
+// `err` is not used (this kernel has no wait that can run out); it keeps the launchers alike.
 RLLM_API int rllm_attention_decode(const void* q, int q_stride, const void* kcache, const void* vcache,
                                    long long num_pages, void* out, int out_stride, const int* kv_lens,
                                    const int* block_table, int bt_stride, int num_seqs, int nh, int nkv, int hd,
                                    int page_size, float scale, int window, int splits, int* err, void* stream) {
+  (void)err;
   if (num_seqs <= 0) return 0;
   if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || nh / nkv > 16) return ERR_BAD_SIZE;
-  if ((page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) || page_size > 4096 / hd)
-    return ERR_BAD_SIZE;                          // a page must fit in one tile of 4096 / hd keys
-  if (splits < 1 || splits > MAX_CLUSTER || num_pages <= 0) return ERR_BAD_SIZE;
+  if (page_size <= 0 || splits < 1 || splits > MAX_CLUSTER || num_pages <= 0) return ERR_BAD_SIZE;
   if (q_stride % 2 || out_stride % 2 || ((uintptr_t)q & 3) || ((uintptr_t)out & 3) ||
-      ((uintptr_t)kcache & 127) || ((uintptr_t)vcache & 127)) return ERR_BAD_ALIGN;
-  int rc = get_enc();
-  if (rc) return rc;
-  CUtensorMap mk, mv;
-  const long long rows = num_pages * nkv * page_size;
-  if ((rc = cache_map(&mk, kcache, rows, hd, page_size))) return rc;
-  if ((rc = cache_map(&mv, vcache, rows, hd, page_size))) return rc;
+      ((uintptr_t)kcache & 15) || ((uintptr_t)vcache & 15)) return ERR_BAD_ALIGN;
   DecParams p;
-  p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out; p.out_stride = out_stride;
+  p.q = (const bf16*)q; p.q_stride = q_stride; p.kcache = (const bf16*)kcache; p.vcache = (const bf16*)vcache;
+  p.out = (bf16*)out; p.out_stride = out_stride;
   p.kv_lens = kv_lens; p.block_table = block_table; p.bt_stride = bt_stride; p.nh = nh; p.nkv = nkv;
   p.page_size = page_size; p.window = window; p.splits = splits; p.scale_log2e = scale * 1.4426950408889634f;
-  p.err = err;
   cudaStream_t s = (cudaStream_t)stream;
-  return hd == 64 ? launch_dec<64>(mk, mv, p, num_seqs, s) : launch_dec<128>(mk, mv, p, num_seqs, s);
+  return hd == 64 ? launch_dec<64>(p, num_seqs, s) : launch_dec<128>(p, num_seqs, s);
 }

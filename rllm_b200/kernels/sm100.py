@@ -2,6 +2,7 @@
 calls. Holds the device error word that a bounded wait sets when it runs out."""
 from __future__ import annotations
 
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p, POINTER, byref
 
 import torch
@@ -236,29 +237,36 @@ def attention_fa(q, kcache, vcache, cu_q, kv_lens, block_table, num_tokens, max_
 
 def decode_supported(q: torch.Tensor, kcache: torch.Tensor, nh: int) -> bool:
     _, nkv, page_size, hd = kcache.shape
-    return (attention_supported(q, kcache) and page_size in (8, 16, 32, 64) and page_size * hd <= 4096
-            and nh // nkv <= 16
-            and kcache.data_ptr() % 128 == 0)
+    return attention_supported(q, kcache) and nh // nkv <= 16 and kcache.data_ptr() % 16 == 0
 
 
 def decode_splits(num_seqs: int, nkv: int, max_kv_len: int, sm_count: int) -> int:
-    """Ranges the keys of a sequence are cut into (= CTAs per cluster, at most 8): enough for
-    about two CTAs per SM, each with at least four 64-key tiles."""
+    """Ranges the keys of a sequence are cut into (= CTAs per cluster, at most 8). Measured on a
+    B200: a CTA costs about as much as 1,150 keys before its first key, two CTAs fit an SM, and
+    CTAs beyond that wait for a free place; the number of ranges with the least
+    (CTAs / places, at least 1) x (1,150 + keys per range) is taken."""
     base = max(1, num_seqs * nkv)
-    want = (2 * sm_count + base // 2) // base
-    return max(1, min(want, max_kv_len // 256, 8))
+    places = int(os.environ.get('ADEC_PLACES', '2')) * sm_count
+    best, best_cost = 1, None
+    for s in range(1, 9):
+        if s > 1 and max_kv_len // s < 64:
+            break
+        cost = max(1.0, base * s / places) * (1150 + max_kv_len / s)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 def attention_decode(q, kcache, vcache, kv_lens, block_table, nh, scale, window, max_kv_len, splits=None,
                      out=None):
-    """Attention for a step in which every sequence brings one token: TMA-fed, merged inside a
-    thread-block cluster (bf16, head size 64 or 128, pages of 8/16/32/64 positions)."""
+    """Attention for a step in which every sequence brings one token: the ranges of a sequence's
+    keys are merged inside a thread-block cluster (bf16, head size 64 or 128, any page size)."""
     st = init(q.device)
     num_pages, nkv, page_size, hd = kcache.shape
     S = kv_lens.numel()
     if not decode_supported(q, kcache, nh) or q.shape[0] != S:
         raise ops.KernelError("attention_decode: one bfloat16 query row per sequence, head size 64 or 128, "
-                              "pages of 8, 16, 32 or 64 positions, at most 16 heads per kv head")
+                              "at most 16 heads per kv head")
     if vcache.shape != kcache.shape or vcache.dtype != kcache.dtype or not kcache.is_contiguous() \
             or not vcache.is_contiguous() or block_table.dtype != torch.int32 or kv_lens.dtype != torch.int32:
         raise ops.KernelError("attention_decode: caches must be contiguous and alike, tables int32")
