@@ -70,11 +70,14 @@ constexpr int MAX_CLUSTER = 8;
 #endif
 constexpr int NORM_MAX_T = 64;        // the fused-norm variants take steps of at most this many tokens
 
-// the most column slots a landing area needs: ranks * ceil(BN / ranks) over 1..8 ranks
+// the most column slots a landing area needs. Tiles of 16: ranks * ceil(BN / ranks) over 1..8
+// ranks. Wider tiles are split over 1, 2, 4 or 8 ranks only, each owning a multiple of 4 columns.
 constexpr int max_slots(int bn) {
   int m = 0;
   for (int s = 1; s <= MAX_CLUSTER; ++s) {
-    const int v = s * ((bn + s - 1) / s);
+    if (bn >= 32 && (s & (s - 1))) continue;
+    const int per = (bn + s - 1) / s;
+    const int v = s * (bn >= 32 ? ((per + 3) & ~3) : per);
     if (v > m) m = v;
   }
   return m;
@@ -89,6 +92,7 @@ template <int BN, bool DUAL> struct Cfg {
   // that two kernels' CTAs are resident side by side; large tiles take what one CTA can have
   static constexpr bool SMALL = BN <= 64;
   static constexpr bool DEDICATED = BN <= 32;                  // landing area of its own
+  static constexpr bool VEC = BN >= 32;                        // parts travel four columns at a time
   static constexpr int SLOTS = max_slots(BN);
   static constexpr int LAND_BYTES = SLOTS * A_TILES * BM * 4;
   // 84 KB + 126 KB (gate/up pair) = 210 KB: any two small-tile kernels of a layer fit one SM together
@@ -201,7 +205,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   __shared__ int abort_flag;
   __shared__ int never_flag;
   __shared__ float ss_part[NORM ? BN : 1];                 // this rank's sum of h^2 per token of the tile
-  __shared__ float ss_land[NORM ? MAX_CLUSTER * BN : 1];   // [rank][slot]: the ranks' parts for the columns owned here
+  __shared__ __align__(16) float ss_land[NORM ? MAX_CLUSTER * BN : 4];   // [rank][slot]: the ranks' parts for the columns owned here
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -457,8 +461,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 
   if (landing) {
     // ---------------------------------------------------------- the ranks' parts meet at the column's owner
+    // Token tiles of 16: column c belongs to rank c % ranks, one float per store. Wider tiles:
+    // rank r owns the cpr columns from r * cpr (cpr a multiple of 4, ranks a power of two), a
+    // thread's values for four columns travel as one 16-byte store, and the owner reads them
+    // back four at a time.
+    constexpr bool VEC = C::VEC;
     const int ncols = min(BN, p.T - t0);                      // token columns that exist
-    const int cpr = (BN + p.splits - 1) / p.splits;           // column slots per rank in a landing area
+    const int cpr = VEC ? (((BN + p.splits - 1) / p.splits + 3) & ~3) : (BN + p.splits - 1) / p.splits;
     __syncwarp();
     tc_fence_before();
     if (clustered) {
@@ -476,25 +485,42 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         tmem_ld16(taddr + c0, g);
         if (DUAL) tmem_ld16(taddr + BN + c0, u);
         tmem_ld_wait();
+        if constexpr (VEC) {
 #pragma unroll
-        for (int jj = 0; jj < 16; ++jj) {
-          const int c = c0 + jj;
-          if (c < ncols) {
-            const int owner = c % p.splits, slot = c / p.splits;
-            const uint32_t off = (uint32_t)((((rank * cpr + slot) * ACCS) * BM + row) * 4);
-            if (clustered) {
-              const uint32_t dst = map_to_rank(land_cta, (uint32_t)owner) + off;
-              st_cluster_f32(dst, __uint_as_float(g[jj]));
-              if (DUAL) st_cluster_f32(dst + BM * 4, __uint_as_float(u[jj]));
-            } else {
-              land[off / 4] = __uint_as_float(g[jj]);
-              if (DUAL) land[off / 4 + BM] = __uint_as_float(u[jj]);
+          for (int q = 0; q < 4; ++q) {
+            const int c = c0 + 4 * q;
+            if (c < ncols) {
+              const int owner = c / cpr, slot = c % cpr;
+              const uint32_t off = (uint32_t)((((rank * ACCS) * BM + row) * cpr + slot) * 4);
+              const uint32_t dst = (clustered ? map_to_rank(land_cta, (uint32_t)owner) : land_cta) + off;
+              st_cluster_v4(dst, __uint_as_float(g[4 * q]), __uint_as_float(g[4 * q + 1]),
+                            __uint_as_float(g[4 * q + 2]), __uint_as_float(g[4 * q + 3]));
+              if (DUAL) st_cluster_v4(dst + (uint32_t)(BM * cpr * 4), __uint_as_float(u[4 * q]),
+                                      __uint_as_float(u[4 * q + 1]), __uint_as_float(u[4 * q + 2]),
+                                      __uint_as_float(u[4 * q + 3]));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < 16; ++jj) {
+            const int c = c0 + jj;
+            if (c < ncols) {
+              const int owner = c % p.splits, slot = c / p.splits;
+              const uint32_t off = (uint32_t)((((rank * cpr + slot) * ACCS) * BM + row) * 4);
+              if (clustered) {
+                const uint32_t dst = map_to_rank(land_cta, (uint32_t)owner) + off;
+                st_cluster_f32(dst, __uint_as_float(g[jj]));
+                if (DUAL) st_cluster_f32(dst + BM * 4, __uint_as_float(u[jj]));
+              } else {
+                land[off / 4] = __uint_as_float(g[jj]);
+                if (DUAL) land[off / 4 + BM] = __uint_as_float(u[jj]);
+              }
             }
           }
         }
       }
       if (NORM && row < ncols) {
-        const int owner = row % p.splits, slot = row / p.splits;
+        const int owner = VEC ? row / cpr : row % p.splits, slot = VEC ? row % cpr : row / p.splits;
         if (clustered) st_cluster_f32(map_to_rank(smem_u32(&ss_land[rank * BN + slot]), (uint32_t)owner), ss_part[row]);
         else ss_land[slot] = ss_part[row];
       }
@@ -508,33 +534,80 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const int d = n % p.rope.hd, half = p.rope.rot_dim >> 1;
         if (d < p.rope.rot_dim) prow = d < half ? row + half : row - half;
       }
+      if constexpr (VEC) {
 #pragma unroll 1
-      for (int slot = 0; slot * p.splits + rank < ncols; ++slot) {
-        const int t = t0 + slot * p.splits + rank;
-        float g = 0.f, u = 0.f, w = 0.f, ssum = 0.f;
-        if (EPI == EPI_ACCUM_F32 && n < p.N) g = __ldcg((const float*)p.C + (size_t)t * p.ldc + n);   // residual
-        float pg[MAX_CLUSTER], pu[MAX_CLUSTER], pw[MAX_CLUSTER], ps[MAX_CLUSTER];
+        for (int slot = 0; slot < cpr && rank * cpr + slot < ncols; slot += 4) {
+          const int c = rank * cpr + slot;                     // first of four columns owned here
+          float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f}, w[4] = {0.f, 0.f, 0.f, 0.f};
+          float ssum[4] = {0.f, 0.f, 0.f, 0.f};
+          if (EPI == EPI_ACCUM_F32 && n < p.N) {               // the four residual values, loads in flight together
 #pragma unroll
-        for (int s = 0; s < MAX_CLUSTER; ++s) {
-          pg[s] = pu[s] = pw[s] = ps[s] = 0.f;
-          if (s < p.splits) {
-            const float* base = land + (size_t)((s * cpr + slot) * ACCS) * BM;
-            pg[s] = base[row];
-            if (DUAL) pu[s] = base[BM + row];
-            if (ROPE) pw[s] = base[prow];
-            if (NORM) ps[s] = ss_land[s * BN + slot];
+            for (int e = 0; e < 4; ++e)
+              if (c + e < ncols) g[e] = __ldcg((const float*)p.C + (size_t)(t0 + c + e) * p.ldc + n);
+          }
+#pragma unroll
+          for (int s = 0; s < MAX_CLUSTER; ++s) {              // rank order
+            if (s < p.splits) {
+              const float* base = land + (size_t)(s * ACCS) * BM * cpr + slot;
+              const float4 vg = *reinterpret_cast<const float4*>(base + (size_t)row * cpr);
+              g[0] += vg.x; g[1] += vg.y; g[2] += vg.z; g[3] += vg.w;
+              if (DUAL) {
+                const float4 vu = *reinterpret_cast<const float4*>(base + (size_t)(BM + row) * cpr);
+                u[0] += vu.x; u[1] += vu.y; u[2] += vu.z; u[3] += vu.w;
+              }
+              if (ROPE) {
+                const float4 vw = *reinterpret_cast<const float4*>(base + (size_t)prow * cpr);
+                w[0] += vw.x; w[1] += vw.y; w[2] += vw.z; w[3] += vw.w;
+              }
+              if (NORM) {
+                const float4 vs = *reinterpret_cast<const float4*>(&ss_land[s * BN + slot]);
+                ssum[0] += vs.x; ssum[1] += vs.y; ssum[2] += vs.z; ssum[3] += vs.w;
+              }
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int t = t0 + c + e;
+            if (c + e >= ncols || n >= p.N) continue;
+            float ge = g[e], ue = u[e], we = w[e];
+            if (NORM) {
+              const float rs = rsqrtf(ssum[e] * inv_k + p.norm.eps);
+              ge *= rs; ue *= rs; we *= rs;
+            }
+            if (ROPE) emit_rope(p, t, n, ge, we);
+            else if (EPI == EPI_ACCUM_F32) ((float*)p.C)[(size_t)t * p.ldc + n] = ge;   // residual + ranks in order
+            else emit<EPI>(p, t, n, ge, ue);
           }
         }
+      } else {
+#pragma unroll 1
+        for (int slot = 0; slot * p.splits + rank < ncols; ++slot) {
+          const int t = t0 + slot * p.splits + rank;
+          float g = 0.f, u = 0.f, w = 0.f, ssum = 0.f;
+          if (EPI == EPI_ACCUM_F32 && n < p.N) g = __ldcg((const float*)p.C + (size_t)t * p.ldc + n);   // residual
+          float pg[MAX_CLUSTER], pu[MAX_CLUSTER], pw[MAX_CLUSTER], ps[MAX_CLUSTER];
 #pragma unroll
-        for (int s = 0; s < MAX_CLUSTER; ++s) { g += pg[s]; u += pu[s]; w += pw[s]; ssum += ps[s]; }   // rank order
-        if (NORM) {
-          const float rs = rsqrtf(ssum * inv_k + p.norm.eps);
-          g *= rs; u *= rs; w *= rs;
-        }
-        if (n < p.N) {
-          if (ROPE) emit_rope(p, t, n, g, w);
-          else if (EPI == EPI_ACCUM_F32) ((float*)p.C)[(size_t)t * p.ldc + n] = g;   // residual + ranks in order
-          else emit<EPI>(p, t, n, g, u);
+          for (int s = 0; s < MAX_CLUSTER; ++s) {
+            pg[s] = pu[s] = pw[s] = ps[s] = 0.f;
+            if (s < p.splits) {
+              const float* base = land + (size_t)((s * cpr + slot) * ACCS) * BM;
+              pg[s] = base[row];
+              if (DUAL) pu[s] = base[BM + row];
+              if (ROPE) pw[s] = base[prow];
+              if (NORM) ps[s] = ss_land[s * BN + slot];
+            }
+          }
+#pragma unroll
+          for (int s = 0; s < MAX_CLUSTER; ++s) { g += pg[s]; u += pu[s]; w += pw[s]; ssum += ps[s]; }   // rank order
+          if (NORM) {
+            const float rs = rsqrtf(ssum * inv_k + p.norm.eps);
+            g *= rs; u *= rs; w *= rs;
+          }
+          if (n < p.N) {
+            if (ROPE) emit_rope(p, t, n, g, w);
+            else if (EPI == EPI_ACCUM_F32) ((float*)p.C)[(size_t)t * p.ldc + n] = g;   // residual + ranks in order
+            else emit<EPI>(p, t, n, g, u);
+          }
         }
       }
     }
@@ -642,15 +715,28 @@ int launch_bn(int bn, bool norm, const CUtensorMap& mw, const CUtensorMap& mx, c
 
 void plan(int epi, int T, int N, int K, int sm_count, bool allow_split, int* bn_out, int* splits_out) {
   const bool dual = epi == EPI_SWIGLU;
-  int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : (T <= 128 || dual) ? 128 : 256;
-  const int tiles = ((N + BM - 1) / BM) * ((T + bn - 1) / bn);
-  const int kb = (K + BK - 1) / BK;
-  int splits = 1;
-  if (allow_split && tiles * 2 <= sm_count) {
-    splits = sm_count / tiles;                              // one CTA per SM, as far as it goes
-    if (splits > kb / 2) splits = kb / 2;                   // at least two K blocks per range
-    if (splits > MAX_CLUSTER) splits = MAX_CLUSTER;
-    if (splits < 1) splits = 1;
+  const int n_tiles = (N + BM - 1) / BM;
+  int bn, splits = 1;
+  if (T <= 64) {
+    // a step of few tokens: one token tile, and ranges of K until every SM has a CTA
+    bn = T <= 16 ? 16 : T <= 32 ? 32 : 64;
+    const int kb = (K + BK - 1) / BK;
+    if (allow_split && n_tiles * 2 <= sm_count) {
+      splits = sm_count / n_tiles;                            // one CTA per SM, as far as it goes
+      if (splits > kb / 2) splits = kb / 2;                   // at least two K blocks per range
+      if (splits > MAX_CLUSTER) splits = MAX_CLUSTER;
+      if (splits < 1) splits = 1;
+      if (bn >= 32) while (splits & (splits - 1)) splits &= splits - 1;   // wider tiles: a power of two
+    }
+  } else {
+    // more tokens: no ranges of K (a partial tile of 128+ columns costs more to merge than it
+    // saves); the widest token tile that still gives most SMs a CTA, else the narrowest
+    const int widest = dual ? 128 : 256;
+    bn = 64;
+    for (int cand = widest; cand >= 128; cand /= 2) {
+      if (n_tiles * ((T + cand - 1) / cand) * 10 >= sm_count * 8) { bn = cand; break; }
+    }
+    if (bn == 64 && T > 512) bn = 128;                        // long prompts on a narrow weight: fewer re-reads
   }
   *bn_out = bn;
   *splits_out = splits;

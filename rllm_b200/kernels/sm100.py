@@ -2,7 +2,6 @@
 calls. Holds the device error word that a bounded wait sets when it runs out."""
 from __future__ import annotations
 
-import os
 from ctypes import c_float, c_int, c_longlong, c_void_p, POINTER, byref
 
 import torch
@@ -244,14 +243,14 @@ def decode_splits(num_seqs: int, nkv: int, max_kv_len: int, sm_count: int) -> in
     """Ranges the keys of a sequence are cut into (= CTAs per cluster, at most 8). Measured on a
     B200: a CTA costs about as much as 1,150 keys before its first key, two CTAs fit an SM, and
     CTAs beyond that wait for a free place; the number of ranges with the least
-    (CTAs / places, at least 1) x (1,150 + keys per range) is taken."""
+    (rounds of CTAs over the places) x (1,150 + keys per range) is taken."""
     base = max(1, num_seqs * nkv)
-    places = int(os.environ.get('ADEC_PLACES', '2')) * sm_count
+    places = 2 * sm_count
     best, best_cost = 1, None
     for s in range(1, 9):
         if s > 1 and max_kv_len // s < 64:
             break
-        cost = max(1.0, base * s / places) * (1150 + max_kv_len / s)
+        cost = -(-base * s // places) * (1150 + max_kv_len / s)
         if best_cost is None or cost < best_cost:
             best, best_cost = s, cost
     return best
