@@ -233,13 +233,18 @@ def main():
 
     # ---------------------------------------------------------------- end to end, host in/out
     def decode_e2e(B):
-        start_ctx = CONTEXT - (W + K) - 1
-        sp = SamplingParams(temperature=0.0, max_tokens=W + K + 1, ignore_eos=True)
-        for _ in range(B):
-            llm.add_request(rand_ids(start_ctx), sp)
-        produced = 0
-        while produced < B * (W + 1):             # prompts and warm-up decode steps
-            produced += sum(o.token is not None for o in llm.step())
+        # Prompts are admitted over a few steps (the token budget holds two of them), so the
+        # requests get a few tokens of slack: nobody finishes, and the batch keeps its size,
+        # until the timed steps are over. What is left is aborted.
+        slack = B + 8
+        start_ctx = CONTEXT - (W + K) - slack
+        sp = SamplingParams(temperature=0.0, max_tokens=W + K + 2 * slack, ignore_eos=True)
+        rids = [llm.add_request(rand_ids(start_ctx), sp) for _ in range(B)]
+        made = {r: 0 for r in rids}
+        while min(made.values()) < W:             # prompts, then warm-up decode steps of the whole batch
+            for o in llm.step():
+                if o.token is not None:
+                    made[o.request_id] += 1
         torch.cuda.synchronize()
         w0 = time.time()
         n = 0
@@ -248,8 +253,9 @@ def main():
         torch.cuda.synchronize()
         dt = time.time() - w0
         windows.append((w0, time.time()))
-        while llm.has_work():
-            llm.step()
+        assert n == B * K, "the batch changed size inside the timed steps"
+        for r in rids:
+            llm.abort(r)
         return n / dt
     e2e_value = decode_e2e(a.batch) if a.phase == "all" else float("nan")
     meta_ints = 3 * a.batch + 3 * a.batch + 2 + a.batch * (1 + CONTEXT // PAGE + 1)

@@ -18,7 +18,10 @@ pytestmark = pytest.mark.gpu
 # layer boundary (measured up to 1.2e-2 on these models).
 TOL = {"float32": 2e-5, "bfloat16": 3e-2}
 
-LENGTHS = {"A": [5, 11, 17, 40, 70], "B": [3, 9, 24, 40, 97], "C": [6, 33, 58, 90, 121]}
+# D and E have the head sizes of the tensor-core attention kernels; their long requests span
+# several key tiles, key ranges and pages, and a window's edge.
+LENGTHS = {"A": [5, 11, 17, 40, 70], "B": [3, 9, 24, 40, 97], "C": [6, 33, 58, 90, 121],
+           "D": [4, 70, 131, 300, 65], "E": [9, 150, 64, 257, 33]}
 
 
 def requests_for(name):

@@ -31,11 +31,31 @@ TINY_C = {  # 4 layers, 6 heads in 3 groups, head 48 (hidden 80 != heads*head), 
     "layer_types": ["sliding_attention", "full_attention", "sliding_attention", "full_attention"],
 }
 
+TINY_D = {  # head size 64 (the tensor-core attention kernels), 6 heads in 2 groups, hidden 192, untied
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 192, "num_hidden_layers": 2, "num_attention_heads": 6,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 320, "vocab_size": 640,
+    "max_position_embeddings": 1024, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 64},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+}
+TINY_E = {  # head size 128, 4 heads on 1 kv head (group of 4), hidden 136 != heads * head, a window layer
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 136, "num_hidden_layers": 2, "num_attention_heads": 4,
+    "num_key_value_heads": 1, "head_dim": 128, "intermediate_size": 264, "vocab_size": 520,
+    "max_position_embeddings": 1024, "rope_theta": 10000.0, "rope_scaling": None,
+    "rms_norm_eps": 2e-6, "tie_word_embeddings": True, "sliding_window": 80,
+    "layer_types": ["full_attention", "sliding_attention"],
+}
+
 # name -> (config, seed, weight std, norm std, page size)
 TINY = {
     "A": (TINY_A, 0, 0.02, 0.0, 16),
     "B": (TINY_B, 1, 0.05, 0.1, 8),
     "C": (TINY_C, 2, 0.08, 0.2, 4),
+    "D": (TINY_D, 3, 0.04, 0.1, 16),
+    "E": (TINY_E, 4, 0.05, 0.0, 8),
 }
 
 
