@@ -25,24 +25,22 @@ namespace {
 
 constexpr int BN = 64;   // keys per tile
 
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
-  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
-  const int n = valid ? 16 : 0;                         // 0 bytes read: the 16 bytes are zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(n) : "memory");
-}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
-  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+__device__ __forceinline__ void ldsm_addr_x4(uint32_t (&r)[4], uint32_t s) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
-  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+__device__ __forceinline__ void ldsm_addr_x4_trans(uint32_t (&r)[4], uint32_t s) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ float fast_exp2(float x) {          // exp2(-inf) = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -61,7 +59,7 @@ struct FaParams {
   const bf16* kc; const bf16* vc;
   bf16* out; int out_stride;
   const int* cu_q; const int* kv_lens; const int* block_table; int bt_stride;
-  int nh, nkv, page_size, window, splits;
+  int nh, nkv, page_size, page_shift, window, splits;
   float scale_log2e;
   float* part_o;      // [(token * nh + head) * splits + z][HD]
   float* part_ml;     // [(token * nh + head) * splits + z][2]
@@ -83,7 +81,8 @@ fa_paged_kernel(const FaParams p) {
 
   const int seq = blockIdx.z;
   const int kvh = blockIdx.y / p.splits, z = blockIdx.y % p.splits;
-  const int tile = blockIdx.x;
+  // the last rows of a prompt see the most keys: those tiles start first, the short ones fill in behind
+  const int tile = gridDim.x - 1 - blockIdx.x;
   const int G = p.nh / p.nkv;
   const int q0 = p.cu_q[seq];
   const int q_len = p.cu_q[seq + 1] - q0;
@@ -134,21 +133,46 @@ fa_paged_kernel(const FaParams p) {
   for (int i = 0; i < DTILES; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
   float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
 
+  // What the 16 rows of this warp can see (the same for all its lanes): a tile wholly inside is
+  // taken without a mask, a tile wholly outside is not computed at all.
+  const int wrow0 = tile * BM + warp * 16;
+  const bool w_active = wrow0 < rows_total;
+  const int wpos_min = kv_len - q_len + (w_active ? wrow0 / G : 0);
+  const int wpos_max = kv_len - q_len + (w_active ? min(rows_total - 1, wrow0 + 15) / G : 0);
+  const int wlo_min = p.window > 0 ? wpos_min - p.window + 1 : 0;     // smallest first visible key of a row
+  const int wlo_max = p.window > 0 ? wpos_max - p.window + 1 : 0;     // largest
+  const bool rows_full = wrow0 + 15 < rows_total;
+
+  // shared-memory addresses of this lane's ldmatrix rows, swizzle included (they do not depend on the tile)
+  const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(Ks), vs_base = (uint32_t)__cvta_generic_to_shared(Vs);
+  const int mat = lane >> 3, rr = lane & 7;
+  uint32_t koff[KSTEPS], voff[DTILES / 2];
+#pragma unroll
+  for (int kk = 0; kk < KSTEPS; ++kk)
+    koff[kk] = (uint32_t)((((mat >> 1) * 8 + rr) * HD + (((2 * kk + (mat & 1)) ^ rr) * 8)) * 2);
+#pragma unroll
+  for (int dp = 0; dp < DTILES / 2; ++dp)
+    voff[dp] = (uint32_t)((((mat & 1) * 8 + rr) * HD + (((2 * dp + (mat >> 1)) ^ rr) * 8)) * 2);
+
   const int* bt = p.block_table + (size_t)seq * p.bt_stride;
+  const int pshift = p.page_shift;                       // log2(page_size), or < 0 when it is no power of two
   auto load_tile = [&](int t, int buf) {
     const int j0 = kv_begin + t * BN;
-    bf16* kd = Ks + buf * BN * HD;
-    bf16* vd = Vs + buf * BN * HD;
+    const uint32_t kd = ks_base + (uint32_t)(buf * BN * HD * 2), vd = vs_base + (uint32_t)(buf * BN * HD * 2);
+#pragma unroll
     for (int c = threadIdx.x; c < BN * CH; c += NT) {
       const int r = c / CH, ch = c % CH;
       const int j = j0 + r;
       bool ok = j < kv_len;
-      int page = ok ? bt[j / p.page_size] : -1;
+      const int pg = pshift >= 0 ? (j >> pshift) : j / p.page_size;
+      const int off = pshift >= 0 ? (j & (p.page_size - 1)) : j % p.page_size;
+      int page = ok ? __ldg(bt + pg) : -1;
       ok = ok && page >= 0;
-      const size_t src = ok ? ((((size_t)page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * HD + ch * 8) : 0;
-      const int dst = r * HD + ((ch ^ (r & 7)) * 8);
-      cp_async16(kd + dst, p.kc + src, ok);
-      cp_async16(vd + dst, p.vc + src, ok);
+      const size_t src = ok ? ((((size_t)page * p.nkv + kvh) * p.page_size + off) * HD + ch * 8) : 0;
+      const uint32_t dst = (uint32_t)((r * HD + ((ch ^ (r & 7)) * 8)) * 2);
+      const int n = ok ? 16 : 0;                          // 0 bytes read: the 16 bytes are zero-filled
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kd + dst), "l"(p.kc + src), "r"(n) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vd + dst), "l"(p.vc + src), "r"(n) : "memory");
     }
   };
 
@@ -161,76 +185,81 @@ fa_paged_kernel(const FaParams p) {
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    const bf16* kt = Ks + buf * BN * HD;
-    const bf16* vt = Vs + buf * BN * HD;
+    const uint32_t kt = ks_base + (uint32_t)(buf * BN * HD * 2);
+    const uint32_t vt = vs_base + (uint32_t)(buf * BN * HD * 2);
     const int j0 = kv_begin + t * BN;
 
-    // ---- scores S = Q K^T : 16 rows x 64 keys
-    float s[BN / 8][4];
+    if (w_active && j0 <= wpos_max && j0 + BN - 1 >= wlo_min) {
+      // ---- scores S = Q K^T : 16 rows x 64 keys; the K fragments of a k-step are fetched together
+      float s[BN / 8][4];
 #pragma unroll
-    for (int i = 0; i < BN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+      for (int i = 0; i < BN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
 #pragma unroll
-    for (int kk = 0; kk < KSTEPS; ++kk) {
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        uint32_t b[BN / 16][4];
 #pragma unroll
-      for (int nt = 0; nt < BN / 8; nt += 2) {
-        uint32_t b[4];
-        const int mat = lane >> 3, rr = lane & 7;
-        const int row = (nt + (mat >> 1)) * 8 + rr;
-        const int ch = 2 * kk + (mat & 1);
-        ldmatrix_x4(b, kt + row * HD + ((ch ^ (row & 7)) * 8));
-        mma_bf16(s[nt], qf[kk], b[0], b[1]);
-        mma_bf16(s[nt + 1], qf[kk], b[2], b[3]);
+        for (int np = 0; np < BN / 16; ++np) ldsm_addr_x4(b[np], kt + koff[kk] + (uint32_t)(np * 16 * HD * 2));
+#pragma unroll
+        for (int np = 0; np < BN / 16; ++np) {
+          mma_bf16(s[2 * np], qf[kk], b[np][0], b[np][1]);
+          mma_bf16(s[2 * np + 1], qf[kk], b[np][2], b[np][3]);
+        }
       }
-    }
-    // ---- scale, mask, running maximum
-    float mxA = -INFINITY, mxB = -INFINITY;
+      // ---- mask (only a tile at an edge of what the warp sees), running maximum
+      if (j0 + BN - 1 > wpos_min || j0 < wlo_max || !rows_full) {
 #pragma unroll
-    for (int nt = 0; nt < BN / 8; ++nt) {
+        for (int nt = 0; nt < BN / 8; ++nt) {
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int j = j0 + nt * 8 + qi * 2 + e;
-        const bool okA = vA && j <= posA && j >= loA;
-        const bool okB = vB && j <= posB && j >= loB;
-        s[nt][e] = okA ? s[nt][e] * p.scale_log2e : -INFINITY;
-        s[nt][2 + e] = okB ? s[nt][2 + e] * p.scale_log2e : -INFINITY;
-        mxA = fmaxf(mxA, s[nt][e]);
-        mxB = fmaxf(mxB, s[nt][2 + e]);
+          for (int e = 0; e < 2; ++e) {
+            const int j = j0 + nt * 8 + qi * 2 + e;
+            if (!(vA && j <= posA && j >= loA)) s[nt][e] = -INFINITY;
+            if (!(vB && j <= posB && j >= loB)) s[nt][2 + e] = -INFINITY;
+          }
+        }
       }
-    }
-    mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
-    mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
-    mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
-    mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
-    const float mnA = fmaxf(mA, mxA), mnB = fmaxf(mB, mxB);
-    const float useA = (mnA == -INFINITY) ? 0.f : mnA, useB = (mnB == -INFINITY) ? 0.f : mnB;
-    const float corrA = exp2f(mA - useA), corrB = exp2f(mB - useB);     // exp2(-inf) = 0
-    mA = mnA; mB = mnB;
-    lA *= corrA; lB *= corrB;
+      float mxA = -INFINITY, mxB = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < DTILES; ++i) { o[i][0] *= corrA; o[i][1] *= corrA; o[i][2] *= corrB; o[i][3] *= corrB; }
-    // ---- probabilities (as bf16 A fragments) and the weighted sum O += P V
-#pragma unroll
-    for (int kb = 0; kb < BN / 16; ++kb) {
-      uint32_t a[4];
-      {
-        const float p0 = exp2f(s[2 * kb][0] - useA), p1 = exp2f(s[2 * kb][1] - useA);
-        const float p2 = exp2f(s[2 * kb][2] - useB), p3 = exp2f(s[2 * kb][3] - useB);
-        const float p4 = exp2f(s[2 * kb + 1][0] - useA), p5 = exp2f(s[2 * kb + 1][1] - useA);
-        const float p6 = exp2f(s[2 * kb + 1][2] - useB), p7 = exp2f(s[2 * kb + 1][3] - useB);
-        lA += p0 + p1 + p4 + p5;
-        lB += p2 + p3 + p6 + p7;
-        a[0] = pack_bf16(p0, p1); a[1] = pack_bf16(p2, p3);
-        a[2] = pack_bf16(p4, p5); a[3] = pack_bf16(p6, p7);
+      for (int nt = 0; nt < BN / 8; ++nt) {
+        mxA = fmaxf(mxA, fmaxf(s[nt][0], s[nt][1]));
+        mxB = fmaxf(mxB, fmaxf(s[nt][2], s[nt][3]));
       }
+      mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
+      mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+      mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
+      mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+      // the running maximum lives in the exp2 domain (the scale is positive: it commutes with max)
+      const float sl = p.scale_log2e;
+      const float mnA = fmaxf(mA, mxA * sl), mnB = fmaxf(mB, mxB * sl);
+      const float useA = (mnA == -INFINITY) ? 0.f : mnA, useB = (mnB == -INFINITY) ? 0.f : mnB;
+      if (__any_sync(0xffffffffu, mnA != mA || mnB != mB)) {      // a new maximum somewhere: rescale
+        const float corrA = fast_exp2(mA - useA), corrB = fast_exp2(mB - useB);     // exp2(-inf) = 0
+        lA *= corrA; lB *= corrB;
 #pragma unroll
-      for (int dn = 0; dn < DTILES; dn += 2) {
-        uint32_t b[4];
-        const int mat = lane >> 3, rr = lane & 7;
-        const int row = kb * 16 + (mat & 1) * 8 + rr;
-        const int ch = dn + (mat >> 1);
-        ldmatrix_x4_trans(b, vt + row * HD + ((ch ^ (row & 7)) * 8));
-        mma_bf16(o[dn], a, b[0], b[1]);
-        mma_bf16(o[dn + 1], a, b[2], b[3]);
+        for (int i = 0; i < DTILES; ++i) { o[i][0] *= corrA; o[i][1] *= corrA; o[i][2] *= corrB; o[i][3] *= corrB; }
+        mA = mnA; mB = mnB;
+      }
+      // ---- probabilities (as bf16 A fragments) and the weighted sum O += P V
+#pragma unroll
+      for (int kb = 0; kb < BN / 16; ++kb) {
+        uint32_t vb[DTILES / 2][4];
+#pragma unroll
+        for (int dp = 0; dp < DTILES / 2; ++dp) ldsm_addr_x4_trans(vb[dp], vt + voff[dp] + (uint32_t)(kb * 16 * HD * 2));
+        uint32_t a[4];
+        {
+          const float p0 = fast_exp2(fmaf(s[2 * kb][0], sl, -useA)), p1 = fast_exp2(fmaf(s[2 * kb][1], sl, -useA));
+          const float p2 = fast_exp2(fmaf(s[2 * kb][2], sl, -useB)), p3 = fast_exp2(fmaf(s[2 * kb][3], sl, -useB));
+          const float p4 = fast_exp2(fmaf(s[2 * kb + 1][0], sl, -useA)), p5 = fast_exp2(fmaf(s[2 * kb + 1][1], sl, -useA));
+          const float p6 = fast_exp2(fmaf(s[2 * kb + 1][2], sl, -useB)), p7 = fast_exp2(fmaf(s[2 * kb + 1][3], sl, -useB));
+          lA += p0 + p1 + p4 + p5;
+          lB += p2 + p3 + p6 + p7;
+          a[0] = pack_bf16(p0, p1); a[1] = pack_bf16(p2, p3);
+          a[2] = pack_bf16(p4, p5); a[3] = pack_bf16(p6, p7);
+        }
+#pragma unroll
+        for (int dp = 0; dp < DTILES / 2; ++dp) {
+          mma_bf16(o[2 * dp], a, vb[dp][0], vb[dp][1]);
+          mma_bf16(o[2 * dp + 1], a, vb[dp][2], vb[dp][3]);
+        }
       }
     }
     __syncthreads();       // everyone is done with this buffer before it is refilled
@@ -326,6 +355,8 @@ RLLM_API int rllm_attention_fa(const void* q, int q_stride, const void* kcache, 
   p.out = (bf16*)out; p.out_stride = out_stride; p.cu_q = cu_q; p.kv_lens = kv_lens;
   p.block_table = block_table; p.bt_stride = bt_stride; p.nh = nh; p.nkv = nkv; p.page_size = page_size;
   p.window = window; p.splits = splits; p.scale_log2e = scale * 1.4426950408889634f;
+  p.page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0) { p.page_shift = 0; while ((1 << p.page_shift) < page_size) ++p.page_shift; }
   p.part_o = part_o; p.part_ml = part_ml;
   cudaStream_t s = (cudaStream_t)stream;
   const int G = nh / nkv;

@@ -617,6 +617,179 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, C::TMEM_COLS); }
 }
 
+// ---------------------------------------------------------------------------- many tokens
+// The same product for steps of more than 64 tokens (prompt portions). One CTA per SM walks the
+// output tiles (token tiles fastest, so the CTAs of a wave share their weight tiles in L2 and a
+// weight byte comes from DRAM once) and keeps two accumulators in TMEM: while the epilogue warps
+// read tile i out of one, the MMA warp already fills the other with tile i + 1, so the tensor
+// cores do not wait for the epilogue. No ranges of K, no rotary or norm fusion here.
+template <int BN, bool DUAL> struct PCfg {
+  static constexpr int A_TILES = DUAL ? 2 : 1;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int W_BYTES = A_TILES * A_BYTES;
+  static constexpr int STAGE_BYTES = W_BYTES + B_BYTES;
+  static constexpr int STAGES_RAW = 208 * 1024 / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES;
+  static constexpr int ACC_COLS = A_TILES * BN;                 // one accumulator set
+  static constexpr int TMEM_COLS = 2 * ACC_COLS <= 64 ? 64 : 2 * ACC_COLS <= 128 ? 128 : 2 * ACC_COLS <= 256 ? 256 : 512;
+  static_assert(2 * ACC_COLS <= 512, "two accumulator sets must fit in TMEM");
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                          const Params p) {
+  constexpr bool DUAL = (EPI == EPI_SWIGLU);
+  typedef PCfg<BN, DUAL> C;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[C::STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[C::STAGES];
+  __shared__ __align__(8) uint64_t acc_full[2];      // MMA warp -> epilogue: this accumulator set is complete
+  __shared__ __align__(8) uint64_t acc_empty[2];     // epilogue -> MMA warp: it has been read out
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ int never_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int t_tiles = (p.T + BN - 1) / BN, n_tiles = (p.N + BM - 1) / BM;
+  const int tiles = t_tiles * n_tiles;
+  const int n_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    abort_flag = 0;
+    never_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) { prefetch_tensormap(&tmap_w); prefetch_tensormap(&tmap_x); }
+  if (warp == 1) { tmem_alloc(&tmem_base_slot, C::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  pdl_launch();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const uint64_t pol_x = policy_evict_last();    // the token tiles are read by every weight tile
+      pdl_wait();                                    // activations come from the kernel before
+      int it = 0, issued = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const int t0 = (tile % t_tiles) * BN, n0 = (tile / t_tiles) * BM;
+        for (int kb = 0; kb < n_kb; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (uint32_t)(it / C::STAGES) & 1u;
+          if (it >= C::STAGES && !mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag)) {
+            abort_flag = 1; record_failure(p.err, 5); ok = false; break;
+          }
+          uint8_t* st = smem + (size_t)s * C::STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
+          const int k = kb * BK;
+          tma_load_2d(st, &tmap_w, &full_bar[s], k, n0);
+          if (DUAL) tma_load_2d(st + C::A_BYTES, &tmap_w, &full_bar[s], k, p.up_row0 + n0);
+          tma_load_2d_hint(st + C::W_BYTES, &tmap_x, &full_bar[s], k, t0, pol_x);
+          issued = it + 1;
+        }
+      }
+      if (abort_flag) {
+        for (int i = max(0, issued - C::STAGES); i < issued; ++i)
+          mbar_wait(&full_bar[i % C::STAGES], (uint32_t)(i / C::STAGES) & 1u, &never_flag, 200000000LL);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      int it = 0, ti = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++ti) {
+        const int buf = ti & 1, use = ti >> 1;
+        if (use > 0 && !mbar_wait(&acc_empty[buf], (uint32_t)(use - 1) & 1u, &abort_flag)) {
+          abort_flag = 1; record_failure(p.err, 6); ok = false; break;
+        }
+        tc_fence_after();
+        const uint32_t acc_addr = tmem_base + (uint32_t)(buf * C::ACC_COLS);
+        for (int kb = 0; kb < n_kb; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (uint32_t)(it / C::STAGES) & 1u;
+          if (!mbar_wait(&full_bar[s], ph, &abort_flag)) { abort_flag = 1; record_failure(p.err, 2); ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + C::W_BYTES;
+          const uint64_t da = umma_desc_sw128(a_addr);
+          const uint64_t db = umma_desc_sw128(b_addr);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+            const uint64_t koff = (uint64_t)(k * UMMA_K * 2 / 16);
+            umma_bf16(acc_addr, da + koff, db + koff, idesc, acc);
+            if (DUAL) {
+              const uint64_t du = umma_desc_sw128(a_addr + C::A_BYTES);
+              umma_bf16(acc_addr + BN, du + koff, db + koff, idesc, acc);
+            }
+          }
+          umma_commit(&empty_bar[s]);
+        }
+        if (ok) umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps (2..5)
+    const int row = (warp & 3) * 32 + lane;
+    pdl_wait();
+    int ti = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++ti) {
+      const int t0 = (tile % t_tiles) * BN, n0 = (tile / t_tiles) * BM;
+      const int n = n0 + row;
+      const int buf = ti & 1, use = ti >> 1;
+      ok = mbar_wait(&acc_full[buf], (uint32_t)use & 1u, &abort_flag);
+      if (!ok) { abort_flag = 1; record_failure(p.err, 3); }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(buf * C::ACC_COLS);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (t0 + c0 >= p.T) break;
+        uint32_t g[16], u[16];
+        tmem_ld16(taddr + c0, g);
+        if (DUAL) tmem_ld16(taddr + BN + c0, u);
+        tmem_ld_wait();
+        if (n < p.N) {
+          if (EPI == EPI_ACCUM_F32) {
+            float* cp = (float*)p.C + (size_t)(t0 + c0) * p.ldc + n;
+            float r[16];
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) r[jj] = (t0 + c0 + jj < p.T) ? __ldcg(cp + (size_t)jj * p.ldc) : 0.f;
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj)
+              if (t0 + c0 + jj < p.T) cp[(size_t)jj * p.ldc] = r[jj] + __uint_as_float(g[jj]);
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) {
+              const int t = t0 + c0 + jj;
+              if (t < p.T) emit<EPI>(p, t, n, __uint_as_float(g[jj]), DUAL ? __uint_as_float(u[jj]) : 0.f);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);      // this warp's quarter of the set is read out
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, C::TMEM_COLS); }
+}
+
 // ------------------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -686,6 +859,36 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 g
     configured = true;
   }
   return launch_ex(tc_gemm_kernel<BN, EPI, NORM>, grid, dim3(THREADS), C::SMEM_BYTES, s, p.splits, mw, mx, p);
+}
+
+template <int BN, int EPI>
+int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int sm_count, cudaStream_t s) {
+  typedef PCfg<BN, EPI == EPI_SWIGLU> C;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(tc_gemm_persistent_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             C::SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return -5; }
+    configured = true;
+  }
+  const int tiles = ((p.T + BN - 1) / BN) * ((p.N + BM - 1) / BM);
+  const int ctas = tiles < sm_count ? tiles : sm_count;
+  return launch_ex(tc_gemm_persistent_kernel<BN, EPI>, dim3(ctas), dim3(THREADS), C::SMEM_BYTES, s, 1, mw, mx, p);
+}
+
+template <int EPI>
+int launch_many(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int sm_count, cudaStream_t s) {
+  if constexpr (EPI == EPI_QKV_ROPE) {
+    return ERR_BAD_SIZE;
+  } else {
+    switch (bn) {
+      case 64: return launch_persistent<64, EPI>(mw, mx, p, sm_count, s);
+      case 128: return launch_persistent<128, EPI>(mw, mx, p, sm_count, s);
+      case 256:
+        if constexpr (EPI != EPI_SWIGLU) return launch_persistent<256, EPI>(mw, mx, p, sm_count, s);
+        break;
+    }
+    return ERR_BAD_SIZE;
+  }
 }
 
 template <int EPI>
@@ -772,6 +975,15 @@ int run(int epi, const void* X, long long ldx, const NormArgs* norm, const void*
   if (grid.y > 65535) return ERR_TOO_LARGE;
   cudaStream_t s = (cudaStream_t)stream;
   const bool nm = norm != nullptr;
+  if (T > 64 && !nm && epi != EPI_QKV_ROPE && splits == 1) {
+    // many tokens: the persistent kernel with two accumulator sets
+    switch (epi) {
+      case EPI_STORE: return launch_many<EPI_STORE>(bn, mw, mx, p, sm_count, s);
+      case EPI_STORE_F32: return launch_many<EPI_STORE_F32>(bn, mw, mx, p, sm_count, s);
+      case EPI_ACCUM_F32: return launch_many<EPI_ACCUM_F32>(bn, mw, mx, p, sm_count, s);
+      case EPI_SWIGLU: return launch_many<EPI_SWIGLU>(bn, mw, mx, p, sm_count, s);
+    }
+  }
   switch (epi) {
     case EPI_STORE: return launch_bn<EPI_STORE>(bn, nm, mw, mx, p, grid, s);
     case EPI_STORE_F32: return launch_bn<EPI_STORE_F32>(bn, nm, mw, mx, p, grid, s);
