@@ -40,6 +40,12 @@ class RequestCache:
     num_tokens: int = 0
     pages: list[list[int]] = field(default_factory=list)
     state_slot: int = -1
+    # `serial` tells two holdings apart even when a request id comes back (a preempted request is
+    # opened again); `epoch` counts the changes to `pages` other than appending a page (a window
+    # gave pages back, a step that did not run was trimmed). A copy of a block-table row is up to
+    # date when serial, epoch and the page counts are what they were when it was made.
+    serial: int = 0
+    epoch: int = 0
 
 
 def pages_for(tokens: int, page_size: int) -> int:
@@ -97,7 +103,8 @@ class CacheManager:
         if request_id in self.live:
             raise CacheError(f"request {request_id!r} is already open")
         slot = self.slots.alloc(request_id)          # OutOfPages when all slots are taken
-        rc = RequestCache(request_id, 0, [[] for _ in self.groups], slot)
+        self._serial = getattr(self, "_serial", 0) + 1
+        rc = RequestCache(request_id, 0, [[] for _ in self.groups], slot, serial=self._serial)
         for tensors in self.state.values():
             for t in tensors.values():
                 t[slot].zero_()
@@ -125,6 +132,9 @@ class CacheManager:
         """Hold pages for positions [num_tokens, new_total) in every group, or none at all."""
         if new_total < rc.num_tokens:
             raise CacheError("a request cannot shrink")
+        total = pages_for(new_total, self.page_size)
+        if all(len(p) >= total for p in rc.pages):       # the common decode step: the last page has room
+            return
         need = self.pages_needed(rc, new_total)
         for gi, g in enumerate(self.groups):
             if need[gi] > g.pool.num_free:
@@ -139,6 +149,7 @@ class CacheManager:
         keep = pages_for(rc.num_tokens, self.page_size)
         for gi, g in enumerate(self.groups):
             while len(rc.pages[gi]) > keep:
+                rc.epoch += 1
                 page = rc.pages[gi].pop()
                 if page >= 0:
                     g.pool.free(page, rc.request_id)
@@ -149,11 +160,14 @@ class CacheManager:
             raise CacheError("commit beyond the reserved pages")
         rc.num_tokens = new_total
         for gi, g in enumerate(self.groups):
+            if g.spec.window is None:                     # every key is kept: nothing to give back
+                continue
             last = min(self.first_needed_page(g, new_total), len(rc.pages[gi]))
             for i in range(last):
                 if rc.pages[gi][i] >= 0:
                     g.pool.free(rc.pages[gi][i], rc.request_id)
                     rc.pages[gi][i] = -1
+                    rc.epoch += 1
 
     def close(self, request_id) -> None:
         rc = self.live.pop(request_id, None)

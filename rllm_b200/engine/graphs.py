@@ -31,7 +31,7 @@ MAX_GRAPHS = 48
 
 
 class _Slot:
-    __slots__ = ("lay", "host", "dev", "ctx", "rows", "graph", "logits", "copied", "launches")
+    __slots__ = ("lay", "host", "dev", "ctx", "rows", "graph", "logits", "copied", "launches", "bound", "head")
 
 
 class DecodeGraphs:
@@ -76,6 +76,15 @@ class DecodeGraphs:
         slot.ctx.extras.pop("starts_host", None)
         slot.graph = slot.logits = None
         slot.copied = torch.cuda.Event()
+        # what the host buffer's block-table rows hold: per row (holding serial, pages written per
+        # group, epoch); a row is rewritten only when another holding takes it or its pages changed
+        # other than by growing, and otherwise grows as its request does
+        slot.bound = [None] * S
+        slot.head = int(lay.offs[8]) if len(eng.cache.groups) == 1 else lay.total   # ints before the first table
+        host = slot.host.numpy()
+        lay.view(host, 2, S)[:] = np.arange(S, dtype=np.int32)          # token s belongs to sequence s
+        lay.view(host, 3, S + 1)[:] = np.arange(S + 1, dtype=np.int32)  # one row each
+        lay.view(host, 6, S)[:] = np.arange(S, dtype=np.int32)          # logits of every row
         return slot
 
     def _capture(self, slot: _Slot) -> None:
@@ -107,6 +116,38 @@ class DecodeGraphs:
         slot.graph = graph
         self.captures += 1
 
+    def _fill(self, slot: _Slot, entries, rcs) -> bool:
+        """The step's metadata into the slot's host buffer: the vectors of S numbers each step, a
+        block-table row only where it changed. Returns whether a table row was touched."""
+        eng = self.engine
+        lay, ps = slot.lay, eng.cache.page_size
+        S, P, G = lay.S, lay.P, lay.G
+        host = slot.host.numpy()
+        starts = [rc.num_tokens for rc in rcs]
+        lay.view(host, 0, S)[:] = [e.tokens[0] for e in entries]
+        lay.view(host, 1, S)[:] = starts
+        lay.view(host, 4, S)[:] = [n + 1 for n in starts]
+        lay.view(host, 5, S)[:] = [rc.state_slot for rc in rcs]
+        dirty = False
+        for g in range(G):
+            lay.view(host, 7 + 2 * g, S)[:] = [rc.pages[g][n // ps] * ps + n % ps for rc, n in zip(rcs, starts)]
+        for s, rc in enumerate(rcs):
+            b = slot.bound[s]
+            counts = [len(p) for p in rc.pages]
+            same = b is not None and b[0] == rc.serial and b[2] == rc.epoch     # only appended to since
+            if same and b[1] == counts:
+                continue
+            dirty = True
+            for g in range(G):
+                o = int(lay.offs[8 + 2 * g]) + s * P
+                pages = rc.pages[g]
+                done = b[1][g] if same else 0
+                if done == 0:
+                    host[o: o + P] = -1
+                host[o + done: o + len(pages)] = pages[done:]
+            slot.bound[s] = (rc.serial, counts, rc.epoch)
+        return dirty
+
     def run(self, entries, rcs, keep: bool = True) -> torch.Tensor | None:
         eng = self.engine
         S = len(entries)
@@ -120,11 +161,13 @@ class DecodeGraphs:
         else:
             self.slots.move_to_end(key)
         slot.copied.synchronize()               # the last copy out of the host buffer is over
-        host = slot.host.numpy()
-        host.fill(-1)
-        eng.fill_meta(host, slot.lay, entries, rcs)
-        slot.lay.view(host, 6, S)[:] = np.arange(S, dtype=np.int32)   # logits of every row
-        slot.dev.copy_(slot.host, non_blocking=True)
+        dirty = self._fill(slot, entries, rcs)
+        if dirty or slot.head == slot.lay.total:
+            slot.dev.copy_(slot.host, non_blocking=True)
+            eng.h2d_bytes += 4 * slot.lay.total
+        else:                                   # no block table changed: the small vectors only
+            slot.dev[: slot.head].copy_(slot.host[: slot.head], non_blocking=True)
+            eng.h2d_bytes += 4 * slot.head
         slot.copied.record()
         if slot.graph is None:
             self._capture(slot)

@@ -154,6 +154,12 @@ class Scheduler:
         failed: list[StepOutput] = []
         budget = self.max_tokens_per_step
         free = list(self.cache.free_pages())
+        # The steady state of serving: nobody waits, everybody decodes, and even if every request
+        # needed a new page in every group the pools would have them. Same plan as the general
+        # rules below give, without counting pages request by request.
+        if not self.waiting and self.running and len(self.running) <= budget \
+                and all(f >= len(self.running) for f in free) and all(r.decoding for r in self.running):
+            return [Planned(r, [r.output[-1]], True) for r in self.running], failed
         pool = [g.pool.num_pages for g in self.cache.groups]
 
         def fits(need):

@@ -64,6 +64,7 @@ class Engine:
         self._err_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.steps_run = 0
         self.graph_steps = 0
+        self.h2d_bytes = 0            # bytes of step metadata copied to the device so far
         if use_graphs is None:
             use_graphs = os.environ.get("RLLM_B200_NO_GRAPHS") != "1"
         self.graphs = None
@@ -197,6 +198,7 @@ class Engine:
         host = torch.full((lay.total,), -1, dtype=torch.int32).pin_memory()
         self.fill_meta(host.numpy(), lay, entries, rcs)
         dev = host.to(self.device, non_blocking=True)
+        self.h2d_bytes += 4 * lay.total
         return self.make_context(dev, lay, q_lens, kv_lens, starts, [rc.state_slot for rc in rcs])
 
     def step(self, entries: list[Entry], keep: bool = True) -> torch.Tensor | None:
