@@ -27,7 +27,7 @@ CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 # "sm100" the tcgen05/TMA kernels that only the bfloat16 path calls.
 LIBRARIES: dict[str, list[str]] = {
     "simt": ["simt_basic.cu", "simt_gemm.cu", "simt_attention.cu", "sampling.cu"],
-    "sm100": ["tc_gemm.cu", "attn_fa.cu", "attn_decode.cu"],
+    "sm100": ["tc_gemm.cu", "attn_fa.cu", "attn_decode.cu", "attn_prefill_tc.cu"],
 }
 
 NVCC_FLAGS = [

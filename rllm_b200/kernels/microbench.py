@@ -4,7 +4,7 @@ ranges of keys) were tuned with, and the small case a profiler is pointed at.
     python -m rllm_b200.kernels.microbench gemm --shape gateup --tokens 1,8,64
     python -m rllm_b200.kernels.microbench gemm --n 3072 --k 2048 --epilogue store --tokens 2048
     python -m rllm_b200.kernels.microbench attn-decode --batch 64 --context 3000 --splits 1,2,3
-    python -m rllm_b200.kernels.microbench attn-prefill --tokens 2048
+    python -m rllm_b200.kernels.microbench attn-prefill --tokens 2048 --kernel tc
     ... --plain 3      # no timing: three plain launches and a synchronize (for ncu -k ... -c ...)
 
 Timing: the kernel runs back to back over `--copies` distinct weight (or cache) tensors, larger
@@ -122,8 +122,13 @@ def cmd_attn_prefill(a) -> None:
     cu, lens = i32([0, T]), i32([T])
     q = torch.randn(T, nh * hd, device=DEV, dtype=torch.bfloat16)
     out = torch.empty_like(q)
-    f = lambda: sm100.attention_fa(q, kc, vc, cu, lens, bt, T, T, T, nh, hd ** -0.5, None, splits=1, out=out)
-    run([f] * 4, a.plain, f"attn-prefill T={T} heads={nh}/{nkv} hd={hd}", flops=4.0 * nh * hd * T * (T + 1) / 2)
+    if a.kernel == "tc":
+        f = lambda: sm100.attention_prefill_tc(q, kc, vc, cu, lens, bt, T, nh, hd ** -0.5, None, out=out)
+    else:
+        f = lambda: sm100.attention_fa(q, kc, vc, cu, lens, bt, T, T, T, nh, hd ** -0.5, None, splits=1, out=out)
+    run([f] * 4, a.plain, f"attn-prefill ({a.kernel}) T={T} heads={nh}/{nkv} hd={hd}",
+        flops=4.0 * nh * hd * T * (T + 1) / 2)
+    sm100.check_error(DEV)
 
 
 def main(argv=None) -> int:
@@ -153,6 +158,8 @@ def main(argv=None) -> int:
                 p.add_argument("--splits", type=ints, default=None)
             else:
                 p.add_argument("--tokens", type=ints, default=[2048])
+                p.add_argument("--kernel", choices=["tc", "fa"], default="tc",
+                               help="tc: tcgen05 kernel (head size 64); fa: mma.sync kernel")
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("microbench: no CUDA device", file=sys.stderr)

@@ -2,6 +2,7 @@
 calls. Holds the device error word that a bounded wait sets when it runs out."""
 from __future__ import annotations
 
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p, POINTER, byref
 
 import torch
@@ -19,6 +20,8 @@ ops.register_signatures("sm100", {
                               _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P],
     "rllm_attention_fa": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_float, c_int, c_int, _P, _P, _P],
+    "rllm_attention_prefill_tc": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
+                                  c_int, c_float, c_int, _P, _P],
     "rllm_attention_decode": [_P, c_int, _P, _P, c_longlong, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_float, c_int, c_int, _P, _P],
 })
@@ -234,6 +237,31 @@ def attention_fa(q, kcache, vcache, cu_q, kv_lens, block_table, num_tokens, max_
     return out
 
 
+TC_ATTENTION_MIN_KEYS = int(os.environ.get("RLLM_B200_TC_ATTENTION_MIN_KEYS", "4096"))
+
+
+def prefill_tc_supported(q: torch.Tensor, kcache: torch.Tensor) -> bool:
+    return (q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and kcache.shape[3] == 64
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and kcache.data_ptr() % 16 == 0)
+
+
+def attention_prefill_tc(q, kcache, vcache, cu_q, kv_lens, block_table, max_q_len, nh, scale, window, out=None):
+    """Prefill attention on the tcgen05 tensor cores (bf16, head size 64): tiles of 128 rows x 128
+    keys, both products with their accumulators in TMEM."""
+    if not prefill_tc_supported(q, kcache):
+        raise ops.KernelError("attention_prefill_tc: bfloat16, head size 64, rows 16-byte aligned")
+    st = init(q.device)
+    _, nkv, page_size, hd = kcache.shape
+    if out is None:
+        out = torch.empty((q.shape[0], nh * hd), dtype=torch.bfloat16, device=q.device)
+    rc = ops._fn("sm100", "rllm_attention_prefill_tc")(
+        q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(), out.data_ptr(), out.stride(0),
+        cu_q.data_ptr(), kv_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0), kv_lens.numel(),
+        max_q_len, nh, nkv, hd, page_size, float(scale), int(window or 0), st.err.data_ptr(), ops._stream())
+    ops._check(rc, "attention_prefill_tc")
+    return out
+
+
 def decode_supported(q: torch.Tensor, kcache: torch.Tensor, nh: int) -> bool:
     _, nkv, page_size, hd = kcache.shape
     return attention_supported(q, kcache) and nh // nkv <= 16 and kcache.data_ptr() % 16 == 0
@@ -288,5 +316,12 @@ def attention(q, cache, ctx, nh, scale, window):
     if ctx.max_q_len == 1 and decode_supported(q, cache.k, nh):
         return attention_decode(q, cache.k, cache.v, ctx.kv_lens, cache.block_table, nh, scale, window,
                                 ctx.max_kv_len)
+    nkv = cache.k.shape[1]
+    if ctx.max_q_len * (nh // nkv) >= 128 and ctx.max_kv_len >= TC_ATTENTION_MIN_KEYS \
+            and prefill_tc_supported(q, cache.k) and os.environ.get("RLLM_B200_NO_TC_ATTENTION") != "1":
+        # long portions over long contexts: tiles of 128 (token, head) rows x 128 keys on the tcgen05
+        # tensor cores (measured ahead of the mma.sync kernel from about 4,096 keys; behind it below)
+        return attention_prefill_tc(q, cache.k, cache.v, ctx.cu_q, ctx.kv_lens, cache.block_table, ctx.max_q_len,
+                                    nh, scale, window)
     return attention_fa(q, cache.k, cache.v, ctx.cu_q, ctx.kv_lens, cache.block_table, ctx.num_tokens,
                         ctx.max_q_len, ctx.max_kv_len, nh, scale, window)

@@ -16,7 +16,7 @@ def rel(a, b):
     return float((a.float().cpu() - b.float().cpu()).abs().max()) / max(float(b.abs().max()), 1e-30)
 
 
-def run(nh, nkv, hd, page, window, lens, q_lens, splits, far=None):
+def run(nh, nkv, hd, page, window, lens, q_lens, splits, far=None, kernel="fa"):
     from rllm_b200.kernels import sm100
     S = len(lens)
     kc, vc, bt, ks, vs = scattered_cache(S, lens, nkv, hd, page, torch.bfloat16, seed=hd + nh)
@@ -37,8 +37,13 @@ def run(nh, nkv, hd, page, window, lens, q_lens, splits, far=None):
     buf = torch.zeros(T, (nh + 2 * nkv) * hd, dtype=torch.bfloat16)
     buf[:, : nh * hd] = q.reshape(T, nh * hd)
     bufd = buf.to(DEV)
-    out = sm100.attention_fa(bufd[:, : nh * hd], kc.to(DEV), vc.to(DEV), i32(cu), i32(lens), bt.to(DEV), T,
-                             max(q_lens), max(lens), nh, hd ** -0.5, window, splits=splits)
+    if kernel == "tc":
+        out = sm100.attention_prefill_tc(bufd[:, : nh * hd], kc.to(DEV), vc.to(DEV), i32(cu), i32(lens), bt.to(DEV),
+                                         max(q_lens), nh, hd ** -0.5, window)
+        sm100.check_error(DEV)
+    else:
+        out = sm100.attention_fa(bufd[:, : nh * hd], kc.to(DEV), vc.to(DEV), i32(cu), i32(lens), bt.to(DEV), T,
+                                 max(q_lens), max(lens), nh, hd ** -0.5, window, splits=splits)
     row = 0
     for s in range(S):
         L, n = lens[s], q_lens[s]
@@ -118,6 +123,17 @@ def test_decode_kernel_with_cluster_merge(splits, nh, nkv, hd, page, window):
     again = sm100.attention_decode(bufd[:, : nh * hd], kc.to(DEV), vc.to(DEV), i32(lens), bt.to(DEV), nh,
                                    hd ** -0.5, window, max(lens), splits=splits)
     assert torch.equal(out, again)
+
+
+@pytest.mark.parametrize("nh,nkv,page,window", [(32, 8, 16, None), (6, 2, 8, None), (3, 1, 5, None), (8, 8, 16, 200),
+                                                (4, 1, 32, 70)])
+def test_prefill_on_tcgen05(nh, nkv, page, window):
+    """The tcgen05 prefill kernel (head size 64) against the plain formula: portions that start
+    in the middle of what the cache holds, lengths on both sides of the 128-row and 128-key
+    tiles, a decode token and a two-token portion in the same launch, windows, and a far key
+    that must dominate its row."""
+    run(nh, nkv, 64, page, window, lens=[300, 517, 1, 130, 128, 700, 40], q_lens=[300, 260, 1, 2, 128, 129, 40],
+        splits=1, far=(1, 11) if window is None else None, kernel="tc")
 
 
 def test_long_prompt_whole_and_chosen_splits():
