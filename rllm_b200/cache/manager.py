@@ -8,6 +8,8 @@ that ends return at once and are handed out again. State layers (`StateSpec`) ge
 per live request from a slot pool, zeroed when the request opens; Llama has none, the pool
 then has no tensors.
 
+The bookkeeping (pools, tables, state slots) is native: csrc/host_runtime.cpp.
+
 Tensor layout per KV layer: K and V each [pages, kv_heads, page_size, head_dim], so that
 one (page, head) is a contiguous [page_size, head_dim] tile.
 Parity: src/model/kv_cache.rs:725-947 (pool), 949-1091 (per-sequence table) of the
@@ -15,12 +17,15 @@ reference; the grouping replaces its `kv_layer_map` (src/model/config.rs:1293-13
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from ..parts.base import KVCacheSpec, LayerCache, StateSpec
-from .pages import CacheError, OutOfPages, PagePool
+from .native import lib
+from .pages import CacheError, Holders, OutOfPages, PagePool
 
 
 @dataclass
@@ -32,20 +37,48 @@ class CacheGroup:
     v: dict[int, torch.Tensor] = field(default_factory=dict)
 
 
-@dataclass
 class RequestCache:
-    """What one live request holds. `pages[g][i]` is the page of positions
-    [i*page_size, (i+1)*page_size) in group g, or -1 once a window has passed it."""
-    request_id: object
-    num_tokens: int = 0
-    pages: list[list[int]] = field(default_factory=list)
-    state_slot: int = -1
-    # `serial` tells two holdings apart even when a request id comes back (a preempted request is
-    # opened again); `epoch` counts the changes to `pages` other than appending a page (a window
-    # gave pages back, a step that did not run was trimmed). A copy of a block-table row is up to
-    # date when serial, epoch and the page counts are what they were when it was made.
-    serial: int = 0
-    epoch: int = 0
+    """What one live request holds; the numbers live in the native tables, this object names
+    them. `pages[g][i]` is the page of positions [i*page_size, (i+1)*page_size) in group g, or
+    -1 once a window has passed it. `serial` tells two holdings apart even when a request id
+    comes back (a preempted request is opened again); `epoch` counts the changes to the tables
+    other than appending a page."""
+    __slots__ = ("_m", "request_id", "handle")
+
+    def __init__(self, manager, request_id, handle: int):
+        self._m, self.request_id, self.handle = manager, request_id, handle
+
+    @property
+    def state_slot(self) -> int:
+        return self.handle
+
+    @property
+    def num_tokens(self) -> int:
+        return self._m._L.cache_num_tokens(self._m._ptr, self.handle) if self.handle >= 0 else 0
+
+    @property
+    def serial(self) -> int:
+        return self._m._L.cache_serial(self._m._ptr, self.handle)
+
+    @property
+    def epoch(self) -> int:
+        return self._m._L.cache_epoch(self._m._ptr, self.handle)
+
+    def num_held(self, group: int) -> int:
+        """Entries of the block table of `group` (given-back pages included)."""
+        return self._m._L.cache_num_held(self._m._ptr, self.handle, group) if self.handle >= 0 else 0
+
+    def pages_array(self, group: int) -> np.ndarray:
+        if self.handle < 0:
+            return np.empty(0, dtype=np.int32)
+        n = self.num_held(group)
+        out = np.empty(max(n, 1), dtype=np.int32)
+        self._m._L.cache_pages(self._m._ptr, self.handle, group, out.ctypes.data, n)
+        return out[:n]
+
+    @property
+    def pages(self) -> list[list[int]]:
+        return [self.pages_array(g).tolist() for g in range(len(self._m.groups))]
 
 
 def pages_for(tokens: int, page_size: int) -> int:
@@ -63,21 +96,36 @@ class CacheManager:
         self.layer_group: dict[int, int] = {}
         self.state_layers: dict[int, StateSpec] = {}
         self.state: dict[int, dict[str, torch.Tensor]] = {}
+        group_specs: list[KVCacheSpec] = []
+        group_layers: list[list[int]] = []
         for layer, spec in enumerate(specs):
             if isinstance(spec, KVCacheSpec):
-                for gi, g in enumerate(self.groups):
-                    if g.spec == spec:
-                        g.layers.append(layer)
+                for gi, gs in enumerate(group_specs):
+                    if gs == spec:
+                        group_layers[gi].append(layer)
                         self.layer_group[layer] = gi
                         break
                 else:
-                    self.layer_group[layer] = len(self.groups)
-                    self.groups.append(CacheGroup(spec, [layer], PagePool(num_pages)))
+                    self.layer_group[layer] = len(group_specs)
+                    group_specs.append(spec)
+                    group_layers.append([layer])
             elif isinstance(spec, StateSpec):
                 self.state_layers[layer] = spec
             elif spec is not None:
                 raise TypeError(f"cache layer {layer}: unknown spec {spec!r}")
-        self.slots = PagePool(max_requests)
+        # the native tables: one pool per group, the state slots, every holding
+        self._L = lib()
+        G = len(group_specs)
+        counts = (ctypes.c_int * max(G, 1))(*([num_pages] * G))
+        windows = (ctypes.c_int * max(G, 1))(*[(-1 if gs.window is None else gs.window) for gs in group_specs])
+        self._ptr = self._L.cache_new(G, counts, windows, page_size, max_requests)
+        if not self._ptr:
+            raise ValueError("the native cache tables could not be made")
+        self.holders = Holders()
+        for gi, (gs, layers) in enumerate(zip(group_specs, group_layers)):
+            pool = PagePool(num_pages, _ptr=self._L.cache_pool(self._ptr, gi), _holders=self.holders, _owner=self)
+            self.groups.append(CacheGroup(gs, layers, pool))
+        self.slots = PagePool(max_requests, _ptr=self._L.cache_slots(self._ptr), _holders=self.holders, _owner=self)
         if allocate:
             for g in self.groups:
                 shape = (num_pages, g.spec.kv_heads, page_size, g.spec.head_dim)
@@ -89,6 +137,11 @@ class CacheManager:
                                      for name, shape, dt in spec.tensors}
         self.live: dict[object, RequestCache] = {}
 
+    def __del__(self):
+        if getattr(self, "_ptr", None):
+            self._L.cache_delete(self._ptr)
+            self._ptr = None
+
     # ------------------------------------------------------------ sizes
     @staticmethod
     def bytes_per_page(specs: list, page_size: int, dtype: torch.dtype) -> int:
@@ -98,16 +151,26 @@ class CacheManager:
     def free_pages(self) -> list[int]:
         return [g.pool.num_free for g in self.groups]
 
+    @staticmethod
+    def _raise(rc: int, what: str):
+        if rc <= -10:
+            raise CacheError(f"{what}: the pool refused a release (code {rc + 10}): a page was freed twice "
+                             f"or is held by another request")
+        raise CacheError(f"{what}: no such holding" if rc == -9 else f"{what}: code {rc}")
+
     # ------------------------------------------------------------ request life cycle
     def open(self, request_id) -> RequestCache:
         if request_id in self.live:
             raise CacheError(f"request {request_id!r} is already open")
-        slot = self.slots.alloc(request_id)          # OutOfPages when all slots are taken
-        self._serial = getattr(self, "_serial", 0) + 1
-        rc = RequestCache(request_id, 0, [[] for _ in self.groups], slot, serial=self._serial)
+        handle = self._L.cache_open(self._ptr, self.holders.key(request_id))
+        if handle == -1:
+            raise OutOfPages("no free state slot")          # all slots are taken
+        if handle < 0:
+            self._raise(handle, "open")
+        rc = RequestCache(self, request_id, handle)
         for tensors in self.state.values():
             for t in tensors.values():
-                t[slot].zero_()
+                t[handle].zero_()
         self.live[request_id] = rc
         return rc
 
@@ -120,70 +183,55 @@ class CacheManager:
 
     def pages_needed(self, rc: RequestCache, new_total: int) -> list[int]:
         """Additional pages per group to hold positions [0, new_total)."""
-        return [max(0, pages_for(new_total, self.page_size) - len(rc.pages[gi]))
-                for gi in range(len(self.groups))]
+        total = pages_for(new_total, self.page_size)
+        return [max(0, total - rc.num_held(gi)) for gi in range(len(self.groups))]
+
+    def held_pages(self, rc: RequestCache) -> list[int]:
+        """Pages per group the request really holds (given-back entries not counted)."""
+        return [int((rc.pages_array(gi) >= 0).sum()) for gi in range(len(self.groups))]
 
     def can_reserve(self, rc: RequestCache | None, new_total: int) -> bool:
-        have = [len(p) for p in rc.pages] if rc is not None else [0] * len(self.groups)
-        need = pages_for(new_total, self.page_size)
-        return all(need - have[gi] <= g.pool.num_free for gi, g in enumerate(self.groups))
+        return bool(self._L.cache_can_reserve(self._ptr, rc.handle if rc is not None else -1, new_total))
 
     def reserve(self, rc: RequestCache, new_total: int) -> None:
         """Hold pages for positions [num_tokens, new_total) in every group, or none at all."""
-        if new_total < rc.num_tokens:
-            raise CacheError("a request cannot shrink")
-        total = pages_for(new_total, self.page_size)
-        if all(len(p) >= total for p in rc.pages):       # the common decode step: the last page has room
+        code = self._L.cache_reserve(self._ptr, rc.handle, new_total)
+        if code == 0:
             return
-        need = self.pages_needed(rc, new_total)
-        for gi, g in enumerate(self.groups):
-            if need[gi] > g.pool.num_free:
-                raise OutOfPages(f"group {gi} needs {need[gi]} pages, {g.pool.num_free} free")
-        for gi, g in enumerate(self.groups):
-            for _ in range(need[gi]):
-                rc.pages[gi].append(g.pool.alloc(rc.request_id))
+        if code == -1:
+            raise OutOfPages(f"not enough free pages for {new_total} positions ({self.free_pages()} free)")
+        if code == -2:
+            raise CacheError("a request cannot shrink")
+        self._raise(code, "reserve")
 
     def trim(self, rc: RequestCache) -> None:
         """Give back pages reserved beyond what the stored positions need (a step that
         did not run)."""
-        keep = pages_for(rc.num_tokens, self.page_size)
-        for gi, g in enumerate(self.groups):
-            while len(rc.pages[gi]) > keep:
-                rc.epoch += 1
-                page = rc.pages[gi].pop()
-                if page >= 0:
-                    g.pool.free(page, rc.request_id)
+        code = self._L.cache_trim(self._ptr, rc.handle)
+        if code:
+            self._raise(code, "trim")
 
     def commit(self, rc: RequestCache, new_total: int) -> None:
         """The step stored positions up to new_total; give back what a window has passed."""
-        if pages_for(new_total, self.page_size) > min((len(p) for p in rc.pages), default=10 ** 9):
+        code = self._L.cache_commit(self._ptr, rc.handle, new_total)
+        if code == -2:
             raise CacheError("commit beyond the reserved pages")
-        rc.num_tokens = new_total
-        for gi, g in enumerate(self.groups):
-            if g.spec.window is None:                     # every key is kept: nothing to give back
-                continue
-            last = min(self.first_needed_page(g, new_total), len(rc.pages[gi]))
-            for i in range(last):
-                if rc.pages[gi][i] >= 0:
-                    g.pool.free(rc.pages[gi][i], rc.request_id)
-                    rc.pages[gi][i] = -1
-                    rc.epoch += 1
+        if code:
+            self._raise(code, "commit")
 
     def close(self, request_id) -> None:
         rc = self.live.pop(request_id, None)
         if rc is None:
             raise CacheError(f"request {request_id!r} is not open")
-        for gi, g in enumerate(self.groups):
-            for page in rc.pages[gi]:
-                if page >= 0:
-                    g.pool.free(page, request_id)
-            rc.pages[gi] = []
-        self.slots.free(rc.state_slot, request_id)
-        rc.state_slot = -1
+        code = self._L.cache_close(self._ptr, rc.handle)
+        rc.handle = -1
+        self.holders.forget(request_id)
+        if code:
+            self._raise(code, "close")
 
     # ------------------------------------------------------------ for the step function
     def slot_of(self, rc: RequestCache, gi: int, position: int) -> int:
-        page = rc.pages[gi][position // self.page_size]
+        page = int(rc.pages_array(gi)[position // self.page_size])
         if page < 0:
             raise CacheError(f"position {position} lies in a page that was given back")
         return page * self.page_size + position % self.page_size
@@ -199,18 +247,12 @@ class CacheManager:
     # ------------------------------------------------------------ checks (tests, debug)
     def check(self) -> None:
         """No page lost, held twice or freed twice; holders are live requests."""
-        for gi, g in enumerate(self.groups):
-            g.pool.check()
-            held = {}
-            for rc in self.live.values():
-                for page in rc.pages[gi]:
-                    if page < 0:
-                        continue
-                    if page in held:
-                        raise CacheError(f"group {gi}: page {page} held by {held[page]!r} and {rc.request_id!r}")
-                    held[page] = rc.request_id
-                    if g.pool.owner(page) != rc.request_id:
-                        raise CacheError(f"group {gi}: page {page} in a table but not held")
-            if len(held) + g.pool.num_free != g.pool.num_pages:
-                raise CacheError(f"group {gi}: {g.pool.num_pages - len(held) - g.pool.num_free} pages lost")
-        self.slots.check()
+        code = self._L.cache_check(self._ptr)
+        if code == 0:
+            return
+        if code >= 1000:
+            raise CacheError("the state slots' free list and holders disagree")
+        gi, what = code // 100 - 1, code % 100
+        names = {4: "a table names a page that does not exist", 5: "a page is in two tables",
+                 6: "a page is in a table but not held by that request", 7: "pages are lost"}
+        raise CacheError(f"group {gi}: {names.get(what, 'the free list and the holders disagree')}")

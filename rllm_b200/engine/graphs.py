@@ -31,7 +31,13 @@ MAX_GRAPHS = 48
 
 
 class _Slot:
-    __slots__ = ("lay", "host", "dev", "ctx", "rows", "graph", "logits", "copied", "launches", "bound", "head")
+    __slots__ = ("lay", "host", "dev", "ctx", "rows", "graph", "logits", "copied", "launches", "head", "handles", "tokens", "rows_state",
+                 "_lib")
+
+    def __del__(self):
+        rs, L = getattr(self, "rows_state", None), getattr(self, "_lib", None)
+        if rs and L is not None:
+            L.rows_delete(rs)
 
 
 class DecodeGraphs:
@@ -47,7 +53,7 @@ class DecodeGraphs:
 
     def _width(self, rcs) -> int:
         G = len(self.engine.cache.groups)
-        need = max((len(rc.pages[g]) for rc in rcs for g in range(G)), default=1)
+        need = max((rc.num_held(g) for rc in rcs for g in range(G)), default=1)
         p = 8
         while p < need:
             p *= 2
@@ -76,10 +82,12 @@ class DecodeGraphs:
         slot.ctx.extras.pop("starts_host", None)
         slot.graph = slot.logits = None
         slot.copied = torch.cuda.Event()
-        # what the host buffer's block-table rows hold: per row (holding serial, pages written per
-        # group, epoch); a row is rewritten only when another holding takes it or its pages changed
-        # other than by growing, and otherwise grows as its request does
-        slot.bound = [None] * S
+        # the native writer remembers what the host buffer's block-table rows hold: a row is
+        # rewritten only when another holding takes it or its pages changed other than by growing
+        slot._lib = eng.cache._L
+        slot.rows_state = slot._lib.rows_new(S, len(eng.cache.groups))
+        slot.handles = np.zeros(S, dtype=np.int32)
+        slot.tokens = np.zeros(S, dtype=np.int32)
         slot.head = int(lay.offs[8]) if len(eng.cache.groups) == 1 else lay.total   # ints before the first table
         host = slot.host.numpy()
         lay.view(host, 2, S)[:] = np.arange(S, dtype=np.int32)          # token s belongs to sequence s
@@ -117,36 +125,18 @@ class DecodeGraphs:
         self.captures += 1
 
     def _fill(self, slot: _Slot, entries, rcs) -> bool:
-        """The step's metadata into the slot's host buffer: the vectors of S numbers each step, a
-        block-table row only where it changed. Returns whether a table row was touched."""
-        eng = self.engine
-        lay, ps = slot.lay, eng.cache.page_size
-        S, P, G = lay.S, lay.P, lay.G
-        host = slot.host.numpy()
-        starts = [rc.num_tokens for rc in rcs]
-        lay.view(host, 0, S)[:] = [e.tokens[0] for e in entries]
-        lay.view(host, 1, S)[:] = starts
-        lay.view(host, 4, S)[:] = [n + 1 for n in starts]
-        lay.view(host, 5, S)[:] = [rc.state_slot for rc in rcs]
-        dirty = False
-        for g in range(G):
-            lay.view(host, 7 + 2 * g, S)[:] = [rc.pages[g][n // ps] * ps + n % ps for rc, n in zip(rcs, starts)]
-        for s, rc in enumerate(rcs):
-            b = slot.bound[s]
-            counts = [len(p) for p in rc.pages]
-            same = b is not None and b[0] == rc.serial and b[2] == rc.epoch     # only appended to since
-            if same and b[1] == counts:
-                continue
-            dirty = True
-            for g in range(G):
-                o = int(lay.offs[8 + 2 * g]) + s * P
-                pages = rc.pages[g]
-                done = b[1][g] if same else 0
-                if done == 0:
-                    host[o: o + P] = -1
-                host[o + done: o + len(pages)] = pages[done:]
-            slot.bound[s] = (rc.serial, counts, rc.epoch)
-        return dirty
+        """The step's metadata into the slot's host buffer (the native writer: the vectors of S
+        numbers each step, a block-table row only where it changed). Returns whether a table row
+        was touched."""
+        cache = self.engine.cache
+        S = slot.lay.S
+        slot.handles[:] = [rc.handle for rc in rcs]
+        slot.tokens[:] = [e.tokens[0] for e in entries]
+        rc = cache._L.fill_decode(cache._ptr, slot.rows_state, S, slot.handles.ctypes.data, slot.tokens.ctypes.data,
+                                  slot.lay.P, slot.host.data_ptr(), slot.lay.offs.ctypes.data)
+        if rc < 0:
+            raise RuntimeError(f"decode metadata could not be written (code {rc})")
+        return rc > 0
 
     def run(self, entries, rcs, keep: bool = True) -> torch.Tensor | None:
         eng = self.engine

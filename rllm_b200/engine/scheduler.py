@@ -117,13 +117,13 @@ class Scheduler:
     def _need(self, req: Request, n_new: int) -> list[int]:
         rc = self.cache.live.get(req.request_id)
         total = pages_for(req.num_stored + n_new, self.cache.page_size)
-        return [max(0, total - (len(rc.pages[g]) if rc else 0)) for g in range(len(self.cache.groups))]
+        return [max(0, total - (rc.num_held(g) if rc else 0)) for g in range(len(self.cache.groups))]
 
     def _held(self, req: Request) -> list[int]:
         rc = self.cache.live.get(req.request_id)
         if rc is None:
             return [0] * len(self.cache.groups)
-        return [sum(1 for p in pages if p >= 0) for pages in rc.pages]
+        return self.cache.held_pages(rc)
 
     def _release(self, req: Request, executor) -> None:
         if req.request_id in self.cache.live:

@@ -161,7 +161,7 @@ class Engine:
                 rows[r] = q0 + w
                 r += 1
             for g in range(G):
-                pages = np.asarray(rc.pages[g], dtype=np.int32)
+                pages = rc.pages_array(g)
                 o = int(lay.offs[8 + 2 * g]) + s * P
                 host[o: o + len(pages)] = pages
                 p = pos[q0:q0 + q]
@@ -193,7 +193,7 @@ class Engine:
         q_lens = [len(e.tokens) for e in entries]
         starts = [rc.num_tokens for rc in rcs]
         kv_lens = [s + q for s, q in zip(starts, q_lens)]
-        P = max(1, max((len(rc.pages[g]) for rc in rcs for g in range(G)), default=1))
+        P = max(1, max((rc.num_held(g) for rc in rcs for g in range(G)), default=1))
         lay = MetaLayout(sum(q_lens), len(entries), P, sum(len(e.want) for e in entries), G)
         host = torch.full((lay.total,), -1, dtype=torch.int32).pin_memory()
         self.fill_meta(host.numpy(), lay, entries, rcs)

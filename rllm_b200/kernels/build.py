@@ -24,10 +24,12 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 
 # library name -> sources. "simt" holds the generic kernels of both precisions;
-# "sm100" the tcgen05/TMA kernels that only the bfloat16 path calls.
+# "sm100" the tcgen05/TMA kernels that only the bfloat16 path calls; "host" the native
+# bookkeeping of the cache manager (plain C++, no device code).
 LIBRARIES: dict[str, list[str]] = {
     "simt": ["simt_basic.cu", "simt_gemm.cu", "simt_attention.cu", "sampling.cu"],
     "sm100": ["tc_gemm.cu", "attn_fa.cu", "attn_decode.cu", "attn_prefill_tc.cu"],
+    "host": ["host_runtime.cpp"],          # no CUDA: the cache manager's bookkeeping and metadata writer
 }
 
 NVCC_FLAGS = [
@@ -125,7 +127,7 @@ def build_library(name: str, verbose_ptxas: bool = False) -> str:
     if os.path.isfile(so) and not jobs:
         return so
     if jobs:
-        _say(f"compiling {len(jobs)} CUDA file(s) of '{name}' for sm_100a into {libdir} "
+        _say(f"compiling {len(jobs)} source file(s) of '{name}' for sm_100a into {libdir} "
              f"(first use only)")
 
         def one(job):
