@@ -135,3 +135,76 @@ def test_random_orders_keep_every_page_accounted(seed):
         m.close(rid)
     m.check()
     assert m.free_pages() == [12, 12] and reused
+
+
+def test_native_decode_metadata_rows_follow_their_holdings():
+    """The native writer of a decode step's metadata: the vectors are right every step, and a
+    block-table row is rewritten exactly when it has to be: when it grew, when another holding
+    took the row (also one with the same request id, after a close), and when a window gave
+    pages back; otherwise the call reports that no row was touched."""
+    import numpy as np
+    from rllm_b200.engine.step import MetaLayout
+    m = manager([FULL, WIN], pages=16, page=4, reqs=4)
+    L, P, S, G = m._L, 8, 2, 2
+    lay = MetaLayout(S, S, P, S, G)
+    host = np.full(lay.total, -7, dtype=np.int32)
+    rows = L.rows_new(S, G)
+    handles, tokens = np.zeros(S, dtype=np.int32), np.zeros(S, dtype=np.int32)
+
+    def fill(rcs, toks):
+        handles[:] = [rc.handle for rc in rcs]
+        tokens[:] = toks
+        return L.fill_decode(m._ptr, rows, S, handles.ctypes.data, tokens.ctypes.data, P, host.ctypes.data,
+                             lay.offs.ctypes.data)
+
+    def table(g):
+        return lay.view(host, 8 + 2 * g, S * P).reshape(S, P)
+
+    def expect(rcs):
+        for s, rc in enumerate(rcs):
+            n = rc.num_tokens
+            assert lay.view(host, 1, S)[s] == n and lay.view(host, 4, S)[s] == n + 1
+            assert lay.view(host, 5, S)[s] == rc.state_slot
+            for g in range(G):
+                pages = rc.pages[g]
+                assert list(table(g)[s, : len(pages)]) == pages and all(table(g)[s, len(pages):] == -1)
+                assert lay.view(host, 7 + 2 * g, S)[s] == pages[n // 4] * 4 + n % 4
+
+    a, b = m.open("a"), m.open("b")
+    for rc, n in ((a, 6), (b, 3)):
+        m.reserve(rc, n); m.commit(rc, n)
+    for rc in (a, b):
+        m.reserve(rc, rc.num_tokens + 1)
+    assert fill([a, b], [11, 12]) == 1 and list(lay.view(host, 0, S)) == [11, 12]
+    expect([a, b])
+    for rc in (a, b):
+        m.commit(rc, rc.num_tokens + 1)
+    # next token: b crosses a page edge (4), a does not (7): the row of b grows, a's stays
+    for rc in (a, b):
+        m.reserve(rc, rc.num_tokens + 1)
+    assert fill([a, b], [13, 14]) == 1
+    expect([a, b])
+    m.commit(a, 8); m.commit(b, 5)
+    m.reserve(a, 9); m.reserve(b, 6)
+    assert fill([a, b], [1, 2]) == 1          # a crossed to its third page
+    expect([a, b])
+    m.commit(a, 9); m.commit(b, 6)
+    m.reserve(a, 10); m.reserve(b, 7)
+    assert fill([a, b], [3, 4]) == 0          # nobody grew, nobody changed: no row touched
+    expect([a, b])
+    # the window (10 keys) passes a's first page: its epoch moves, its rows are rewritten with -1 in front
+    for n in range(10, 15):
+        m.commit(a, n); m.reserve(a, n + 1)
+    assert a.pages[1][0] == -1 and fill([a, b], [5, 6]) == 1
+    expect([a, b])
+    # b ends; a request with the same id takes the same row and slot: the row is written afresh
+    m.close("b")
+    b2 = m.open("b")
+    m.reserve(b2, 2); m.commit(b2, 1)
+    assert fill([a, b2], [7, 8]) == 1
+    expect([a, b2])
+    # a token without a page is refused, not written past the table
+    m.reserve(b2, 4); m.commit(b2, 4)         # its one page is full and no page is reserved for position 4
+    assert fill([a, b2], [9, 9]) < 0
+    L.rows_delete(rows)
+    m.check()
