@@ -68,7 +68,10 @@ constexpr int MAX_CLUSTER = 8;
 #ifndef SMALL_DUAL_KB
 #define SMALL_DUAL_KB 126
 #endif
-constexpr int NORM_MAX_T = 64;        // the fused-norm variants take steps of at most this many tokens
+#ifndef NORM_MAX_TOKENS
+#define NORM_MAX_TOKENS 64
+#endif
+constexpr int NORM_MAX_T = NORM_MAX_TOKENS;        // the fused-norm variants take steps of at most this many tokens
 
 // the most column slots a landing area needs. Tiles of 16: ranks * ceil(BN / ranks) over 1..8
 // ranks. Wider tiles are split over 1, 2, 4 or 8 ranks only, each owning a multiple of 4 columns.
@@ -642,6 +645,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                           const Params p) {
   constexpr bool DUAL = (EPI == EPI_SWIGLU);
+  constexpr bool ROPE = (EPI == EPI_QKV_ROPE);
   typedef PCfg<BN, DUAL> C;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[C::STAGES];
@@ -651,6 +655,10 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ int never_flag;
+  // rotary epilogue: a row's pair partner lies 16+ rows away, in another warp's TMEM lanes; the
+  // epilogue warps pass 16 columns at a time through this buffer (two halves, used in turn)
+  __shared__ float xch[ROPE ? 2 * 16 * BM : 1];
+  __shared__ int epi_fail;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -663,6 +671,7 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
     for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
     abort_flag = 0;
     never_flag = 0;
+    epi_fail = 0;
     fence_barrier_init();
   }
   if (warp == 0 && lane == 0) { prefetch_tensormap(&tmap_w); prefetch_tensormap(&tmap_x); }
@@ -752,8 +761,18 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
       ok = mbar_wait(&acc_full[buf], (uint32_t)use & 1u, &abort_flag);
       if (!ok) { abort_flag = 1; record_failure(p.err, 3); }
       ok = __all_sync(0xffffffffu, ok);
+      if (ROPE) {                                        // the four warps leave together or not at all
+        if (!ok) epi_fail = 1;
+        epilogue_warps_sync();
+        ok = epi_fail == 0;
+      }
       if (!ok) break;
       tc_fence_after();
+      int prow = row;                                    // the pair partner of this row (same tile: heads do not straddle tiles)
+      if (ROPE) {
+        const int d = n % p.rope.hd, half = p.rope.rot_dim >> 1;
+        if (d < p.rope.rot_dim) prow = d < half ? row + half : row - half;
+      }
       const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(buf * C::ACC_COLS);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -762,7 +781,19 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
         tmem_ld16(taddr + c0, g);
         if (DUAL) tmem_ld16(taddr + BN + c0, u);
         tmem_ld_wait();
-        if (n < p.N) {
+        if (ROPE) {
+          float* xb = xch + ((c0 >> 4) & 1) * 16 * BM;
+#pragma unroll
+          for (int jj = 0; jj < 16; ++jj) xb[jj * BM + row] = __uint_as_float(g[jj]);
+          epilogue_warps_sync();
+          if (n < p.N) {
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) {
+              const int t = t0 + c0 + jj;
+              if (t < p.T) emit_rope(p, t, n, __uint_as_float(g[jj]), xb[jj * BM + prow]);
+            }
+          }
+        } else if (n < p.N) {
           if (EPI == EPI_ACCUM_F32) {
             float* cp = (float*)p.C + (size_t)(t0 + c0) * p.ldc + n;
             float r[16];
@@ -877,18 +908,14 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const Params
 
 template <int EPI>
 int launch_many(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int sm_count, cudaStream_t s) {
-  if constexpr (EPI == EPI_QKV_ROPE) {
-    return ERR_BAD_SIZE;
-  } else {
-    switch (bn) {
-      case 64: return launch_persistent<64, EPI>(mw, mx, p, sm_count, s);
-      case 128: return launch_persistent<128, EPI>(mw, mx, p, sm_count, s);
-      case 256:
-        if constexpr (EPI != EPI_SWIGLU) return launch_persistent<256, EPI>(mw, mx, p, sm_count, s);
-        break;
-    }
-    return ERR_BAD_SIZE;
+  switch (bn) {
+    case 64: return launch_persistent<64, EPI>(mw, mx, p, sm_count, s);
+    case 128: return launch_persistent<128, EPI>(mw, mx, p, sm_count, s);
+    case 256:
+      if constexpr (EPI != EPI_SWIGLU) return launch_persistent<256, EPI>(mw, mx, p, sm_count, s);
+      break;
   }
+  return ERR_BAD_SIZE;
 }
 
 template <int EPI>
@@ -975,13 +1002,14 @@ int run(int epi, const void* X, long long ldx, const NormArgs* norm, const void*
   if (grid.y > 65535) return ERR_TOO_LARGE;
   cudaStream_t s = (cudaStream_t)stream;
   const bool nm = norm != nullptr;
-  if (T > 64 && !nm && epi != EPI_QKV_ROPE && splits == 1) {
+  if (T > 64 && !nm && splits == 1) {
     // many tokens: the persistent kernel with two accumulator sets
     switch (epi) {
       case EPI_STORE: return launch_many<EPI_STORE>(bn, mw, mx, p, sm_count, s);
       case EPI_STORE_F32: return launch_many<EPI_STORE_F32>(bn, mw, mx, p, sm_count, s);
       case EPI_ACCUM_F32: return launch_many<EPI_ACCUM_F32>(bn, mw, mx, p, sm_count, s);
       case EPI_SWIGLU: return launch_many<EPI_SWIGLU>(bn, mw, mx, p, sm_count, s);
+      case EPI_QKV_ROPE: return launch_many<EPI_QKV_ROPE>(bn, mw, mx, p, sm_count, s);
     }
   }
   switch (epi) {

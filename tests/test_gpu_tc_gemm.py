@@ -117,6 +117,7 @@ def test_plan_splits_small_batches_only():
     assert sm100.plan(ops.EPI_ACCUM_F32, 64, 2048, 8192) == (64, 8)
     assert sm100.plan(ops.EPI_STORE, 8, 3072, 2048, split=False) == (16, 1)
     assert sm100.plan(ops.EPI_STORE, 2048, 3072, 2048) == (256, 1)
+    assert sm100.plan(ops.EPI_ACCUM_F32, 2048, 2048, 8192) == (256, 1)
     assert sm100.plan(ops.EPI_SWIGLU, 2048, 8192, 2048) == (128, 1)
     assert sm100.plan(ops.EPI_STORE_F32, 8, 128256, 2048) == (16, 1)
 
