@@ -1,7 +1,7 @@
 // Prefill attention over the paged bfloat16 cache on the 5th-generation tensor cores (tcgen05),
 // head size 64: both products of a tile run as UMMA with their accumulators in TMEM.
 //
-// A CTA owns 128 rows, (query token, query head) pairs of ONE kv head (row r of a sequence is
+// A work item is 128 rows, (query token, query head) pairs of ONE kv head (row r of a sequence is
 // token r / G, head kvh*G + r % G, as in the mma.sync kernel), and walks the keys the rows can
 // see in tiles of 128:
 //   warps 0..3  fetch the Q rows once and the K and V tiles through the block table with
@@ -59,6 +59,7 @@ struct PfParams {
   bf16* out; int out_stride;
   const int* cu_q; const int* kv_lens; const int* block_table; int bt_stride;
   int nh, nkv, page_size, page_shift, window;
+  int row_tiles, num_seqs, sm_count;
   float scale_log2e;
   int* err;
 };
@@ -99,17 +100,8 @@ attn_prefill_tc_kernel(const PfParams p) {
   const uint32_t q_s = smem_u32(smem);
   const uint32_t k_s = q_s + TILE_BYTES, v_s = k_s + KVS * TILE_BYTES, p_s = v_s + KVS * TILE_BYTES;
 
-  const int seq = blockIdx.z, kvh = blockIdx.y;
-  const int tile = gridDim.x - 1 - blockIdx.x;          // the rows that see the most keys start first
   const int G = p.nh / p.nkv;
-
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < KVS; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4 * SPLIT); mbar_init(&pv_full[i], 1); }
-    abort_flag = 0;
-    for (int i = 0; i < 4; ++i) pair_fail[i] = 0;
-    fence_barrier_init();
-  }
+  if (threadIdx.x == 0) abort_flag = 0;
   if (warp == MMA_WARP) { tmem_alloc(&tmem_base_slot, TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
@@ -118,12 +110,32 @@ attn_prefill_tc_kernel(const PfParams p) {
   pdl_wait();                                           // q and the newest keys come from the kernel before
   const uint32_t tmem_base = tmem_base_slot;
 
+  // The CTAs (one per SM) share the (row tile, kv head, sequence) items out among themselves:
+  // items are numbered from the row tiles that see the most keys down, and round r gives CTA c
+  // item r * C + c, or r * C + (C - 1 - c) in odd rounds, so that every CTA gets a like share of
+  // long and short ones.
+  const int items = p.row_tiles * p.nkv * p.num_seqs;
+  for (int round = 0;; ++round) {
+  const int item = round * (int)gridDim.x + ((round & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
+  if (item >= items) break;
+  const int tile = p.row_tiles - 1 - item / (p.nkv * p.num_seqs);
+  const int kvh = item % p.nkv, seq = (item / p.nkv) % p.num_seqs;
+  __syncthreads();                                      // everybody has left the item before
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < KVS; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4 * SPLIT); mbar_init(&pv_full[i], 1); }
+    for (int i = 0; i < 4; ++i) pair_fail[i] = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (abort_flag) break;                                // a wait ran out in an earlier item: the kernel's output is void anyway
+
   const int q0 = p.cu_q[seq];
   const int q_len = p.cu_q[seq + 1] - q0;
   const int kv_len = p.kv_lens[seq];
   const int rows_total = q_len * G;
-  const bool cta_active = tile * PM < rows_total;       // uniform: a CTA beyond the sequence's rows only frees its TMEM
-  // keys this CTA's rows can see at all
+  const bool cta_active = tile * PM < rows_total;       // uniform: an item beyond the sequence's rows is empty
+  // keys this item's rows can see at all
   const int tok_first = (tile * PM) / G;
   const int tok_last = min(q_len - 1, (tile * PM + PM - 1) / G);
   const int p_min = kv_len - q_len + tok_first, p_max = kv_len - q_len + tok_last;
@@ -226,6 +238,11 @@ attn_prefill_tc_kernel(const PfParams p) {
         umma_commit(&kv_empty[t % KVS]);                // K and V of this stage are read
         umma_commit(&pv_full[s]);
       }
+      // nothing of this item may still be on its way to a barrier when the next item sets them up again
+      for (int t = max(0, n_tiles - KVS); t < n_tiles && ok; ++t)
+        if (!mbar_wait(&kv_empty[t % KVS], (uint32_t)(t / KVS) & 1u, &abort_flag)) {
+          abort_flag = 1; record_failure(p.err, 26, t); ok = false;
+        }
     }
   } else if (n_tiles > 0) {
     // ------------------------------------------------------------ softmax warps
@@ -364,6 +381,7 @@ attn_prefill_tc_kernel(const PfParams p) {
       }
     }
   }
+  }   // items
   tc_fence_before();
   __syncthreads();
   if (warp == MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
@@ -373,12 +391,13 @@ attn_prefill_tc_kernel(const PfParams p) {
 
 // q: [T, ...] bf16 rows with stride q_stride, head h at h*64; out likewise (16-byte aligned rows).
 // kcache / vcache: [pages][nkv][page_size][64] bf16. cu_q [S+1], kv_lens [S], block_table [S, bt_stride].
-// max_q_len: the longest portion in the batch (sizes the grid). Head size 64 only.
+// max_q_len: the longest portion in the batch (sizes the list of work items). Head size 64 only.
+// sm_count: CTAs to launch at most (0: asked from the device).
 RLLM_API int rllm_attention_prefill_tc(const void* q, int q_stride, const void* kcache, const void* vcache,
                                        void* out, int out_stride, const int* cu_q, const int* kv_lens,
                                        const int* block_table, int bt_stride, int num_seqs, int max_q_len,
                                        int nh, int nkv, int hd, int page_size, float scale, int window,
-                                       int* err, void* stream) {
+                                       int* err, int sm_count, void* stream) {
   if (num_seqs <= 0 || max_q_len <= 0) return 0;
   if (hd != HD || nkv <= 0 || nh % nkv || page_size <= 0) return ERR_BAD_SIZE;
   if (q_stride % 8 || out_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
@@ -397,7 +416,17 @@ RLLM_API int rllm_attention_prefill_tc(const void* q, int q_stride, const void* 
   if ((page_size & (page_size - 1)) == 0) { p.page_shift = 0; while ((1 << p.page_shift) < page_size) ++p.page_shift; }
   p.window = window; p.scale_log2e = scale * 1.4426950408889634f; p.err = err;
   const int G = nh / nkv;
-  dim3 grid((max_q_len * G + PM - 1) / PM, nkv, num_seqs);
-  if (grid.y > 65535 || grid.z > 65535) return ERR_TOO_LARGE;
-  return launch_ex(attn_prefill_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, 1, p);
+  p.row_tiles = (max_q_len * G + PM - 1) / PM; p.num_seqs = num_seqs;
+  const long long items = (long long)p.row_tiles * nkv * num_seqs;
+  if (items > 2147483647LL) return ERR_TOO_LARGE;
+  int sms = sm_count;
+  if (sms <= 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+      cudaGetLastError();
+      return -5;
+    }
+  }
+  const int ctas = items < sms ? (int)items : sms;
+  return launch_ex(attn_prefill_tc_kernel, dim3(ctas), dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, 1, p);
 }

@@ -21,7 +21,7 @@ ops.register_signatures("sm100", {
     "rllm_attention_fa": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_float, c_int, c_int, _P, _P, _P],
     "rllm_attention_prefill_tc": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
-                                  c_int, c_float, c_int, _P, _P],
+                                  c_int, c_float, c_int, _P, c_int, _P],
     "rllm_attention_decode": [_P, c_int, _P, _P, c_longlong, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_float, c_int, c_int, _P, _P],
 })
@@ -237,7 +237,7 @@ def attention_fa(q, kcache, vcache, cu_q, kv_lens, block_table, num_tokens, max_
     return out
 
 
-TC_ATTENTION_MIN_KEYS = int(os.environ.get("RLLM_B200_TC_ATTENTION_MIN_KEYS", "4096"))
+TC_ATTENTION_MIN_KEYS = int(os.environ.get("RLLM_B200_TC_ATTENTION_MIN_KEYS", "2048"))
 
 
 def prefill_tc_supported(q: torch.Tensor, kcache: torch.Tensor) -> bool:
@@ -257,7 +257,8 @@ def attention_prefill_tc(q, kcache, vcache, cu_q, kv_lens, block_table, max_q_le
     rc = ops._fn("sm100", "rllm_attention_prefill_tc")(
         q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(), out.data_ptr(), out.stride(0),
         cu_q.data_ptr(), kv_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0), kv_lens.numel(),
-        max_q_len, nh, nkv, hd, page_size, float(scale), int(window or 0), st.err.data_ptr(), ops._stream())
+        max_q_len, nh, nkv, hd, page_size, float(scale), int(window or 0), st.err.data_ptr(), st.sm_count,
+        ops._stream())
     ops._check(rc, "attention_prefill_tc")
     return out
 
@@ -320,7 +321,7 @@ def attention(q, cache, ctx, nh, scale, window):
     if ctx.max_q_len * (nh // nkv) >= 128 and ctx.max_kv_len >= TC_ATTENTION_MIN_KEYS \
             and prefill_tc_supported(q, cache.k) and os.environ.get("RLLM_B200_NO_TC_ATTENTION") != "1":
         # long portions over long contexts: tiles of 128 (token, head) rows x 128 keys on the tcgen05
-        # tensor cores (measured ahead of the mma.sync kernel from about 4,096 keys; behind it below)
+        # tensor cores (measured level with the mma.sync kernel at 2,048 keys, ahead of it beyond, behind it below)
         return attention_prefill_tc(q, cache.k, cache.v, ctx.cu_q, ctx.kv_lens, cache.block_table, ctx.max_q_len,
                                     nh, scale, window)
     return attention_fa(q, cache.k, cache.v, ctx.cu_q, ctx.kv_lens, cache.block_table, ctx.num_tokens,
