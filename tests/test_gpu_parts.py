@@ -58,6 +58,37 @@ def test_rmsnorm_part(dtype):
     assert rel(part.forward(x.to(DEV), ctx), P.rms_norm(x, part.weight.float().cpu(), 3e-6)) <= TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", list(DT))
+def test_deferred_norm_is_the_same_norm(dtype):
+    """`RMSNorm.deferred` hands a consumer the norm to run inside its own first product. On the
+    32-bit path it is computed at once (the very tensor `forward` gives); on the serving path it
+    stays deferred, the product that takes it matches norm-then-product within bfloat16
+    rounding, chosen rows included, and `tensor()` is bit for bit the norm kernel's output."""
+    from rllm_b200.kernels.backend import Normed
+    from rllm_b200.parts import RMSNorm
+    part = RMSNorm(192, 1e-5)
+    part.weight = (1 + rnd(192, seed=1, scale=0.2)).to(DT[dtype]).to(DEV)
+    h = Harness(dtype, [])
+    ctx, _ = h.context([("a", 7)])
+    x = rnd(7, 192, seed=2, scale=4.0).to(DEV)
+    w = (rnd(320, 192, seed=3, scale=192 ** -0.5)).to(DT[dtype]).to(DEV)
+    plain = part.forward(x, ctx)
+    d = part.deferred(x, ctx)
+    be = ctx.backend
+    if dtype == "float32":
+        assert torch.equal(d, plain)
+        return
+    assert isinstance(d, Normed) and d.shape == (7, 192)
+    want = P.rms_norm(x.float().cpu(), part.weight.float().cpu(), 1e-5) @ w.float().cpu().t()
+    assert rel(be.linear(d, w), want) <= TOL[dtype]                     # fused: norm inside the product
+    assert d._tensor is None                                            # ... and nothing was materialised
+    assert rel(be.linear_f32(part.deferred(x, ctx), w), want) <= TOL[dtype]
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    assert rel(be.linear_f32(part.deferred(x, ctx, rows), w), want[[6, 0, 3]]) <= TOL[dtype]
+    assert torch.equal(d.tensor(), plain) and d.tensor() is d.tensor()  # the norm kernel's own output, once
+    assert torch.equal(part.deferred(x, ctx, rows).tensor(), plain[rows.long()])
+
+
 def test_rotary_part_tables_follow_the_scaling_rule():
     from rllm_b200.config.llama import RopeScaling
     from rllm_b200.parts import RotaryEmbedding
