@@ -214,6 +214,59 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ p
   }
 }
 
+// The same for bfloat16 with whole heads rotated (rot_dim == hd, hd a multiple of 16) and the
+// step's table of angles: eight pairs per thread, 16-byte loads and stores.
+__global__ void rope_cache_vec_kernel(bf16* __restrict__ qkv, const float2* __restrict__ cos_sin,
+                                      const int* __restrict__ slots, bf16* __restrict__ kcache,
+                                      bf16* __restrict__ vcache, int nh, int nkv, int hd, int page_size) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int half = hd / 2, cph = half / 8;             // chunks of eight pairs per head
+  bf16* row = qkv + (size_t)t * (nh + 2 * nkv) * hd;
+  const int slot = slots ? slots[t] : -1;
+  const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+  const float2* cs_row = cos_sin + (size_t)t * half;
+  for (int idx = threadIdx.x; idx < (nh + nkv) * cph; idx += blockDim.x) {
+    const int head = idx / cph, c = idx % cph;
+    bf16* hp = row + (size_t)head * hd + 8 * c;
+    const uint4 ra = *reinterpret_cast<const uint4*>(hp), rb = *reinterpret_cast<const uint4*>(hp + half);
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&ra);
+    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&rb);
+    const float4* cs4 = reinterpret_cast<const float4*>(cs_row + 8 * c);     // (cos, sin) pairs, two per float4
+    uint4 oa, ob;
+    uint32_t* oa32 = reinterpret_cast<uint32_t*>(&oa);
+    uint32_t* ob32 = reinterpret_cast<uint32_t*>(&ob);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float4 cs = cs4[e];                         // pair 2e: (x, y), pair 2e + 1: (z, w)
+      const float a0 = __low2float(a2[e]), a1 = __high2float(a2[e]);
+      const float b0 = __low2float(b2[e]), b1 = __high2float(b2[e]);
+      const __nv_bfloat162 na = __floats2bfloat162_rn(a0 * cs.x - b0 * cs.y, a1 * cs.z - b1 * cs.w);
+      const __nv_bfloat162 nb = __floats2bfloat162_rn(a0 * cs.y + b0 * cs.x, a1 * cs.w + b1 * cs.z);
+      oa32[e] = *reinterpret_cast<const uint32_t*>(&na);
+      ob32[e] = *reinterpret_cast<const uint32_t*>(&nb);
+    }
+    if (head < nh) {
+      *reinterpret_cast<uint4*>(hp) = oa;
+      *reinterpret_cast<uint4*>(hp + half) = ob;
+    } else if (slot >= 0) {
+      bf16* dst = kcache + (((size_t)page * nkv + (head - nh)) * page_size + off) * hd + 8 * c;
+      *reinterpret_cast<uint4*>(dst) = oa;
+      *reinterpret_cast<uint4*>(dst + half) = ob;
+    }
+  }
+  if (slot >= 0) {
+    const bf16* vrow = row + (size_t)(nh + nkv) * hd;
+    const int vph = hd / 8;
+    for (int idx = threadIdx.x; idx < nkv * vph; idx += blockDim.x) {
+      const int kvh = idx / vph, c = idx % vph;
+      *reinterpret_cast<uint4*>(vcache + (((size_t)page * nkv + kvh) * page_size + off) * hd + 8 * c) =
+          *reinterpret_cast<const uint4*>(vrow + (size_t)kvh * hd + 8 * c);
+    }
+  }
+}
+
 // cos_sin: the table of rllm_rope_table for these positions ([T][rot_dim / 2] float2), or null.
 RLLM_API int rllm_rope_cache_write(void* qkv, int dt, const int* positions, const float* inv_freq,
                                    const void* cos_sin, const int* slots, void* kcache, void* vcache, int T, int nh,
@@ -224,6 +277,11 @@ RLLM_API int rllm_rope_cache_write(void* qkv, int dt, const int* positions, cons
   int rc = 0;
   const int work = (nh + nkv) * hd / 2;
   const int threads = work >= 512 ? 256 : (work >= 128 ? 128 : 64);
+  const bool aligned = (((uintptr_t)qkv | (uintptr_t)cos_sin) & 15) == 0 &&
+                       (!slots || (((uintptr_t)kcache | (uintptr_t)vcache) & 15) == 0);
+  if (dt == DT_BF16 && cos_sin && rot_dim == hd && hd % 16 == 0 && aligned)
+    return launch_ex(rope_cache_vec_kernel, dim3(T), dim3(128), 0, s, 1, (bf16*)qkv, (const float2*)cos_sin, slots,
+                     (bf16*)kcache, (bf16*)vcache, nh, nkv, hd, page_size);
   if (dt == DT_F32)
     rc = launch_ex(rope_cache_kernel<float>, dim3(T), dim3(threads), 0, s, 1, (float*)qkv, positions, inv_freq, (const float2*)cos_sin, slots,
                                                    (float*)kcache, (float*)vcache, nh, nkv, hd,
