@@ -94,7 +94,8 @@ template <int BN, bool DUAL> struct Cfg {
   // token tiles up to 64 (decode, small mixed steps) stay under half an SM's shared memory so
   // that two kernels' CTAs are resident side by side; large tiles take what one CTA can have
   static constexpr bool SMALL = BN <= 64;
-  static constexpr bool DEDICATED = BN <= 32;                  // landing area of its own
+  // landing area of its own (the gate/up pair at 32 tokens would be left with two stages: it lands in the ring)
+  static constexpr bool DEDICATED = BN <= 16 || (BN == 32 && !DUAL);
   static constexpr bool VEC = BN >= 32;                        // parts travel four columns at a time
   static constexpr int SLOTS = max_slots(BN);
   static constexpr int LAND_BYTES = SLOTS * A_TILES * BM * 4;
@@ -926,7 +927,6 @@ int launch_bn(int bn, bool norm, const CUtensorMap& mw, const CUtensorMap& mx, c
       switch (bn) {
         case 16: return launch<16, EPI, true>(mw, mx, p, grid, s);
         case 32: return launch<32, EPI, true>(mw, mx, p, grid, s);
-        case 64: return launch<64, EPI, true>(mw, mx, p, grid, s);
       }
     }
     return ERR_BAD_SIZE;
@@ -934,11 +934,6 @@ int launch_bn(int bn, bool norm, const CUtensorMap& mw, const CUtensorMap& mx, c
   switch (bn) {
     case 16: return launch<16, EPI, false>(mw, mx, p, grid, s);
     case 32: return launch<32, EPI, false>(mw, mx, p, grid, s);
-    case 64: return launch<64, EPI, false>(mw, mx, p, grid, s);
-    case 128: return launch<128, EPI, false>(mw, mx, p, grid, s);
-    case 256:
-      if constexpr (EPI != EPI_SWIGLU) return launch<256, EPI, false>(mw, mx, p, grid, s);
-      break;
   }
   return ERR_BAD_SIZE;
 }
@@ -948,8 +943,8 @@ void plan(int epi, int T, int N, int K, int sm_count, bool allow_split, int* bn_
   const int n_tiles = (N + BM - 1) / BM;
   int bn, splits = 1;
   if (T <= 64) {
-    // a step of few tokens: one token tile, and ranges of K until every SM has a CTA
-    bn = T <= 16 ? 16 : T <= 32 ? 32 : 64;
+    // a step of few tokens: one or two token tiles, and ranges of K until every SM has a CTA
+    bn = T <= 16 ? 16 : 32;     // 33 to 64 tokens: two tiles of 32 land their parts faster than one of 64
     const int kb = (K + BK - 1) / BK;
     if (allow_split && n_tiles * 2 <= sm_count) {
       splits = sm_count / n_tiles;                            // one CTA per SM, as far as it goes

@@ -114,7 +114,7 @@ def test_plan_splits_small_batches_only():
     from rllm_b200.kernels import ops, sm100
     bn, splits = sm100.plan(ops.EPI_STORE, 8, 3072, 2048)
     assert bn == 16 and 2 <= splits <= 8                 # 24 tiles: a cluster of ranges of K per tile
-    assert sm100.plan(ops.EPI_ACCUM_F32, 64, 2048, 8192) == (64, 8)
+    assert sm100.plan(ops.EPI_ACCUM_F32, 64, 2048, 8192) == (32, 8)      # two tiles of 32 tokens
     assert sm100.plan(ops.EPI_STORE, 8, 3072, 2048, split=False) == (16, 1)
     assert sm100.plan(ops.EPI_STORE, 2048, 3072, 2048) == (256, 1)
     assert sm100.plan(ops.EPI_ACCUM_F32, 2048, 2048, 8192) == (256, 1)
