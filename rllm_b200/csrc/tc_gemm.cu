@@ -214,8 +214,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
 
-  const int n0 = blockIdx.x * BM;          // first weight row / output feature of the tile
-  const int t0 = blockIdx.y * BN;          // first token of the tile
+  // token tiles are the fastest grid index: the CTAs that share a weight tile start together and
+  // all but the first find it in L2
+  const int n0 = blockIdx.y * BM;          // first weight row / output feature of the tile
+  const int t0 = blockIdx.x * BN;          // first token of the tile
   const bool clustered = p.splits > 1;
   const bool landing = clustered || ROPE;  // the epilogue goes through the landing area
   const int rank = clustered ? (int)cluster_rank() : 0;
@@ -993,7 +995,7 @@ int run(int epi, const void* X, long long ldx, const NormArgs* norm, const void*
   p.C = Cout; p.ldc = (int)ldc; p.T = T; p.N = N; p.K = K; p.up_row0 = N; p.splits = splits; p.err = err;
   p.rope = rope ? *rope : RopeArgs{};
   p.norm = norm ? *norm : NormArgs{};
-  dim3 grid((N + BM - 1) / BM, (T + bn - 1) / bn, splits);
+  dim3 grid((T + bn - 1) / bn, (N + BM - 1) / BM, splits);
   if (grid.y > 65535) return ERR_TOO_LARGE;
   cudaStream_t s = (cudaStream_t)stream;
   const bool nm = norm != nullptr;
