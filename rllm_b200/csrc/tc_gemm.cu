@@ -944,20 +944,24 @@ void plan(int epi, int T, int N, int K, int sm_count, bool allow_split, int* bn_
   const bool dual = epi == EPI_SWIGLU;
   const int n_tiles = (N + BM - 1) / BM;
   int bn, splits = 1;
-  if (T <= 64) {
-    // a step of few tokens: one or two token tiles, and ranges of K until every SM has a CTA
-    bn = T <= 16 ? 16 : 32;     // 33 to 64 tokens: two tiles of 32 land their parts faster than one of 64
-    const int kb = (K + BK - 1) / BK;
-    if (allow_split && n_tiles * 2 <= sm_count) {
-      splits = sm_count / n_tiles;                            // one CTA per SM, as far as it goes
-      if (splits > kb / 2) splits = kb / 2;                   // at least two K blocks per range
-      if (splits > MAX_CLUSTER) splits = MAX_CLUSTER;
-      if (splits < 1) splits = 1;
-      if (bn >= 32) while (splits & (splits - 1)) splits &= splits - 1;   // wider tiles: a power of two
-    }
+  const int kb = (K + BK - 1) / BK;
+  if (allow_split && n_tiles * 2 <= sm_count) {
+    splits = sm_count / n_tiles;                              // one CTA per SM, as far as it goes
+    if (splits > kb / 2) splits = kb / 2;                     // at least two K blocks per range
+    if (splits > MAX_CLUSTER) splits = MAX_CLUSTER;
+    if (splits < 1) splits = 1;
+  }
+  // A step of few tokens: token tiles of 16 or 32 (33 to 64 tokens: two tiles of 32 land their
+  // parts faster than one of 64), and ranges of K until every SM has a CTA. Up to 128 tokens the
+  // same holds for a narrow weight that would give the persistent kernel under a quarter of the SMs.
+  const bool few = T <= 64 || (T <= 128 && splits > 1 && n_tiles * ((T + 63) / 64) * 4 <= sm_count);
+  if (few) {
+    bn = T <= 16 ? 16 : 32;
+    if (bn >= 32) while (splits & (splits - 1)) splits &= splits - 1;     // wider tiles: a power of two
   } else {
     // more tokens: no ranges of K (a partial tile of 128+ columns costs more to merge than it
     // saves); the widest token tile that still gives most SMs a CTA, else the narrowest
+    splits = 1;
     const int widest = dual ? 128 : 256;
     bn = 64;
     for (int cand = widest; cand >= 128; cand /= 2) {
@@ -999,7 +1003,7 @@ int run(int epi, const void* X, long long ldx, const NormArgs* norm, const void*
   if (grid.y > 65535) return ERR_TOO_LARGE;
   cudaStream_t s = (cudaStream_t)stream;
   const bool nm = norm != nullptr;
-  if (T > 64 && !nm && splits == 1) {
+  if (bn >= 64) {
     // many tokens: the persistent kernel with two accumulator sets
     switch (epi) {
       case EPI_STORE: return launch_many<EPI_STORE>(bn, mw, mx, p, sm_count, s);

@@ -17,7 +17,7 @@ def rel(a, b):
 
 
 SHAPES = [(1, 128, 64), (8, 384, 200), (16, 100, 72), (17, 3072, 2048), (64, 2048, 2048), (100, 640, 520),
-          (128, 256, 8192), (300, 1000, 264), (1, 128256, 256), (8, 2048, 8192), (600, 512, 1024)]
+          (128, 256, 8192), (65, 2048, 4096), (96, 200, 1024), (300, 1000, 264), (1, 128256, 256), (8, 2048, 8192), (600, 512, 1024)]
 
 
 @pytest.mark.parametrize("T,N,K", SHAPES)
@@ -115,6 +115,9 @@ def test_plan_splits_small_batches_only():
     bn, splits = sm100.plan(ops.EPI_STORE, 8, 3072, 2048)
     assert bn == 16 and 2 <= splits <= 8                 # 24 tiles: a cluster of ranges of K per tile
     assert sm100.plan(ops.EPI_ACCUM_F32, 64, 2048, 8192) == (32, 8)      # two tiles of 32 tokens
+    assert sm100.plan(ops.EPI_ACCUM_F32, 128, 2048, 8192) == (32, 8)     # a narrow weight keeps its ranges of K
+    assert sm100.plan(ops.EPI_ACCUM_F32, 129, 2048, 8192) == (64, 1)
+    assert sm100.plan(ops.EPI_STORE, 128, 3072, 2048) == (64, 1)
     assert sm100.plan(ops.EPI_STORE, 8, 3072, 2048, split=False) == (16, 1)
     assert sm100.plan(ops.EPI_STORE, 2048, 3072, 2048) == (256, 1)
     assert sm100.plan(ops.EPI_ACCUM_F32, 2048, 2048, 8192) == (256, 1)
