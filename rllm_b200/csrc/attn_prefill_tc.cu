@@ -4,9 +4,11 @@
 // A work item is 128 rows, (query token, query head) pairs of ONE kv head (row r of a sequence is
 // token r / G, head kvh*G + r % G, as in the mma.sync kernel), and walks the keys the rows can
 // see in tiles of 128:
-//   warps 0..3  fetch the Q rows once and the K and V tiles through the block table with
-//               16-byte cp.async into 128-byte swizzled shared memory (four stages, one
-//               per warp), taking turns tile by tile;
+//   warps 0..3  fetch the Q rows once and the K and V tiles through the block table into 128-byte
+//               swizzled shared memory, four stages. Pages of a power of two from 8 keys up come
+//               by TMA, one copy per page (or per 128 keys of a larger page) and cache, issued by
+//               warp 0 alone and counted by the stage's mbarrier; any other page size comes by
+//               16-byte cp.async, the four warps taking turns tile by tile, one stage each;
 //   warp 4      one thread issues the products:  S = Q K^T  (M 128, N 128 keys, K 64) into one of
 //               two S accumulators, and  PV = P V  (M 128, N 64, K 128 keys) with P read from
 //               shared memory and V as it lies in the cache tile (an MN-major operand: the
@@ -25,6 +27,8 @@
 // in an orderly way (copies drained, TMEM freed).
 #include "common.cuh"
 #include "sm100.cuh"
+#include <mutex>
+#include <unordered_map>
 
 using namespace rllm;
 using namespace sm100;
@@ -59,6 +63,7 @@ struct PfParams {
   bf16* out; int out_stride;
   const int* cu_q; const int* kv_lens; const int* block_table; int bt_stride;
   int nh, nkv, page_size, page_shift, window;
+  int box_rows;          // TMA variant: keys per copy = min(page size, 128)
   int row_tiles, num_seqs, sm_count;
   float scale_log2e;
   int* err;
@@ -86,8 +91,11 @@ __host__ __device__ constexpr uint32_t idesc(int M, int N, bool b_mn_major) {
   return umma_idesc_bf16(M, N) | (b_mn_major ? (1u << 16) : 0u);
 }
 
+// TMA: the K and V tiles come by tensor copies over the caches seen as [pages * kv heads][page size][64].
+template <bool TMA>
 __global__ void __launch_bounds__(THREADS, 1)
-attn_prefill_tc_kernel(const PfParams p) {
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                       const PfParams p) {
   extern __shared__ uint8_t pf_smem_raw[];
   __shared__ __align__(8) uint64_t kv_full[KVS], kv_empty[KVS], s_full[2], p_full[2], pv_full[2];
   __shared__ uint32_t tmem_base_slot;
@@ -102,6 +110,15 @@ attn_prefill_tc_kernel(const PfParams p) {
 
   const int G = p.nh / p.nkv;
   if (threadIdx.x == 0) abort_flag = 0;
+  if (TMA) {
+    // A copy brings whole pages: rows past a sequence's last key keep what the stage held before.
+    // The scores of such keys are masked, and their weights are exact zeros, but zero times what
+    // an earlier kernel left here need not be zero: start from zeros (later leftovers are keys).
+    if (warp == 0 && lane == 0) { prefetch_tensormap(&tmap_k); prefetch_tensormap(&tmap_v); }
+    uint4* kv = reinterpret_cast<uint4*>(smem + TILE_BYTES);
+    for (int i = threadIdx.x; i < 2 * KVS * TILE_BYTES / 16; i += THREADS) kv[i] = make_uint4(0, 0, 0, 0);
+    fence_proxy_async();
+  }
   if (warp == MMA_WARP) { tmem_alloc(&tmem_base_slot, TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
@@ -143,7 +160,56 @@ attn_prefill_tc_kernel(const PfParams p) {
   kv_begin = kv_begin / PN * PN;
   const int n_tiles = cta_active ? (p_max + 1 - kv_begin + PN - 1) / PN : 0;
 
-  if (warp < LOADERS) {
+  if (warp < LOADERS && TMA) {
+    // ------------------------------------------------------------ loader (TMA): warp 0 alone, tile after tile.
+    // Lane c looks up the page of the tile's c-th copy; lane 0 tells the stage's barrier how many
+    // bytes are coming; every lane with a page issues its two copies. Nothing waits for a tile to
+    // land: up to KVS tiles are on their way.
+    if (warp == 0) {
+      const int* bt = p.block_table + (size_t)seq * p.bt_stride;
+      const int copies = PN / p.box_rows;                  // per tile and cache
+      const uint32_t copy_bytes = (uint32_t)p.box_rows * HD * 2;
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t % KVS;
+        if (t >= KVS) {
+          int w_ok = 1;
+          if (lane == 0 && !mbar_wait(&kv_empty[s], (uint32_t)(t / KVS - 1) & 1u, &abort_flag)) {
+            abort_flag = 1; record_failure(p.err, 21, t); w_ok = 0;
+          }
+          if (__shfl_sync(0xffffffffu, w_ok, 0) == 0) break;
+        }
+        if (t == 0) {
+          // the Q rows of the CTA, rows beyond the sequence zero; landed before the first tile is announced
+          const int ch = lane & 7, rbase = lane >> 3;
+#pragma unroll 4
+          for (int i = 0; i < 32; ++i) {
+            const int r = rbase + 4 * i;
+            const int row = tile * PM + r;
+            const bool valid = row < rows_total;
+            const int tok = valid ? row / G : 0, head = kvh * G + (valid ? row % G : 0);
+            const bf16* src = p.q + (size_t)(q0 + tok) * p.q_stride + (size_t)head * HD + ch * 8;
+            cp_async16z(q_s + (uint32_t)(r * 128 + ((ch ^ (r & 7)) << 4)), src, valid);
+          }
+          cp_async_commit();
+          cp_async_wait<0>();
+          fence_proxy_async();
+          __syncwarp();
+        }
+        const int j = kv_begin + t * PN + lane * p.box_rows;            // first key of this lane's copy
+        const bool mine = lane < copies && j < kv_len;
+        const int page = mine ? __ldg(bt + (j >> p.page_shift)) : 0;
+        const uint32_t n = __popc(__ballot_sync(0xffffffffu, mine));
+        if (lane == 0) mbar_expect_tx(&kv_full[s], 2 * n * copy_bytes);
+        __syncwarp();
+        if (mine) {
+          const uint32_t dst = (uint32_t)s * TILE_BYTES + (uint32_t)lane * copy_bytes;
+          const int off = j & (p.page_size - 1);
+          tma_load_3d(k_s + dst, &tmap_k, &kv_full[s], 0, off, page * p.nkv + kvh);
+          tma_load_3d(v_s + dst, &tmap_v, &kv_full[s], 0, off, page * p.nkv + kvh);
+        }
+      }
+    }
+  } else if (warp < LOADERS) {
     // ------------------------------------------------------------ loaders: warp w fetches the tiles w, w + 4, ...
     // whole, waits until they have landed and announces them at once, so a tile is ready long
     // before its turn (up to KVS tiles are on the way, from different warps).
@@ -387,27 +453,81 @@ attn_prefill_tc_kernel(const PfParams p) {
   if (warp == MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 }
 
+// ---- tensor maps over the caches (they live as long as the process, like the caches' addresses)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+std::mutex g_mu;
+struct MapKey {
+  const void* p; long long planes; int page_size;
+  bool operator==(const MapKey& o) const { return p == o.p && planes == o.planes && page_size == o.page_size; }
+};
+struct MapHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.p) ^ (std::hash<long long>()(k.planes * 2654435761LL + k.page_size) << 1);
+  }
+};
+std::unordered_map<MapKey, CUtensorMap, MapHash> g_maps;
+
+// cache [planes = pages * kv heads][page_size][64] bf16; a copy brings box_rows keys of one plane
+int cache_map(CUtensorMap* out, const void* ptr, long long planes, int page_size, int box_rows) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || !fn) {
+      cudaGetLastError();
+      return -5;
+    }
+    g_encode = (EncodeTiledFn)fn;
+  }
+  MapKey key{ptr, planes, page_size};
+  auto it = g_maps.find(key);
+  if (it == g_maps.end()) {
+    CUtensorMap m;
+    cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)page_size, (cuuint64_t)planes};
+    cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)page_size * HD * 2};
+    cuuint32_t box[3] = {(cuuint32_t)HD, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    if (g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return -5;
+    if (g_maps.size() > 4096) g_maps.clear();
+    it = g_maps.emplace(key, m).first;
+  }
+  *out = it->second;
+  return 0;
+}
+
+template <bool TMA>
+int launch_pf(const CUtensorMap& mk, const CUtensorMap& mv, const PfParams& p, int ctas, cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_prefill_tc_kernel<TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
+        cudaSuccess) { cudaGetLastError(); return -5; }
+    configured = true;
+  }
+  return launch_ex(attn_prefill_tc_kernel<TMA>, dim3(ctas), dim3(THREADS), SMEM_BYTES, s, 1, mk, mv, p);
+}
+
 }  // namespace
 
 // q: [T, ...] bf16 rows with stride q_stride, head h at h*64; out likewise (16-byte aligned rows).
-// kcache / vcache: [pages][nkv][page_size][64] bf16. cu_q [S+1], kv_lens [S], block_table [S, bt_stride].
+// kcache / vcache: [num_pages][nkv][page_size][64] bf16. cu_q [S+1], kv_lens [S], block_table [S, bt_stride].
 // max_q_len: the longest portion in the batch (sizes the list of work items). Head size 64 only.
 // sm_count: CTAs to launch at most (0: asked from the device).
 RLLM_API int rllm_attention_prefill_tc(const void* q, int q_stride, const void* kcache, const void* vcache,
                                        void* out, int out_stride, const int* cu_q, const int* kv_lens,
                                        const int* block_table, int bt_stride, int num_seqs, int max_q_len,
-                                       int nh, int nkv, int hd, int page_size, float scale, int window,
+                                       int num_pages, int nh, int nkv, int hd, int page_size, float scale, int window,
                                        int* err, int sm_count, void* stream) {
   if (num_seqs <= 0 || max_q_len <= 0) return 0;
-  if (hd != HD || nkv <= 0 || nh % nkv || page_size <= 0) return ERR_BAD_SIZE;
+  if (hd != HD || nkv <= 0 || nh % nkv || page_size <= 0 || num_pages <= 0) return ERR_BAD_SIZE;
   if (q_stride % 8 || out_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
       ((uintptr_t)kcache & 15) || ((uintptr_t)vcache & 15)) return ERR_BAD_ALIGN;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
-        cudaSuccess) { cudaGetLastError(); return -5; }
-    configured = true;
-  }
   PfParams p;
   p.q = (const bf16*)q; p.q_stride = q_stride; p.kc = (const bf16*)kcache; p.vc = (const bf16*)vcache;
   p.out = (bf16*)out; p.out_stride = out_stride; p.cu_q = cu_q; p.kv_lens = kv_lens;
@@ -428,5 +548,18 @@ RLLM_API int rllm_attention_prefill_tc(const void* q, int q_stride, const void* 
     }
   }
   const int ctas = items < sms ? (int)items : sms;
-  return launch_ex(attn_prefill_tc_kernel, dim3(ctas), dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, 1, p);
+  // pages of a power of two from 8 keys up (whole 1 KB swizzle atoms) come by tensor copies
+  const bool tma = p.page_shift >= 3 && (long long)num_pages * nkv <= 2147483647LL;
+  CUtensorMap mk, mv;
+  if (tma) {
+    p.box_rows = page_size < PN ? page_size : PN;
+    int rc;
+    if ((rc = cache_map(&mk, kcache, (long long)num_pages * nkv, page_size, p.box_rows))) return rc;
+    if ((rc = cache_map(&mv, vcache, (long long)num_pages * nkv, page_size, p.box_rows))) return rc;
+    return launch_pf<true>(mk, mv, p, ctas, (cudaStream_t)stream);
+  }
+  p.box_rows = 0;
+  memset(&mk, 0, sizeof(mk));
+  mv = mk;
+  return launch_pf<false>(mk, mv, p, ctas, (cudaStream_t)stream);
 }

@@ -21,7 +21,7 @@ ops.register_signatures("sm100", {
     "rllm_attention_fa": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_float, c_int, c_int, _P, _P, _P],
     "rllm_attention_prefill_tc": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
-                                  c_int, c_float, c_int, _P, c_int, _P],
+                                  c_int, c_int, c_float, c_int, _P, c_int, _P],
     "rllm_attention_decode": [_P, c_int, _P, _P, c_longlong, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_float, c_int, c_int, _P, _P],
 })
@@ -257,8 +257,8 @@ def attention_prefill_tc(q, kcache, vcache, cu_q, kv_lens, block_table, max_q_le
     rc = ops._fn("sm100", "rllm_attention_prefill_tc")(
         q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(), out.data_ptr(), out.stride(0),
         cu_q.data_ptr(), kv_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0), kv_lens.numel(),
-        max_q_len, nh, nkv, hd, page_size, float(scale), int(window or 0), st.err.data_ptr(), st.sm_count,
-        ops._stream())
+        max_q_len, kcache.shape[0], nh, nkv, hd, page_size, float(scale), int(window or 0), st.err.data_ptr(),
+        st.sm_count, ops._stream())
     ops._check(rc, "attention_prefill_tc")
     return out
 

@@ -126,7 +126,7 @@ def test_decode_kernel_with_cluster_merge(splits, nh, nkv, hd, page, window):
 
 
 @pytest.mark.parametrize("nh,nkv,page,window", [(32, 8, 16, None), (6, 2, 8, None), (3, 1, 5, None), (8, 8, 16, 200),
-                                                (4, 1, 32, 70)])
+                                                (4, 1, 32, 70), (8, 2, 128, None), (4, 2, 256, 300)])
 def test_prefill_on_tcgen05(nh, nkv, page, window):
     """The tcgen05 prefill kernel (head size 64) against the plain formula: portions that start
     in the middle of what the cache holds, lengths on both sides of the 128-row and 128-key
