@@ -1,30 +1,35 @@
 // Prefill attention over the paged bfloat16 cache on the 5th-generation tensor cores (tcgen05),
 // head size 64: both products of a tile run as UMMA with their accumulators in TMEM.
 //
-// A work item is 128 rows, (query token, query head) pairs of ONE kv head (row r of a sequence is
-// token r / G, head kvh*G + r % G, as in the mma.sync kernel), and walks the keys the rows can
-// see in tiles of 128:
-//   warps 0..3  fetch the Q rows once and the K and V tiles through the block table into 128-byte
-//               swizzled shared memory, four stages. Pages of a power of two from 8 keys up come
+// A work item is a pair of row tiles, 2 x 128 rows: (query token, query head) pairs of ONE kv head
+// (row r of a sequence is token r / G, head kvh*G + r % G, as in the mma.sync kernel). Both tiles
+// walk the keys they can see in tiles of 128 and share every K and V tile that is fetched:
+//   warps 0..2  fetch the Q rows once and the K and V tiles through the block table into 128-byte
+//               swizzled shared memory, three stages. Pages of a power of two from 8 keys up come
 //               by TMA, one copy per page (or per 128 keys of a larger page) and cache, issued by
 //               warp 0 alone and counted by the stage's mbarrier; any other page size comes by
-//               16-byte cp.async, the four warps taking turns tile by tile, one stage each;
-//   warp 4      one thread issues the products:  S = Q K^T  (M 128, N 128 keys, K 64) into one of
-//               two S accumulators, and  PV = P V  (M 128, N 64, K 128 keys) with P read from
-//               shared memory and V as it lies in the cache tile (an MN-major operand: the
-//               contraction runs over key rows);
-//   warps 5..12 two threads per row (64 keys of the tile and 32 output values each): read S from
-//               TMEM, keep the running maximum and sum in float with exp2, write P as bf16 in
-//               the swizzled layout of an A operand, and add the tile's PV (read from TMEM) into
-//               the row's output values in registers, rescaled when the maximum moved.
-// S of tile t + 1 is computed while the softmax of tile t runs (two S and two PV accumulators,
-// 384 TMEM columns). A key j is visible when j <= position of the row and j > position - window.
+//               16-byte cp.async, the three warps taking turns tile by tile, one stage each;
+//   warp 3      one thread issues the products of both row tiles in turn:  S = Q K^T  (M 128,
+//               N 128 keys, K 64) into the row tile's S accumulator, and  PV = P V  (M 128, N 64,
+//               K 128 keys) with P read from shared memory and V as it lies in the cache tile (an
+//               MN-major operand: the contraction runs over key rows);
+//   warps 4..7  the softmax of the first row tile, one thread per row; warps 8..11 of the second.
+//               A thread reads its row of S from TMEM twice, 32 keys at a time: once for the
+//               maximum, once for exp2, the sum and P as bf16 in the swizzled layout of an A
+//               operand. Between the two it adds the PV of the tile before (read from TMEM) into
+//               the row's 64 output values in registers, rescaled when the maximum moved.
+// The (row tile, K tile) steps are numbered k = 0, 1, ... in the order A0 B0 A1 B1 ...; S of step k
+// lands in accumulator k % 3, so while both row tiles are in their softmax the scores of the step
+// after are computed already, and a row tile that has written its P goes on at once: the four warp
+// schedulers always have a warp with work (two warps each, one of either tile).
+// TMEM: three S accumulators and PV of both tiles, 512 columns.
+// A key j is visible when j <= position of the row and j > position - window.
 //
 // Formulas: src/gpu/cuda/shaders/attention.cu:573-618 and :328-388 of the reference (scale,
 // softmax with the maximum subtracted, weighted V, head h -> kv head h / G, window); unlike the
 // reference's prefill kernel a portion also sees what earlier steps left in the cache.
 // Every mbarrier wait is bounded; a wait that runs out records an error word and the CTA leaves
-// in an orderly way (copies drained, TMEM freed).
+// in an orderly way (TMEM freed).
 #include "common.cuh"
 #include "sm100.cuh"
 #include <mutex>
@@ -35,27 +40,24 @@ using namespace sm100;
 
 namespace {
 
-constexpr int PM = 128;          // rows per CTA
+constexpr int PM = 128;          // rows per row tile
 constexpr int PN = 128;          // keys per tile
 constexpr int HD = 64;
-constexpr int LOADERS = 4;       // loader warps
+constexpr int RT = 2;            // row tiles per work item
+constexpr int LOADERS = 3;       // loader warps
 constexpr int MMA_WARP = LOADERS;
-#ifndef PF_SPLIT
-#define PF_SPLIT 2
-#endif
-constexpr int SPLIT = PF_SPLIT;  // softmax warps per TMEM lane quadrant: each takes 128 / SPLIT keys of a tile
-constexpr int KT = PN / SPLIT;   // keys per softmax thread and tile
-constexpr int OD = HD / SPLIT;   // output values per softmax thread
-constexpr int SOFTMAX_WARP0 = LOADERS + 1;
-constexpr int THREADS = (LOADERS + 1 + 4 * SPLIT) * 32;   // warps 0..3 load, warp 4 issues the products, the rest softmax
-constexpr int TILE_BYTES = PN * HD * 2;          // 16 KB: one K or V tile, and Q
+constexpr int SOFTMAX_WARP0 = LOADERS + 1;      // a multiple of 4: warp w reads TMEM lanes 32 (w % 4) ...
+static_assert(SOFTMAX_WARP0 % 4 == 0, "softmax warp w must own TMEM lane quadrant w % 4");
+constexpr int THREADS = (LOADERS + 1 + 4 * RT) * 32;
+constexpr int TILE_BYTES = PN * HD * 2;          // 16 KB: one K or V tile, one row tile of Q
 constexpr int P_BYTES = PM * PN * 2;             // 32 KB: two 64-key sub-tiles of 16 KB
-constexpr int KVS = LOADERS;     // K/V stages: loader warp w always fills stage w (tiles w, w + KVS, ...), so its
-                                 // waits on that stage's barriers follow one another phase by phase; a warp
+constexpr int KVS = LOADERS;     // K/V stages. Without TMA loader warp w always fills stage w (tiles w, w + KVS, ...),
+                                 // so its waits on that stage's barriers follow one another phase by phase; a warp
                                  // that moved between stages could be two phases ahead, which a parity cannot tell
-constexpr int SMEM_BYTES = 1024 + TILE_BYTES * (1 + 2 * KVS) + 2 * P_BYTES;    // Q, K[KVS], V[KVS], P[2]
-constexpr int TMEM_COLS = 512;   // S[2] x 128 + PV[2] x 64 = 384
-constexpr int S_COL = 0, PV_COL = 256;
+constexpr int SMEM_BYTES = 1024 + TILE_BYTES * (RT + 2 * KVS) + RT * P_BYTES;    // Q[2], K[KVS], V[KVS], P[2]
+constexpr int SB = 3;            // S accumulators: one per row tile in its softmax, one being computed ahead
+constexpr int TMEM_COLS = 512;   // S[3] x 128 + PV[2] x 64
+constexpr int S_COL = 0, PV_COL = SB * PN;
 
 struct PfParams {
   const bf16* q; int q_stride;
@@ -64,7 +66,7 @@ struct PfParams {
   const int* cu_q; const int* kv_lens; const int* block_table; int bt_stride;
   int nh, nkv, page_size, page_shift, window;
   int box_rows;          // TMA variant: keys per copy = min(page size, 128)
-  int row_tiles, num_seqs, sm_count;
+  int row_pairs, num_seqs, sm_count;
   float scale_log2e;
   int* err;
 };
@@ -97,16 +99,14 @@ __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                        const PfParams p) {
   extern __shared__ uint8_t pf_smem_raw[];
-  __shared__ __align__(8) uint64_t kv_full[KVS], kv_empty[KVS], s_full[2], p_full[2], pv_full[2];
+  __shared__ __align__(8) uint64_t kv_full[KVS], kv_empty[KVS], s_full[SB], p_full[RT], pv_full[RT];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ int pair_fail[4];       // a wait of one of a quadrant's two warps ran out: both leave together
-  __shared__ float xmax[SPLIT][PM];      // what the two warps of a lane quadrant tell each other (maximum, sum)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* smem = (uint8_t*)(((uintptr_t)pf_smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t q_s = smem_u32(smem);
-  const uint32_t k_s = q_s + TILE_BYTES, v_s = k_s + KVS * TILE_BYTES, p_s = v_s + KVS * TILE_BYTES;
+  const uint32_t k_s = q_s + RT * TILE_BYTES, v_s = k_s + KVS * TILE_BYTES, p_s = v_s + KVS * TILE_BYTES;
 
   const int G = p.nh / p.nkv;
   if (threadIdx.x == 0) abort_flag = 0;
@@ -115,7 +115,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     // The scores of such keys are masked, and their weights are exact zeros, but zero times what
     // an earlier kernel left here need not be zero: start from zeros (later leftovers are keys).
     if (warp == 0 && lane == 0) { prefetch_tensormap(&tmap_k); prefetch_tensormap(&tmap_v); }
-    uint4* kv = reinterpret_cast<uint4*>(smem + TILE_BYTES);
+    uint4* kv = reinterpret_cast<uint4*>(smem + RT * TILE_BYTES);
     for (int i = threadIdx.x; i < 2 * KVS * TILE_BYTES / 16; i += THREADS) kv[i] = make_uint4(0, 0, 0, 0);
     fence_proxy_async();
   }
@@ -127,21 +127,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   pdl_wait();                                           // q and the newest keys come from the kernel before
   const uint32_t tmem_base = tmem_base_slot;
 
-  // The CTAs (one per SM) share the (row tile, kv head, sequence) items out among themselves:
-  // items are numbered from the row tiles that see the most keys down, and round r gives CTA c
-  // item r * C + c, or r * C + (C - 1 - c) in odd rounds, so that every CTA gets a like share of
-  // long and short ones.
-  const int items = p.row_tiles * p.nkv * p.num_seqs;
+  // The CTAs (one per SM) share the (pair of row tiles, kv head, sequence) items out among
+  // themselves: items are numbered from the row tiles that see the most keys down, and round r
+  // gives CTA c item r * C + c, or r * C + (C - 1 - c) in odd rounds, so that every CTA gets a
+  // like share of long and short ones.
+  const int items = p.row_pairs * p.nkv * p.num_seqs;
   for (int round = 0;; ++round) {
   const int item = round * (int)gridDim.x + ((round & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
   if (item >= items) break;
-  const int tile = p.row_tiles - 1 - item / (p.nkv * p.num_seqs);
+  const int tile0 = (p.row_pairs - 1 - item / (p.nkv * p.num_seqs)) * RT;      // first of the item's row tiles
   const int kvh = item % p.nkv, seq = (item / p.nkv) % p.num_seqs;
   __syncthreads();                                      // everybody has left the item before
   if (threadIdx.x == 0) {
     for (int i = 0; i < KVS; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4 * SPLIT); mbar_init(&pv_full[i], 1); }
-    for (int i = 0; i < 4; ++i) pair_fail[i] = 0;
+    for (int i = 0; i < SB; ++i) mbar_init(&s_full[i], 1);
+    for (int i = 0; i < RT; ++i) { mbar_init(&p_full[i], 4); mbar_init(&pv_full[i], 1); }
     fence_barrier_init();
   }
   __syncthreads();
@@ -151,14 +151,36 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   const int q_len = p.cu_q[seq + 1] - q0;
   const int kv_len = p.kv_lens[seq];
   const int rows_total = q_len * G;
-  const bool cta_active = tile * PM < rows_total;       // uniform: an item beyond the sequence's rows is empty
-  // keys this item's rows can see at all
-  const int tok_first = (tile * PM) / G;
-  const int tok_last = min(q_len - 1, (tile * PM + PM - 1) / G);
-  const int p_min = kv_len - q_len + tok_first, p_max = kv_len - q_len + tok_last;
-  int kv_begin = (p.window > 0 && p_min - p.window + 1 > 0) ? p_min - p.window + 1 : 0;
-  kv_begin = kv_begin / PN * PN;
-  const int n_tiles = cta_active ? (p_max + 1 - kv_begin + PN - 1) / PN : 0;
+  // keys the item's rows can see at all: from the first row's window (or 0) to the last row's position.
+  // The later row tile sees at least as far as the earlier one; both start from the same tile.
+  int kv_begin = 0, n_t[RT];
+  {
+    const int p_min = kv_len - q_len + (tile0 * PM) / G;
+    if (p.window > 0 && p_min - p.window + 1 > 0) kv_begin = (p_min - p.window + 1) / PN * PN;
+#pragma unroll
+    for (int g = 0; g < RT; ++g) {
+      const bool active = (tile0 + g) * PM < rows_total;         // uniform: a row tile beyond the sequence's rows is empty
+      const int p_max = kv_len - q_len + min(q_len - 1, ((tile0 + g) * PM + PM - 1) / G);
+      n_t[g] = active ? (p_max + 1 - kv_begin + PN - 1) / PN : 0;
+    }
+  }
+  const int n_tiles = max(n_t[0], n_t[1]);
+  // step k is (row tile, K tile) = (k & 1, k >> 1) while both row tiles have tiles left, then the later one alone
+  const int n_both = min(n_t[0], n_t[1]), g_long = n_t[1] > n_t[0] ? 1 : 0, n_steps = n_t[0] + n_t[1];
+
+  // the Q rows of both row tiles, rows beyond the sequence zero (one warp, before its first K/V tile)
+  auto load_q = [&]() {
+    const int ch = lane & 7, rbase = lane >> 3;
+#pragma unroll 4
+    for (int i = 0; i < RT * 32; ++i) {
+      const int r = rbase + 4 * i;
+      const int row = tile0 * PM + r;
+      const bool valid = row < rows_total;
+      const int tok = valid ? row / G : 0, head = kvh * G + (valid ? row % G : 0);
+      const bf16* src = p.q + (size_t)(q0 + tok) * p.q_stride + (size_t)head * HD + ch * 8;
+      cp_async16z(q_s + (uint32_t)(r * 128 + ((ch ^ (r & 7)) << 4)), src, valid);
+    }
+  };
 
   if (warp < LOADERS && TMA) {
     // ------------------------------------------------------------ loader (TMA): warp 0 alone, tile after tile.
@@ -179,17 +201,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
           if (__shfl_sync(0xffffffffu, w_ok, 0) == 0) break;
         }
         if (t == 0) {
-          // the Q rows of the CTA, rows beyond the sequence zero; landed before the first tile is announced
-          const int ch = lane & 7, rbase = lane >> 3;
-#pragma unroll 4
-          for (int i = 0; i < 32; ++i) {
-            const int r = rbase + 4 * i;
-            const int row = tile * PM + r;
-            const bool valid = row < rows_total;
-            const int tok = valid ? row / G : 0, head = kvh * G + (valid ? row % G : 0);
-            const bf16* src = p.q + (size_t)(q0 + tok) * p.q_stride + (size_t)head * HD + ch * 8;
-            cp_async16z(q_s + (uint32_t)(r * 128 + ((ch ^ (r & 7)) << 4)), src, valid);
-          }
+          load_q();                                         // landed before the first tile is announced
           cp_async_commit();
           cp_async_wait<0>();
           fence_proxy_async();
@@ -210,9 +222,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
       }
     }
   } else if (warp < LOADERS) {
-    // ------------------------------------------------------------ loaders: warp w fetches the tiles w, w + 4, ...
-    // whole, waits until they have landed and announces them at once, so a tile is ready long
-    // before its turn (up to KVS tiles are on the way, from different warps).
+    // ------------------------------------------------------------ loaders (any page size): warp w fetches the
+    // tiles w, w + 3, ... whole, waits until they have landed and announces them at once, so a
+    // tile is ready long before its turn (up to KVS tiles are on the way, from different warps).
     const int* bt = p.block_table + (size_t)seq * p.bt_stride;
     const int ch = lane & 7;                              // this lane's 16-byte chunk of a 128-byte row
     const int rbase = lane >> 3;                          // its rows: rbase + 4 i, i < 32
@@ -225,18 +237,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         }
         if (__shfl_sync(0xffffffffu, w_ok, 0) == 0) break;
       }
-      if (t == 0) {
-        // the Q rows of the CTA, rows beyond the sequence zero
-#pragma unroll 4
-        for (int i = 0; i < 32; ++i) {
-          const int r = rbase + 4 * i;
-          const int row = tile * PM + r;
-          const bool valid = row < rows_total;
-          const int tok = valid ? row / G : 0, head = kvh * G + (valid ? row % G : 0);
-          const bf16* src = p.q + (size_t)(q0 + tok) * p.q_stride + (size_t)head * HD + ch * 8;
-          cp_async16z(q_s + (uint32_t)(r * 128 + ((ch ^ (r & 7)) << 4)), src, valid);
-        }
-      }
+      if (t == 0) load_q();
       const int j0 = kv_begin + t * PN;
       const uint32_t kd = k_s + (uint32_t)s * TILE_BYTES, vd = v_s + (uint32_t)s * TILE_BYTES;
 #pragma unroll 1
@@ -267,42 +268,49 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
       if (lane == 0) mbar_arrive(&kv_full[s]);
     }
   } else if (warp == MMA_WARP) {
-    // ------------------------------------------------------------ the products (one thread)
+    // ------------------------------------------------------------ the products (one thread), the row tiles in turn
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t id_s = idesc(PM, PN, false);
       constexpr uint32_t id_pv = idesc(PM, HD, true);
       bool ok = true;
-      auto issue_s = [&](int t) {
-        const int s = t & 1, ks = t % KVS;
+      auto step = [&](int k, int& g, int& t) {
+        if (k < 2 * n_both) { g = k & 1; t = k >> 1; } else { g = g_long; t = n_both + (k - 2 * n_both); }
+      };
+      auto issue_s = [&](int k) {                         // S of step k into accumulator k % 3
+        int g, t;
+        step(k, g, t);
+        const int ks = t % KVS;
         if (!mbar_wait(&kv_full[ks], (uint32_t)(t / KVS) & 1u, &abort_flag)) {
           abort_flag = 1; record_failure(p.err, 22, t); ok = false; return;
         }
         tc_fence_after();
-        const uint64_t dq = umma_desc_sw128(q_s), dk = umma_desc_sw128(k_s + (uint32_t)ks * TILE_BYTES);
+        const uint64_t dq = umma_desc_sw128(q_s + (uint32_t)g * TILE_BYTES);
+        const uint64_t dk = umma_desc_sw128(k_s + (uint32_t)ks * TILE_BYTES);
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          umma_bf16(tmem_base + S_COL + (uint32_t)s * PN, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), id_s, k > 0);
-        umma_commit(&s_full[s]);
+        for (int kk = 0; kk < HD / 16; ++kk)
+          umma_bf16(tmem_base + S_COL + (uint32_t)(k % SB) * PN, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), id_s, kk > 0);
+        umma_commit(&s_full[k % SB]);
       };
-      issue_s(0);
-      for (int t = 0; t < n_tiles && ok; ++t) {
-        const int s = t & 1;
-        if (t + 1 < n_tiles) issue_s(t + 1);            // the next scores while this tile's softmax runs
-        if (!ok) break;
-        if (!mbar_wait(&p_full[s], (uint32_t)(t >> 1) & 1u, &abort_flag)) {
+      for (int k = 0; k < SB && k < n_steps && ok; ++k) issue_s(k);
+      for (int k = 0; k < n_steps && ok; ++k) {
+        int g, t;
+        step(k, g, t);
+        // P of this step is written (so its S is read, and the row tile's PV before is read too)
+        if (!mbar_wait(&p_full[g], (uint32_t)t & 1u, &abort_flag)) {
           abort_flag = 1; record_failure(p.err, 23, t); ok = false; break;
         }
         tc_fence_after();
-        const uint32_t pa = p_s + (uint32_t)s * P_BYTES, va = v_s + (uint32_t)(t % KVS) * TILE_BYTES;
+        const uint32_t pa = p_s + (uint32_t)g * P_BYTES, va = v_s + (uint32_t)(t % KVS) * TILE_BYTES;
 #pragma unroll
         for (int ks = 0; ks < PN / 16; ++ks) {
           // P: K-major, two 64-key sub-tiles of 16 KB; V: MN-major, 16 key rows = 2 KB per step
           const uint64_t dp = umma_desc_sw128(pa + (uint32_t)(ks >> 2) * TILE_BYTES) + (uint64_t)((ks & 3) * 2);
           const uint64_t dv = umma_desc_sw128(va + (uint32_t)ks * 2048u);
-          umma_bf16(tmem_base + PV_COL + (uint32_t)s * HD, dp, dv, id_pv, ks > 0);
+          umma_bf16(tmem_base + PV_COL + (uint32_t)g * HD, dp, dv, id_pv, ks > 0);
         }
-        umma_commit(&kv_empty[t % KVS]);                // K and V of this stage are read
-        umma_commit(&pv_full[s]);
+        umma_commit(&pv_full[g]);
+        if (g == 1 || t >= n_both) umma_commit(&kv_empty[t % KVS]);     // the last reader of this K and V stage
+        if (k + SB < n_steps) issue_s(k + SB);            // its accumulator is the one this step's softmax has just left
       }
       // nothing of this item may still be on its way to a barrier when the next item sets them up again
       for (int t = max(0, n_tiles - KVS); t < n_tiles && ok; ++t)
@@ -310,136 +318,115 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
           abort_flag = 1; record_failure(p.err, 26, t); ok = false;
         }
     }
-  } else if (n_tiles > 0) {
-    // ------------------------------------------------------------ softmax warps
-    // SPLIT warps share each TMEM lane quadrant (a warp may only read the 32 lanes of its index
-    // mod 4): warps w, w + 4, ... serve the same 32 rows, each KT keys of a tile and OD of the 64
-    // output values. They agree on the row's maximum through shared memory; each keeps the sum
-    // of its own exponentials, added at the end. More warps per quadrant hide the TMEM latency.
-    const int quad = warp & 3;
-    const int half = (warp - SOFTMAX_WARP0) >> 2;       // which KT keys of a tile, which OD output values
+  } else if (n_t[(warp - SOFTMAX_WARP0) >> 2] > 0) {
+    // ------------------------------------------------------------ softmax warps: one thread per row
+    const int g = (warp - SOFTMAX_WARP0) >> 2;           // the row tile
+    const int n_mine = n_t[g];
+    const int quad = warp & 3;                            // the TMEM lanes this warp may read: 32 quad ...
     const int r = quad * 32 + lane;
-    const int row = tile * PM + r;
+    const int row = (tile0 + g) * PM + r;
     const bool valid = row < rows_total;
     const int tok = valid ? row / G : 0, head = kvh * G + (valid ? row % G : 0);
     const int pos = kv_len - q_len + tok;
     const int lo = p.window > 0 ? pos - p.window + 1 : 0;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t pv_addr = lane_addr + PV_COL + (uint32_t)g * HD;
+    uint32_t s_addr = 0;                                  // this step's S accumulator
+    const uint32_t prow = p_s + (uint32_t)g * P_BYTES + (uint32_t)(r * 128);
     const float sl = p.scale_log2e;
-    float o[OD];
+    float o[HD];
 #pragma unroll
-    for (int i = 0; i < OD; ++i) o[i] = 0.f;
+    for (int i = 0; i < HD; ++i) o[i] = 0.f;
     float m = -INFINITY, l = 0.f, corr_prev = 1.f;
     bool ok = true;
-    auto pair_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + quad), "n"(32 * SPLIT) : "memory"); };
 
-    auto add_pv = [&](int t, float corr) {              // O = O * corr + PV(t), this thread's 32 values
-      const int s = t & 1;
-      bool got = mbar_wait(&pv_full[s], (uint32_t)(t >> 1) & 1u, &abort_flag);
-      if (!got) { abort_flag = 1; record_failure(p.err, 25, t); }
-      got = __all_sync(0xffffffffu, got);
-      if (!got) { ok = false; return; }
-      tc_fence_after();
-      uint32_t v[OD / 16][16];
+    auto wait_on = [&](uint64_t* bar, uint32_t parity, int role, int t) -> bool {
+      bool got = mbar_wait(bar, parity, &abort_flag);
+      if (!got) { abort_flag = 1; record_failure(p.err, role, t); }
+      return __all_sync(0xffffffffu, got);
+    };
+    // 64 scores of the row: keys jc .. jc + 63 of the tile, the hidden ones -inf
+    auto scores = [&](int jc, uint32_t col, uint32_t (&a)[32], uint32_t (&b)[32]) {
+      tmem_ld32(s_addr + col, a);
+      tmem_ld32(s_addr + col + 32, b);
+      tmem_ld_wait();
+      if (!valid || jc + 63 > pos || jc < lo) {           // some key is hidden from this row
 #pragma unroll
-      for (int q2 = 0; q2 < OD / 16; ++q2) tmem_ld16(lane_addr + PV_COL + (uint32_t)s * HD + half * OD + 16 * q2, v[q2]);
+        for (int i = 0; i < 32; ++i) {
+          if (!(valid && jc + i <= pos && jc + i >= lo)) a[i] = 0xff800000u;
+          if (!(valid && jc + 32 + i <= pos && jc + 32 + i >= lo)) b[i] = 0xff800000u;
+        }
+      }
+    };
+    auto add_pv = [&](int t, float corr) -> bool {        // O = O * corr + PV(t)
+      if (!wait_on(&pv_full[g], (uint32_t)t & 1u, 25, t)) return false;
+      tc_fence_after();
+      uint32_t a[32], b[32];
+      tmem_ld32(pv_addr, a);
+      tmem_ld32(pv_addr + 32, b);
       tmem_ld_wait();
 #pragma unroll
-      for (int q2 = 0; q2 < OD / 16; ++q2)
-#pragma unroll
-        for (int i = 0; i < 16; ++i) o[16 * q2 + i] = fmaf(o[16 * q2 + i], corr, __uint_as_float(v[q2][i]));
+      for (int i = 0; i < 32; ++i) {
+        o[i] = fmaf(o[i], corr, __uint_as_float(a[i]));
+        o[32 + i] = fmaf(o[32 + i], corr, __uint_as_float(b[i]));
+      }
       tc_fence_before();
+      return true;
     };
 
-    for (int t = 0; t < n_tiles; ++t) {
-      const int s = t & 1;
-      const int j0 = kv_begin + t * PN + half * KT;       // first key of this thread's KT
-      if (ok) {
-        bool got = mbar_wait(&s_full[s], (uint32_t)(t >> 1) & 1u, &abort_flag);
-        if (!got) { abort_flag = 1; record_failure(p.err, 24, t); }
-        got = __all_sync(0xffffffffu, got);
-        if (!got) ok = false;
-      }
-      if (!ok) pair_fail[quad] = 1;
-      // ---- this thread's KT scores, read once
-      constexpr int NQ = KT / 16;
-      uint32_t v[NQ][16];
-      if (ok) {
-        tc_fence_after();
-        const uint32_t s_addr = lane_addr + S_COL + (uint32_t)s * PN + half * KT;
-#pragma unroll
-        for (int q4 = 0; q4 < NQ; ++q4) tmem_ld16(s_addr + 16 * q4, v[q4]);
-        tmem_ld_wait();
-      }
-      const bool edge = !valid || j0 + KT - 1 > pos || j0 < lo;      // some key is hidden from this row
+    for (int t = 0; t < n_mine; ++t) {
+      const int j0 = kv_begin + t * PN;
+      const int k = t < n_both ? 2 * t + g : 2 * n_both + (t - n_both);
+      s_addr = lane_addr + S_COL + (uint32_t)(k % SB) * PN;
+      if (!wait_on(&s_full[k % SB], (uint32_t)(k / SB) & 1u, 24, t)) { ok = false; break; }
+      tc_fence_after();
+      // ---- first reading: the row's maximum
       float mx = -INFINITY;
-      if (ok) {
-        if (edge) {
 #pragma unroll
-          for (int q4 = 0; q4 < NQ; ++q4)
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t a[32], b[32];
+        scores(j0 + 64 * hf, 64 * hf, a, b);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int j = j0 + 16 * q4 + i;
-              if (!(valid && j <= pos && j >= lo)) v[q4][i] = 0xff800000u;      // -inf
-            }
-        }
-#pragma unroll
-        for (int q4 = 0; q4 < NQ; ++q4)
-#pragma unroll
-          for (int i = 0; i < 16; ++i) mx = fmaxf(mx, __uint_as_float(v[q4][i]));
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(a[i]), __uint_as_float(b[i])));
       }
-      // ---- the row's maximum over both halves (the barrier is met also after a failed wait)
-      xmax[half][r] = mx;
-      pair_sync();
-#pragma unroll
-      for (int h2 = 0; h2 < SPLIT; ++h2) mx = fmaxf(mx, xmax[h2][r]);
-      const bool leave = pair_fail[quad] != 0;
-      pair_sync();                                        // both have read before the next tile writes
-      if (leave) { ok = false; break; }
       const float m_new = fmaxf(m, mx * sl);              // the scale is positive: it commutes with max
       const float use = (m_new == -INFINITY) ? 0.f : m_new;
       const float corr = fast_exp2(m - use);              // exp2(-inf) = 0
       m = m_new;
       l *= corr;
-      // ---- exponentials, their sum, P as bf16 into the A-operand layout (64-key sub-tiles of 16 KB)
-      const int kc0 = half * KT;                          // first key column of this thread within the tile
-      const uint32_t prow = p_s + (uint32_t)s * P_BYTES + (uint32_t)(kc0 >> 6) * TILE_BYTES + (uint32_t)(r * 128);
+      // ---- the tile before this one: its PV is ready by now (and has read P, which is written next)
+      if (t > 0 && !add_pv(t - 1, corr_prev)) { ok = false; break; }
+      // ---- second reading: exponentials, their sum, P as bf16 into the A-operand layout
 #pragma unroll
-      for (int q4 = 0; q4 < NQ; ++q4) {
-        float e[16];
+      for (int hf = 0; hf < 2; ++hf) {                    // a 64-key sub-tile of 16 KB each
+        uint32_t a[32], b[32];
+        scores(j0 + 64 * hf, 64 * hf, a, b);
+        const uint32_t base = prow + (uint32_t)hf * TILE_BYTES;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          e[i] = fast_exp2(fmaf(__uint_as_float(v[q4][i]), sl, -use));     // hidden keys hold -inf: 0
-          l += e[i];
+        for (int q8 = 0; q8 < 8; ++q8) {                  // 8 keys = one 16-byte chunk
+          float e[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t sv = q8 < 4 ? a[8 * q8 + i] : b[8 * (q8 - 4) + i];
+            e[i] = fast_exp2(fmaf(__uint_as_float(sv), sl, -use));        // hidden keys hold -inf: 0
+            l += e[i];
+          }
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + (uint32_t)((q8 ^ (r & 7)) << 4)),
+                       "r"(pack_bf16(e[0], e[1])), "r"(pack_bf16(e[2], e[3])), "r"(pack_bf16(e[4], e[5])),
+                       "r"(pack_bf16(e[6], e[7])) : "memory");
         }
-        const int ch = ((kc0 & 63) >> 3) + 2 * q4;        // first of two 16-byte chunks
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + (uint32_t)(((ch) ^ (r & 7)) << 4)),
-                     "r"(pack_bf16(e[0], e[1])), "r"(pack_bf16(e[2], e[3])), "r"(pack_bf16(e[4], e[5])),
-                     "r"(pack_bf16(e[6], e[7])) : "memory");
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + (uint32_t)(((ch + 1) ^ (r & 7)) << 4)),
-                     "r"(pack_bf16(e[8], e[9])), "r"(pack_bf16(e[10], e[11])), "r"(pack_bf16(e[12], e[13])),
-                     "r"(pack_bf16(e[14], e[15])) : "memory");
       }
       tc_fence_before();
       fence_proxy_async();                                // P is read by the tensor core's proxy
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[s]);
-      // ---- the tile before this one: its PV is ready by now; fold it into the row's output
-      if (t > 0) add_pv(t - 1, corr_prev);
+      if (lane == 0) mbar_arrive(&p_full[g]);
       corr_prev = corr;
     }
-    if (ok) add_pv(n_tiles - 1, corr_prev);             // every tile's PV entered with its own tile's factor
-    // ---- the two halves' sums of exponentials meet (met also after a failed wait)
-    xmax[half][r] = l;
-    pair_sync();
-    l = 0.f;
-#pragma unroll
-    for (int h2 = 0; h2 < SPLIT; ++h2) l += xmax[h2][r];       // the same order in every thread of the row
-    if (ok && valid) {
+    if (ok && add_pv(n_mine - 1, corr_prev) && valid) {   // every tile's PV entered with its own tile's factor
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      bf16* dst = p.out + (size_t)(q0 + tok) * p.out_stride + (size_t)head * HD + half * OD;
+      bf16* dst = p.out + (size_t)(q0 + tok) * p.out_stride + (size_t)head * HD;
 #pragma unroll
-      for (int c = 0; c < OD; c += 8) {
+      for (int c = 0; c < HD; c += 8) {
         uint4 w;
         w.x = pack_bf16(o[c] * inv, o[c + 1] * inv); w.y = pack_bf16(o[c + 2] * inv, o[c + 3] * inv);
         w.z = pack_bf16(o[c + 4] * inv, o[c + 5] * inv); w.w = pack_bf16(o[c + 6] * inv, o[c + 7] * inv);
@@ -536,8 +523,8 @@ RLLM_API int rllm_attention_prefill_tc(const void* q, int q_stride, const void* 
   if ((page_size & (page_size - 1)) == 0) { p.page_shift = 0; while ((1 << p.page_shift) < page_size) ++p.page_shift; }
   p.window = window; p.scale_log2e = scale * 1.4426950408889634f; p.err = err;
   const int G = nh / nkv;
-  p.row_tiles = (max_q_len * G + PM - 1) / PM; p.num_seqs = num_seqs;
-  const long long items = (long long)p.row_tiles * nkv * num_seqs;
+  p.row_pairs = (max_q_len * G + RT * PM - 1) / (RT * PM); p.num_seqs = num_seqs;
+  const long long items = (long long)p.row_pairs * nkv * num_seqs;
   if (items > 2147483647LL) return ERR_TOO_LARGE;
   int sms = sm_count;
   if (sms <= 0) {
