@@ -14,10 +14,13 @@
 //               K 128 keys) with P read from shared memory and V as it lies in the cache tile (an
 //               MN-major operand: the contraction runs over key rows);
 //   warps 4..7  the softmax of the first row tile, one thread per row; warps 8..11 of the second.
-//               A thread reads its row of S from TMEM twice, 32 keys at a time: once for the
-//               maximum, once for exp2, the sum and P as bf16 in the swizzled layout of an A
-//               operand. Between the two it adds the PV of the tile before (read from TMEM) into
-//               the row's 64 output values in registers, rescaled when the maximum moved.
+//               A thread reads its row of S (128 scores) from TMEM, takes the maximum, exp2 and
+//               the sum in float and writes P as bf16 in the swizzled layout of an A operand.
+//               The row's output stays in TMEM, where PV of tile after tile is added up. The
+//               exponentials are taken against a maximum that is moved only when the true one
+//               has grown by more than 2^8 since (P then stays below 2^8, which bf16 holds as
+//               well as values below 1); when it moves, the thread scales its row of the output
+//               in TMEM (tcgen05.ld / st) before the next PV is added.
 // The (row tile, K tile) steps are numbered k = 0, 1, ... in the order A0 B0 A1 B1 ...; S of step k
 // lands in accumulator k % 3, so while both row tiles are in their softmax the scores of the step
 // after are computed already, and a row tile that has written its P goes on at once: the four warp
@@ -33,6 +36,7 @@
 #include "common.cuh"
 #include "sm100.cuh"
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 using namespace rllm;
@@ -49,6 +53,9 @@ constexpr int MMA_WARP = LOADERS;
 constexpr int SOFTMAX_WARP0 = LOADERS + 1;      // a multiple of 4: warp w reads TMEM lanes 32 (w % 4) ...
 static_assert(SOFTMAX_WARP0 % 4 == 0, "softmax warp w must own TMEM lane quadrant w % 4");
 constexpr int THREADS = (LOADERS + 1 + 4 * RT) * 32;
+// registers per thread: 168 each at launch (65,536 / 384, in eights); then 4 warps keep 56 and 8 warps have 224
+constexpr int REGS_LOW = 56, REGS_HIGH = 224;
+static_assert(SOFTMAX_WARP0 * 32 * REGS_LOW + 4 * RT * 32 * REGS_HIGH <= 168 * THREADS, "more registers than the launch has");
 constexpr int TILE_BYTES = PN * HD * 2;          // 16 KB: one K or V tile, one row tile of Q
 constexpr int P_BYTES = PM * PN * 2;             // 32 KB: two 64-key sub-tiles of 16 KB
 constexpr int KVS = LOADERS;     // K/V stages. Without TMA loader warp w always fills stage w (tiles w, w + KVS, ...),
@@ -99,7 +106,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                        const PfParams p) {
   extern __shared__ uint8_t pf_smem_raw[];
-  __shared__ __align__(8) uint64_t kv_full[KVS], kv_empty[KVS], s_full[SB], p_full[RT], pv_full[RT];
+  __shared__ __align__(8) uint64_t kv_full[KVS], kv_empty[KVS], s_full[SB], p_full[RT], pv_full[RT], q_full;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -131,6 +138,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   // themselves: items are numbered from the row tiles that see the most keys down, and round r
   // gives CTA c item r * C + c, or r * C + (C - 1 - c) in odd rounds, so that every CTA gets a
   // like share of long and short ones.
+  // The warps 0..3 (loaders, products) need few registers, the softmax warps many (a row of 128
+  // scores each): the first warpgroup gives registers up, the other two take them, and each side
+  // walks the items in its own copy of the loop (the block-wide barriers are the same ones).
+  auto walk = [&](auto softmax_side) {
+  constexpr bool SOFTMAX = decltype(softmax_side)::value;
   const int items = p.row_pairs * p.nkv * p.num_seqs;
   for (int round = 0;; ++round) {
   const int item = round * (int)gridDim.x + ((round & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
@@ -142,6 +154,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     for (int i = 0; i < KVS; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
     for (int i = 0; i < SB; ++i) mbar_init(&s_full[i], 1);
     for (int i = 0; i < RT; ++i) { mbar_init(&p_full[i], 4); mbar_init(&pv_full[i], 1); }
+    mbar_init(&q_full, RT);
     fence_barrier_init();
   }
   __syncthreads();
@@ -168,12 +181,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   // step k is (row tile, K tile) = (k & 1, k >> 1) while both row tiles have tiles left, then the later one alone
   const int n_both = min(n_t[0], n_t[1]), g_long = n_t[1] > n_t[0] ? 1 : 0, n_steps = n_t[0] + n_t[1];
 
-  // the Q rows of both row tiles, rows beyond the sequence zero (one warp, before its first K/V tile)
-  auto load_q = [&]() {
+  // Q rows r0 .. r0 + n - 1 of the item (one warp), rows beyond the sequence zero
+  auto load_q = [&](int r0, int n) {
     const int ch = lane & 7, rbase = lane >> 3;
 #pragma unroll 4
-    for (int i = 0; i < RT * 32; ++i) {
-      const int r = rbase + 4 * i;
+    for (int i = 0; i < n / 4; ++i) {
+      const int r = r0 + rbase + 4 * i;
       const int row = tile0 * PM + r;
       const bool valid = row < rows_total;
       const int tok = valid ? row / G : 0, head = kvh * G + (valid ? row % G : 0);
@@ -182,6 +195,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     }
   };
 
+  if constexpr (!SOFTMAX) {
   if (warp < LOADERS && TMA) {
     // ------------------------------------------------------------ loader (TMA): warp 0 alone, tile after tile.
     // Lane c looks up the page of the tile's c-th copy; lane 0 tells the stage's barrier how many
@@ -200,13 +214,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
           }
           if (__shfl_sync(0xffffffffu, w_ok, 0) == 0) break;
         }
-        if (t == 0) {
-          load_q();                                         // landed before the first tile is announced
-          cp_async_commit();
-          cp_async_wait<0>();
-          fence_proxy_async();
-          __syncwarp();
-        }
         const int j = kv_begin + t * PN + lane * p.box_rows;            // first key of this lane's copy
         const bool mine = lane < copies && j < kv_len;
         const int page = mine ? __ldg(bt + (j >> p.page_shift)) : 0;
@@ -220,6 +227,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
           tma_load_3d(v_s + dst, &tmap_v, &kv_full[s], 0, off, page * p.nkv + kvh);
         }
       }
+    } else if (warp - 1 < RT) {
+      // warps 1 and 2: the Q rows of one row tile each, meanwhile
+      if (n_t[warp - 1] > 0) {
+        load_q((warp - 1) * PM, PM);
+        cp_async_commit();
+        cp_async_wait<0>();
+        fence_proxy_async();
+        __syncwarp();
+      }
+      if (lane == 0) mbar_arrive(&q_full);
     }
   } else if (warp < LOADERS) {
     // ------------------------------------------------------------ loaders (any page size): warp w fetches the
@@ -237,7 +254,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         }
         if (__shfl_sync(0xffffffffu, w_ok, 0) == 0) break;
       }
-      if (t == 0) load_q();
+      if (t == 0) load_q(0, RT * PM);                     // lands with the tile, announced by its barrier
       const int j0 = kv_begin + t * PN;
       const uint32_t kd = k_s + (uint32_t)s * TILE_BYTES, vd = v_s + (uint32_t)s * TILE_BYTES;
 #pragma unroll 1
@@ -291,6 +308,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
           umma_bf16(tmem_base + S_COL + (uint32_t)(k % SB) * PN, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), id_s, kk > 0);
         umma_commit(&s_full[k % SB]);
       };
+      if (TMA && !mbar_wait(&q_full, 0u, &abort_flag)) { abort_flag = 1; record_failure(p.err, 27, 0); ok = false; }
+      tc_fence_after();
       for (int k = 0; k < SB && k < n_steps && ok; ++k) issue_s(k);
       for (int k = 0; k < n_steps && ok; ++k) {
         int g, t;
@@ -306,7 +325,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
           // P: K-major, two 64-key sub-tiles of 16 KB; V: MN-major, 16 key rows = 2 KB per step
           const uint64_t dp = umma_desc_sw128(pa + (uint32_t)(ks >> 2) * TILE_BYTES) + (uint64_t)((ks & 3) * 2);
           const uint64_t dv = umma_desc_sw128(va + (uint32_t)ks * 2048u);
-          umma_bf16(tmem_base + PV_COL + (uint32_t)g * HD, dp, dv, id_pv, ks > 0);
+          umma_bf16(tmem_base + PV_COL + (uint32_t)g * HD, dp, dv, id_pv, t > 0 || ks > 0);    // added up over the tiles
         }
         umma_commit(&pv_full[g]);
         if (g == 1 || t >= n_both) umma_commit(&kv_empty[t % KVS]);     // the last reader of this K and V stage
@@ -318,7 +337,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
           abort_flag = 1; record_failure(p.err, 26, t); ok = false;
         }
     }
-  } else if (n_t[(warp - SOFTMAX_WARP0) >> 2] > 0) {
+  }
+  } else {
+  if (n_t[(warp - SOFTMAX_WARP0) >> 2] > 0) {
     // ------------------------------------------------------------ softmax warps: one thread per row
     const int g = (warp - SOFTMAX_WARP0) >> 2;           // the row tile
     const int n_mine = n_t[g];
@@ -331,13 +352,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     const int lo = p.window > 0 ? pos - p.window + 1 : 0;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     const uint32_t pv_addr = lane_addr + PV_COL + (uint32_t)g * HD;
-    uint32_t s_addr = 0;                                  // this step's S accumulator
     const uint32_t prow = p_s + (uint32_t)g * P_BYTES + (uint32_t)(r * 128);
     const float sl = p.scale_log2e;
-    float o[HD];
-#pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.f;
-    float m = -INFINITY, l = 0.f, corr_prev = 1.f;
+    float m = -INFINITY, l = 0.f;       // m: what the exponentials are taken against, up to 2^8 behind the true maximum
     bool ok = true;
 
     auto wait_on = [&](uint64_t* bar, uint32_t parity, int role, int t) -> bool {
@@ -345,73 +362,74 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
       if (!got) { abort_flag = 1; record_failure(p.err, role, t); }
       return __all_sync(0xffffffffu, got);
     };
-    // 64 scores of the row: keys jc .. jc + 63 of the tile, the hidden ones -inf
-    auto scores = [&](int jc, uint32_t col, uint32_t (&a)[32], uint32_t (&b)[32]) {
-      tmem_ld32(s_addr + col, a);
-      tmem_ld32(s_addr + col + 32, b);
-      tmem_ld_wait();
-      if (!valid || jc + 63 > pos || jc < lo) {           // some key is hidden from this row
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (!(valid && jc + i <= pos && jc + i >= lo)) a[i] = 0xff800000u;
-          if (!(valid && jc + 32 + i <= pos && jc + 32 + i >= lo)) b[i] = 0xff800000u;
-        }
-      }
-    };
-    auto add_pv = [&](int t, float corr) -> bool {        // O = O * corr + PV(t)
-      if (!wait_on(&pv_full[g], (uint32_t)t & 1u, 25, t)) return false;
-      tc_fence_after();
-      uint32_t a[32], b[32];
-      tmem_ld32(pv_addr, a);
-      tmem_ld32(pv_addr + 32, b);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        o[i] = fmaf(o[i], corr, __uint_as_float(a[i]));
-        o[32 + i] = fmaf(o[32 + i], corr, __uint_as_float(b[i]));
-      }
-      tc_fence_before();
-      return true;
-    };
 
     for (int t = 0; t < n_mine; ++t) {
       const int j0 = kv_begin + t * PN;
       const int k = t < n_both ? 2 * t + g : 2 * n_both + (t - n_both);
-      s_addr = lane_addr + S_COL + (uint32_t)(k % SB) * PN;
+      const uint32_t s_addr = lane_addr + S_COL + (uint32_t)(k % SB) * PN;      // this step's S accumulator
       if (!wait_on(&s_full[k % SB], (uint32_t)(k / SB) & 1u, 24, t)) { ok = false; break; }
       tc_fence_after();
-      // ---- first reading: the row's maximum
-      float mx = -INFINITY;
+      // ---- the row's 128 scores, the hidden ones -inf, and their maximum
+      uint32_t v[4][32];
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t a[32], b[32];
-        scores(j0 + 64 * hf, 64 * hf, a, b);
+      for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + 32 * c, v[c]);
+      tmem_ld_wait();
+      if (!valid || j0 + PN - 1 > pos || j0 < lo) {        // some key is hidden from this row
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(a[i]), __uint_as_float(b[i])));
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int j = j0 + 32 * c + i;
+            if (!(valid && j <= pos && j >= lo)) v[c][i] = 0xff800000u;
+          }
       }
-      const float m_new = fmaxf(m, mx * sl);              // the scale is positive: it commutes with max
-      const float use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = fast_exp2(m - use);              // exp2(-inf) = 0
-      m = m_new;
-      l *= corr;
-      // ---- the tile before this one: its PV is ready by now (and has read P, which is written next)
-      if (t > 0 && !add_pv(t - 1, corr_prev)) { ok = false; break; }
-      // ---- second reading: exponentials, their sum, P as bf16 into the A-operand layout
+      float mq[4];                                        // four chains side by side, not one of 64 links
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {                    // a 64-key sub-tile of 16 KB each
-        uint32_t a[32], b[32];
-        scores(j0 + 64 * hf, 64 * hf, a, b);
-        const uint32_t base = prow + (uint32_t)hf * TILE_BYTES;
+      for (int c = 0; c < 4; ++c) {
+        mq[c] = -INFINITY;
 #pragma unroll
-        for (int q8 = 0; q8 < 8; ++q8) {                  // 8 keys = one 16-byte chunk
+        for (int i = 0; i < 32; i += 2) mq[c] = fmax3(mq[c], __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]));
+      }
+      const float mx = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
+      const float cand = fmaxf(m, mx * sl);               // the scale is positive: it commutes with max
+      const bool move = cand > m + 8.f;                   // also the first visible key (m = -inf)
+      float corr = 1.f;
+      if (move) { corr = fast_exp2(m - cand); m = cand; l *= corr; }      // exp2(-inf) = 0
+      if (t > 0) {
+        // the PV of the tile before is complete: P may be written again, the output may be touched
+        if (!wait_on(&pv_full[g], (uint32_t)(t - 1) & 1u, 25, t)) { ok = false; break; }
+        if (__any_sync(0xffffffffu, move)) {
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < HD / 16; ++c) {
+            uint32_t ov[16];
+            tmem_ld16(pv_addr + 16 * c, ov);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+            tmem_st16(pv_addr + 16 * c, ov);
+          }
+          tmem_st_wait();
+        }
+      }
+      // ---- exponentials, their sum, P as bf16 into the A-operand layout
+      const float use = (m == -INFINITY) ? 0.f : m;
+      float lq[8];                                        // partial sums side by side, added up in a fixed order
+#pragma unroll
+      for (int i = 0; i < 8; ++i) lq[i] = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t base = prow + (uint32_t)(c >> 1) * TILE_BYTES;      // a 64-key sub-tile of 16 KB
+#pragma unroll
+        for (int q8 = 0; q8 < 4; ++q8) {                  // 8 keys = one 16-byte chunk
           float e[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const uint32_t sv = q8 < 4 ? a[8 * q8 + i] : b[8 * (q8 - 4) + i];
-            e[i] = fast_exp2(fmaf(__uint_as_float(sv), sl, -use));        // hidden keys hold -inf: 0
-            l += e[i];
+            e[i] = fast_exp2(fmaf(__uint_as_float(v[c][8 * q8 + i]), sl, -use));      // hidden keys hold -inf: 0
+            lq[i] += e[i];
           }
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + (uint32_t)((q8 ^ (r & 7)) << 4)),
+          const int ch = (c & 1) * 4 + q8;
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + (uint32_t)((ch ^ (r & 7)) << 4)),
                        "r"(pack_bf16(e[0], e[1])), "r"(pack_bf16(e[2], e[3])), "r"(pack_bf16(e[4], e[5])),
                        "r"(pack_bf16(e[6], e[7])) : "memory");
         }
@@ -420,21 +438,42 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
       fence_proxy_async();                                // P is read by the tensor core's proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[g]);
-      corr_prev = corr;
+      l += ((lq[0] + lq[1]) + (lq[2] + lq[3])) + ((lq[4] + lq[5]) + (lq[6] + lq[7]));
     }
-    if (ok && add_pv(n_mine - 1, corr_prev) && valid) {   // every tile's PV entered with its own tile's factor
+    if (ok && wait_on(&pv_full[g], (uint32_t)(n_mine - 1) & 1u, 25, n_mine)) {
+      tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = p.out + (size_t)(q0 + tok) * p.out_stride + (size_t)head * HD;
 #pragma unroll
-      for (int c = 0; c < HD; c += 8) {
-        uint4 w;
-        w.x = pack_bf16(o[c] * inv, o[c + 1] * inv); w.y = pack_bf16(o[c + 2] * inv, o[c + 3] * inv);
-        w.z = pack_bf16(o[c + 4] * inv, o[c + 5] * inv); w.w = pack_bf16(o[c + 6] * inv, o[c + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + c) = w;
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t ov[32];
+        tmem_ld32(pv_addr + 32 * c, ov);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack_bf16(__uint_as_float(ov[i]) * inv, __uint_as_float(ov[i + 1]) * inv);
+            w.y = pack_bf16(__uint_as_float(ov[i + 2]) * inv, __uint_as_float(ov[i + 3]) * inv);
+            w.z = pack_bf16(__uint_as_float(ov[i + 4]) * inv, __uint_as_float(ov[i + 5]) * inv);
+            w.w = pack_bf16(__uint_as_float(ov[i + 6]) * inv, __uint_as_float(ov[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + 32 * c + i) = w;
+          }
+        }
       }
+      tc_fence_before();
     }
   }
+  }
   }   // items
+  };
+  if (warp < SOFTMAX_WARP0) {
+    regs_give_up<REGS_LOW>();
+    walk(std::false_type{});
+  } else {
+    regs_take<REGS_HIGH>();
+    walk(std::true_type{});
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
