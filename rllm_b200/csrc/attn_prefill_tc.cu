@@ -42,6 +42,9 @@
 using namespace rllm;
 using namespace sm100;
 
+#ifndef PF_EXPERIMENT
+#define PF_EXPERIMENT 0
+#endif
 namespace {
 
 constexpr int PM = 128;          // rows per row tile
@@ -58,9 +61,10 @@ constexpr int REGS_LOW = 56, REGS_HIGH = 224;
 static_assert(SOFTMAX_WARP0 * 32 * REGS_LOW + 4 * RT * 32 * REGS_HIGH <= 168 * THREADS, "more registers than the launch has");
 constexpr int TILE_BYTES = PN * HD * 2;          // 16 KB: one K or V tile, one row tile of Q
 constexpr int P_BYTES = PM * PN * 2;             // 32 KB: two 64-key sub-tiles of 16 KB
-constexpr int KVS = LOADERS;     // K/V stages. Without TMA loader warp w always fills stage w (tiles w, w + KVS, ...),
-                                 // so its waits on that stage's barriers follow one another phase by phase; a warp
-                                 // that moved between stages could be two phases ahead, which a parity cannot tell
+constexpr int KVS = 4;           // K/V stages with TMA (one loader, tile after tile). Without TMA only LOADERS of them
+                                 // are used: loader warp w always fills stage w (tiles w, w + 3, ...), so its waits
+                                 // on that stage's barriers follow one another phase by phase; a warp that moved
+                                 // between stages could be two phases ahead, which a parity cannot tell
 constexpr int SMEM_BYTES = 1024 + TILE_BYTES * (RT + 2 * KVS) + RT * P_BYTES;    // Q[2], K[KVS], V[KVS], P[2]
 constexpr int SB = 3;            // S accumulators: one per row tile in its softmax, one being computed ahead
 constexpr int TMEM_COLS = 512;   // S[3] x 128 + PV[2] x 64
@@ -79,6 +83,9 @@ struct PfParams {
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {          // exp2(-inf) = 0
+#if PF_EXPERIMENT == 1
+  return x * 0.001f;
+#endif
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
@@ -106,7 +113,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                        const PfParams p) {
   extern __shared__ uint8_t pf_smem_raw[];
-  __shared__ __align__(8) uint64_t kv_full[KVS], kv_empty[KVS], s_full[SB], p_full[RT], pv_full[RT], q_full;
+  __shared__ __align__(8) uint64_t kv_full[KVS], kv_empty[KVS], s_full[SB], s_free[SB], p_full[RT], pv_full[RT], q_full;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -116,6 +123,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   const uint32_t k_s = q_s + RT * TILE_BYTES, v_s = k_s + KVS * TILE_BYTES, p_s = v_s + KVS * TILE_BYTES;
 
   const int G = p.nh / p.nkv;
+  constexpr int NST = TMA ? KVS : LOADERS;              // K/V stages in use
   if (threadIdx.x == 0) abort_flag = 0;
   if (TMA) {
     // A copy brings whole pages: rows past a sequence's last key keep what the stage held before.
@@ -152,7 +160,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   __syncthreads();                                      // everybody has left the item before
   if (threadIdx.x == 0) {
     for (int i = 0; i < KVS; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < SB; ++i) mbar_init(&s_full[i], 1);
+    for (int i = 0; i < SB; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4); }
     for (int i = 0; i < RT; ++i) { mbar_init(&p_full[i], 4); mbar_init(&pv_full[i], 1); }
     mbar_init(&q_full, RT);
     fence_barrier_init();
@@ -196,20 +204,68 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   };
 
   if constexpr (!SOFTMAX) {
+  // ---- the products. Step k is (row tile g, K tile t); its S lands in accumulator k % 3.
+  constexpr uint32_t id_s = idesc(PM, PN, false);
+  constexpr uint32_t id_pv = idesc(PM, HD, true);
+  auto step = [&](int k, int& g, int& t) {
+    if (k < 2 * n_both) { g = k & 1; t = k >> 1; } else { g = g_long; t = n_both + (k - 2 * n_both); }
+  };
+  // descriptors move with the address: 16 bytes are one unit of the start-address field
+  const uint64_t dq0 = umma_desc_sw128(q_s), dk0 = umma_desc_sw128(k_s), dv0 = umma_desc_sw128(v_s),
+                 dp0 = umma_desc_sw128(p_s);
+  auto issue_s = [&](int k, bool& ok) {                 // S = Q K^T of step k (one thread)
+    int g, t;
+    step(k, g, t);
+    const int ks = t % NST;
+    if (k >= SB) {
+      // the accumulator's scores of step k - 3 are in their threads' registers
+      if (!mbar_wait(&s_free[k % SB], (uint32_t)(k / SB - 1) & 1u, &abort_flag)) {
+        abort_flag = 1; record_failure(p.err, 28, k); ok = false; return;
+      }
+    }
+    if (!mbar_wait(&kv_full[ks], (uint32_t)(t / NST) & 1u, &abort_flag)) {
+      abort_flag = 1; record_failure(p.err, 22, t); ok = false; return;
+    }
+    tc_fence_after();
+    const uint64_t dq = dq0 + (uint64_t)(g * (TILE_BYTES >> 4)), dk = dk0 + (uint64_t)(ks * (TILE_BYTES >> 4));
+    const uint32_t acc = tmem_base + S_COL + (uint32_t)(k % SB) * PN;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) umma_bf16(acc, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), id_s, kk > 0);
+    umma_commit(&s_full[k % SB]);
+  };
+  auto issue_pv = [&](int k, bool& ok) {                // PV of step k, added to the row tile's output (one thread)
+    int g, t;
+    step(k, g, t);
+    // P of this step is written (and the row tile's PV before is complete: its threads waited for it)
+    if (!mbar_wait(&p_full[g], (uint32_t)t & 1u, &abort_flag)) {
+      abort_flag = 1; record_failure(p.err, 23, t); ok = false; return;
+    }
+    tc_fence_after();
+    const uint64_t dp = dp0 + (uint64_t)(g * (P_BYTES >> 4)), dv = dv0 + (uint64_t)((t % NST) * (TILE_BYTES >> 4));
+    const uint32_t acc = tmem_base + PV_COL + (uint32_t)g * HD;
+#pragma unroll
+    for (int ks = 0; ks < PN / 16; ++ks) {
+      // P: K-major, two 64-key sub-tiles of 16 KB, 32 bytes per 16 keys; V: MN-major, 16 key rows = 2 KB per step
+      umma_bf16(acc, dp + (uint64_t)((ks >> 2) * (TILE_BYTES >> 4) + (ks & 3) * 2), dv + (uint64_t)(ks * (2048 >> 4)),
+                id_pv, t > 0 || ks > 0);
+    }
+    umma_commit(&pv_full[g]);
+    if (g == 1 || t >= n_both) umma_commit(&kv_empty[t % NST]);     // the last reader of this K and V stage
+  };
   if (warp < LOADERS && TMA) {
     // ------------------------------------------------------------ loader (TMA): warp 0 alone, tile after tile.
     // Lane c looks up the page of the tile's c-th copy; lane 0 tells the stage's barrier how many
     // bytes are coming; every lane with a page issues its two copies. Nothing waits for a tile to
-    // land: up to KVS tiles are on their way.
+    // land: up to NST tiles are on their way.
     if (warp == 0) {
       const int* bt = p.block_table + (size_t)seq * p.bt_stride;
       const int copies = PN / p.box_rows;                  // per tile and cache
       const uint32_t copy_bytes = (uint32_t)p.box_rows * HD * 2;
       for (int t = 0; t < n_tiles; ++t) {
-        const int s = t % KVS;
-        if (t >= KVS) {
+        const int s = t % NST;
+        if (t >= NST) {
           int w_ok = 1;
-          if (lane == 0 && !mbar_wait(&kv_empty[s], (uint32_t)(t / KVS - 1) & 1u, &abort_flag)) {
+          if (lane == 0 && !mbar_wait(&kv_empty[s], (uint32_t)(t / NST - 1) & 1u, &abort_flag)) {
             abort_flag = 1; record_failure(p.err, 21, t); w_ok = 0;
           }
           if (__shfl_sync(0xffffffffu, w_ok, 0) == 0) break;
@@ -237,19 +293,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         __syncwarp();
       }
       if (lane == 0) mbar_arrive(&q_full);
+      if (warp == 2 && lane == 0 && n_steps > 0) {
+        // ... and warp 2 then issues the S products, as far ahead as accumulators are free
+        bool ok = true;
+        if (!mbar_wait(&q_full, 0u, &abort_flag)) { abort_flag = 1; record_failure(p.err, 27, 0); ok = false; }
+        for (int k = 0; k < n_steps && ok; ++k) issue_s(k, ok);
+      }
     }
   } else if (warp < LOADERS) {
     // ------------------------------------------------------------ loaders (any page size): warp w fetches the
     // tiles w, w + 3, ... whole, waits until they have landed and announces them at once, so a
-    // tile is ready long before its turn (up to KVS tiles are on the way, from different warps).
+    // tile is ready long before its turn (up to NST tiles are on the way, from different warps).
     const int* bt = p.block_table + (size_t)seq * p.bt_stride;
     const int ch = lane & 7;                              // this lane's 16-byte chunk of a 128-byte row
     const int rbase = lane >> 3;                          // its rows: rbase + 4 i, i < 32
     for (int t = warp; t < n_tiles; t += LOADERS) {
-      const int s = t % KVS;
-      if (t >= KVS) {
+      const int s = t % NST;
+      if (t >= NST) {
         int w_ok = 1;
-        if (lane == 0 && !mbar_wait(&kv_empty[s], (uint32_t)(t / KVS - 1) & 1u, &abort_flag)) {
+        if (lane == 0 && !mbar_wait(&kv_empty[s], (uint32_t)(t / NST - 1) & 1u, &abort_flag)) {
           abort_flag = 1; record_failure(p.err, 21, t); w_ok = 0;
         }
         if (__shfl_sync(0xffffffffu, w_ok, 0) == 0) break;
@@ -285,55 +347,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
       if (lane == 0) mbar_arrive(&kv_full[s]);
     }
   } else if (warp == MMA_WARP) {
-    // ------------------------------------------------------------ the products (one thread), the row tiles in turn
+    // ------------------------------------------------------------ the PV products (one thread); without
+    // TMA the loaders are all busy and this thread issues S as well, three steps ahead
     if (lane == 0 && n_tiles > 0) {
-      constexpr uint32_t id_s = idesc(PM, PN, false);
-      constexpr uint32_t id_pv = idesc(PM, HD, true);
       bool ok = true;
-      auto step = [&](int k, int& g, int& t) {
-        if (k < 2 * n_both) { g = k & 1; t = k >> 1; } else { g = g_long; t = n_both + (k - 2 * n_both); }
-      };
-      auto issue_s = [&](int k) {                         // S of step k into accumulator k % 3
-        int g, t;
-        step(k, g, t);
-        const int ks = t % KVS;
-        if (!mbar_wait(&kv_full[ks], (uint32_t)(t / KVS) & 1u, &abort_flag)) {
-          abort_flag = 1; record_failure(p.err, 22, t); ok = false; return;
-        }
-        tc_fence_after();
-        const uint64_t dq = umma_desc_sw128(q_s + (uint32_t)g * TILE_BYTES);
-        const uint64_t dk = umma_desc_sw128(k_s + (uint32_t)ks * TILE_BYTES);
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk)
-          umma_bf16(tmem_base + S_COL + (uint32_t)(k % SB) * PN, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), id_s, kk > 0);
-        umma_commit(&s_full[k % SB]);
-      };
-      if (TMA && !mbar_wait(&q_full, 0u, &abort_flag)) { abort_flag = 1; record_failure(p.err, 27, 0); ok = false; }
-      tc_fence_after();
-      for (int k = 0; k < SB && k < n_steps && ok; ++k) issue_s(k);
+      if (!TMA)
+        for (int k = 0; k < SB && k < n_steps && ok; ++k) issue_s(k, ok);
       for (int k = 0; k < n_steps && ok; ++k) {
-        int g, t;
-        step(k, g, t);
-        // P of this step is written (so its S is read, and the row tile's PV before is read too)
-        if (!mbar_wait(&p_full[g], (uint32_t)t & 1u, &abort_flag)) {
-          abort_flag = 1; record_failure(p.err, 23, t); ok = false; break;
-        }
-        tc_fence_after();
-        const uint32_t pa = p_s + (uint32_t)g * P_BYTES, va = v_s + (uint32_t)(t % KVS) * TILE_BYTES;
-#pragma unroll
-        for (int ks = 0; ks < PN / 16; ++ks) {
-          // P: K-major, two 64-key sub-tiles of 16 KB; V: MN-major, 16 key rows = 2 KB per step
-          const uint64_t dp = umma_desc_sw128(pa + (uint32_t)(ks >> 2) * TILE_BYTES) + (uint64_t)((ks & 3) * 2);
-          const uint64_t dv = umma_desc_sw128(va + (uint32_t)ks * 2048u);
-          umma_bf16(tmem_base + PV_COL + (uint32_t)g * HD, dp, dv, id_pv, t > 0 || ks > 0);    // added up over the tiles
-        }
-        umma_commit(&pv_full[g]);
-        if (g == 1 || t >= n_both) umma_commit(&kv_empty[t % KVS]);     // the last reader of this K and V stage
-        if (k + SB < n_steps) issue_s(k + SB);            // its accumulator is the one this step's softmax has just left
+        issue_pv(k, ok);
+        if (!TMA && ok && k + SB < n_steps) issue_s(k + SB, ok);
       }
       // nothing of this item may still be on its way to a barrier when the next item sets them up again
-      for (int t = max(0, n_tiles - KVS); t < n_tiles && ok; ++t)
-        if (!mbar_wait(&kv_empty[t % KVS], (uint32_t)(t / KVS) & 1u, &abort_flag)) {
+      for (int t = max(0, n_tiles - NST); t < n_tiles && ok; ++t)
+        if (!mbar_wait(&kv_empty[t % NST], (uint32_t)(t / NST) & 1u, &abort_flag)) {
           abort_flag = 1; record_failure(p.err, 26, t); ok = false;
         }
     }
@@ -372,8 +398,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
       // ---- the row's 128 scores, the hidden ones -inf, and their maximum
       uint32_t v[4][32];
 #pragma unroll
+#if PF_EXPERIMENT == 2
+      for (int c = 0; c < 4; ++c) for (int i = 0; i < 32; ++i) v[c][i] = __float_as_uint((float)(i + c + t) * 0.01f);
+#else
       for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + 32 * c, v[c]);
       tmem_ld_wait();
+#endif
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[k % SB]);        // the accumulator may take the scores of step k + 3
       if (!valid || j0 + PN - 1 > pos || j0 < lo) {        // some key is hidden from this row
 #pragma unroll
         for (int c = 0; c < 4; ++c)
@@ -435,7 +468,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         }
       }
       tc_fence_before();
+#if PF_EXPERIMENT != 3
       fence_proxy_async();                                // P is read by the tensor core's proxy
+#endif
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[g]);
       l += ((lq[0] + lq[1]) + (lq[2] + lq[3])) + ((lq[4] + lq[5]) + (lq[6] + lq[7]));
