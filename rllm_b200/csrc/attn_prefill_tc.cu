@@ -42,9 +42,6 @@
 using namespace rllm;
 using namespace sm100;
 
-#ifndef PF_EXPERIMENT
-#define PF_EXPERIMENT 0
-#endif
 namespace {
 
 constexpr int PM = 128;          // rows per row tile
@@ -83,9 +80,6 @@ struct PfParams {
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {          // exp2(-inf) = 0
-#if PF_EXPERIMENT == 1
-  return x * 0.001f;
-#endif
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
@@ -157,6 +151,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   if (item >= items) break;
   const int tile0 = (p.row_pairs - 1 - item / (p.nkv * p.num_seqs)) * RT;      // first of the item's row tiles
   const int kvh = item % p.nkv, seq = (item / p.nkv) % p.num_seqs;
+  // an item beyond its sequence's rows (a short portion beside long ones) is skipped by all threads alike
+  if (tile0 * PM >= (p.cu_q[seq + 1] - p.cu_q[seq]) * G) continue;
   __syncthreads();                                      // everybody has left the item before
   if (threadIdx.x == 0) {
     for (int i = 0; i < KVS; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
@@ -398,12 +394,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
       // ---- the row's 128 scores, the hidden ones -inf, and their maximum
       uint32_t v[4][32];
 #pragma unroll
-#if PF_EXPERIMENT == 2
-      for (int c = 0; c < 4; ++c) for (int i = 0; i < 32; ++i) v[c][i] = __float_as_uint((float)(i + c + t) * 0.01f);
-#else
       for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + 32 * c, v[c]);
       tmem_ld_wait();
-#endif
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[k % SB]);        // the accumulator may take the scores of step k + 3
@@ -468,9 +460,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         }
       }
       tc_fence_before();
-#if PF_EXPERIMENT != 3
       fence_proxy_async();                                // P is read by the tensor core's proxy
-#endif
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[g]);
       l += ((lq[0] + lq[1]) + (lq[2] + lq[3])) + ((lq[4] + lq[5]) + (lq[6] + lq[7]));

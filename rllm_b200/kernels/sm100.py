@@ -237,7 +237,7 @@ def attention_fa(q, kcache, vcache, cu_q, kv_lens, block_table, num_tokens, max_
     return out
 
 
-TC_ATTENTION_MIN_KEYS = int(os.environ.get("RLLM_B200_TC_ATTENTION_MIN_KEYS", "2048"))
+TC_ATTENTION_MIN_KEYS = int(os.environ.get("RLLM_B200_TC_ATTENTION_MIN_KEYS", "1024"))
 
 
 def prefill_tc_supported(q: torch.Tensor, kcache: torch.Tensor) -> bool:
@@ -321,7 +321,7 @@ def attention(q, cache, ctx, nh, scale, window):
     if ctx.max_q_len * (nh // nkv) >= 128 and ctx.max_kv_len >= TC_ATTENTION_MIN_KEYS \
             and prefill_tc_supported(q, cache.k) and os.environ.get("RLLM_B200_NO_TC_ATTENTION") != "1":
         # long portions over long contexts: tiles of 128 (token, head) rows x 128 keys on the tcgen05
-        # tensor cores (measured level with the mma.sync kernel at 2,048 keys, ahead of it beyond, behind it below)
+        # tensor cores (measured level with the mma.sync kernel at 512 keys, 1.4 x at 1,024, 2.3 x at 2,048)
         return attention_prefill_tc(q, cache.k, cache.v, ctx.cu_q, ctx.kv_lens, cache.block_table, ctx.max_q_len,
                                     nh, scale, window)
     return attention_fa(q, cache.k, cache.v, ctx.cu_q, ctx.kv_lens, cache.block_table, ctx.num_tokens,
