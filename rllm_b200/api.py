@@ -9,6 +9,8 @@ mirrors the reference's `InferenceEngine::step` loop (src/engine/mod.rs:82-117):
 from __future__ import annotations
 
 import os
+
+import torch
 from dataclasses import replace
 
 from .engine.factory import load_engine, parse_dtype, random_engine
@@ -36,6 +38,11 @@ class LLM:
         self.scheduler = Scheduler(self.engine.cache, max_active, max_tokens_per_step, max_chunk)
         self.sampler = Sampler(self.engine.backend)
         self._tokenizer = None
+        # a step that was launched ahead: (plan, its drawn tokens: device tensor, host copy, event)
+        self._ahead = None
+        self._pinned = []                        # host buffers the drawn tokens are copied into, in turn
+        self.run_ahead = os.environ.get("RLLM_B200_NO_RUN_AHEAD") != "1"
+        self.steps_ahead = 0
 
     # ---- the reference's engine loop
     def add_request(self, prompt_token_ids: list[int], params: SamplingParams | None = None) -> int:
@@ -47,18 +54,56 @@ class LLM:
     def has_work(self) -> bool:
         return self.scheduler.has_work()
 
-    def step(self) -> list[StepOutput]:
-        """One scheduler step: plan, run the batch, sample, finish and free."""
-        plan, failed = self.scheduler.schedule(self.engine)
-        if not plan:
-            return failed
-        logits = self.engine.step(self.scheduler.entries(plan), keep=False)
+    def _launch(self, plan, feed=None, ahead: int = 0):
+        """Run the plan's batch and draw its tokens; returns them on the device (or None).
+        `ahead`: how many tokens each request is about to get that its `output` lacks."""
+        logits = self.engine.step(self.scheduler.entries(plan), keep=False, feed=feed)
         sampled = [p.request for p in plan if p.samples]
+        if not sampled:
+            return None
+        drawn = self.sampler.draw(logits, [r.params for r in sampled], [r.seed for r in sampled],
+                                  [len(r.output) + ahead for r in sampled], [r.output for r in sampled])
+        # their way to the host starts now, before anything else is put on the stream behind them
+        if not self._pinned:
+            n = max(self.scheduler.max_active, 1)
+            self._pinned = [torch.empty(n, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._pinned.reverse()
+        host = self._pinned[0][: drawn.numel()]
+        host.copy_(drawn, non_blocking=True)
+        arrived = torch.cuda.Event()
+        arrived.record()
+        return drawn, host, arrived
+
+    def step(self) -> list[StepOutput]:
+        """One scheduler step: plan, run the batch, sample, finish and free.
+
+        In the steady state of decoding the step after this one is launched before this one's
+        tokens are read (`Scheduler.plan_ahead`): its token ids go from the sampling kernel's
+        output into the step's metadata on the device, so the GPU does not wait while the host
+        reads the tokens, records them and plans. Each call still returns the tokens of exactly
+        one step; a request that met its end token has one unused position computed for it."""
+        failed: list[StepOutput] = []
+        if self._ahead is not None:
+            plan, drawn = self._ahead
+            self._ahead = None
+        else:
+            plan, failed = self.scheduler.schedule(self.engine)
+            if not plan:
+                return failed
+            drawn = self._launch(plan)
+        if self.run_ahead and drawn is not None:
+            nxt = self.scheduler.plan_ahead(plan)
+            if nxt is not None and self.engine.takes_feed(self.scheduler.entries(nxt)):
+                self._ahead = (nxt, self._launch(nxt, feed=drawn[0], ahead=1))
+                self.steps_ahead += 1
         tokens = []
-        if sampled:
-            tokens = self.sampler(logits, [r.params for r in sampled], [r.seed for r in sampled],
-                                  [len(r.output) for r in sampled], [r.output for r in sampled])
-        return failed + self.scheduler.advance(plan, tokens, self.engine)
+        if drawn is not None:
+            drawn[2].synchronize()               # this step's tokens only; the step ahead keeps running
+            tokens = drawn[1].tolist()
+        outs = failed + self.scheduler.advance(plan, tokens, self.engine)
+        if self._ahead is not None and all(p.request.finished for p in self._ahead[0]):
+            self._ahead = None                   # nobody is left to take its tokens
+        return outs
 
     # ---- whole generations
     def generate(self, prompts, params: SamplingParams | list[SamplingParams] | None = None,

@@ -129,6 +129,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   const int row = blockIdx.x;
   const float* x = logits + (size_t)row * V;
   const float T = temperature[row];
+  if (!(T > 0.f)) return;            // a greedy row: the caller has put its argmax into out[row] already
   const float invT = 1.f / T;
   const int tid = threadIdx.x;
 
@@ -231,7 +232,7 @@ RLLM_API int rllm_argmax(const float* logits, int R, int V, int* out, void* stre
 }
 
 // Per-row parameter arrays of length R; top_k / top_p / min_p may be null (off).
-// temperature must be > 0 (the caller sends temperature 0 to rllm_argmax).
+// A row whose temperature is not > 0 is left as it is: the caller runs rllm_argmax into `out` first.
 RLLM_API int rllm_sample(const float* logits, int R, int V, const float* temperature,
                          const int* top_k, const float* top_p, const float* min_p,
                          const float* uniform, int* out, void* stream) {

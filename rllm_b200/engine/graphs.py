@@ -138,7 +138,10 @@ class DecodeGraphs:
             raise RuntimeError(f"decode metadata could not be written (code {rc})")
         return rc > 0
 
-    def run(self, entries, rcs, keep: bool = True) -> torch.Tensor | None:
+    def run(self, entries, rcs, keep: bool = True, feed: torch.Tensor | None = None) -> torch.Tensor | None:
+        """Replay the graph of this shape. `feed`: int32 [S] on the device, the entries' token ids
+        (those in `entries` are then placeholders): the step can be launched before the host has
+        seen the tokens that the step before it drew."""
         eng = self.engine
         S = len(entries)
         key = (S, self._width(rcs))
@@ -159,6 +162,8 @@ class DecodeGraphs:
             slot.dev[: slot.head].copy_(slot.host[: slot.head], non_blocking=True)
             eng.h2d_bytes += 4 * slot.head
         slot.copied.record()
+        if feed is not None:
+            slot.dev[:S].copy_(feed)                # after the copy above, in stream order
         if slot.graph is None:
             self._capture(slot)
         slot.graph.replay()

@@ -228,12 +228,35 @@ class Scheduler:
         return plan, failed
 
     # ------------------------------------------------------------------ after the step ran
+    def plan_ahead(self, plan: list[Planned]) -> list[Planned] | None:
+        """The plan of the step after `plan`, made before `plan`'s tokens are known, or None if
+        that cannot be told yet. It can when `plan` is the steady state (nobody waits, everybody
+        decodes and is sampled), the next step is too unless a request meets its end-of-sequence
+        token, and nothing about a request's next step hangs on the token it is about to get: no
+        request reaches its token limit, none is penalised for tokens it has produced. The tokens
+        of the returned plan are placeholders; a request that did end in `plan` is passed over
+        when the step ahead is recorded (`advance`), its extra token dropped."""
+        if self.waiting or not plan or len(plan) != len(self.running) or len(plan) > self.max_tokens_per_step:
+            return None
+        for p, r in zip(plan, self.running):
+            if p.request is not r or not p.samples or len(p.tokens) != 1 or r.pending or r.finished:
+                return None
+            if len(r.output) + 2 > r.params.max_tokens or r.params.has_penalties:
+                return None                      # it ends with the coming token, or its draw needs the history
+        if not all(f >= len(plan) for f in self.cache.free_pages()):
+            return None
+        return [Planned(r, [0], True) for r in self.running]
+
     def advance(self, plan: list[Planned], tokens: list[int], executor=None) -> list[StepOutput]:
         """Record what the step stored and sampled; finish and free what is done. `tokens`
         are the sampled tokens of the planned requests with `samples`, in plan order."""
         outs, it = [], iter(tokens)
         for p in plan:
             req = p.request
+            if req.finished:                     # ended (or aborted) while this step was under way
+                if p.samples:
+                    next(it)
+                continue
             req.num_stored += len(p.tokens)
             if not req.decoding:
                 req.pending = req.pending[len(p.tokens):]

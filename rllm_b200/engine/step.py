@@ -201,16 +201,26 @@ class Engine:
         self.h2d_bytes += 4 * lay.total
         return self.make_context(dev, lay, q_lens, kv_lens, starts, [rc.state_slot for rc in rcs])
 
-    def step(self, entries: list[Entry], keep: bool = True) -> torch.Tensor | None:
+    def takes_feed(self, entries: list[Entry]) -> bool:
+        """Can this batch take its token ids from the device (`step(..., feed=)`)? Only steps that
+        replay a graph read their metadata from a buffer that outlives the call."""
+        return self.graphs is not None and all(e.request_id in self.cache.live for e in entries) \
+            and self.graphs.takes(entries, [self.cache.live[e.request_id] for e in entries])
+
+    def step(self, entries: list[Entry], keep: bool = True, feed: torch.Tensor | None = None) -> torch.Tensor | None:
         """Run one batch; returns float32 logits [wanted places, vocab] on the device, in
         the order of the entries and of each `want` (None if nothing is wanted).
         Raises OutOfPages, leaving every request as it was, if the pages do not suffice.
         `keep=False`: the caller reads the logits before the next step, so they may live
-        in a buffer that the next step overwrites (saves a copy)."""
+        in a buffer that the next step overwrites (saves a copy).
+        `feed`: the entries' token ids as an int32 tensor on the device, one per entry (see
+        `takes_feed`); the ids in `entries` are placeholders then."""
+        if feed is not None and not self.takes_feed(entries):
+            raise StepError("token ids can be fed from the device only to a step that replays a graph")
         rcs = self.prepare(entries)
         logits = None
         if self.graphs is not None and self.graphs.takes(entries, rcs):
-            logits = self.graphs.run(entries, rcs, keep)
+            logits = self.graphs.run(entries, rcs, keep, feed)
             self.graph_steps += 1
         else:
             ctx, rows = self.build_context(entries, rcs)

@@ -173,5 +173,5 @@ class Backend:
     def argmax(self, logits):
         return ops.argmax(logits)
 
-    def sample(self, logits, temperature, uniform, top_k=None, top_p=None, min_p=None):
-        return ops.sample(logits, temperature, uniform, top_k, top_p, min_p)
+    def sample(self, logits, temperature, uniform, top_k=None, top_p=None, min_p=None, out=None):
+        return ops.sample(logits, temperature, uniform, top_k, top_p, min_p, out=out)

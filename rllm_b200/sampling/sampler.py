@@ -17,17 +17,23 @@ class Sampler:
 
     def __call__(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int],
                  indices: list[int], histories: list[list[int]] | None = None) -> list[int]:
+        """The drawn tokens as a host list (waits for the device)."""
+        return self.draw(logits, params, seeds, indices, histories).tolist()
+
+    def draw(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int],
+             indices: list[int], histories: list[list[int]] | None = None) -> torch.Tensor:
         """logits float32 [R, V]; row r is drawn with params[r] and the uniform number of
-        (seeds[r], indices[r]). `histories[r]`: the tokens generated so far (for penalties)."""
+        (seeds[r], indices[r]). `histories[r]`: the tokens generated so far (for penalties).
+        Returns int32 [R] on the device; nothing here waits for it."""
         R = logits.shape[0]
         assert R == len(params) == len(seeds) == len(indices)
         if any(p.has_penalties for p in params):
             logits = self._penalise(logits, params, histories)
         be = self.backend
         if all(p.greedy for p in params):
-            return be.argmax(logits).tolist()
+            return be.argmax(logits)
         f32 = dict(dtype=torch.float32, device=self.device)
-        temp = torch.tensor([p.temperature if not p.greedy else 1.0 for p in params], **f32)
+        temp = torch.tensor([p.temperature if not p.greedy else 0.0 for p in params], **f32)
         u = torch.tensor([uniform(s, i) for s, i in zip(seeds, indices)], **f32)
         top_k = top_p = min_p = None
         if any(p.top_k > 0 for p in params):
@@ -36,11 +42,9 @@ class Sampler:
             top_p = torch.tensor([p.top_p for p in params], **f32)
         if any(p.min_p > 0.0 for p in params):
             min_p = torch.tensor([p.min_p for p in params], **f32)
-        drawn = be.sample(logits, temp, u, top_k, top_p, min_p).tolist()
-        if any(p.greedy for p in params):
-            best = be.argmax(logits).tolist()
-            drawn = [b if p.greedy else d for p, b, d in zip(params, best, drawn)]
-        return drawn
+        # greedy rows beside drawn ones: argmax of every row first; the draw skips rows of temperature 0
+        out = be.argmax(logits) if any(p.greedy for p in params) else None
+        return be.sample(logits, temp, u, top_k, top_p, min_p, out=out)
 
     def _penalise(self, logits, params, histories):
         """logit[token] -= frequency_penalty * count + presence_penalty for tokens already

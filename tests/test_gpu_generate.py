@@ -115,6 +115,48 @@ def test_long_decoding_and_first_tokens(dirs, dtype, tol):
     replay.compare(got, replay.plain_logits(dirs[name], {"a": toks}), tol, f"long decode {dtype}")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_change_nothing(dirs, dtype):
+    """In the steady state of decoding a step is launched before the tokens of the step before
+    it are read. The same requests with and without that: the same tokens, finish reasons and
+    step-by-step outputs, also when requests meet an end token or their limit at different
+    times, are drawn with a temperature, or are aborted half-way; and every page comes back."""
+    from rllm_b200.sampling import SamplingParams
+    name = "D"
+    cfg, _ = P.read_model_dir(dirs[name])
+    V = cfg["vocab_size"]
+    prompts = [tiny.random_prompt(n, V, 900 + n) for n in (5, 19, 33, 8)]
+    # a first run without limits tells which tokens come; some of them then serve as end tokens
+    free = llm(dirs[name], name, dtype, num_pages=64)
+    free.run_ahead = False
+    base = free.generate(prompts, SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True))
+    sps = [SamplingParams(temperature=0.0, max_tokens=40, eos_token_ids=(base[0][13],)),
+           SamplingParams(temperature=0.0, max_tokens=23),
+           SamplingParams(temperature=0.7, top_p=0.9, max_tokens=40, seed=5, eos_token_ids=(base[2][30],)),
+           SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)]
+
+    def run(ahead):
+        m = llm(dirs[name], name, dtype, num_pages=64)
+        m.run_ahead = ahead
+        rids = [m.add_request(p, sp) for p, sp in zip(prompts, sps)]
+        log, steps = [], 0
+        while m.has_work():
+            outs = m.step()
+            steps += 1
+            log.append(sorted((o.request_id, o.token, o.finished, o.finish_reason) for o in outs))
+            if steps == 30:
+                assert m.abort(rids[3])
+        m.engine.cache.check()
+        assert m.engine.cache.free_pages() == [64]
+        return log, [m.scheduler.requests[r].output for r in rids], m.steps_ahead
+
+    log0, out0, ahead0 = run(False)
+    log1, out1, ahead1 = run(True)
+    assert ahead0 == 0 and ahead1 > 10
+    assert out1 == out0 and log1 == log0
+    assert len(out0[0]) <= 14 and out0[0][-1] == base[0][13] and len(out0[1]) == 23
+
+
 def test_sampling_params_defaults_follow_the_reference():
     from rllm_b200.sampling import SamplingParams
     sp = SamplingParams()

@@ -175,3 +175,49 @@ def test_seed_is_fixed_per_request():
     a = s.add_request([1], SamplingParams(seed=42))
     b = s.add_request([1], SamplingParams())
     assert s.requests[a].seed == 42 and isinstance(s.requests[b].seed, int)
+
+
+def test_a_step_is_planned_ahead_only_in_the_steady_state():
+    """`plan_ahead` gives the next step's plan before this step's tokens are known: when nobody
+    waits, everybody decodes, no request ends with the coming token by its limit, none is
+    penalised for what it produced, and pages are left. A request that ends meanwhile is passed
+    over when the step ahead is recorded."""
+    s, ex = make(pages=64, page=4, max_tokens_per_step=100)
+    a = s.add_request([1, 2, 3], SamplingParams(max_tokens=6, eos_token_ids=(7,)))
+    b = s.add_request([4, 5], SamplingParams(max_tokens=4))
+    plan, _ = s.schedule(ex)
+    assert s.plan_ahead(plan) is None                      # prompts: what follows hangs on their tokens
+    ex.step(s.entries(plan))
+    s.advance(plan, [10, 20], ex)
+    plan, _ = s.schedule(ex)                               # both decode: a has 1 token, b has 1
+    nxt = s.plan_ahead(plan)
+    assert [p.request.request_id for p in nxt] == [a, b] and all(p.samples and len(p.tokens) == 1 for p in nxt)
+    ex.step(s.entries(plan))
+    ex.step(s.entries(nxt))                                # launched ahead
+    s.advance(plan, [11, 21], ex)                          # outputs: a [10, 11], b [20, 21]
+    # `nxt` brings b its third token, the step after it the fourth and last: that one may still be
+    # planned ahead, none beyond it
+    nxt2 = s.plan_ahead(nxt)
+    assert nxt2 is not None
+    ex.step(s.entries(nxt2))
+    outs = s.advance(nxt, [7, 22], ex)                     # a meets its end token
+    assert [(o.request_id, o.token, o.finished) for o in outs] == [(a, 7, True), (b, 22, False)]
+    assert s.plan_ahead(nxt2) is None                      # a has gone; and b ends with the coming token
+    # the step that was under way when a ended drops a's token
+    outs = s.advance(nxt2, [99, 23], ex)
+    assert [(o.request_id, o.token, o.finished, o.finish_reason) for o in outs] == [(b, 23, True, "max_tokens")]
+    assert s.requests[a].output == [10, 11, 7] and s.requests[b].output == [20, 21, 22, 23]
+    assert not s.has_work() and ex.cache.free_pages() == [64]
+    # a request that is penalised for its tokens, or somebody waiting: not planned ahead
+    c = s.add_request([1], SamplingParams(max_tokens=9, frequency_penalty=0.5))
+    run_step(s, ex)
+    plan, _ = s.schedule(ex)
+    assert [p.request.request_id for p in plan] == [c] and s.plan_ahead(plan) is None
+    s.abort(c, ex)
+    d = s.add_request([1], SamplingParams(max_tokens=9))
+    run_step(s, ex)
+    plan, _ = s.schedule(ex)
+    assert [p.request.request_id for p in plan] == [d] and s.plan_ahead(plan) is not None
+    s.add_request([2], SamplingParams(max_tokens=9))
+    assert s.plan_ahead(plan) is None
+    ex.cache.check()
