@@ -66,10 +66,12 @@ class LLM:
         # their way to the host starts now, before anything else is put on the stream behind them
         if not self._pinned:
             n = max(self.scheduler.max_active, 1)
-            self._pinned = [torch.empty(n, dtype=torch.int32).pin_memory() for _ in range(2)]
+            self._pinned = [torch.zeros(n + 2, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._pinned.reverse()
-        host = self._pinned[0][: drawn.numel()]
+        buf = self._pinned[0]
+        host = buf[: drawn.numel()]
         host.copy_(drawn, non_blocking=True)
+        buf[-2:].copy_(self.engine.error_words, non_blocking=True)      # and the device's error words with them
         arrived = torch.cuda.Event()
         arrived.record()
         return drawn, host, arrived
@@ -100,6 +102,9 @@ class LLM:
         if drawn is not None:
             drawn[2].synchronize()               # this step's tokens only; the step ahead keeps running
             tokens = drawn[1].tolist()
+            if self._pinned[0][-2] or self._pinned[0][-1] or self._pinned[1][-2] or self._pinned[1][-1]:
+                self._ahead = None
+                self.engine.check()              # raises: a kernel gave up waiting, or a token id was out of range
         outs = failed + self.scheduler.advance(plan, tokens, self.engine)
         if self._ahead is not None and all(p.request.finished for p in self._ahead[0]):
             self._ahead = None                   # nobody is left to take its tokens

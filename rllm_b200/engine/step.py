@@ -61,7 +61,13 @@ class Engine:
         self.model, self.backend, self.cache = model, backend, cache
         self.device = backend.device
         self.vocab = model.vocab_size
-        self._err_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # two device words: [0] a kernel's bounded wait ran out, [1] a token id outside the table
+        if backend.fast:
+            from ..kernels import sm100
+            self.error_words = sm100.init(self.device).err
+        else:
+            self.error_words = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self._err_flag = self.error_words[1:2]
         self.steps_run = 0
         self.graph_steps = 0
         self.h2d_bytes = 0            # bytes of step metadata copied to the device so far
@@ -90,10 +96,11 @@ class Engine:
         """Read the device error words (one small copy): a token id outside the table, or a
         kernel whose bounded wait ran out. Callers that read results back anyway call this at
         the same time."""
-        if int(self._err_flag.item()):
+        wait, token = self.error_words.tolist()
+        if token:
             self._err_flag.zero_()
             raise StepError("a token id outside the embedding table reached the device")
-        if self.backend.fast:
+        if wait and self.backend.fast:
             from ..kernels import sm100
             sm100.check_error(self.device)
 

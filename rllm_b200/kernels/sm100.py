@@ -30,7 +30,9 @@ ops.register_signatures("sm100", {
 class _State:
     def __init__(self, device):
         self.device = device
-        self.err = torch.zeros(1, dtype=torch.int32, device=device)
+        # word 0: set by a kernel whose bounded wait ran out; word 1: for the engine's own flag
+        # (a token id outside the table), so that one small copy brings both to the host
+        self.err = torch.zeros(2, dtype=torch.int32, device=device)
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
 
 
@@ -53,9 +55,9 @@ def init(device) -> _State:
 def check_error(device) -> None:
     """Raise if a kernel's bounded wait ran out since the last check (reads the device word)."""
     st = init(device)
-    code = int(st.err.item())
+    code = int(st.err[0].item())
     if code:
-        st.err.zero_()
+        st.err[0].zero_()
         raise ops.KernelError(f"a kernel's bounded wait ran out (role {code & 0xff}, detail {code >> 8}); "
                               f"its output is not valid")
 

@@ -157,6 +157,21 @@ def test_steps_launched_ahead_change_nothing(dirs, dtype):
     assert len(out0[0]) <= 14 and out0[0][-1] == base[0][13] and len(out0[1]) == 23
 
 
+def test_the_step_loop_reports_a_kernel_that_gave_up(dirs):
+    """A kernel whose bounded wait ran out sets a device word and returns; the words travel to the
+    host with every step's tokens, and `LLM.step` raises. (The word is set by hand here.)"""
+    from rllm_b200.kernels.ops import KernelError
+    from rllm_b200.sampling import SamplingParams
+    m = llm(dirs["D"], "D", "bfloat16", num_pages=32)
+    m.add_request([1, 2, 3], SamplingParams(temperature=0.0, max_tokens=20))
+    m.step(); m.step()
+    m.engine.error_words[0] = 3 | (5 << 8)
+    with pytest.raises(KernelError, match="role 3, detail 5"):
+        for _ in range(3):
+            m.step()
+    m.engine.check()                                         # read and cleared
+
+
 def test_sampling_params_defaults_follow_the_reference():
     from rllm_b200.sampling import SamplingParams
     sp = SamplingParams()
