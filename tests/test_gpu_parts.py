@@ -1,6 +1,7 @@
-"""Each part alone against the plain implementation's function for it, and a toy mixer with
-state of its own, defined here, that is registered, built into a model and stepped without
-a change to the package."""
+"""Each part alone against the plain implementation's function for it; and toy parts defined
+here (a mixer with state of its own, a feed-forward with routing, a position encoding that adds
+instead of rotating) that are registered, built into toy models beside the package's own parts
+and stepped without a change to the package."""
 from dataclasses import dataclass
 
 import pytest
@@ -318,3 +319,174 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype):
         assert sorted(eng.cache.state_layers) == [1, 3]
         got = replay.run_in_process(eng, steps)
         replay.compare(got, want, {"float32": 2e-5, "bfloat16": 3e-2}[dtype], f"toy {dtype} {family.__name__}")
+
+
+# ------------------------------------------------------------------------------------------
+# a toy feed-forward with routing and a toy position encoding, on some layers of a toy model
+# ------------------------------------------------------------------------------------------
+
+def make_routed_toy():
+    from rllm_b200.config import ModelConfig, register_architecture
+    from rllm_b200.models import LayerCall, Model
+    from rllm_b200.parts import (Embedding, GQAttention, OutputHead, Param, Part, PreNormBlock,
+                                 RMSNorm, RotaryEmbedding, Source, SwiGLU, make_part, register_part)
+
+    class AdditivePosition(Part):
+        """q and k of every head get a learned vector of their position (mod `period`) added;
+        then k and v go to the layer's pages. Stands where the rotary part stands."""
+
+        def __init__(self, head_dim, period):
+            self.head_dim, self.period, self.table = head_dim, period, None
+
+        def params(self):
+            return [Param("table", (Source("pos_table", (self.period, self.head_dim)),), role="vector")]
+
+        def rotate_and_store(self, qkv, ctx, cache, nh, nkv):
+            T, hd = qkv.shape[0], self.head_dim
+            add = self.table.float()[(ctx.positions % self.period).long()]            # [T, hd]
+            qk = qkv[:, : (nh + nkv) * hd].view(T, nh + nkv, hd)
+            qk.copy_((qk.float() + add[:, None, :]).to(qkv.dtype))
+            k = qkv[:, nh * hd: (nh + nkv) * hd].view(T, nkv, hd)
+            v = qkv[:, (nh + nkv) * hd:].view(T, nkv, hd)
+            ps = cache.k.shape[2]
+            keep = cache.slots >= 0
+            page, off = (cache.slots[keep] // ps).long(), (cache.slots[keep] % ps).long()
+            cache.k[page, :, off, :] = k[keep]
+            cache.v[page, :, off, :] = v[keep]
+
+    class RoutedFFN(Part):
+        """Every token goes to the one expert its router logit (32-bit) is largest for; the
+        expert's SwiGLU output enters the residual stream weighted with the softmax of the logits."""
+
+        def __init__(self, hidden, intermediate, experts):
+            self.hidden, self.intermediate, self.experts = hidden, intermediate, experts
+
+        def params(self):
+            H, I = self.hidden, self.intermediate
+            ps = [Param("router", (Source("router.weight", (self.experts, H)),), role="vector")]
+            for e in range(self.experts):
+                ps.append(Param(f"gate_up{e}", (Source(f"experts.{e}.gate_proj.weight", (I, H)),
+                                                Source(f"experts.{e}.up_proj.weight", (I, H)))))
+                ps.append(Param(f"down{e}", (Source(f"experts.{e}.down_proj.weight", (H, I)),)))
+            return ps
+
+        def forward(self, x, ctx, residual):
+            be = ctx.backend
+            logits = x.float() @ self.router.float().t()
+            prob = torch.softmax(logits, dim=-1)
+            choice = logits.argmax(dim=-1)
+            for e in range(self.experts):
+                rows = (choice == e).nonzero().flatten()              # read on the host: not graph safe
+                if rows.numel() == 0:
+                    continue
+                act = be.linear_swiglu(x[rows].contiguous(), getattr(self, f"gate_up{e}"))
+                out = be.linear(act, getattr(self, f"down{e}")).float()
+                residual.index_add_(0, rows, out * prob[rows, e, None])
+
+    register_part("position", "additive", AdditivePosition)
+    register_part("ffn", "routed", RoutedFFN)
+
+    @dataclass(frozen=True)
+    class RoutedConfig(ModelConfig):
+        hidden: int
+        vocab: int
+        layers: tuple          # per layer: (position kind, ffn kind)
+        experts: int
+        period: int
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["toy_hidden"], raw["toy_vocab"], tuple(tuple(x) for x in raw["toy_layers"]),
+                       raw["toy_experts"], raw["toy_period"])
+
+    def build(cfg):
+        emb = Embedding(cfg.vocab, cfg.hidden); emb.prefix = "model."
+        blocks = []
+        for i, (pos, ffn) in enumerate(cfg.layers):
+            position = make_part("position", "additive", head_dim=16, period=cfg.period) if pos == "additive" \
+                else RotaryEmbedding(16, 10000.0)
+            feed = make_part("ffn", "routed", hidden=cfg.hidden, intermediate=cfg.hidden, experts=cfg.experts) \
+                if ffn == "routed" else SwiGLU(cfg.hidden, 2 * cfg.hidden)
+            b = PreNormBlock(RMSNorm(cfg.hidden, 1e-5), GQAttention(cfg.hidden, 3, 1, 16, position),
+                             RMSNorm(cfg.hidden, 1e-5), feed)
+            b.set_prefix(f"model.layers.{i}.")
+            blocks.append(b)
+        norm = RMSNorm(cfg.hidden, 1e-5); norm.prefix = "model.norm."
+        head = OutputHead(cfg.vocab, cfg.hidden, norm, emb); head.prefix = "lm_head."
+        return Model(cfg, emb, blocks, [LayerCall(i, i, True) for i in range(len(blocks))], head)
+
+    register_architecture("ToyRoutedForCausalLM", RoutedConfig, build, model_types=("toy_routed",))
+
+
+ROUTED = {"architectures": ["ToyRoutedForCausalLM"], "toy_hidden": 40, "toy_vocab": 90, "toy_experts": 3,
+          "toy_period": 7,
+          "toy_layers": [["additive", "routed"], ["rope", "swiglu"], ["rope", "routed"], ["additive", "swiglu"]]}
+
+
+def routed_plain(w, ids, cfg=ROUTED):
+    ids = torch.as_tensor(ids)
+    T = ids.numel()
+    pos = torch.arange(T)
+    f = P.rope_inv_freq(16, 10000.0, None)
+    h = P.embedding(w["model.embed_tokens.weight"], ids)
+    choices = []
+    for i, (pk, fk) in enumerate(cfg["toy_layers"]):
+        p = f"model.layers.{i}."
+        n = P.rms_norm(h, w[p + "input_layernorm.weight"], 1e-5)
+        q = P.linear(n, w[p + "self_attn.q_proj.weight"]).view(T, 3, 16)
+        k = P.linear(n, w[p + "self_attn.k_proj.weight"]).view(T, 1, 16)
+        v = P.linear(n, w[p + "self_attn.v_proj.weight"]).view(T, 1, 16)
+        if pk == "additive":
+            add = w[p + "self_attn.pos_table"][pos % cfg["toy_period"]][:, None, :]
+            q, k = q + add, k + add
+        else:
+            q, k = P.rope(q, pos, f), P.rope(k, pos, f)
+        h = h + P.linear(P.attention(q, k, v, 0.25).reshape(T, 48), w[p + "self_attn.o_proj.weight"])
+        n = P.rms_norm(h, w[p + "post_attention_layernorm.weight"], 1e-5)
+        if fk == "routed":
+            logits = P.linear(n, w[p + "mlp.router.weight"])
+            prob = torch.softmax(logits, dim=-1)
+            choice = logits.argmax(dim=-1)
+            choices.append(choice)
+            out = torch.zeros_like(h)
+            for t in range(T):
+                e = int(choice[t])
+                q_ = f"{p}mlp.experts.{e}."
+                out[t] = prob[t, e] * P.swiglu(n[t: t + 1], w[q_ + "gate_proj.weight"], w[q_ + "up_proj.weight"],
+                                               w[q_ + "down_proj.weight"])[0]
+            h = h + out
+        else:
+            h = h + P.swiglu(n, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                             w[p + "mlp.down_proj.weight"])
+    return P.linear(P.rms_norm(h, w["model.norm.weight"], 1e-5), w["model.embed_tokens.weight"]), choices
+
+
+def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
+    """A feed-forward with routing and a position encoding other than the rotary one, defined
+    here, registered and chosen layer by layer beside the package's own parts; stepped whole, in
+    portions and mixed, with pages used again. In 32-bit only: with hard routing a near tie
+    between two experts may go the other way in bfloat16, which is the routing's nature and no
+    fault of a kernel."""
+    from rllm_b200.config import registered_architectures
+    from rllm_b200.engine import load_engine
+    from rllm_b200.parts import registered_parts
+    from rllm_b200.weights import write_random_model
+    if "ToyRoutedForCausalLM" not in registered_architectures():
+        make_routed_toy()
+    assert "routed" in registered_parts("ffn") and "additive" in registered_parts("position")
+    d = write_random_model(ROUTED, 11, str(tmp_path / "routed"), std=0.15, norm_std=0.1)
+    _, w = P.read_model_dir(d)
+    reqs = {f"r{i}": tiny.random_prompt(n, 90, 60 + i) for i, n in enumerate([12, 33, 20, 45])}
+    want, used = {}, set()
+    for rid, toks in reqs.items():
+        lg, choices = routed_plain(w, toks)
+        want.update({(rid, i): lg.numpy()[i] for i in range(len(toks))})
+        used |= {int(c) for ch in choices for c in ch}
+    assert used == {0, 1, 2}                                 # every expert gets tokens
+    for family in (replay.whole, replay.portions, replay.mixed):
+        steps = family(reqs)
+        eng = load_engine(d, dtype="float32", page_size=4, max_tokens=replay.max_live_tokens(steps, reqs),
+                          max_requests=4)
+        assert eng.graphs is None                            # a part reads the step on the host: no graphs
+        got = replay.run_in_process(eng, steps)
+        replay.compare(got, want, 2e-5, f"routed toy {family.__name__}")
