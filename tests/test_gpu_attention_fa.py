@@ -136,6 +136,28 @@ def test_prefill_on_tcgen05(nh, nkv, page, window):
         splits=1, far=(1, 11) if window is None else None, kernel="tc")
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_prefill_on_tcgen05_random_shapes(seed):
+    """Random batches for the tcgen05 prefill kernel against the plain formula: group sizes 1 to 8,
+    pages of 4 to 64 keys (tensor copies from 8 up, cp.async below and for sizes that are no power
+    of two), portions that end a row tile, a pair of row tiles or a key tile exactly or one short
+    or one over, contexts before the portion of 0 to 300 keys, and windows on some."""
+    import random
+    r = random.Random(100 + seed)
+    nkv = r.choice([1, 2, 3])
+    G = r.choice([1, 2, 4, 8])
+    page = r.choice([4, 8, 16, 64, 12, 32])
+    window = r.choice([None, None, 40, 200])
+    edges = [128 // G, 256 // G, 128, 256, 384]
+    q_lens, lens = [], []
+    for _ in range(r.randint(2, 5)):
+        q = max(1, r.choice(edges) * r.randint(1, 2) + r.choice([-1, 0, 1]) if r.random() < 0.7 else r.randint(1, 300))
+        q = min(q, 520)
+        q_lens.append(q)
+        lens.append(q + r.choice([0, 0, 1, 127, 128, r.randint(0, 300)]))
+    run(nkv * G, nkv, 64, page, window, lens=lens, q_lens=q_lens, splits=1, kernel="tc")
+
+
 def test_long_prompt_whole_and_chosen_splits():
     from rllm_b200.kernels import sm100
     run(8, 2, 64, 16, None, lens=[1500], q_lens=[1500], splits=1, far=(0, 3))
