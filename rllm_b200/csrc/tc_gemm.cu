@@ -3,16 +3,17 @@
 //     C[T, N] = X[T, K] * W[N, K]^T          (X activations, W weights as stored, both K-major)
 //
 // The weight tile is the MMA's A operand (M = 128 weight rows) and the token tile is its B
-// operand (N = BN tokens, 16..256), so a decode step with a handful of tokens still fills the
-// 128-row MMA and streams every weight byte exactly once; a prefill uses BN = 256 (128 with the
-// gate/up pair). The accumulator D[weight row (TMEM lane), token (TMEM column)] is read back
+// operand (N = BN tokens), so a decode step with a handful of tokens still fills the 128-row MMA
+// and streams every weight byte exactly once. Steps of up to 64 tokens (128 for a narrow weight)
+// run token tiles of 16 or 32 in the first kernel below; more tokens run tiles of 64 to 256 (128
+// with the gate/up pair) in the persistent kernel further down. The accumulator D[weight row (TMEM lane), token (TMEM column)] is read back
 // with tcgen05.ld by four epilogue warps, thread = weight row, and written as C[token][row].
 //
 // One CTA = one 128 x BN output tile over a range of K: warp 0 issues TMA loads into a ring of
 // shared-memory stages, warp 1 issues the MMAs (one thread) and owns the TMEM allocation,
 // warps 2-5 run the epilogue.
 //
-// Fused RMSNorm (NORM variants, token tiles up to 64): X is not read by TMA. The input is the
+// Fused RMSNorm (NORM variants, steps of up to 64 tokens): X is not read by TMA. The input is the
 // float residual stream h and a norm weight g; warps 2-5 build the B operand themselves, stage
 // by stage: bf16(h[t,k] * g[k]) written in the 128-byte swizzled layout the MMA expects, while
 // they add up h[t,k]^2. Since rsqrt(mean(h^2) + eps) is one number per token it commutes with
@@ -25,9 +26,9 @@
 // of the sum of squares) into the owner's shared memory through distributed shared memory,
 // one cluster barrier later the owner adds the parts in rank order from its own shared memory
 // and runs the epilogue. Nothing goes through global memory and the sum does not depend on
-// timing. For token tiles up to 32 the landing area is a region of its own, so a rank pushes as
-// soon as its own products are done; larger tiles land in the (by then idle) stage ring after
-// one more cluster barrier.
+// timing. The landing area is a region of its own, so a rank pushes as soon as its own products
+// are done; only the gate/up pair at 32 tokens, which that region would leave with two stages,
+// lands in the (by then idle) stage ring after one more cluster barrier.
 //
 // Programmatic dependent launch: the kernel lets its successor start at once, and itself
 // fetches its first weight tiles (which no earlier kernel writes) before it waits for its
