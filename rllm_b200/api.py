@@ -63,17 +63,23 @@ class LLM:
             return None
         drawn = self.sampler.draw(logits, [r.params for r in sampled], [r.seed for r in sampled],
                                   [len(r.output) + ahead for r in sampled], [r.output for r in sampled])
-        # their way to the host starts now, before anything else is put on the stream behind them
+        # Their way to the host goes over a stream of its own, which waits for the draw only: the
+        # step launched behind them on the main stream does not wait for a copy engine.
         if not self._pinned:
             n = max(self.scheduler.max_active, 1)
             self._pinned = [torch.zeros(n + 2, dtype=torch.int32).pin_memory() for _ in range(2)]
+            self._copy_stream = torch.cuda.Stream(self.engine.device)
         self._pinned.reverse()
         buf = self._pinned[0]
         host = buf[: drawn.numel()]
-        host.copy_(drawn, non_blocking=True)
-        buf[-2:].copy_(self.engine.error_words, non_blocking=True)      # and the device's error words with them
+        drawn_at = torch.cuda.Event()
+        drawn_at.record()
         arrived = torch.cuda.Event()
-        arrived.record()
+        with torch.cuda.stream(self._copy_stream):
+            self._copy_stream.wait_event(drawn_at)
+            host.copy_(drawn, non_blocking=True)
+            buf[-2:].copy_(self.engine.error_words, non_blocking=True)      # and the device's error words with them
+            arrived.record()
         return drawn, host, arrived
 
     def step(self) -> list[StepOutput]:

@@ -35,6 +35,26 @@ RLLM_API int rllm_embed(const int* ids, const void* table, int table_dt, float* 
   return rc;
 }
 
+// ---------------------------------------------------------------- a step's metadata onto the device
+// The int32 words of a step's metadata, read straight out of pinned host memory (mapped into the
+// device's address space) into the buffer the step's kernels read. The first n_feed words, the
+// token ids, come from a device vector instead when one is given: the tokens the step before drew.
+// One kernel on the compute stream stands where a host-to-device copy and a device-to-device copy
+// would each wait for a copy engine to take over and hand back.
+__global__ void step_meta_kernel(const int* __restrict__ host_src, int* __restrict__ dst, int n,
+                                 const int* __restrict__ feed, int n_feed) {
+  pdl_launch();
+  pdl_wait();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    dst[i] = (feed != nullptr && i < n_feed) ? feed[i] : host_src[i];
+}
+
+RLLM_API int rllm_step_meta(const int* host_src, int* dst, int n, const int* feed, int n_feed, void* stream) {
+  if (n <= 0) return 0;
+  const int blocks = (n + 255) / 256 < 32 ? (n + 255) / 256 : 32;
+  return launch_ex(step_meta_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, 1, host_src, dst, n, feed, n_feed);
+}
+
 // ---------------------------------------------------------------- RMSNorm
 // y = x * rsqrt(mean(x^2) + eps) * w   (reference: src/gpu/cuda/shaders/rms_norm.cu:78-115)
 // x is the float residual stream; w float or bf16; y float or bf16.

@@ -155,15 +155,12 @@ class DecodeGraphs:
             self.slots.move_to_end(key)
         slot.copied.synchronize()               # the last copy out of the host buffer is over
         dirty = self._fill(slot, entries, rcs)
-        if dirty or slot.head == slot.lay.total:
-            slot.dev.copy_(slot.host, non_blocking=True)
-            eng.h2d_bytes += 4 * slot.lay.total
-        else:                                   # no block table changed: the small vectors only
-            slot.dev[: slot.head].copy_(slot.host[: slot.head], non_blocking=True)
-            eng.h2d_bytes += 4 * slot.head
+        # one small kernel reads the words out of the pinned buffer (all of them if a block table
+        # changed, else the vectors in front) and takes the token ids from `feed` if that is given
+        n = slot.lay.total if dirty else slot.head
+        ops.step_meta(slot.host, slot.dev, n, feed)
+        eng.h2d_bytes += 4 * n
         slot.copied.record()
-        if feed is not None:
-            slot.dev[:S].copy_(feed)                # after the copy above, in stream order
         if slot.graph is None:
             self._capture(slot)
         slot.graph.replay()

@@ -35,6 +35,7 @@ _SIGS = {
         "rllm_rope_cache_write": [_P, c_int, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
                                   c_int, _P],
         "rllm_gather_rows": [_P, _P, _P, c_int, c_int, _P],
+        "rllm_step_meta": [_P, _P, c_int, _P, c_int, _P],
         "rllm_add_into": [_P, _P, c_int, c_longlong, _P],
         "rllm_silu_gate": [_P, _P, c_int, c_int, c_int, _P],
         "rllm_gemm_simt": [c_int, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
@@ -267,6 +268,20 @@ def paged_attention_simt(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Te
         block_table.stride(0), T, nh, nkv, hd, page_size, float(scale), int(window or 0), _stream()),
         "paged_attention_simt")
     return out
+
+
+def step_meta(host: torch.Tensor, dev: torch.Tensor, n: int, feed: torch.Tensor | None = None) -> None:
+    """The first `n` int32 words of the pinned host buffer into the device buffer, by a kernel that
+    reads the host memory directly; the leading `feed.numel()` words from the device vector `feed`
+    instead, if given."""
+    if host.dtype != torch.int32 or dev.dtype != torch.int32 or not host.is_pinned() or not dev.is_cuda \
+            or not (0 < n <= min(host.numel(), dev.numel())):
+        raise KernelError("step_meta takes a pinned int32 host buffer, an int32 device buffer and a count within both")
+    if feed is not None and (feed.dtype != torch.int32 or not feed.is_cuda or not feed.is_contiguous()
+                             or feed.numel() > n):
+        raise KernelError("step_meta: feed must be a contiguous int32 device vector no longer than the count")
+    _check(_fn("simt", "rllm_step_meta")(host.data_ptr(), dev.data_ptr(), n, _ptr(feed),
+                                         0 if feed is None else feed.numel(), _stream()), "step_meta")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
