@@ -157,6 +157,52 @@ def test_steps_launched_ahead_change_nothing(dirs, dtype):
     assert len(out0[0]) <= 14 and out0[0][-1] == base[0][13] and len(out0[1]) == 23
 
 
+@pytest.mark.parametrize("seed", [0, 1])
+def test_random_traffic_is_the_same_with_and_without_steps_ahead(dirs, seed):
+    """Forty requests of random lengths and limits arrive over time at a pool too small for them
+    (so requests wait, are preempted and recomputed), some with end tokens, some drawn with a
+    temperature, a few aborted: token for token the same with steps launched ahead and without,
+    and every page is back at the end."""
+    import random
+    from rllm_b200.sampling import SamplingParams
+    name = "D"
+    cfg, _ = P.read_model_dir(dirs[name])
+    V = cfg["vocab_size"]
+
+    def run(ahead):
+        r = random.Random(seed)
+        m = llm(dirs[name], name, "float32", num_pages=18, max_active=6, max_tokens_per_step=48, max_chunk=32)
+        m.run_ahead = ahead
+        todo = []
+        for i in range(40):
+            sp = SamplingParams(temperature=r.choice([0.0, 0.0, 0.9]), top_p=r.choice([1.0, 0.8]),
+                                max_tokens=r.randint(1, 40), seed=1000 + i,
+                                eos_token_ids=tuple(r.sample(range(V), r.choice([0, 0, 40]))))
+            todo.append((r.randint(0, 60), tiny.random_prompt(r.randint(1, 70), V, 300 + i), sp))
+        abort_at = {r.randint(5, 80): r.randint(0, 39) for _ in range(4)}
+        rids, step = {}, 0
+        while todo or m.has_work():
+            for item in [t for t in todo if t[0] <= step]:
+                todo.remove(item)
+                rids[len(rids)] = m.add_request(item[1], item[2])
+            if step in abort_at and abort_at[step] in rids:
+                m.abort(rids[abort_at[step]])
+            if m.has_work():
+                m.step()
+            step += 1
+            assert step < 5000
+        m.engine.cache.check()
+        assert m.engine.cache.free_pages() == [18]
+        reqs = m.scheduler.requests
+        return [(reqs[rids[i]].output, reqs[rids[i]].finish_reason) for i in sorted(rids)], \
+            m.scheduler.preempted_total, m.steps_ahead
+
+    a, pre_a, ahead_a = run(False)
+    b, pre_b, ahead_b = run(True)
+    assert ahead_a == 0 and ahead_b > 0 and pre_a > 0
+    assert a == b
+
+
 def test_the_step_loop_reports_a_kernel_that_gave_up(dirs):
     """A kernel whose bounded wait ran out sets a device word and returns; the words travel to the
     host with every step's tokens, and `LLM.step` raises. (The word is set by hand here.)"""
