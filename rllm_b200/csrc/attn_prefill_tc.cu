@@ -1,5 +1,7 @@
 // Prefill attention over the paged bfloat16 cache on the 5th-generation tensor cores (tcgen05),
-// head size 64: both products of a tile run as UMMA with their accumulators in TMEM.
+// head sizes 64 and 128: both products of a tile run as UMMA with their accumulators in TMEM.
+// The text below gives the sizes for head size 64 (key tiles of 128); with 128 a key tile has 64
+// keys, a row's scores are 64, and Q, K and V are two 128-byte atoms wide (see `Shape`).
 //
 // A work item is a pair of row tiles, 2 x 128 rows: (query token, query head) pairs of ONE kv head
 // (row r of a sequence is token r / G, head kvh*G + r % G, as in the mma.sync kernel). Both tiles
@@ -45,8 +47,6 @@ using namespace sm100;
 namespace {
 
 constexpr int PM = 128;          // rows per row tile
-constexpr int PN = 128;          // keys per tile
-constexpr int HD = 64;
 constexpr int RT = 2;            // row tiles per work item
 constexpr int LOADERS = 3;       // loader warps
 constexpr int MMA_WARP = LOADERS;
@@ -56,16 +56,30 @@ constexpr int THREADS = (LOADERS + 1 + 4 * RT) * 32;
 // registers per thread: 168 each at launch (65,536 / 384, in eights); then 4 warps keep 56 and 8 warps have 224
 constexpr int REGS_LOW = 56, REGS_HIGH = 224;
 static_assert(SOFTMAX_WARP0 * 32 * REGS_LOW + 4 * RT * 32 * REGS_HIGH <= 168 * THREADS, "more registers than the launch has");
-constexpr int TILE_BYTES = PN * HD * 2;          // 16 KB: one K or V tile, one row tile of Q
-constexpr int P_BYTES = PM * PN * 2;             // 32 KB: two 64-key sub-tiles of 16 KB
+constexpr int KV_TILE_BYTES = 16384;             // one K or V tile: 128 keys of 64 values, or 64 keys of 128
 constexpr int KVS = 4;           // K/V stages with TMA (one loader, tile after tile). Without TMA only LOADERS of them
                                  // are used: loader warp w always fills stage w (tiles w, w + 3, ...), so its waits
                                  // on that stage's barriers follow one another phase by phase; a warp that moved
                                  // between stages could be two phases ahead, which a parity cannot tell
-constexpr int SMEM_BYTES = 1024 + TILE_BYTES * (RT + 2 * KVS) + RT * P_BYTES;    // Q[2], K[KVS], V[KVS], P[2]
 constexpr int SB = 3;            // S accumulators: one per row tile in its softmax, one being computed ahead
-constexpr int TMEM_COLS = 512;   // S[3] x 128 + PV[2] x 64
-constexpr int S_COL = 0, PV_COL = SB * PN;
+constexpr int TMEM_COLS = 512;
+
+// Sizes that follow from the head size (64 or 128). Operands lie in shared memory as "atoms" of
+// 128-byte rows (64 values), swizzled: a tile wider than 64 values is several atoms one after the other.
+template <int HD> struct Shape {
+  static_assert(HD == 64 || HD == 128, "head sizes 64 and 128");
+  static constexpr int PN = HD == 64 ? 128 : 64;     // keys per tile (a K or V tile is 16 KB either way)
+  static constexpr int HA = HD / 64;                 // atoms along the head dimension (Q, K, V)
+  static constexpr int KA = PN / 64;                 // atoms along the keys (P)
+  static constexpr int ATOM_ROWS = PM * 128;         // bytes of one atom of Q or P (128 rows)
+  static constexpr int ATOM_KEYS = PN * 128;         // bytes of one atom of K or V (PN rows)
+  static constexpr int Q_BYTES = HA * ATOM_ROWS;     // one row tile of Q
+  static constexpr int P_BYTES = KA * ATOM_ROWS;     // one row tile of P
+  static constexpr int SMEM_BYTES = 1024 + RT * Q_BYTES + 2 * KVS * KV_TILE_BYTES + RT * P_BYTES;   // Q[2], K[KVS], V[KVS], P[2]
+  static constexpr int S_COL = 0, O_COL = SB * PN;   // TMEM: three S accumulators, then the output of both row tiles
+  static_assert(O_COL + RT * HD <= TMEM_COLS, "S and the outputs must fit in TMEM");
+  static_assert(HA * ATOM_KEYS == KV_TILE_BYTES, "a K or V tile is 16 KB");
+};
 
 struct PfParams {
   const bf16* q; int q_stride;
@@ -101,8 +115,8 @@ __host__ __device__ constexpr uint32_t idesc(int M, int N, bool b_mn_major) {
   return umma_idesc_bf16(M, N) | (b_mn_major ? (1u << 16) : 0u);
 }
 
-// TMA: the K and V tiles come by tensor copies over the caches seen as [pages * kv heads][page size][64].
-template <bool TMA>
+// TMA: the K and V tiles come by tensor copies over the caches seen as [pages * kv heads][page size][HD].
+template <int HD, bool TMA>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                        const PfParams p) {
@@ -113,8 +127,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* smem = (uint8_t*)(((uintptr_t)pf_smem_raw + 1023) & ~(uintptr_t)1023);
+  typedef Shape<HD> C;
+  constexpr int PN = C::PN;
   const uint32_t q_s = smem_u32(smem);
-  const uint32_t k_s = q_s + RT * TILE_BYTES, v_s = k_s + KVS * TILE_BYTES, p_s = v_s + KVS * TILE_BYTES;
+  const uint32_t k_s = q_s + RT * C::Q_BYTES, v_s = k_s + KVS * KV_TILE_BYTES, p_s = v_s + KVS * KV_TILE_BYTES;
 
   const int G = p.nh / p.nkv;
   constexpr int NST = TMA ? KVS : LOADERS;              // K/V stages in use
@@ -124,8 +140,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     // The scores of such keys are masked, and their weights are exact zeros, but zero times what
     // an earlier kernel left here need not be zero: start from zeros (later leftovers are keys).
     if (warp == 0 && lane == 0) { prefetch_tensormap(&tmap_k); prefetch_tensormap(&tmap_v); }
-    uint4* kv = reinterpret_cast<uint4*>(smem + RT * TILE_BYTES);
-    for (int i = threadIdx.x; i < 2 * KVS * TILE_BYTES / 16; i += THREADS) kv[i] = make_uint4(0, 0, 0, 0);
+    uint4* kv = reinterpret_cast<uint4*>(smem + RT * C::Q_BYTES);
+    for (int i = threadIdx.x; i < 2 * KVS * KV_TILE_BYTES / 16; i += THREADS) kv[i] = make_uint4(0, 0, 0, 0);
     fence_proxy_async();
   }
   if (warp == MMA_WARP) { tmem_alloc(&tmem_base_slot, TMEM_COLS); tmem_relinquish(); }
@@ -190,19 +206,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     const int ch = lane & 7, rbase = lane >> 3;
 #pragma unroll 4
     for (int i = 0; i < n / 4; ++i) {
-      const int r = r0 + rbase + 4 * i;
+      const int r = r0 + rbase + 4 * i;                  // row of the item: row tile r / 128, row r % 128 of it
       const int row = tile0 * PM + r;
       const bool valid = row < rows_total;
       const int tok = valid ? row / G : 0, head = kvh * G + (valid ? row % G : 0);
       const bf16* src = p.q + (size_t)(q0 + tok) * p.q_stride + (size_t)head * HD + ch * 8;
-      cp_async16z(q_s + (uint32_t)(r * 128 + ((ch ^ (r & 7)) << 4)), src, valid);
+      const uint32_t dst = q_s + (uint32_t)((r / PM) * C::Q_BYTES + (r % PM) * 128 + ((ch ^ (r & 7)) << 4));
+#pragma unroll
+      for (int a = 0; a < C::HA; ++a) cp_async16z(dst + (uint32_t)(a * C::ATOM_ROWS), src + a * 64, valid);
     }
   };
 
   if constexpr (!SOFTMAX) {
   // ---- the products. Step k is (row tile g, K tile t); its S lands in accumulator k % 3.
   constexpr uint32_t id_s = idesc(PM, PN, false);
-  constexpr uint32_t id_pv = idesc(PM, HD, true);
+  constexpr uint32_t id_pv = idesc(PM, 64, true);       // 64 output values at a time
   auto step = [&](int k, int& g, int& t) {
     if (k < 2 * n_both) { g = k & 1; t = k >> 1; } else { g = g_long; t = n_both + (k - 2 * n_both); }
   };
@@ -223,10 +241,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
       abort_flag = 1; record_failure(p.err, 22, t); ok = false; return;
     }
     tc_fence_after();
-    const uint64_t dq = dq0 + (uint64_t)(g * (TILE_BYTES >> 4)), dk = dk0 + (uint64_t)(ks * (TILE_BYTES >> 4));
-    const uint32_t acc = tmem_base + S_COL + (uint32_t)(k % SB) * PN;
+    const uint64_t dq = dq0 + (uint64_t)(g * (C::Q_BYTES >> 4)), dk = dk0 + (uint64_t)(ks * (KV_TILE_BYTES >> 4));
+    const uint32_t acc = tmem_base + C::S_COL + (uint32_t)(k % SB) * PN;
 #pragma unroll
-    for (int kk = 0; kk < HD / 16; ++kk) umma_bf16(acc, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), id_s, kk > 0);
+    for (int kk = 0; kk < HD / 16; ++kk)                // 16 values a product: atom kk / 4, 32 bytes on within it
+      umma_bf16(acc, dq + (uint64_t)((kk >> 2) * (C::ATOM_ROWS >> 4) + (kk & 3) * 2),
+                dk + (uint64_t)((kk >> 2) * (C::ATOM_KEYS >> 4) + (kk & 3) * 2), id_s, kk > 0);
     umma_commit(&s_full[k % SB]);
   };
   auto issue_pv = [&](int k, bool& ok) {                // PV of step k, added to the row tile's output (one thread)
@@ -237,14 +257,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
       abort_flag = 1; record_failure(p.err, 23, t); ok = false; return;
     }
     tc_fence_after();
-    const uint64_t dp = dp0 + (uint64_t)(g * (P_BYTES >> 4)), dv = dv0 + (uint64_t)((t % NST) * (TILE_BYTES >> 4));
-    const uint32_t acc = tmem_base + PV_COL + (uint32_t)g * HD;
+    const uint64_t dp = dp0 + (uint64_t)(g * (C::P_BYTES >> 4)), dv = dv0 + (uint64_t)((t % NST) * (KV_TILE_BYTES >> 4));
+    const uint32_t acc = tmem_base + C::O_COL + (uint32_t)g * HD;
 #pragma unroll
-    for (int ks = 0; ks < PN / 16; ++ks) {
-      // P: K-major, two 64-key sub-tiles of 16 KB, 32 bytes per 16 keys; V: MN-major, 16 key rows = 2 KB per step
-      umma_bf16(acc, dp + (uint64_t)((ks >> 2) * (TILE_BYTES >> 4) + (ks & 3) * 2), dv + (uint64_t)(ks * (2048 >> 4)),
-                id_pv, t > 0 || ks > 0);
-    }
+    for (int a = 0; a < C::HA; ++a)                     // 64 output values = one atom of V
+#pragma unroll
+      for (int ks = 0; ks < PN / 16; ++ks) {
+        // P: K-major, atoms of 64 keys, 32 bytes per 16 keys; V: MN-major, 16 key rows = 2 KB per step
+        umma_bf16(acc + (uint32_t)(a * 64), dp + (uint64_t)((ks >> 2) * (C::ATOM_ROWS >> 4) + (ks & 3) * 2),
+                  dv + (uint64_t)(a * (C::ATOM_KEYS >> 4) + ks * (2048 >> 4)), id_pv, t > 0 || ks > 0);
+      }
     umma_commit(&pv_full[g]);
     if (g == 1 || t >= n_both) umma_commit(&kv_empty[t % NST]);     // the last reader of this K and V stage
   };
@@ -255,8 +277,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     // land: up to NST tiles are on their way.
     if (warp == 0) {
       const int* bt = p.block_table + (size_t)seq * p.bt_stride;
-      const int copies = PN / p.box_rows;                  // per tile and cache
-      const uint32_t copy_bytes = (uint32_t)p.box_rows * HD * 2;
+      const int copies = PN / p.box_rows;                  // runs of keys per tile; each is one copy per atom and cache
+      const uint32_t copy_bytes = (uint32_t)p.box_rows * 128;
+      const int cp = lane / C::HA, at = lane % C::HA;      // this lane's run of keys and its atom of 64 values
       for (int t = 0; t < n_tiles; ++t) {
         const int s = t % NST;
         if (t >= NST) {
@@ -266,17 +289,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
           }
           if (__shfl_sync(0xffffffffu, w_ok, 0) == 0) break;
         }
-        const int j = kv_begin + t * PN + lane * p.box_rows;            // first key of this lane's copy
-        const bool mine = lane < copies && j < kv_len;
+        const int j = kv_begin + t * PN + cp * p.box_rows;              // first key of this lane's copy
+        const bool mine = cp < copies && j < kv_len;
         const int page = mine ? __ldg(bt + (j >> p.page_shift)) : 0;
         const uint32_t n = __popc(__ballot_sync(0xffffffffu, mine));
         if (lane == 0) mbar_expect_tx(&kv_full[s], 2 * n * copy_bytes);
         __syncwarp();
         if (mine) {
-          const uint32_t dst = (uint32_t)s * TILE_BYTES + (uint32_t)lane * copy_bytes;
+          const uint32_t dst = (uint32_t)s * KV_TILE_BYTES + (uint32_t)at * C::ATOM_KEYS + (uint32_t)cp * copy_bytes;
           const int off = j & (p.page_size - 1);
-          tma_load_3d(k_s + dst, &tmap_k, &kv_full[s], 0, off, page * p.nkv + kvh);
-          tma_load_3d(v_s + dst, &tmap_v, &kv_full[s], 0, off, page * p.nkv + kvh);
+          tma_load_3d(k_s + dst, &tmap_k, &kv_full[s], at * 64, off, page * p.nkv + kvh);
+          tma_load_3d(v_s + dst, &tmap_v, &kv_full[s], at * 64, off, page * p.nkv + kvh);
         }
       }
     } else if (warp - 1 < RT) {
@@ -302,7 +325,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     // tile is ready long before its turn (up to NST tiles are on the way, from different warps).
     const int* bt = p.block_table + (size_t)seq * p.bt_stride;
     const int ch = lane & 7;                              // this lane's 16-byte chunk of a 128-byte row
-    const int rbase = lane >> 3;                          // its rows: rbase + 4 i, i < 32
+    const int rbase = lane >> 3;                          // its rows: rbase + 4 i, i < PN / 4
     for (int t = warp; t < n_tiles; t += LOADERS) {
       const int s = t % NST;
       if (t >= NST) {
@@ -314,9 +337,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
       }
       if (t == 0) load_q(0, RT * PM);                     // lands with the tile, announced by its barrier
       const int j0 = kv_begin + t * PN;
-      const uint32_t kd = k_s + (uint32_t)s * TILE_BYTES, vd = v_s + (uint32_t)s * TILE_BYTES;
+      const uint32_t kd = k_s + (uint32_t)s * KV_TILE_BYTES, vd = v_s + (uint32_t)s * KV_TILE_BYTES;
 #pragma unroll 1
-      for (int i0 = 0; i0 < 32; i0 += 8) {
+      for (int i0 = 0; i0 < PN / 4; i0 += 8) {
         int page[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {                     // eight page lookups in flight together
@@ -332,8 +355,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
           const bool valid = page[i] >= 0;
           const size_t src = valid ? ((((size_t)page[i] * p.nkv + kvh) * p.page_size + off) * HD + ch * 8) : 0;
           const uint32_t dst = (uint32_t)(r * 128 + ((ch ^ (r & 7)) << 4));
-          cp_async16z(kd + dst, p.kc + src, valid);
-          cp_async16z(vd + dst, p.vc + src, valid);
+#pragma unroll
+          for (int a = 0; a < C::HA; ++a) {
+            cp_async16z(kd + dst + (uint32_t)(a * C::ATOM_KEYS), p.kc + src + a * 64, valid);
+            cp_async16z(vd + dst + (uint32_t)(a * C::ATOM_KEYS), p.vc + src + a * 64, valid);
+          }
         }
       }
       cp_async_commit();
@@ -373,8 +399,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     const int pos = kv_len - q_len + tok;
     const int lo = p.window > 0 ? pos - p.window + 1 : 0;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const uint32_t pv_addr = lane_addr + PV_COL + (uint32_t)g * HD;
-    const uint32_t prow = p_s + (uint32_t)g * P_BYTES + (uint32_t)(r * 128);
+    const uint32_t pv_addr = lane_addr + C::O_COL + (uint32_t)g * HD;
+    const uint32_t prow = p_s + (uint32_t)g * C::P_BYTES + (uint32_t)(r * 128);
+    constexpr int NC = PN / 32;                           // the row's scores come 32 at a time
     const float sl = p.scale_log2e;
     float m = -INFINITY, l = 0.f;       // m: what the exponentials are taken against, up to 2^8 behind the true maximum
     bool ok = true;
@@ -388,34 +415,36 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     for (int t = 0; t < n_mine; ++t) {
       const int j0 = kv_begin + t * PN;
       const int k = t < n_both ? 2 * t + g : 2 * n_both + (t - n_both);
-      const uint32_t s_addr = lane_addr + S_COL + (uint32_t)(k % SB) * PN;      // this step's S accumulator
+      const uint32_t s_addr = lane_addr + C::S_COL + (uint32_t)(k % SB) * PN;   // this step's S accumulator
       if (!wait_on(&s_full[k % SB], (uint32_t)(k / SB) & 1u, 24, t)) { ok = false; break; }
       tc_fence_after();
-      // ---- the row's 128 scores, the hidden ones -inf, and their maximum
-      uint32_t v[4][32];
+      // ---- the row's PN scores, the hidden ones -inf, and their maximum
+      uint32_t v[NC][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + 32 * c, v[c]);
+      for (int c = 0; c < NC; ++c) tmem_ld32(s_addr + 32 * c, v[c]);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[k % SB]);        // the accumulator may take the scores of step k + 3
       if (!valid || j0 + PN - 1 > pos || j0 < lo) {        // some key is hidden from this row
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < NC; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int j = j0 + 32 * c + i;
             if (!(valid && j <= pos && j >= lo)) v[c][i] = 0xff800000u;
           }
       }
-      float mq[4];                                        // four chains side by side, not one of 64 links
+      float mq[NC];                                       // chains side by side, not one of 64 links
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < NC; ++c) {
         mq[c] = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 32; i += 2) mq[c] = fmax3(mq[c], __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]));
       }
-      const float mx = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
+      float mx = mq[0];
+#pragma unroll
+      for (int c = 1; c < NC; ++c) mx = fmaxf(mx, mq[c]);
       const float cand = fmaxf(m, mx * sl);               // the scale is positive: it commutes with max
       const bool move = cand > m + 8.f;                   // also the first visible key (m = -inf)
       float corr = 1.f;
@@ -443,8 +472,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
 #pragma unroll
       for (int i = 0; i < 8; ++i) lq[i] = 0.f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const uint32_t base = prow + (uint32_t)(c >> 1) * TILE_BYTES;      // a 64-key sub-tile of 16 KB
+      for (int c = 0; c < NC; ++c) {
+        const uint32_t base = prow + (uint32_t)(c >> 1) * C::ATOM_ROWS;    // an atom of 64 keys
 #pragma unroll
         for (int q8 = 0; q8 < 4; ++q8) {                  // 8 keys = one 16-byte chunk
           float e[8];
@@ -512,18 +541,18 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 EncodeTiledFn g_encode = nullptr;
 std::mutex g_mu;
 struct MapKey {
-  const void* p; long long planes; int page_size;
-  bool operator==(const MapKey& o) const { return p == o.p && planes == o.planes && page_size == o.page_size; }
+  const void* p; long long planes; int page_size, hd;
+  bool operator==(const MapKey& o) const { return p == o.p && planes == o.planes && page_size == o.page_size && hd == o.hd; }
 };
 struct MapHash {
   size_t operator()(const MapKey& k) const {
-    return std::hash<const void*>()(k.p) ^ (std::hash<long long>()(k.planes * 2654435761LL + k.page_size) << 1);
+    return std::hash<const void*>()(k.p) ^ (std::hash<long long>()(k.planes * 2654435761LL + k.page_size * 257 + k.hd) << 1);
   }
 };
 std::unordered_map<MapKey, CUtensorMap, MapHash> g_maps;
 
-// cache [planes = pages * kv heads][page_size][64] bf16; a copy brings box_rows keys of one plane
-int cache_map(CUtensorMap* out, const void* ptr, long long planes, int page_size, int box_rows) {
+// cache [planes = pages * kv heads][page_size][hd] bf16; a copy brings 64 values of box_rows keys of one plane
+int cache_map(CUtensorMap* out, const void* ptr, long long planes, int page_size, int hd, int box_rows) {
   std::lock_guard<std::mutex> lk(g_mu);
   if (!g_encode) {
     void* fn = nullptr;
@@ -535,13 +564,13 @@ int cache_map(CUtensorMap* out, const void* ptr, long long planes, int page_size
     }
     g_encode = (EncodeTiledFn)fn;
   }
-  MapKey key{ptr, planes, page_size};
+  MapKey key{ptr, planes, page_size, hd};
   auto it = g_maps.find(key);
   if (it == g_maps.end()) {
     CUtensorMap m;
-    cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)page_size, (cuuint64_t)planes};
-    cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)page_size * HD * 2};
-    cuuint32_t box[3] = {(cuuint32_t)HD, (cuuint32_t)box_rows, 1};
+    cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)page_size, (cuuint64_t)planes};
+    cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)page_size * hd * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     if (g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -553,22 +582,22 @@ int cache_map(CUtensorMap* out, const void* ptr, long long planes, int page_size
   return 0;
 }
 
-template <bool TMA>
+template <int HD, bool TMA>
 int launch_pf(const CUtensorMap& mk, const CUtensorMap& mv, const PfParams& p, int ctas, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attn_prefill_tc_kernel<TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
-        cudaSuccess) { cudaGetLastError(); return -5; }
+    if (cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Shape<HD>::SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return -5; }
     configured = true;
   }
-  return launch_ex(attn_prefill_tc_kernel<TMA>, dim3(ctas), dim3(THREADS), SMEM_BYTES, s, 1, mk, mv, p);
+  return launch_ex(attn_prefill_tc_kernel<HD, TMA>, dim3(ctas), dim3(THREADS), Shape<HD>::SMEM_BYTES, s, 1, mk, mv, p);
 }
 
 }  // namespace
 
-// q: [T, ...] bf16 rows with stride q_stride, head h at h*64; out likewise (16-byte aligned rows).
-// kcache / vcache: [num_pages][nkv][page_size][64] bf16. cu_q [S+1], kv_lens [S], block_table [S, bt_stride].
-// max_q_len: the longest portion in the batch (sizes the list of work items). Head size 64 only.
+// q: [T, ...] bf16 rows with stride q_stride, head h at h*hd; out likewise (16-byte aligned rows).
+// kcache / vcache: [num_pages][nkv][page_size][hd] bf16. cu_q [S+1], kv_lens [S], block_table [S, bt_stride].
+// max_q_len: the longest portion in the batch (sizes the list of work items). Head sizes 64 and 128.
 // sm_count: CTAs to launch at most (0: asked from the device).
 RLLM_API int rllm_attention_prefill_tc(const void* q, int q_stride, const void* kcache, const void* vcache,
                                        void* out, int out_stride, const int* cu_q, const int* kv_lens,
@@ -576,7 +605,7 @@ RLLM_API int rllm_attention_prefill_tc(const void* q, int q_stride, const void* 
                                        int num_pages, int nh, int nkv, int hd, int page_size, float scale, int window,
                                        int* err, int sm_count, void* stream) {
   if (num_seqs <= 0 || max_q_len <= 0) return 0;
-  if (hd != HD || nkv <= 0 || nh % nkv || page_size <= 0 || num_pages <= 0) return ERR_BAD_SIZE;
+  if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || page_size <= 0 || num_pages <= 0) return ERR_BAD_SIZE;
   if (q_stride % 8 || out_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
       ((uintptr_t)kcache & 15) || ((uintptr_t)vcache & 15)) return ERR_BAD_ALIGN;
   PfParams p;
@@ -602,15 +631,17 @@ RLLM_API int rllm_attention_prefill_tc(const void* q, int q_stride, const void* 
   // pages of a power of two from 8 keys up (whole 1 KB swizzle atoms) come by tensor copies
   const bool tma = p.page_shift >= 3 && (long long)num_pages * nkv <= 2147483647LL;
   CUtensorMap mk, mv;
+  cudaStream_t s = (cudaStream_t)stream;
   if (tma) {
-    p.box_rows = page_size < PN ? page_size : PN;
+    const int pn = hd == 64 ? Shape<64>::PN : Shape<128>::PN;
+    p.box_rows = page_size < pn ? page_size : pn;
     int rc;
-    if ((rc = cache_map(&mk, kcache, (long long)num_pages * nkv, page_size, p.box_rows))) return rc;
-    if ((rc = cache_map(&mv, vcache, (long long)num_pages * nkv, page_size, p.box_rows))) return rc;
-    return launch_pf<true>(mk, mv, p, ctas, (cudaStream_t)stream);
+    if ((rc = cache_map(&mk, kcache, (long long)num_pages * nkv, page_size, hd, p.box_rows))) return rc;
+    if ((rc = cache_map(&mv, vcache, (long long)num_pages * nkv, page_size, hd, p.box_rows))) return rc;
+    return hd == 64 ? launch_pf<64, true>(mk, mv, p, ctas, s) : launch_pf<128, true>(mk, mv, p, ctas, s);
   }
   p.box_rows = 0;
   memset(&mk, 0, sizeof(mk));
   mv = mk;
-  return launch_pf<false>(mk, mv, p, ctas, (cudaStream_t)stream);
+  return hd == 64 ? launch_pf<64, false>(mk, mv, p, ctas, s) : launch_pf<128, false>(mk, mv, p, ctas, s);
 }

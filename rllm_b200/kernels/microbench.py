@@ -159,7 +159,7 @@ def main(argv=None) -> int:
             else:
                 p.add_argument("--tokens", type=ints, default=[2048])
                 p.add_argument("--kernel", choices=["tc", "fa"], default="tc",
-                               help="tc: tcgen05 kernel (head size 64); fa: mma.sync kernel")
+                               help="tc: tcgen05 kernel (head sizes 64 and 128); fa: mma.sync kernel")
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("microbench: no CUDA device", file=sys.stderr)

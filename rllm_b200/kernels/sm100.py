@@ -243,15 +243,15 @@ TC_ATTENTION_MIN_KEYS = int(os.environ.get("RLLM_B200_TC_ATTENTION_MIN_KEYS", "1
 
 
 def prefill_tc_supported(q: torch.Tensor, kcache: torch.Tensor) -> bool:
-    return (q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and kcache.shape[3] == 64
-            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and kcache.data_ptr() % 16 == 0)
+    return (q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and kcache.shape[3] in (64, 128)
+            and kcache.is_contiguous() and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and kcache.data_ptr() % 16 == 0)
 
 
 def attention_prefill_tc(q, kcache, vcache, cu_q, kv_lens, block_table, max_q_len, nh, scale, window, out=None):
-    """Prefill attention on the tcgen05 tensor cores (bf16, head size 64): tiles of 128 rows x 128
-    keys, both products with their accumulators in TMEM."""
+    """Prefill attention on the tcgen05 tensor cores (bf16, head size 64 or 128): tiles of 128 rows x
+    128 (64) keys, both products with their accumulators in TMEM."""
     if not prefill_tc_supported(q, kcache):
-        raise ops.KernelError("attention_prefill_tc: bfloat16, head size 64, rows 16-byte aligned")
+        raise ops.KernelError("attention_prefill_tc: bfloat16, head size 64 or 128, rows 16-byte aligned")
     st = init(q.device)
     _, nkv, page_size, hd = kcache.shape
     if out is None:

@@ -125,14 +125,15 @@ def test_decode_kernel_with_cluster_merge(splits, nh, nkv, hd, page, window):
     assert torch.equal(out, again)
 
 
+@pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("nh,nkv,page,window", [(32, 8, 16, None), (6, 2, 8, None), (3, 1, 5, None), (8, 8, 16, 200),
                                                 (4, 1, 32, 70), (8, 2, 128, None), (4, 2, 256, 300)])
-def test_prefill_on_tcgen05(nh, nkv, page, window):
-    """The tcgen05 prefill kernel (head size 64) against the plain formula: portions that start
-    in the middle of what the cache holds, lengths on both sides of the 128-row and 128-key
-    tiles, a decode token and a two-token portion in the same launch, windows, and a far key
+def test_prefill_on_tcgen05(nh, nkv, page, window, hd):
+    """The tcgen05 prefill kernel (head sizes 64 and 128) against the plain formula: portions that
+    start in the middle of what the cache holds, lengths on both sides of the 128-row and the
+    key tiles, a decode token and a two-token portion in the same launch, windows, and a far key
     that must dominate its row."""
-    run(nh, nkv, 64, page, window, lens=[300, 517, 1, 130, 128, 700, 40], q_lens=[300, 260, 1, 2, 128, 129, 40],
+    run(nh, nkv, hd, page, window, lens=[300, 517, 1, 130, 128, 700, 40], q_lens=[300, 260, 1, 2, 128, 129, 40],
         splits=1, far=(1, 11) if window is None else None, kernel="tc")
 
 
@@ -155,7 +156,7 @@ def test_prefill_on_tcgen05_random_shapes(seed):
         q = min(q, 520)
         q_lens.append(q)
         lens.append(q + r.choice([0, 0, 1, 127, 128, r.randint(0, 300)]))
-    run(nkv * G, nkv, 64, page, window, lens=lens, q_lens=q_lens, splits=1, kernel="tc")
+    run(nkv * G, nkv, r.choice([64, 128]), page, window, lens=lens, q_lens=q_lens, splits=1, kernel="tc")
 
 
 def test_long_prompt_whole_and_chosen_splits():
