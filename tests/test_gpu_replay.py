@@ -68,6 +68,26 @@ def test_family_matches_plain(model_dirs, plain, name, dtype, family):
     print(f"tiny-{name} {dtype} {family}: worst relative error {worst:.2e}")
 
 
+@pytest.mark.parametrize("name", ["D", "E"])
+@pytest.mark.parametrize("family", list(FAMILIES))
+def test_family_with_the_tcgen05_prefill_attention(model_dirs, plain, name, family, monkeypatch):
+    """The engine takes the tcgen05 prefill attention from 1,024 keys; here from 16, so that the
+    short requests of the tiny models (head sizes 64 and 128, a window on one layer of E) go
+    through it in every family, beside decode tokens and with pages used again."""
+    from rllm_b200.kernels import sm100
+    monkeypatch.setattr(sm100, "TC_ATTENTION_MIN_KEYS", 16)
+    calls = []
+    real = sm100.attention_prefill_tc
+    monkeypatch.setattr(sm100, "attention_prefill_tc", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    reqs = requests_for(name)
+    steps = FAMILIES[family](reqs)
+    eng = engine_for(model_dirs[name], name, "bfloat16", replay.max_live_tokens(steps, reqs))
+    got = replay.run_in_process(eng, steps)
+    replay.compare(got, plain[name], TOL["bfloat16"], f"tiny-{name} bfloat16 {family} (tcgen05 attention)")
+    if family in ("whole", "prefill_then_decode"):      # the other families' portions may all be under 128 rows
+        assert calls, "the tcgen05 prefill kernel was not used"
+
+
 @pytest.mark.parametrize("name", list(tiny.TINY))
 def test_float32_is_the_same_however_it_is_cut(model_dirs, name):
     """In 32-bit every family gives bit-identical logits: each output element is summed in
