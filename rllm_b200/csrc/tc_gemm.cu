@@ -290,25 +290,23 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      // a descriptor moves with its address (16 bytes a unit): one is built, the rest are sums.
+      // This thread's time per K block is what paces the weight stream at small token tiles.
+      const uint64_t d0 = umma_desc_sw128(smem_u32(smem));
       bool ok = true;
       for (int i = 0; i < n_kb && ok; ++i) {
         const int s = i % C::STAGES;
         const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
         if (!mbar_wait(&full_bar[s], ph, &abort_flag)) { abort_flag = 1; record_failure(p.err, 2); ok = false; break; }
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
-        const uint32_t b_addr = a_addr + W_BYTES;
-        const uint64_t da = umma_desc_sw128(a_addr);
-        const uint64_t db = umma_desc_sw128(b_addr);
+        const uint64_t da = d0 + (uint64_t)(s * (C::STAGE_BYTES >> 4));
+        const uint64_t db = da + (uint64_t)(W_BYTES >> 4);
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k) {
           const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
           const uint64_t koff = (uint64_t)(k * UMMA_K * 2 / 16);
           umma_bf16(tmem_base, da + koff, db + koff, idesc, acc);
-          if (DUAL) {
-            const uint64_t du = umma_desc_sw128(a_addr + C::A_BYTES);
-            umma_bf16(tmem_base + BN, du + koff, db + koff, idesc, acc);
-          }
+          if (DUAL) umma_bf16(tmem_base + BN, da + (uint64_t)(C::A_BYTES >> 4) + koff, db + koff, idesc, acc);
         }
         umma_commit(&empty_bar[s]);      // the stage is free once these MMAs have read it
       }
