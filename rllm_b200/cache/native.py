@@ -18,6 +18,7 @@ _SIGS = {
     "rllm_cache_num_tokens": (_I, [_P, _I]), "rllm_cache_serial": (_LL, [_P, _I]), "rllm_cache_epoch": (_I, [_P, _I]),
     "rllm_cache_num_held": (_I, [_P, _I, _I]), "rllm_cache_pages": (_I, [_P, _I, _I, _P, _I]),
     "rllm_cache_check": (_I, [_P]), "rllm_rows_new": (_P, [_I, _I]), "rllm_rows_delete": (None, [_P]),
+    "rllm_rows_forget": (None, [_P, _I]),
     "rllm_fill_decode": (_I, [_P, _P, _I, _P, _P, _I, _P, _P]),
 }
 

@@ -277,8 +277,17 @@ RLLM_API int rllm_cache_check(void* cv) {
 // ------------------------------------------------------------------------------------ decode metadata
 RLLM_API void* rllm_rows_new(int S, int G) { return new Rows(S, G); }
 RLLM_API void rllm_rows_delete(void* r) { delete static_cast<Rows*>(r); }
+// Rows `from` and up no longer hold what they were written with (the caller has put stand-in rows there).
+RLLM_API void rllm_rows_forget(void* r, int from) {
+  Rows* rows = static_cast<Rows*>(r);
+  for (int s = from < 0 ? 0 : from; s < rows->S; ++s) {
+    rows->serial[(size_t)s] = -1;
+    for (int g = 0; g < rows->G; ++g) rows->count[(size_t)s * rows->G + g] = 0;
+  }
+}
 
-// The metadata of a step in which each of S holdings brings one token, into `host` (int32):
+// The metadata of a step in which each of S holdings brings one token, into the first S rows of
+// `host` (int32; the buffer may have more rows than S, which this leaves alone):
 //   offs[0] ids | offs[1] positions | offs[4] key counts | offs[5] state slots |
 //   per group g: offs[7 + 2g] cache slot of the new token, offs[8 + 2g] block table [S, P].
 // (Vectors 2, 3 and 6 do not change from step to step and are written when the buffer is made.)
@@ -288,7 +297,7 @@ RLLM_API int rllm_fill_decode(void* cv, void* rv, int S, const int* handles, con
   Cache* c = static_cast<Cache*>(cv);
   Rows* rows = static_cast<Rows*>(rv);
   const int G = (int)c->pools.size();
-  if (S != rows->S || G != rows->G) return -3;
+  if (S > rows->S || G != rows->G) return -3;
   const int ps = c->page_size;
   int dirty = 0;
   for (int s = 0; s < S; ++s) {

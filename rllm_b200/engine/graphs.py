@@ -6,11 +6,15 @@ step is therefore captured once per shape and replayed: the same kernels, on the
 reading the step's metadata (token ids, positions, slots, block tables, key counts) from a
 device buffer at a fixed address that is refilled before every replay.
 
-A graph is keyed by (number of requests, block-table width). The width is the pages of the
-longest request rounded up to a power of two, so that a request growing by a token a step
-meets a new graph only when its length doubles. Everything a kernel's launch shape depends
-on (grid sizes, how many ranges the keys are cut into) follows from the key; what differs
-from step to step is read on the device.
+A graph is keyed by (rows, block-table width). The width is the pages of the longest request
+rounded up to a power of two, so that a request growing by a token a step meets a new graph
+only when its length doubles. The rows are the number of requests rounded up to a size from a
+short list (every size up to 8, then steps of 4, 8 and 16): a capture costs about thirty
+replays, and a batch that shrinks request by request would otherwise meet a new graph at every
+step. Rows beyond the requests are stand-ins: one token at position 0 that sees one key (the
+first of page 0, whatever it holds) and writes none; their logits are not returned. Everything
+a kernel's launch shape depends on (grid sizes, how many ranges the keys are cut into) follows
+from the key; what differs from step to step is read on the device.
 
 Only models whose parts all declare `graph_safe` (they read nothing of the step on the
 host) are captured; any other model runs launch by launch.
@@ -30,9 +34,17 @@ MAX_GRAPH_BATCH = 256
 MAX_GRAPHS = 48
 
 
+def padded_rows(S: int) -> int:
+    """The graph size that serves S requests."""
+    if S <= 8:
+        return S
+    step = 4 if S <= 32 else 8 if S <= 64 else 16
+    return (S + step - 1) // step * step
+
+
 class _Slot:
     __slots__ = ("lay", "host", "dev", "ctx", "rows", "graph", "logits", "copied", "launches", "head", "handles", "tokens", "rows_state",
-                 "_lib")
+                 "live", "_lib")
 
     def __del__(self):
         rs, L = getattr(self, "rows_state", None), getattr(self, "_lib", None)
@@ -89,6 +101,7 @@ class DecodeGraphs:
         slot.handles = np.zeros(S, dtype=np.int32)
         slot.tokens = np.zeros(S, dtype=np.int32)
         slot.head = int(lay.offs[8]) if len(eng.cache.groups) == 1 else lay.total   # ints before the first table
+        slot.live = S                                                   # rows that held requests in the last step
         host = slot.host.numpy()
         lay.view(host, 2, S)[:] = np.arange(S, dtype=np.int32)          # token s belongs to sequence s
         lay.view(host, 3, S + 1)[:] = np.arange(S + 1, dtype=np.int32)  # one row each
@@ -129,14 +142,29 @@ class DecodeGraphs:
         numbers each step, a block-table row only where it changed). Returns whether a table row
         was touched."""
         cache = self.engine.cache
-        S = slot.lay.S
-        slot.handles[:] = [rc.handle for rc in rcs]
-        slot.tokens[:] = [e.tokens[0] for e in entries]
+        S, lay = len(entries), slot.lay
+        slot.handles[:S] = [rc.handle for rc in rcs]
+        slot.tokens[:S] = [e.tokens[0] for e in entries]
         rc = cache._L.fill_decode(cache._ptr, slot.rows_state, S, slot.handles.ctypes.data, slot.tokens.ctypes.data,
-                                  slot.lay.P, slot.host.data_ptr(), slot.lay.offs.ctypes.data)
+                                  lay.P, slot.host.data_ptr(), lay.offs.ctypes.data)
         if rc < 0:
             raise RuntimeError(f"decode metadata could not be written (code {rc})")
-        return rc > 0
+        dirty = rc > 0
+        if S != slot.live:
+            # rows S.. stand in for requests that are not there: token 0 at position 0, one key
+            # (page 0, offset 0), nothing written, no state
+            host = slot.host.numpy()
+            for i, v in ((0, 0), (1, 0), (4, 1), (5, -1)):
+                lay.view(host, i, lay.S)[S:] = v
+            for g in range(lay.G):
+                lay.view(host, 7 + 2 * g, lay.S)[S:] = -1
+                table = lay.view(host, 8 + 2 * g, lay.S * lay.P).reshape(lay.S, lay.P)
+                table[S:] = -1
+                table[S:, 0] = 0
+            cache._L.rows_forget(slot.rows_state, S)
+            slot.live = S
+            dirty = True
+        return dirty
 
     def run(self, entries, rcs, keep: bool = True, feed: torch.Tensor | None = None) -> torch.Tensor | None:
         """Replay the graph of this shape. `feed`: int32 [S] on the device, the entries' token ids
@@ -144,7 +172,7 @@ class DecodeGraphs:
         seen the tokens that the step before it drew."""
         eng = self.engine
         S = len(entries)
-        key = (S, self._width(rcs))
+        key = (padded_rows(S), self._width(rcs))
         slot = self.slots.get(key)
         if slot is None:
             slot = self._new_slot(*key)
@@ -169,6 +197,6 @@ class DecodeGraphs:
         if not wanted:
             return None
         if len(wanted) == S:
-            return slot.logits.clone() if keep else slot.logits
+            return slot.logits[:S].clone() if keep else slot.logits[:S]
         idx = torch.tensor(wanted, dtype=torch.int32).to(eng.device)
         return ops.gather_rows(slot.logits, idx)

@@ -203,6 +203,35 @@ def test_random_traffic_is_the_same_with_and_without_steps_ahead(dirs, seed):
     assert a == b
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_shrinking_batch_reuses_padded_graphs(dirs, dtype):
+    """Thirteen requests decode together and end one after the other. Decode graphs come in a
+    short list of sizes (13 requests run in the graph for 16, the rows beyond them are stand-ins),
+    so the batch meets a handful of captures on its way down, not one per size; and every
+    request's tokens are what it gets alone."""
+    from rllm_b200.engine.graphs import padded_rows
+    from rllm_b200.sampling import SamplingParams
+    assert [padded_rows(n) for n in (1, 8, 9, 12, 13, 33, 64, 65, 200)] == [1, 8, 12, 12, 16, 40, 64, 80, 208]
+    name = "D"
+    cfg, w = P.read_model_dir(dirs[name])
+    prompts = [tiny.random_prompt(3 + 2 * i, cfg["vocab_size"], 500 + i) for i in range(13)]
+    sps = [SamplingParams(temperature=0.0, max_tokens=4 + 3 * i) for i in range(13)]
+    m = llm(dirs[name], name, dtype, num_pages=64, max_active=16)
+    outs = m.generate(prompts, sps)
+    sizes = sorted({k[0] for k in m.engine.graphs.slots})
+    assert set(sizes) <= {1, 2, 3, 4, 5, 6, 7, 8, 12, 16} and 16 in sizes and 12 in sizes
+    for p_, sp, o in zip(prompts, sps, outs):
+        assert len(o) == sp.max_tokens
+        if dtype == "float32":
+            assert o == P.greedy(cfg, w, p_, sp.max_tokens)
+        else:       # a near tie may go either way in bfloat16: each token against the plain logits of its own history
+            lg = P.forward(cfg, w, p_ + o[:-1])[len(p_) - 1:]
+            for i, tok in enumerate(o):
+                assert float(lg[i].max() - lg[i, tok]) <= 3e-2 * float(lg.abs().max()), (i, tok)
+    m.engine.cache.check()
+    assert m.engine.cache.free_pages() == [64]
+
+
 def test_the_step_loop_reports_a_kernel_that_gave_up(dirs):
     """A kernel whose bounded wait ran out sets a device word and returns; the words travel to the
     host with every step's tokens, and `LLM.step` raises. (The word is set by hand here.)"""
