@@ -123,7 +123,8 @@ class DecodeGraphs:
         before = ops.LAUNCHES
         # Nothing may be destroyed while the capture runs: a dead cycle that holds another
         # engine's graphs or pinned buffers, collected in the middle of it, invalidates it.
-        gc.collect()
+        # So the collector is off meanwhile (a collection beforehand would cost as much as the
+        # capture itself).
         gc_was_on = gc.isenabled()
         gc.disable()
         try:
