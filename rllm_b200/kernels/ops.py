@@ -79,7 +79,13 @@ def _check(rc: int, what: str, launches: int = 1) -> None:
     raise KernelError(f"{what}: CUDA launch failed with error {rc}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current stream's handle (asked once per launch: the short way, where torch has it)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 

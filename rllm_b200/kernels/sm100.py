@@ -320,10 +320,26 @@ def attention(q, cache, ctx, nh, scale, window):
         return attention_decode(q, cache.k, cache.v, ctx.kv_lens, cache.block_table, nh, scale, window,
                                 ctx.max_kv_len)
     nkv = cache.k.shape[1]
-    if ctx.max_q_len * (nh // nkv) >= 128 and ctx.max_kv_len >= TC_ATTENTION_MIN_KEYS \
+    G = nh // nkv
+    if ctx.max_q_len * G >= 128 and ctx.max_kv_len >= TC_ATTENTION_MIN_KEYS \
             and prefill_tc_supported(q, cache.k) and os.environ.get("RLLM_B200_NO_TC_ATTENTION") != "1":
         # long portions over long contexts: tiles of 128 (token, head) rows x 128 keys on the tcgen05
         # tensor cores (measured level with the mma.sync kernel at 512 keys, 1.4 x at 1,024, 2.3 x at 2,048)
+        lens = ctx.q_lens_host
+        D = 0                    # sequences in front that bring one token each (the scheduler puts decoding first)
+        if lens is not None and ctx.kv_lens_host is not None and decode_supported(q, cache.k, nh):
+            while D < len(lens) and lens[D] == 1:
+                D += 1
+        if 0 < D < len(lens) and max(lens[D:]) * G >= 128:
+            # a mixed step: the decode kernel for the single tokens (a row tile of the other kernel
+            # would hold one token's heads and nothing else), the portions after them on tcgen05
+            hd = cache.k.shape[3]
+            out = torch.empty((q.shape[0], nh * hd), dtype=torch.bfloat16, device=q.device)
+            attention_decode(q[:D], cache.k, cache.v, ctx.kv_lens[:D], cache.block_table[:D], nh, scale, window,
+                             max(ctx.kv_lens_host[:D]), out=out[:D])
+            attention_prefill_tc(q, cache.k, cache.v, ctx.cu_q[D:], ctx.kv_lens[D:], cache.block_table[D:],
+                                 max(lens[D:]), nh, scale, window, out=out)
+            return out
         return attention_prefill_tc(q, cache.k, cache.v, ctx.cu_q, ctx.kv_lens, cache.block_table, ctx.max_q_len,
                                     nh, scale, window)
     return attention_fa(q, cache.k, cache.v, ctx.cu_q, ctx.kv_lens, cache.block_table, ctx.num_tokens,

@@ -88,6 +88,38 @@ def test_family_with_the_tcgen05_prefill_attention(model_dirs, plain, name, fami
         assert calls, "the tcgen05 prefill kernel was not used"
 
 
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_long_portions_beside_decode_tokens(model_dirs, plain, name, monkeypatch):
+    """A step as the scheduler builds it under load: requests that decode in front, then a prompt
+    portion long enough for the tcgen05 prefill attention. The single tokens then go to the decode
+    kernel and the portion to the tcgen05 kernel, in one step, into one output."""
+    from rllm_b200.kernels import sm100
+    monkeypatch.setattr(sm100, "TC_ATTENTION_MIN_KEYS", 16)
+    used = {"decode": 0, "tc": 0}
+    real_d, real_t = sm100.attention_decode, sm100.attention_prefill_tc
+    monkeypatch.setattr(sm100, "attention_decode", lambda *a, **k: (used.__setitem__("decode", used["decode"] + 1), real_d(*a, **k))[1])
+    monkeypatch.setattr(sm100, "attention_prefill_tc", lambda *a, **k: (used.__setitem__("tc", used["tc"] + 1), real_t(*a, **k))[1])
+    reqs = requests_for(name)
+    a, b, c, d = "r1", "r2", "r3", "r4"          # D: 70, 131, 300, 65 tokens; E: 150, 64, 257, 33
+    ent = lambda r, lo, hi: {"id": r, "tokens": reqs[r][lo:hi], "want": list(range(hi - lo))}
+    na, nb, nc, nd = (len(reqs[r]) for r in (a, b, c, d))
+    steps = [{"entries": [ent(a, 0, na - 3)], "end": []},
+             {"entries": [ent(b, 0, nb - 3)], "end": []},
+             {"entries": [ent(a, na - 3, na - 2), ent(b, nb - 3, nb - 2), ent(c, 0, 120)], "end": []},
+             {"entries": [ent(a, na - 2, na - 1), ent(b, nb - 2, nb - 1), ent(c, 120, nc - 1), ent(d, 0, nd)], "end": [d]},
+             {"entries": [ent(a, na - 1, na), ent(b, nb - 1, nb), ent(c, nc - 1, nc)], "end": [a, b, c]}]
+    for i, s in enumerate(steps):
+        s["step"] = i
+    eng = engine_for(model_dirs[name], name, "bfloat16", replay.max_live_tokens(steps, reqs))
+    before = dict(used)
+    got = replay.run_in_process(eng, steps)
+    want = {k: v for k, v in plain[name].items() if k[0] in (a, b, c, d)}
+    replay.compare(got, want, TOL["bfloat16"], f"tiny-{name} bfloat16 portions beside decode tokens")
+    # steps 2 and 3 each went to both kernels, in every layer
+    layers = tiny.TINY[name][0]["num_hidden_layers"]
+    assert used["tc"] - before["tc"] >= 4 * layers and used["decode"] - before["decode"] >= 3 * layers
+
+
 @pytest.mark.parametrize("name", list(tiny.TINY))
 def test_float32_is_the_same_however_it_is_cut(model_dirs, name):
     """In 32-bit every family gives bit-identical logits: each output element is summed in
