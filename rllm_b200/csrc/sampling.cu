@@ -10,6 +10,7 @@
 // threshold are all kept, as in sampler.rs:397-403.
 #include "common.cuh"
 #include "sm100.cuh"
+#include <type_traits>
 using namespace rllm;
 
 namespace {
@@ -221,6 +222,256 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
 #undef EXPV
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// The same pipeline with the row kept in shared memory: the CTAs of a cluster (up to 8 along z)
+// take a slice of the vocabulary each, hold its scaled logits (then its probabilities) in shared
+// memory, and every reduction runs block -> cluster through distributed shared memory, the ranks'
+// parts always added in rank order, so that every CTA gets the same bits and takes the same way.
+// The two thresholds (k-th largest logit; the largest probability tau with mass{p >= tau} >= top_p)
+// are found on the bit pattern of a float as in the kernel above, but with eight probes a pass,
+// which narrows the interval ninefold: 11 passes instead of 32, over shared memory instead of L2.
+constexpr int SAMPLE_SPLIT = 8;            // CTAs per row at most
+constexpr int SAMPLE_SLICE_MAX = 32768;    // floats of the row a CTA keeps (128 KB)
+constexpr int WAYS = 8;                    // probes per pass
+
+struct SampleShared {
+  float red_f[32][WAYS];
+  int red_i[32][WAYS];
+  float part_f[2][WAYS];     // this CTA's parts of a reduction, by parity of the reduction's number
+  int part_i[2][WAYS];
+  float tot_f[WAYS];
+  int tot_i[WAYS];
+  int pick_thread, last_thread;
+};
+
+// v[j] of every thread of every CTA of the cluster added up (MAX: the largest), same result everywhere.
+// `seq` counts the reductions of the kernel: the parts are double-buffered by its parity, so that one
+// cluster barrier a reduction is enough (a rank two reductions ahead cannot exist: it needs this one's result).
+template <typename T, bool MAX>
+__device__ __forceinline__ void cluster_reduce(T (&v)[WAYS], T (*red)[WAYS], T (*part)[WAYS], T* tot, int& seq,
+                                               int splits) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  auto join = [](T a, T b) { return MAX ? (b > a ? b : a) : a + b; };
+#pragma unroll
+  for (int j = 0; j < WAYS; ++j) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v[j] = join(v[j], __shfl_xor_sync(0xffffffffu, v[j], o));
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int j = 0; j < WAYS; ++j) red[warp][j] = v[j];
+  }
+  __syncthreads();
+  const int par = seq & 1;
+  if (warp < WAYS) {                               // warp j joins the 32 warps' values of probe j
+    T a = red[lane][warp];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a = join(a, __shfl_xor_sync(0xffffffffu, a, o));
+    if (lane == 0) part[par][warp] = a;
+  }
+  if (splits > 1) {
+    sm100::cluster_sync_all();                     // every rank's parts are written (and visible)
+    if (warp == 0) {
+      // lane = 8 (r & 3) + j reads the parts of ranks r and r + 4 for probe j; two exchanges join the four pairs
+      const int j = lane & 7, r = lane >> 3;
+      auto remote = [&](int rr) -> T {
+        if (rr >= splits) return MAX ? (T)-INFINITY : (T)0;
+        const uint32_t addr = sm100::map_to_rank(sm100::smem_u32(&part[par][j]), (uint32_t)rr);
+        if constexpr (std::is_same<T, float>::value) return sm100::ld_cluster_f32(addr);
+        else return (T)sm100::ld_cluster_u32(addr);
+      };
+      T a = join(remote(r), remote(r + 4));
+      a = join(a, __shfl_xor_sync(0xffffffffu, a, 8));
+      a = join(a, __shfl_xor_sync(0xffffffffu, a, 16));
+      if (lane < WAYS) tot[lane] = a;
+    }
+  } else {
+    __syncthreads();
+    if (threadIdx.x < WAYS) tot[threadIdx.x] = part[par][threadIdx.x];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < WAYS; ++j) v[j] = tot[j];
+  ++seq;
+  __syncthreads();                                  // tot and red may be written again
+}
+
+// probes t_1 < ... < t_WAYS in (lo, hi], evenly spread (clipped to hi when the interval is short)
+__device__ __forceinline__ void probes(unsigned lo, unsigned hi, unsigned (&t)[WAYS]) {
+  const unsigned long long span = (unsigned long long)hi - lo;          // >= 1
+  const unsigned long long step = span / (WAYS + 1) > 0 ? span / (WAYS + 1) : 1;
+#pragma unroll
+  for (int j = 0; j < WAYS; ++j) {
+    const unsigned long long x = (unsigned long long)lo + (unsigned long long)(j + 1) * step;
+    t[j] = x > hi ? hi : (unsigned)x;
+  }
+}
+
+__global__ void __launch_bounds__(THREADS)
+sample_cluster_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
+                      const int* __restrict__ top_k, const float* __restrict__ top_p,
+                      const float* __restrict__ min_p, const float* __restrict__ uniform,
+                      int* __restrict__ out, int splits, int per) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ float vals[];                  // the slice: scaled logits, later probabilities
+  __shared__ SampleShared sh;
+  const int row = blockIdx.x;
+  const float T = temperature[row];
+  if (!(T > 0.f)) return;            // a greedy row (the same for every CTA of its cluster): out[row] holds its argmax
+  const float invT = 1.f / T;
+  const int tid = threadIdx.x;
+  const int rank = splits > 1 ? (int)sm100::cluster_rank() : 0;
+  const int b = min(V, rank * per), n = min(V, b + per) - b;
+  const float* x = logits + (size_t)row * V + b;
+  for (int i = tid; i < n; i += THREADS) vals[i] = x[i] * invT;
+  __syncthreads();
+  int seq = 0;
+  float f8[WAYS];
+  int i8[WAYS];
+
+  // 1. top-k threshold on the scaled logits: the largest key t with count{key >= t} >= k (ties kept)
+  float thr = -INFINITY;
+  const int k = top_k ? top_k[row] : 0;
+  if (k > 0 && k < V) {
+    unsigned lo = 0u, hi = 0xffffffffu;
+    while (lo < hi) {
+      unsigned t[WAYS];
+      probes(lo, hi, t);
+#pragma unroll
+      for (int j = 0; j < WAYS; ++j) i8[j] = 0;
+      for (int i = tid; i < n; i += THREADS) {
+        const unsigned key = f2key(vals[i]);
+#pragma unroll
+        for (int j = 0; j < WAYS; ++j) i8[j] += (key >= t[j]);
+      }
+      cluster_reduce<int, false>(i8, sh.red_i, sh.part_i, sh.tot_i, seq, splits);
+      int best = -1;                                // the largest probe that still has k at or above it
+#pragma unroll
+      for (int j = 0; j < WAYS; ++j) if (i8[j] >= k) best = j;
+      const unsigned nlo = best >= 0 ? t[best] : lo;
+      const unsigned nhi = best == WAYS - 1 ? hi : t[best + 1] - 1u;
+      lo = nlo; hi = nhi < nlo ? nlo : nhi;
+    }
+    thr = key2f(lo);
+  }
+  // 2. softmax over the kept logits: e = exp(v - max), 0 for the dropped
+#pragma unroll
+  for (int j = 0; j < WAYS; ++j) f8[j] = -INFINITY;
+  for (int i = tid; i < n; i += THREADS) { const float v = vals[i]; if (v >= thr) f8[0] = fmaxf(f8[0], v); }
+  cluster_reduce<float, true>(f8, sh.red_f, sh.part_f, sh.tot_f, seq, splits);
+  const float mx = f8[0];
+  const float emin = min_p ? fmaxf(min_p[row], 0.f) : 0.f;
+#pragma unroll
+  for (int j = 0; j < WAYS; ++j) f8[j] = 0.f;
+  for (int i = tid; i < n; i += THREADS) {
+    const float v = vals[i];
+    const float e = v >= thr ? expf(v - mx) : 0.f;
+    vals[i] = e;
+    f8[0] += e;
+    // 3. min-p: drop p < min_p * max p. The largest e is 1, so the rule is e < min_p, exact in the e domain
+    if (e >= emin) f8[1] += e;
+  }
+  cluster_reduce<float, false>(f8, sh.red_f, sh.part_f, sh.tot_f, seq, splits);
+  const float inv_sum = 1.f / (emin > 0.f ? f8[1] : f8[0]);
+  for (int i = tid; i < n; i += THREADS) { const float e = vals[i]; vals[i] = e >= emin ? e * inv_sum : 0.f; }
+  __syncthreads();
+  // 4. top-p: the largest tau with mass{p >= tau} >= top_p
+  const float tp = top_p ? top_p[row] : 1.f;
+  float tau = 0.f, mass = 1.f;
+  if (tp < 1.f) {
+    unsigned lo = 0u, hi = __float_as_uint(1.0f);
+    while (lo < hi) {
+      unsigned t[WAYS];
+      probes(lo, hi, t);
+#pragma unroll
+      for (int j = 0; j < WAYS; ++j) f8[j] = 0.f;
+      for (int i = tid; i < n; i += THREADS) {
+        const float pr = vals[i];
+#pragma unroll
+        for (int j = 0; j < WAYS; ++j) if (pr >= __uint_as_float(t[j])) f8[j] += pr;
+      }
+      cluster_reduce<float, false>(f8, sh.red_f, sh.part_f, sh.tot_f, seq, splits);
+      int best = -1;
+#pragma unroll
+      for (int j = 0; j < WAYS; ++j) if (f8[j] >= tp) best = j;
+      const unsigned nlo = best >= 0 ? t[best] : lo;
+      const unsigned nhi = best == WAYS - 1 ? hi : t[best + 1] - 1u;
+      lo = nlo; hi = nhi < nlo ? nlo : nhi;
+    }
+    tau = __uint_as_float(lo);
+  }
+  // 5. inverse CDF in vocabulary order: the first i with cumulative > u * mass. Every thread adds up a
+  //    run of consecutive entries, every CTA its slice; the slices before this one give its offset.
+  const int per_t = (n + THREADS - 1) / THREADS;
+  const int tb = min(n, tid * per_t), te = min(n, tb + per_t);
+  float local = 0.f;
+  for (int i = tb; i < te; ++i) { const float pr = vals[i]; if (pr >= tau && pr > 0.f) local += pr; }
+  // the masses before each thread's run, in a fixed order: lanes within a warp, then the warps
+  const int lane = tid & 31, warp = tid >> 5;
+  float incl = local;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) { const float t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+  if (lane == 31) sh.red_f[warp][0] = incl;
+  if (tid == 0) { sh.pick_thread = 0x7fffffff; sh.last_thread = -1; }
+  __syncthreads();
+  if (warp == 0) {
+    const float w = sh.red_f[lane][0];              // THREADS / 32 = 32 warps
+    float wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const float t = __shfl_up_sync(0xffffffffu, wi, o); if (lane >= o) wi += t; }
+    sh.red_f[lane][1] = wi - w;
+    if (lane == 31) sh.part_f[seq & 1][0] = wi;     // the slice's mass
+  }
+  __syncthreads();
+  const float excl = sh.red_f[warp][1] + (incl - local);
+  float slice_mass[SAMPLE_SPLIT];
+  if (splits > 1) sm100::cluster_sync_all();
+  for (int r = 0; r < splits; ++r)
+    slice_mass[r] = splits > 1 ? sm100::ld_cluster_f32(sm100::map_to_rank(sm100::smem_u32(&sh.part_f[seq & 1][0]), (uint32_t)r))
+                               : sh.part_f[seq & 1][0];
+  ++seq;
+  mass = 0.f;
+  for (int r = 0; r < splits; ++r) mass += slice_mass[r];
+  const float target = uniform[row] * mass;
+  // which slice holds the target; if rounding leaves none above it, the last slice with mass
+  int owner = -1, last_with_mass = -1;
+  float before = 0.f, before_owner = 0.f;
+  for (int r = 0; r < splits; ++r) {
+    if (slice_mass[r] > 0.f) last_with_mass = r;
+    if (owner < 0 && before + slice_mass[r] > target) { owner = r; before_owner = before; }
+    before += slice_mass[r];
+  }
+  const bool fallback = owner < 0;
+  if (fallback) owner = last_with_mass < 0 ? 0 : last_with_mass;
+  if (rank == owner) {
+    // the first thread whose run takes the cumulative mass past the target; else the last one with mass
+    const float cum0 = before_owner + excl;
+    if (local > 0.f) {
+      atomicMax(&sh.last_thread, tid);
+      if (!fallback && cum0 + local > target) atomicMin(&sh.pick_thread, tid);
+    }
+    __syncthreads();
+    const bool none = sh.pick_thread == 0x7fffffff;
+    const int pick = none ? (sh.last_thread < 0 ? 0 : sh.last_thread) : sh.pick_thread;
+    if (tid == pick) {
+      float cum = none ? 0.f : cum0;
+      const float tgt = none ? INFINITY : target;
+      int chosen = -1, last = -1;
+      for (int i = tb; i < te; ++i) {
+        const float pr = vals[i];
+        if (!(pr >= tau && pr > 0.f)) continue;
+        last = i;
+        cum += pr;
+        if (cum > tgt) { chosen = i; break; }
+      }
+      out[row] = b + (chosen >= 0 ? chosen : (last >= 0 ? last : 0));
+    }
+  }
+  if (splits > 1) sm100::cluster_sync_all();        // nobody leaves while another rank may still read its parts
+}
+
 }  // namespace
 
 RLLM_API int rllm_argmax(const float* logits, int R, int V, int* out, void* stream) {
@@ -238,7 +489,20 @@ RLLM_API int rllm_sample(const float* logits, int R, int V, const float* tempera
                          const float* uniform, int* out, void* stream) {
   if (R <= 0) return 0;
   if (V <= 0) return ERR_BAD_SIZE;
-  int rc = launch_ex(sample_kernel, dim3(R), dim3(THREADS), 0, (cudaStream_t)stream, 1, logits, V, temperature, top_k, top_p,
-                                                         min_p, uniform, out);
-  return rc;
+  // the row in the shared memory of 1 to 8 CTAs; a vocabulary beyond that goes the slow way, through L2
+  int splits = 1;
+  while (splits < SAMPLE_SPLIT && (V + splits - 1) / splits > SAMPLE_SLICE_MAX / 2) splits *= 2;
+  const int per = ((V + splits - 1) / splits + 3) & ~3;
+  if (per <= SAMPLE_SLICE_MAX) {
+    static bool configured = false;
+    if (!configured) {
+      if (cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               SAMPLE_SLICE_MAX * 4) != cudaSuccess) { cudaGetLastError(); return -5; }
+      configured = true;
+    }
+    return launch_ex(sample_cluster_kernel, dim3(R, 1, splits), dim3(THREADS), (size_t)per * 4, (cudaStream_t)stream,
+                     splits, logits, V, temperature, top_k, top_p, min_p, uniform, out, splits, per);
+  }
+  return launch_ex(sample_kernel, dim3(R), dim3(THREADS), 0, (cudaStream_t)stream, 1, logits, V, temperature, top_k, top_p,
+                   min_p, uniform, out);
 }

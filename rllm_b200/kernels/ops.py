@@ -304,7 +304,8 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
 def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
            top_k: torch.Tensor | None = None, top_p: torch.Tensor | None = None,
            min_p: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
-    """One draw per row with per-row parameters (device vectors of length R)."""
+    """One draw per row with per-row parameters: vectors of length R on the device, or in pinned host
+    memory, which the kernel then reads itself (a few words a row; no copy to wait for)."""
     _cuda(logits, "logits")
     if logits.dtype != torch.float32 or logits.dim() != 2 or not logits.is_contiguous():
         raise KernelError("sample takes contiguous float32 logits [R, V]")
@@ -312,8 +313,8 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
     for t, n, d in ((temperature, "temperature", torch.float32), (uniform, "uniform", torch.float32),
                     (top_k, "top_k", torch.int32), (top_p, "top_p", torch.float32),
                     (min_p, "min_p", torch.float32)):
-        if t is not None and (t.dtype != d or t.numel() != R or not t.is_cuda):
-            raise KernelError(f"{n} must be a CUDA {d} vector of length {R}")
+        if t is not None and (t.dtype != d or t.numel() != R or not (t.is_cuda or t.is_pinned()) or not t.is_contiguous()):
+            raise KernelError(f"{n} must be a {d} vector of length {R} on the device or in pinned host memory")
     if out is None:
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
     _check(_fn("simt", "rllm_sample")(logits.data_ptr(), R, V, temperature.data_ptr(), _ptr(top_k),

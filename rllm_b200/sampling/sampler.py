@@ -14,6 +14,7 @@ class Sampler:
     def __init__(self, backend):
         self.backend = backend
         self.device = backend.device
+        self._ring, self._turn = [], 0
 
     def __call__(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int],
                  indices: list[int], histories: list[list[int]] | None = None) -> list[int]:
@@ -32,19 +33,41 @@ class Sampler:
         be = self.backend
         if all(p.greedy for p in params):
             return be.argmax(logits)
-        f32 = dict(dtype=torch.float32, device=self.device)
-        temp = torch.tensor([p.temperature if not p.greedy else 0.0 for p in params], **f32)
-        u = torch.tensor([uniform(s, i) for s, i in zip(seeds, indices)], **f32)
+        # The rows' parameters go into pinned host memory that the kernel reads itself: nothing is
+        # copied, so nothing waits for the stream (steps are launched ahead of the host). Four
+        # buffers take turns; one is written again only after the kernel that read it has run.
+        buf, ints, done = self._staging(R)
+        done.synchronize()
+        a = buf.numpy()
+        a[0, :R] = [p.temperature if not p.greedy else 0.0 for p in params]
+        a[1, :R] = [uniform(s, i) for s, i in zip(seeds, indices)]
         top_k = top_p = min_p = None
         if any(p.top_k > 0 for p in params):
-            top_k = torch.tensor([p.top_k for p in params], dtype=torch.int32, device=self.device)
+            ints.numpy()[2, :R] = [p.top_k for p in params]
+            top_k = ints[2, :R]
         if any(p.top_p < 1.0 for p in params):
-            top_p = torch.tensor([p.top_p for p in params], **f32)
+            a[3, :R] = [p.top_p for p in params]
+            top_p = buf[3, :R]
         if any(p.min_p > 0.0 for p in params):
-            min_p = torch.tensor([p.min_p for p in params], **f32)
+            a[4, :R] = [p.min_p for p in params]
+            min_p = buf[4, :R]
         # greedy rows beside drawn ones: argmax of every row first; the draw skips rows of temperature 0
         out = be.argmax(logits) if any(p.greedy for p in params) else None
-        return be.sample(logits, temp, u, top_k, top_p, min_p, out=out)
+        drawn = be.sample(logits, buf[0, :R], buf[1, :R], top_k, top_p, min_p, out=out)
+        done.record()
+        return drawn
+
+    def _staging(self, R: int):
+        """The next of four pinned parameter buffers [5, rows] (float32, and the same memory seen as
+        int32 for top-k), with the event that tells when its last reader has run."""
+        if not self._ring or self._ring[0][0].shape[1] < R:
+            cap = max(64, 1 << (R - 1).bit_length())
+            self._ring = []
+            for _ in range(4):
+                buf = torch.zeros((5, cap), dtype=torch.float32).pin_memory()
+                self._ring.append((buf, buf.view(torch.int32), torch.cuda.Event()))
+        self._turn = (self._turn + 1) % len(self._ring)
+        return self._ring[self._turn]
 
     def _penalise(self, logits, params, histories):
         """logit[token] -= frequency_penalty * count + presence_penalty for tokens already

@@ -206,7 +206,7 @@ def test_argmax_lowest_index_wins_and_large_vocab():
     assert ops().argmax(y.to(DEV)).tolist() == torch.argmax(y, -1).tolist()
 
 
-@pytest.mark.parametrize("V", [256, 1000, 50257])
+@pytest.mark.parametrize("V", [256, 1000, 50257, 128256, 300000])
 @pytest.mark.parametrize("temperature,top_k,top_p,min_p", [
     (1.0, 0, 1.0, 0.0), (0.8, 0, 1.0, 0.0), (1.3, 40, 1.0, 0.0), (1.0, 0, 0.9, 0.0),
     (0.7, 0, 1.0, 0.05), (1.1, 50, 0.8, 0.02), (1.0, 1, 1.0, 0.0)])
