@@ -474,6 +474,24 @@ sample_cluster_kernel(const float* __restrict__ logits, int V, const float* __re
 
 }  // namespace
 
+// logits[rows[i], cols[i]] += vals[i], i < n (the penalties of tokens already produced: a handful of
+// entries; the three lists may lie in pinned host memory). (row, col) pairs are distinct.
+__global__ void add_at_kernel(float* __restrict__ logits, int V, const int* __restrict__ rows,
+                              const int* __restrict__ cols, const float* __restrict__ vals, int n) {
+  pdl_launch();
+  pdl_wait();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    logits[(size_t)rows[i] * V + cols[i]] += vals[i];
+}
+
+RLLM_API int rllm_add_at(float* logits, int R, int V, const int* rows, const int* cols, const float* vals, int n,
+                         void* stream) {
+  if (n <= 0) return 0;
+  if (R <= 0 || V <= 0) return ERR_BAD_SIZE;
+  const int blocks = (n + 255) / 256 < 64 ? (n + 255) / 256 : 64;
+  return launch_ex(add_at_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, 1, logits, V, rows, cols, vals, n);
+}
+
 RLLM_API int rllm_argmax(const float* logits, int R, int V, int* out, void* stream) {
   if (R <= 0) return 0;
   if (V <= 0) return ERR_BAD_SIZE;

@@ -173,5 +173,8 @@ class Backend:
     def argmax(self, logits):
         return ops.argmax(logits)
 
+    def add_at(self, logits, rows, cols, vals):
+        return ops.add_at(logits, rows, cols, vals)
+
     def sample(self, logits, temperature, uniform, top_k=None, top_p=None, min_p=None, out=None):
         return ops.sample(logits, temperature, uniform, top_k, top_p, min_p, out=out)

@@ -43,6 +43,7 @@ _SIGS = {
                                       c_int, c_int, c_int, c_int, c_float, c_int, _P],
         "rllm_argmax": [_P, c_int, c_int, _P, _P],
         "rllm_sample": [_P, c_int, c_int, _P, _P, _P, _P, _P, _P, _P],
+        "rllm_add_at": [_P, c_int, c_int, _P, _P, _P, c_int, _P],
     },
 }
 _fn_cache: dict[str, object] = {}
@@ -299,6 +300,22 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
     _check(_fn("simt", "rllm_argmax")(logits.data_ptr(), R, V, out.data_ptr(), _stream()), "argmax")
     return out
+
+
+def add_at(logits: torch.Tensor, rows: torch.Tensor, cols: torch.Tensor, vals: torch.Tensor) -> None:
+    """logits[rows[i], cols[i]] += vals[i] in place; distinct (row, col) pairs, every one inside the
+    matrix (the caller's duty: they are not checked on the device). The lists: int32, int32, float32
+    on the device or in pinned host memory."""
+    _cuda(logits, "logits")
+    if logits.dtype != torch.float32 or logits.dim() != 2 or not logits.is_contiguous():
+        raise KernelError("add_at takes contiguous float32 logits [R, V]")
+    n = rows.numel()
+    for t, d in ((rows, torch.int32), (cols, torch.int32), (vals, torch.float32)):
+        if t.dtype != d or t.numel() != n or not (t.is_cuda or t.is_pinned()) or not t.is_contiguous():
+            raise KernelError("add_at: rows and cols int32, vals float32, alike in length, on the device or pinned")
+    R, V = logits.shape
+    _check(_fn("simt", "rllm_add_at")(logits.data_ptr(), R, V, rows.data_ptr(), cols.data_ptr(), vals.data_ptr(), n,
+                                      _stream()), "add_at")
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,

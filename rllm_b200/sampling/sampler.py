@@ -15,6 +15,7 @@ class Sampler:
         self.backend = backend
         self.device = backend.device
         self._ring, self._turn = [], 0
+        self._held = []          # pinned lists a kernel may still read, each with its event
 
     def __call__(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int],
                  indices: list[int], histories: list[list[int]] | None = None) -> list[int]:
@@ -71,8 +72,8 @@ class Sampler:
 
     def _penalise(self, logits, params, histories):
         """logit[token] -= frequency_penalty * count + presence_penalty for tokens already
-        generated (src/model/sampler.rs:341-350). A handful of entries per row: a scatter of
-        host-computed values into a copy of the logits."""
+        generated (src/model/sampler.rs:341-350). A handful of entries per row: host-computed
+        values added into a copy of the logits by a small kernel."""
         rows, cols, vals = [], [], []
         for r, (p, hist) in enumerate(zip(params, histories or [[]] * len(params))):
             if not p.has_penalties or not hist:
@@ -86,6 +87,13 @@ class Sampler:
         if not rows:
             return logits
         out = logits.clone()
-        out.index_put_((torch.tensor(rows, device=self.device), torch.tensor(cols, device=self.device)),
-                       torch.tensor(vals, dtype=torch.float32, device=self.device), accumulate=True)
+        n = len(rows)
+        lists = torch.empty((3, n), dtype=torch.int32).pin_memory()     # read by the kernel; kept until it has run
+        a = lists.numpy()
+        a[0], a[1] = rows, cols
+        lists[2].view(torch.float32).numpy()[:] = vals
+        self.backend.add_at(out, lists[0], lists[1], lists[2].view(torch.float32))
+        done = torch.cuda.Event()
+        done.record()
+        self._held = [(l, e) for l, e in self._held if not e.query()] + [(lists, done)]
         return out
