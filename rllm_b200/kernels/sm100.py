@@ -239,7 +239,7 @@ def attention_fa(q, kcache, vcache, cu_q, kv_lens, block_table, num_tokens, max_
     return out
 
 
-TC_ATTENTION_MIN_KEYS = int(os.environ.get("RLLM_B200_TC_ATTENTION_MIN_KEYS", "1024"))
+TC_ATTENTION_MIN_KEYS = int(os.environ.get("RLLM_B200_TC_ATTENTION_MIN_KEYS", "512"))
 
 
 def prefill_tc_supported(q: torch.Tensor, kcache: torch.Tensor) -> bool:
@@ -324,7 +324,8 @@ def attention(q, cache, ctx, nh, scale, window):
     if ctx.max_q_len * G >= 128 and ctx.max_kv_len >= TC_ATTENTION_MIN_KEYS \
             and prefill_tc_supported(q, cache.k) and os.environ.get("RLLM_B200_NO_TC_ATTENTION") != "1":
         # long portions over long contexts: tiles of 128 (token, head) rows x 128 keys on the tcgen05
-        # tensor cores (measured level with the mma.sync kernel at 512 keys, 1.4 x at 1,024, 2.3 x at 2,048)
+        # tensor cores (measured against the mma.sync kernel, head size 64: level at 512 keys, 1.4 x at
+        # 1,024, 2.3 x at 2,048; head size 128: 1.2 x at 512, 2 x at 1,024, 3.2 x at 2,048; behind at 256)
         lens = ctx.q_lens_host
         D = 0                    # sequences in front that bring one token each (the scheduler puts decoding first)
         if lens is not None and ctx.kv_lens_host is not None and decode_supported(q, cache.k, nh):

@@ -71,7 +71,7 @@ def test_family_matches_plain(model_dirs, plain, name, dtype, family):
 @pytest.mark.parametrize("name", ["D", "E"])
 @pytest.mark.parametrize("family", list(FAMILIES))
 def test_family_with_the_tcgen05_prefill_attention(model_dirs, plain, name, family, monkeypatch):
-    """The engine takes the tcgen05 prefill attention from 1,024 keys; here from 16, so that the
+    """The engine takes the tcgen05 prefill attention from 512 keys; here from 16, so that the
     short requests of the tiny models (head sizes 64 and 128, a window on one layer of E) go
     through it in every family, beside decode tokens and with pages used again."""
     from rllm_b200.kernels import sm100
