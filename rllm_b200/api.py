@@ -116,6 +116,18 @@ class LLM:
             self._ahead = None                   # nobody is left to take its tokens
         return outs
 
+    def warm_up(self, prompt_len: int = 2048) -> None:
+        """Run a throw-away request (a prompt portion as long as the token budget allows, then a few
+        decoded tokens) so that what happens once per process happens now: the kernels' modules
+        are loaded, their attributes set, the first decode graph is captured. The first real
+        request then costs what every later one costs."""
+        vocab = self.engine.vocab
+        n = max(1, min(prompt_len, self.scheduler.max_tokens_per_step,
+                       (min(self.engine.cache.free_pages()) - 1) * self.engine.cache.page_size - 8))
+        prompt = [(7 * i + 1) % vocab for i in range(n)]
+        self.generate([prompt], SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))
+        self.generate([prompt[:5]], SamplingParams(temperature=0.8, top_p=0.9, max_tokens=2, ignore_eos=True, seed=0))
+
     # ---- whole generations
     def generate(self, prompts, params: SamplingParams | list[SamplingParams] | None = None,
                  **overrides) -> list[list[int]]:

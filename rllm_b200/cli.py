@@ -64,6 +64,7 @@ def _load(a, max_active: int):
               num_pages=a.kv_pages, max_active=max_active)
     if a.random_weights is None:
         llm.model_dir = a.model
+    llm.warm_up()          # modules loaded, a first graph captured: the first request is not the slow one
     print(f"[rllm] model loaded in {time.time() - t0:.1f}s", file=sys.stderr)
     return llm
 
