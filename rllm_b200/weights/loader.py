@@ -17,8 +17,11 @@ import torch
 
 from .safetensors_io import TensorStore
 
-# names that may sit in a checkpoint without belonging to any part
-IGNORABLE = ("*.rotary_emb.inv_freq",)
+# Names that may sit in a checkpoint without belonging to any part: the rotary tables some exporters
+# store, and the output matrix of a model that ties it to the embedding (a redundant copy; the
+# reference never looks for it then, src/model/loader/mod.rs:693-702). Where a model does own
+# `lm_head.weight` the name is expected and this list is not asked.
+IGNORABLE = ("*.rotary_emb.inv_freq", "lm_head.weight")
 
 
 class WeightError(RuntimeError):

@@ -66,7 +66,8 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     del t["model.layers.1.mlp.up_proj.weight"], t["model.norm.weight"]
     t["model.layers.0.self_attn.k_proj.weight"] = torch.zeros(16, 64, dtype=torch.bfloat16)
     t["model.layers.0.self_attn.qkv_proj.weight"] = torch.zeros(4, 4, dtype=torch.bfloat16)
-    t["lm_head.weight"] = torch.zeros(256, 64, dtype=torch.bfloat16)       # tied model: not wanted
+    t["model.layers.1.mlp.gate_up_proj.weight"] = torch.zeros(4, 4, dtype=torch.bfloat16)
+    t["lm_head.weight"] = torch.zeros(256, 64, dtype=torch.bfloat16)       # tied model: a redundant copy, passed over
     t["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)     # harmless leftover
     t["model.layers.0.input_layernorm.weight"] = torch.ones(64, dtype=torch.int32)
     d = tmp_path / "m"; d.mkdir()
@@ -75,7 +76,7 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
         load_weights(model, str(d), torch.bfloat16, "cpu")
     err = e.value
     assert err.missing == ["model.layers.1.mlp.up_proj.weight", "model.norm.weight"]
-    assert err.unexpected == ["lm_head.weight", "model.layers.0.self_attn.qkv_proj.weight"]
+    assert err.unexpected == ["model.layers.0.self_attn.qkv_proj.weight", "model.layers.1.mlp.gate_up_proj.weight"]
     assert [(n, tuple(exp), tuple(got)) for n, exp, got in err.wrong_shape] == \
         [("model.layers.0.self_attn.k_proj.weight", (32, 64), (16, 64))]
     assert err.wrong_dtype == [("model.layers.0.input_layernorm.weight", "I32")]
