@@ -203,8 +203,8 @@ def test_random_traffic_is_the_same_with_and_without_steps_ahead(dirs, seed):
     assert a == b
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_a_shrinking_batch_reuses_padded_graphs(dirs, dtype):
+@pytest.mark.parametrize("name,dtype", [("D", "float32"), ("D", "bfloat16"), ("C", "float32")])
+def test_a_shrinking_batch_reuses_padded_graphs(dirs, name, dtype):
     """Thirteen requests decode together and end one after the other. Decode graphs come in a
     short list of sizes (13 requests run in the graph for 16, the rows beyond them are stand-ins),
     so the batch meets a handful of captures on its way down, not one per size; and every
@@ -212,11 +212,11 @@ def test_a_shrinking_batch_reuses_padded_graphs(dirs, dtype):
     from rllm_b200.engine.graphs import padded_rows
     from rllm_b200.sampling import SamplingParams
     assert [padded_rows(n) for n in (1, 8, 9, 12, 13, 33, 64, 65, 200)] == [1, 8, 12, 12, 16, 40, 64, 80, 208]
-    name = "D"
-    cfg, w = P.read_model_dir(dirs[name])
+    cfg, w = P.read_model_dir(dirs[name])      # C: two groups of layers (all keys, a window of 24), pages of 4
     prompts = [tiny.random_prompt(3 + 2 * i, cfg["vocab_size"], 500 + i) for i in range(13)]
     sps = [SamplingParams(temperature=0.0, max_tokens=4 + 3 * i) for i in range(13)]
-    m = llm(dirs[name], name, dtype, num_pages=64, max_active=16)
+    pages = 64 if name == "D" else 400
+    m = llm(dirs[name], name, dtype, num_pages=pages, max_active=16)
     outs = m.generate(prompts, sps)
     sizes = sorted({k[0] for k in m.engine.graphs.slots})
     assert set(sizes) <= {1, 2, 3, 4, 5, 6, 7, 8, 12, 16} and 16 in sizes and 12 in sizes
@@ -229,7 +229,7 @@ def test_a_shrinking_batch_reuses_padded_graphs(dirs, dtype):
             for i, tok in enumerate(o):
                 assert float(lg[i].max() - lg[i, tok]) <= 3e-2 * float(lg.abs().max()), (i, tok)
     m.engine.cache.check()
-    assert m.engine.cache.free_pages() == [64]
+    assert set(m.engine.cache.free_pages()) == {pages}
 
 
 def test_the_step_loop_reports_a_kernel_that_gave_up(dirs):
