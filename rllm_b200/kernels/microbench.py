@@ -5,6 +5,7 @@ ranges of keys) were tuned with, and the small case a profiler is pointed at.
     python -m rllm_b200.kernels.microbench gemm --n 3072 --k 2048 --epilogue store --tokens 2048
     python -m rllm_b200.kernels.microbench attn-decode --batch 64 --context 3000 --splits 1,2,3
     python -m rllm_b200.kernels.microbench attn-prefill --tokens 2048 --kernel tc
+    python -m rllm_b200.kernels.microbench sample --rows 8 --top-p 0.9
     ... --plain 3      # no timing: three plain launches and a synchronize (for ncu -k ... -c ...)
 
 Timing: the kernel runs back to back over `--copies` distinct weight (or cache) tensors, larger
@@ -131,10 +132,36 @@ def cmd_attn_prefill(a) -> None:
     sm100.check_error(DEV)
 
 
+def cmd_sample(a) -> None:
+    R, V = a.rows, a.vocab
+    logits = torch.randn(R, V, device=DEV) * 3
+    vec = lambda v, dt=torch.float32: torch.full((R,), v, dtype=dt, device=DEV)
+    u = torch.rand(R, device=DEV)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    if a.temperature <= 0:
+        f = lambda: ops.argmax(logits, out=out)
+        what = "argmax"
+    else:
+        kw = dict(top_k=vec(a.top_k, torch.int32) if a.top_k > 0 else None, top_p=vec(a.top_p) if a.top_p < 1 else None,
+                  min_p=vec(a.min_p) if a.min_p > 0 else None)
+        temp = vec(a.temperature)
+        f = lambda: ops.sample(logits, temp, u, out=out, **kw)
+        what = f"temperature {a.temperature} top-k {a.top_k} top-p {a.top_p} min-p {a.min_p}"
+    run([f] * 4, a.plain, f"sample rows={R} vocab={V} {what}", nbytes=R * V * 4)
+
+
 def main(argv=None) -> int:
     ints = lambda s: [int(x) for x in s.split(",")]
     ap = argparse.ArgumentParser(prog="python -m rllm_b200.kernels.microbench", description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="cmd", required=True)
+    p = sub.add_parser("sample")
+    p.add_argument("--plain", type=int, default=0, help="N plain launches instead of timing")
+    p.add_argument("--rows", type=int, default=8)
+    p.add_argument("--vocab", type=int, default=128256)
+    p.add_argument("--temperature", type=float, default=0.8, help="0: the argmax kernel")
+    p.add_argument("--top-k", type=int, default=0)
+    p.add_argument("--top-p", type=float, default=1.0)
+    p.add_argument("--min-p", type=float, default=0.0)
     for name in ("gemm", "attn-decode", "attn-prefill"):
         p = sub.add_parser(name)
         p.add_argument("--plain", type=int, default=0, help="N plain launches instead of timing")
@@ -164,7 +191,7 @@ def main(argv=None) -> int:
     if not torch.cuda.is_available():
         print("microbench: no CUDA device", file=sys.stderr)
         return 1
-    {"gemm": cmd_gemm, "attn-decode": cmd_attn_decode, "attn-prefill": cmd_attn_prefill}[a.cmd](a)
+    {"gemm": cmd_gemm, "attn-decode": cmd_attn_decode, "attn-prefill": cmd_attn_prefill, "sample": cmd_sample}[a.cmd](a)
     return 0
 
 
