@@ -11,7 +11,7 @@
 //
 // One CTA = one 128 x BN output tile over a range of K: warp 0 issues TMA loads into a ring of
 // shared-memory stages, warp 1 issues the MMAs (one thread) and owns the TMEM allocation,
-// warps 2-5 run the epilogue.
+// warps 2-5 run the epilogue. The small-tile kernel has a second MMA warp (6), see `Cfg::TWO`.
 //
 // Fused RMSNorm (NORM variants, steps of up to 64 tokens): X is not read by TMA. The input is the
 // float residual stream h and a norm weight g; warps 2-5 build the B operand themselves, stage
@@ -62,12 +62,13 @@ constexpr int BM = 128;        // weight rows per tile (MMA M)
 constexpr int BK = 64;         // K per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;   // warp 0 TMA, warp 1 MMA + TMEM, warps 2..5 epilogue
+constexpr int THREADS_SMALL = 224;   // the small-tile kernel has a second MMA warp (6)
 constexpr int MAX_CLUSTER = 8;
 #ifndef SMALL_KB
 #define SMALL_KB 84
 #endif
 #ifndef SMALL_DUAL_KB
-#define SMALL_DUAL_KB 126
+#define SMALL_DUAL_KB 138
 #endif
 #ifndef NORM_MAX_TOKENS
 #define NORM_MAX_TOKENS 64
@@ -95,20 +96,29 @@ template <int BN, bool DUAL> struct Cfg {
   // token tiles up to 64 (decode, small mixed steps) stay under half an SM's shared memory so
   // that two kernels' CTAs are resident side by side; large tiles take what one CTA can have
   static constexpr bool SMALL = BN <= 64;
-  // landing area of its own (the gate/up pair at 32 tokens would be left with two stages: it lands in the ring)
-  static constexpr bool DEDICATED = BN <= 16 || (BN == 32 && !DUAL);
+  // a landing area of its own only where it leaves an even number of stages (see TWO): tiles of 16 of
+  // a single weight tile; the others land in the (by then idle) stage ring
+  static constexpr bool DEDICATED = BN <= 16 && !DUAL;
   static constexpr bool VEC = BN >= 32;                        // parts travel four columns at a time
   static constexpr int SLOTS = max_slots(BN);
   static constexpr int LAND_BYTES = SLOTS * A_TILES * BM * 4;
-  // 84 KB + 126 KB (gate/up pair) = 210 KB: any two small-tile kernels of a layer fit one SM together
+  // 84 KB + 138 KB (gate/up pair) = 222 KB: any two small-tile kernels of a layer fit one SM together
   static constexpr int BUDGET = (SMALL ? (DUAL ? SMALL_DUAL_KB : SMALL_KB) : 200) * 1024 - 1024 - (DEDICATED ? LAND_BYTES : 0);
   static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : (STAGES_RAW < 2 ? 2 : STAGES_RAW);
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int SMEM_BYTES = 1024 + RING_BYTES + (DEDICATED ? LAND_BYTES : 0);   // + alignment slack
-  static constexpr int ACC_COLS = A_TILES * BN;
-  static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128
-                                   : ACC_COLS <= 256 ? 256 : 512;
+  // Two MMA-issuing threads take the K blocks in turn, each into an accumulator set of its own,
+  // when the stages are even in number: K block i lies in stage i % STAGES, so each stage then
+  // belongs to one of the two for good, and a thread that waits for a stage's next filling has
+  // itself consumed the filling before. (With an odd number a thread could ask for a stage's
+  // second filling before the first, which another thread consumes, has even arrived: TMA copies
+  // land in any order, and a parity cannot tell "not yet" from "twice".)
+  static constexpr bool TWO = SMALL && STAGES % 2 == 0;
+  static constexpr int ACC_COLS = A_TILES * BN;                 // one accumulator set
+  static constexpr int ALL_COLS = (TWO ? 2 : 1) * ACC_COLS;
+  static constexpr int TMEM_COLS = ALL_COLS <= 32 ? 32 : ALL_COLS <= 64 ? 64 : ALL_COLS <= 128 ? 128
+                                   : ALL_COLS <= 256 ? 256 : 512;
   static_assert(DEDICATED || LAND_BYTES <= RING_BYTES, "the landing area must fit in the stage ring");
 };
 
@@ -193,7 +203,7 @@ __device__ __forceinline__ void epilogue_warps_sync() {       // warps 2..5 only
 }
 
 template <int BN, int EPI, bool NORM>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS_SMALL, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const Params p) {
   constexpr bool DUAL = (EPI == EPI_SWIGLU);
@@ -226,12 +236,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   const int kb_begin = (int)((long long)rank * kb_total / p.splits);
   const int kb_end = (int)((long long)(rank + 1) * kb_total / p.splits);
   const int n_kb = kb_end - kb_begin;
+  const bool two_sets = C::TWO && n_kb >= 2;       // else the second accumulator set is never written
   // float [ranks][slots per rank][ACCS][BM]: partial columns pushed here by every rank
   float* land = reinterpret_cast<float*>(C::DEDICATED ? smem + C::RING_BYTES : smem);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], NORM ? 5 : 1); mbar_init(&empty_bar[s], 1); }
-    mbar_init(&acc_bar, 1);
+    mbar_init(&acc_bar, two_sets ? 2 : 1);         // one arrival per MMA thread that has K blocks
     abort_flag = 0;
     never_flag = 0;
     fence_barrier_init();
@@ -286,15 +297,21 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           mbar_wait(&full_bar[i % C::STAGES], (uint32_t)(i / C::STAGES) & 1u, &never_flag, 200000000LL);
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (warp == 1 || (C::TWO && warp == 6)) {
+    // ------------------------------------------------------------ MMA issuers
+    // Issuing a tcgen05.mma or a commit costs its thread some 50 ns whatever the size, and a token
+    // tile of 16 or 32 needs five of them (nine with a gate/up pair) for every K block: one thread
+    // would hold the weight stream at about 60 GB/s per SM. With an even number of stages two
+    // threads (warps 1 and 6) take the K blocks in turn; the epilogue adds their accumulator sets.
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
-      // a descriptor moves with its address (16 bytes a unit): one is built, the rest are sums.
-      // This thread's time per K block is what paces the weight stream at small token tiles.
+      constexpr int STEP = C::TWO ? 2 : 1;
+      const int w = warp == 1 ? 0 : 1;
+      const uint32_t acc_addr = tmem_base + (uint32_t)(w * C::ACC_COLS);
+      // a descriptor moves with its address (16 bytes a unit): one is built, the rest are sums
       const uint64_t d0 = umma_desc_sw128(smem_u32(smem));
       bool ok = true;
-      for (int i = 0; i < n_kb && ok; ++i) {
+      for (int i = w; i < n_kb && ok; i += STEP) {
         const int s = i % C::STAGES;
         const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
         if (!mbar_wait(&full_bar[s], ph, &abort_flag)) { abort_flag = 1; record_failure(p.err, 2); ok = false; break; }
@@ -303,21 +320,33 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const uint64_t db = da + (uint64_t)(W_BYTES >> 4);
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k) {
-          const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+          const uint32_t acc = (i > w || k > 0) ? 1u : 0u;
           const uint64_t koff = (uint64_t)(k * UMMA_K * 2 / 16);
-          umma_bf16(tmem_base, da + koff, db + koff, idesc, acc);
-          if (DUAL) umma_bf16(tmem_base + BN, da + (uint64_t)(C::A_BYTES >> 4) + koff, db + koff, idesc, acc);
+          umma_bf16(acc_addr, da + koff, db + koff, idesc, acc);
+          if (DUAL) umma_bf16(acc_addr + BN, da + (uint64_t)(C::A_BYTES >> 4) + koff, db + koff, idesc, acc);
         }
         umma_commit(&empty_bar[s]);      // the stage is free once these MMAs have read it
       }
-      if (ok) umma_commit(&acc_bar);      // accumulators complete
+      if (ok && n_kb > w) umma_commit(&acc_bar);      // this thread's accumulator set is complete
     }
   }
   bool epi_ok = false;
   const int row = (warp & 3) * 32 + lane;         // TMEM lanes [32 (warp & 3), +32) belong to this warp
   const int n = n0 + row;                         // output feature of this thread
   const float inv_k = 1.f / (float)p.K;
-  if (warp >= 2) {
+  const bool epi_warp = warp >= 2 && warp <= 5;
+  // 16 accumulator columns of this thread's row: the sum of the two sets where there are two
+  auto ld_acc = [&](uint32_t addr, uint32_t (&v)[16]) {
+    tmem_ld16(addr, v);
+    if (two_sets) {
+      uint32_t w2[16];
+      tmem_ld16(addr + (uint32_t)C::ACC_COLS, w2);
+      tmem_ld_wait();
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj) v[jj] = __float_as_uint(__uint_as_float(v[jj]) + __uint_as_float(w2[jj]));
+    }
+  };
+  if (epi_warp) {
     // ------------------------------------------------------------ epilogue warps (2..5)
     pdl_wait();                                   // nothing is read or written before the predecessor is done
     if (NORM) {
@@ -431,8 +460,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       for (int c0 = 0; c0 < BN; c0 += 16) {
         if (t0 + c0 >= p.T) break;
         uint32_t g[16], u[16];
-        tmem_ld16(taddr + c0, g);
-        if (DUAL) tmem_ld16(taddr + BN + c0, u);
+        ld_acc(taddr + c0, g);
+        if (DUAL) ld_acc(taddr + BN + c0, u);
         tmem_ld_wait();
         if (NORM) {
 #pragma unroll
@@ -480,15 +509,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       if (!C::DEDICATED) cluster_arrive();
       cluster_wait();
     }
-    if (warp >= 2 && epi_ok) {
+    if (epi_warp && epi_ok) {
       const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
       const uint32_t land_cta = smem_u32(land);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         if (c0 >= ncols) break;
         uint32_t g[16], u[16];
-        tmem_ld16(taddr + c0, g);
-        if (DUAL) tmem_ld16(taddr + BN + c0, u);
+        ld_acc(taddr + c0, g);
+        if (DUAL) ld_acc(taddr + BN + c0, u);
         tmem_ld_wait();
         if constexpr (VEC) {
 #pragma unroll
@@ -532,7 +561,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     }
     __syncwarp();
     if (clustered) { cluster_arrive(); cluster_wait(); } else __syncthreads();     // every part has landed
-    if (warp >= 2 && !abort_flag) {
+    if (epi_warp && !abort_flag) {
       // the pair partner of this row under the rotary epilogue (same tile: heads do not straddle tiles)
       int prow = row;
       if (ROPE) {
@@ -891,7 +920,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 g
                              C::SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return -5; }
     configured = true;
   }
-  return launch_ex(tc_gemm_kernel<BN, EPI, NORM>, grid, dim3(THREADS), C::SMEM_BYTES, s, p.splits, mw, mx, p);
+  return launch_ex(tc_gemm_kernel<BN, EPI, NORM>, grid, dim3(THREADS_SMALL), C::SMEM_BYTES, s, p.splits, mw, mx, p);
 }
 
 template <int BN, int EPI>
