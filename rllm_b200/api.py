@@ -61,8 +61,9 @@ class LLM:
         sampled = [p.request for p in plan if p.samples]
         if not sampled:
             return None
-        drawn = self.sampler.draw(logits, [r.params for r in sampled], [r.seed for r in sampled],
-                                  [len(r.output) + ahead for r in sampled], [r.output for r in sampled])
+        drawn, lps = self.sampler.draw(logits, [r.params for r in sampled], [r.seed for r in sampled],
+                                       [len(r.output) + ahead for r in sampled], [r.output for r in sampled],
+                                       logprobs=True)
         # Their way to the host goes over a stream of its own, which waits for the draw only: the
         # step launched behind them on the main stream does not wait for a copy engine.
         if not self._pinned:
@@ -75,12 +76,21 @@ class LLM:
         drawn_at = torch.cuda.Event()
         drawn_at.record()
         arrived = torch.cuda.Event()
+        lp_host = None
         with torch.cuda.stream(self._copy_stream):
             self._copy_stream.wait_event(drawn_at)
             host.copy_(drawn, non_blocking=True)
             buf[-2:].copy_(self.engine.error_words, non_blocking=True)      # and the device's error words with them
+            if lps is not None:                  # log-probabilities were asked for: they travel with the tokens
+                rows, lp, ids = lps
+                lp_host = (rows, torch.empty(lp.shape, dtype=lp.dtype).pin_memory(),
+                           torch.empty(ids.shape, dtype=ids.dtype).pin_memory())
+                lp_host[1].copy_(lp, non_blocking=True)
+                lp_host[2].copy_(ids, non_blocking=True)
+                lp.record_stream(self._copy_stream)
+                ids.record_stream(self._copy_stream)
             arrived.record()
-        return drawn, host, arrived
+        return drawn, host, arrived, lp_host
 
     def step(self) -> list[StepOutput]:
         """One scheduler step: plan, run the batch, sample, finish and free.
@@ -104,17 +114,31 @@ class LLM:
             if nxt is not None and self.engine.takes_feed(self.scheduler.entries(nxt)):
                 self._ahead = (nxt, self._launch(nxt, feed=drawn[0], ahead=1))
                 self.steps_ahead += 1
-        tokens = []
+        tokens, logprobs = [], None
         if drawn is not None:
             drawn[2].synchronize()               # this step's tokens only; the step ahead keeps running
             tokens = drawn[1].tolist()
+            if drawn[3] is not None:
+                logprobs = self._logprobs(plan, *drawn[3])
             if self._pinned[0][-2] or self._pinned[0][-1] or self._pinned[1][-2] or self._pinned[1][-1]:
                 self._ahead = None
                 self.engine.check()              # raises: a kernel gave up waiting, or a token id was out of range
-        outs = failed + self.scheduler.advance(plan, tokens, self.engine)
+        outs = failed + self.scheduler.advance(plan, tokens, self.engine, logprobs)
         if self._ahead is not None and all(p.request.finished for p in self._ahead[0]):
             self._ahead = None                   # nobody is left to take its tokens
         return outs
+
+    @staticmethod
+    def _logprobs(plan, rows, lp, ids) -> dict:
+        """{index among the step's sampled requests: (ln p of its token, [(token, ln p), ...])}, each
+        list cut to the request's own `top_logprobs` and to the tokens that exist."""
+        sampled = [p.request for p in plan if p.samples]
+        lp, ids = lp.tolist(), ids.tolist()
+        out = {}
+        for i, r in enumerate(rows):
+            n = sampled[r].params.top_logprobs
+            out[r] = (lp[i][0], [(t, v) for t, v in zip(ids[i][:n], lp[i][1: 1 + n]) if t >= 0])
+        return out
 
     def warm_up(self, prompt_len: int = 2048) -> None:
         """Run a throw-away request (a prompt portion as long as the token budget allows, then a few
@@ -130,9 +154,10 @@ class LLM:
 
     # ---- whole generations
     def generate(self, prompts, params: SamplingParams | list[SamplingParams] | None = None,
-                 **overrides) -> list[list[int]]:
+                 details: bool = False, **overrides):
         """Token ids in, generated token ids out, one list per prompt (all prompts run
-        concurrently, as `rllm batch` does)."""
+        concurrently, as `rllm batch` does). With `details` the requests themselves come back
+        (`output`, `logprobs`, `finish_reason`, `preemptions`)."""
         if prompts and isinstance(prompts[0], int):
             prompts = [prompts]
         base = params or SamplingParams()
@@ -144,7 +169,7 @@ class LLM:
             self.step()
         self.engine.check()
         reqs = [self.scheduler.requests.pop(i) for i in ids]
-        return [r.output for r in reqs]
+        return reqs if details else [r.output for r in reqs]
 
     # ---- optional text I/O
     def tokenizer(self):

@@ -492,6 +492,110 @@ RLLM_API int rllm_add_at(float* logits, int R, int V, const int* rows, const int
   return launch_ex(add_at_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, 1, logits, V, rows, cols, vals, n);
 }
 
+// Log-probabilities of the distribution the draw starts from: softmax of x/T (x itself for a greedy
+// row) over the logits that top-k keeps, before min-p and top-p (src/model/sampler.rs:421-428,
+// 501-541). One block per listed row: lp[i][0] = ln p(chosen[row]) (-inf if top-k dropped it),
+// lp[i][1 + j] and ids[i][j] = the j-th most probable token, j < n_top, equals by rising index;
+// where fewer than n_top tokens are kept the rest is (-inf, -1).
+constexpr int TOP_LOGPROBS_MAX = 20;
+
+__global__ void __launch_bounds__(THREADS)
+logprobs_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
+                const int* __restrict__ top_k, const int* __restrict__ chosen, const int* __restrict__ rows,
+                int n_top, float* __restrict__ lp, int* __restrict__ ids) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float redf[32];
+  __shared__ int redi[32];
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  __shared__ float pick_v;
+  __shared__ int pick_i;
+  const int row = rows[blockIdx.x];
+  const float* x = logits + (size_t)row * V;
+  const float T = temperature[row];
+  const float invT = T > 0.f ? 1.f / T : 1.f;
+  const int tid = threadIdx.x;
+  float thr = -INFINITY;
+  const int k = top_k ? top_k[row] : 0;
+  if (k > 0 && k < V) {
+    unsigned lo = 0u, hi = 0xffffffffu;      // largest key with count(key' >= key) >= k
+    while (lo < hi) {
+      const unsigned mid = lo + ((hi - lo) >> 1) + 1u;
+      int c = 0;
+      for (int i = tid; i < V; i += THREADS) c += (f2key(x[i] * invT) >= mid);
+      c = block_sum_i(c, redi);
+      if (c >= k) lo = mid; else hi = mid - 1u;
+    }
+    thr = key2f(lo);
+  }
+  float mx = -INFINITY;
+  for (int i = tid; i < V; i += THREADS) { const float v = x[i] * invT; if (v >= thr) mx = fmaxf(mx, v); }
+  mx = block_max(mx, redf);
+  float sum = 0.f;
+  for (int i = tid; i < V; i += THREADS) { const float v = x[i] * invT; if (v >= thr) sum += expf(v - mx); }
+  sum = block_sum_f(sum, redf);
+  const float lse = mx + logf(sum);
+  float* lp_row = lp + (size_t)blockIdx.x * (1 + n_top);
+  int* id_row = ids + (size_t)blockIdx.x * (n_top > 0 ? n_top : 1);
+  if (tid == 0) {
+    const int c = chosen[row];
+    const float v = (c >= 0 && c < V) ? x[c] * invT : -INFINITY;
+    lp_row[0] = v >= thr ? v - lse : -INFINITY;
+  }
+  // the n_top largest, one pass each: the largest (value, then lowest index) that comes after the last pick
+  float last_v = INFINITY; int last_i = -1;
+  for (int j = 0; j < n_top; ++j) {
+    float best = -INFINITY; int bi = 0x7fffffff;
+    for (int i = tid; i < V; i += THREADS) {
+      const float v = x[i] * invT;
+      if (v >= thr && (v < last_v || (v == last_v && i > last_i))) argmax_take(best, bi, v, i);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      argmax_take(best, bi, ov, oi);
+    }
+    const int lane = tid & 31, warp = tid >> 5;
+    __syncthreads();                           // the last round's pick has been read by everybody
+    if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+      best = sv[lane]; bi = si[lane];          // THREADS / 32 = 32 warps
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        argmax_take(best, bi, ov, oi);
+      }
+      if (lane == 0) {
+        pick_v = best; pick_i = bi;
+        const bool found = bi != 0x7fffffff;
+        lp_row[1 + j] = found ? best - lse : -INFINITY;
+        id_row[j] = found ? bi : -1;
+      }
+    }
+    __syncthreads();
+    last_v = pick_v; last_i = pick_i;
+    if (last_i == 0x7fffffff) {                // nothing is left: the rest of the list is empty
+      if (tid == 0) for (int r = j + 1; r < n_top; ++r) { lp_row[1 + r] = -INFINITY; id_row[r] = -1; }
+      break;
+    }
+  }
+}
+
+// rows: the n rows of `logits` (and of temperature, top_k, chosen) that want them; lp float [n, 1 + n_top],
+// ids int [n, n_top]. temperature, top_k and rows may lie in pinned host memory.
+RLLM_API int rllm_logprobs(const float* logits, int R, int V, const float* temperature, const int* top_k,
+                           const int* chosen, const int* rows, int n, int n_top, float* lp, int* ids,
+                           void* stream) {
+  if (n <= 0) return 0;
+  if (R <= 0 || V <= 0 || n_top < 0 || n_top > TOP_LOGPROBS_MAX) return ERR_BAD_SIZE;
+  return launch_ex(logprobs_kernel, dim3(n), dim3(THREADS), 0, (cudaStream_t)stream, 1, logits, V, temperature, top_k,
+                   chosen, rows, n_top, lp, ids);
+}
+
 RLLM_API int rllm_argmax(const float* logits, int R, int V, int* out, void* stream) {
   if (R <= 0) return 0;
   if (V <= 0) return ERR_BAD_SIZE;

@@ -39,6 +39,8 @@ class Request:
     params: SamplingParams
     seed: int
     output: list[int] = field(default_factory=list)
+    # with params.logprobs: (ln p of the token, [(token, ln p) of the most probable ones]) per output token
+    logprobs: list[tuple[float, list[tuple[int, float]]]] = field(default_factory=list)
     # tokens to store before the next sample: prompt (+ output after a preemption)
     pending: list[int] = field(default_factory=list)
     num_stored: int = 0          # tokens whose keys/values are in the cache
@@ -66,6 +68,8 @@ class StepOutput:
     token: int | None
     finished: bool
     finish_reason: str | None = None
+    logprob: float | None = None                          # with params.logprobs
+    top_logprobs: list[tuple[int, float]] | None = None
 
 
 class Scheduler:
@@ -247,12 +251,17 @@ class Scheduler:
             return None
         return [Planned(r, [0], True) for r in self.running]
 
-    def advance(self, plan: list[Planned], tokens: list[int], executor=None) -> list[StepOutput]:
+    def advance(self, plan: list[Planned], tokens: list[int], executor=None,
+                logprobs: dict | None = None) -> list[StepOutput]:
         """Record what the step stored and sampled; finish and free what is done. `tokens`
-        are the sampled tokens of the planned requests with `samples`, in plan order."""
+        are the sampled tokens of the planned requests with `samples`, in plan order;
+        `logprobs` maps an index into `tokens` to (ln p, [(token, ln p), ...]) for the requests
+        that asked for them."""
         outs, it = [], iter(tokens)
+        nth = -1
         for p in plan:
             req = p.request
+            nth += p.samples
             if req.finished:                     # ended (or aborted) while this step was under way
                 if p.samples:
                     next(it)
@@ -271,7 +280,11 @@ class Scheduler:
                 reason = "max_tokens"
             if reason:
                 self._finish(req, reason, executor)
-            outs.append(StepOutput(req.request_id, tok, reason is not None, reason))
+            lp = logprobs.get(nth) if logprobs else None
+            if lp is not None:
+                req.logprobs.append(lp)
+            outs.append(StepOutput(req.request_id, tok, reason is not None, reason,
+                                   lp[0] if lp else None, lp[1] if lp else None))
         return outs
 
     def entries(self, plan: list[Planned]) -> list[Entry]:

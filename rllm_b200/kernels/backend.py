@@ -176,5 +176,8 @@ class Backend:
     def add_at(self, logits, rows, cols, vals):
         return ops.add_at(logits, rows, cols, vals)
 
+    def logprobs(self, logits, temperature, top_k, chosen, rows, n_top):
+        return ops.logprobs(logits, temperature, top_k, chosen, rows, n_top)
+
     def sample(self, logits, temperature, uniform, top_k=None, top_p=None, min_p=None, out=None):
         return ops.sample(logits, temperature, uniform, top_k, top_p, min_p, out=out)

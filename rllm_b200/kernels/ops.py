@@ -44,6 +44,7 @@ _SIGS = {
         "rllm_argmax": [_P, c_int, c_int, _P, _P],
         "rllm_sample": [_P, c_int, c_int, _P, _P, _P, _P, _P, _P, _P],
         "rllm_add_at": [_P, c_int, c_int, _P, _P, _P, c_int, _P],
+        "rllm_logprobs": [_P, c_int, c_int, _P, _P, _P, _P, c_int, c_int, _P, _P, _P],
     },
 }
 _fn_cache: dict[str, object] = {}
@@ -316,6 +317,36 @@ def add_at(logits: torch.Tensor, rows: torch.Tensor, cols: torch.Tensor, vals: t
     R, V = logits.shape
     _check(_fn("simt", "rllm_add_at")(logits.data_ptr(), R, V, rows.data_ptr(), cols.data_ptr(), vals.data_ptr(), n,
                                       _stream()), "add_at")
+
+
+TOP_LOGPROBS_MAX = 20
+
+
+def logprobs(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor | None, chosen: torch.Tensor,
+             rows: torch.Tensor, n_top: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """For each listed row of float32 logits [R, V]: ln p of the chosen token and the n_top most
+    probable tokens under softmax(x / T over what top-k keeps), x itself where T is 0. Returns
+    (float32 [n, 1 + n_top], int32 [n, n_top]) on the device; an entry that does not exist is
+    (-inf, -1). temperature [R] float32, top_k [R] int32 or None and rows [n] int32 on the device
+    or pinned; chosen [R] int32 on the device."""
+    _cuda(logits, "logits")
+    if logits.dtype != torch.float32 or logits.dim() != 2 or not logits.is_contiguous():
+        raise KernelError("logprobs takes contiguous float32 logits [R, V]")
+    R, V = logits.shape
+    n = rows.numel()
+    if not 0 <= n_top <= TOP_LOGPROBS_MAX:
+        raise KernelError(f"top_logprobs must be 0..{TOP_LOGPROBS_MAX}, got {n_top}")
+    for t, name, d, ln in ((temperature, "temperature", torch.float32, R), (top_k, "top_k", torch.int32, R),
+                           (rows, "rows", torch.int32, n)):
+        if t is not None and (t.dtype != d or t.numel() != ln or not (t.is_cuda or t.is_pinned()) or not t.is_contiguous()):
+            raise KernelError(f"logprobs: {name} must be a {d} vector of length {ln} on the device or pinned")
+    if chosen.dtype != torch.int32 or chosen.numel() != R or not chosen.is_cuda or not chosen.is_contiguous():
+        raise KernelError(f"logprobs: chosen must be an int32 vector of length {R} on the device")
+    lp = torch.empty((n, 1 + n_top), dtype=torch.float32, device=logits.device)
+    ids = torch.empty((n, max(n_top, 1)), dtype=torch.int32, device=logits.device)
+    _check(_fn("simt", "rllm_logprobs")(logits.data_ptr(), R, V, temperature.data_ptr(), _ptr(top_k), chosen.data_ptr(),
+                                        rows.data_ptr(), n, n_top, lp.data_ptr(), ids.data_ptr(), _stream()), "logprobs")
+    return lp, ids[:, :n_top]
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,

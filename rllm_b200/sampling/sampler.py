@@ -1,7 +1,7 @@
 """Chooses tokens from a step's logits on the device: argmax rows and sampled rows in one
 pass each, parameters per row. Pipeline of the reference's `sample_from_logits`
-(src/model/sampler.rs:328-547): penalties -> temperature -> top-k -> softmax -> min-p ->
-top-p -> inverse CDF."""
+(src/model/sampler.rs:328-547): penalties -> logit bias -> temperature -> top-k -> softmax
+[-> log-probabilities] -> min-p -> top-p -> inverse CDF."""
 from __future__ import annotations
 
 import torch
@@ -23,17 +23,41 @@ class Sampler:
         return self.draw(logits, params, seeds, indices, histories).tolist()
 
     def draw(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int],
-             indices: list[int], histories: list[list[int]] | None = None) -> torch.Tensor:
+             indices: list[int], histories: list[list[int]] | None = None, logprobs: bool = False):
         """logits float32 [R, V]; row r is drawn with params[r] and the uniform number of
         (seeds[r], indices[r]). `histories[r]`: the tokens generated so far (for penalties).
-        Returns int32 [R] on the device; nothing here waits for it."""
+        Returns int32 [R] on the device; nothing here waits for it. With `logprobs` it returns
+        (tokens, None) or (tokens, (rows, lp, ids)) for the rows whose parameters ask for
+        log-probabilities: lp float32 [n, 1 + N], ids int32 [n, N] on the device, N the largest
+        `top_logprobs` among them (`ops.logprobs`)."""
+        drawn, logits = self._draw(logits, params, seeds, indices, histories)
+        if not logprobs:
+            return drawn
+        rows = [r for r, p in enumerate(params) if p.logprobs]
+        if not rows:
+            return drawn, None
+        R = len(params)
+        n_top = max(params[r].top_logprobs for r in rows)
+        buf, ints, done = self._staging(R)
+        done.synchronize()
+        buf.numpy()[0, :R] = [p.temperature for p in params]
+        ia = ints.numpy()
+        ia[1, :R] = [p.top_k for p in params]
+        ia[2, :len(rows)] = rows
+        lp, ids = self.backend.logprobs(logits, buf[0, :R], ints[1, :R] if any(p.top_k > 0 for p in params) else None,
+                                        drawn, ints[2, :len(rows)], n_top)
+        done.record()
+        return drawn, (rows, lp, ids)
+
+    def _draw(self, logits, params, seeds, indices, histories):
+        """The drawn tokens and the logits they were drawn from (after penalties and bias)."""
         R = logits.shape[0]
         assert R == len(params) == len(seeds) == len(indices)
-        if any(p.has_penalties for p in params):
-            logits = self._penalise(logits, params, histories)
+        if any(p.has_penalties or p.logit_bias for p in params):
+            logits = self._adjust(logits, params, histories)
         be = self.backend
         if all(p.greedy for p in params):
-            return be.argmax(logits)
+            return be.argmax(logits), logits
         # The rows' parameters go into pinned host memory that the kernel reads itself: nothing is
         # copied, so nothing waits for the stream (steps are launched ahead of the host). Four
         # buffers take turns; one is written again only after the kernel that read it has run.
@@ -56,7 +80,7 @@ class Sampler:
         out = be.argmax(logits) if any(p.greedy for p in params) else None
         drawn = be.sample(logits, buf[0, :R], buf[1, :R], top_k, top_p, min_p, out=out)
         done.record()
-        return drawn
+        return drawn, logits
 
     def _staging(self, R: int):
         """The next of four pinned parameter buffers [5, rows] (float32, and the same memory seen as
@@ -70,20 +94,27 @@ class Sampler:
         self._turn = (self._turn + 1) % len(self._ring)
         return self._ring[self._turn]
 
-    def _penalise(self, logits, params, histories):
+    def _adjust(self, logits, params, histories):
         """logit[token] -= frequency_penalty * count + presence_penalty for tokens already
-        generated (src/model/sampler.rs:341-350). A handful of entries per row: host-computed
-        values added into a copy of the logits by a small kernel."""
+        generated, then logit[token] += logit_bias[token] (src/model/sampler.rs:341-358). A
+        handful of entries per row: host-computed values added into a copy of the logits by a
+        small kernel."""
+        V = logits.shape[1]
         rows, cols, vals = [], [], []
         for r, (p, hist) in enumerate(zip(params, histories or [[]] * len(params))):
-            if not p.has_penalties or not hist:
-                continue
-            counts: dict[int, int] = {}
-            for t in hist:
-                counts[t] = counts.get(t, 0) + 1
-            for t, c in counts.items():
-                rows.append(r); cols.append(t)
-                vals.append(-(p.frequency_penalty * c + p.presence_penalty))
+            delta: dict[int, float] = {}
+            if p.has_penalties and hist:
+                counts: dict[int, int] = {}
+                for t in hist:
+                    counts[t] = counts.get(t, 0) + 1
+                for t, c in counts.items():
+                    if t < V:
+                        delta[t] = -(p.frequency_penalty * c + p.presence_penalty)
+            for t, b in p.logit_bias:
+                if t < V:
+                    delta[t] = delta.get(t, 0.0) + b
+            for t, d in delta.items():
+                rows.append(r); cols.append(t); vals.append(d)
         if not rows:
             return logits
         out = logits.clone()

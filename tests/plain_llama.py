@@ -278,3 +278,35 @@ def sample_from_probs(p: torch.Tensor, u: float) -> int:
     if idx.numel():
         return int(idx[0])
     return int((p > 0).nonzero()[-1])
+
+
+def adjust_logits(logits: torch.Tensor, history: list[int], frequency_penalty: float = 0.0,
+                  presence_penalty: float = 0.0, logit_bias: dict[int, float] | None = None) -> torch.Tensor:
+    """Penalties for tokens already generated, then the per-token bias, on the raw logits
+    (before the temperature). src/model/sampler.rs:341-358."""
+    x = logits.to(torch.float32).clone()
+    V = x.numel()
+    if frequency_penalty != 0.0 or presence_penalty != 0.0:
+        for t in set(history):
+            if t < V:
+                x[t] -= frequency_penalty * history.count(t) + presence_penalty
+    for t, b in (logit_bias or {}).items():
+        if t < V:
+            x[t] += b
+    return x
+
+
+def logprobs(logits: torch.Tensor, temperature: float, top_k: int, chosen: int, n_top: int):
+    """ln p of the chosen token and of the n_top most probable ones under the distribution
+    before min-p and top-p: softmax of x/T (of x when T is 0) over what top-k keeps; tokens of
+    probability 0 are not listed. src/model/sampler.rs:372-428, 501-541."""
+    x = logits.to(torch.float64)
+    if temperature != 0.0:
+        x = x / temperature
+    V = x.numel()
+    if 0 < top_k < V:
+        thr = torch.topk(x, top_k).values[-1]
+        x = torch.where(x < thr, torch.full_like(x, float("-inf")), x)
+    lp = torch.log_softmax(x, dim=-1)
+    order = sorted(range(V), key=lambda i: (-float(lp[i]), i))[:n_top]
+    return float(lp[chosen]), [(i, float(lp[i])) for i in order if lp[i] > float("-inf")]

@@ -267,6 +267,68 @@ def test_penalties_change_the_choice(dirs):
     assert plain[0] == pen[0]
 
 
+def test_logit_bias_bans_and_forces_tokens(dirs):
+    """A bias of -100 on the tokens greedy decoding would choose removes them from the output; a
+    large bias on one token makes it the answer everywhere; ids beyond the vocabulary are passed
+    over; the first token without bias is the plain one."""
+    from rllm_b200.sampling import SamplingParams
+    name = "B"
+    cfg, w = P.read_model_dir(dirs[name])
+    V = cfg["vocab_size"]
+    prompt = tiny.random_prompt(11, V, 5)
+    m = llm(dirs[name], name, "float32", num_pages=32)
+    plain = m.generate([prompt], SamplingParams(temperature=0.0, max_tokens=8))[0]
+    assert plain == P.greedy(cfg, w, prompt, 8)
+    banned = {t: -100.0 for t in set(plain)}
+    banned[V + 5] = 3.0
+    got = m.generate([prompt], SamplingParams(temperature=0.0, max_tokens=8, logit_bias=banned))[0]
+    assert not set(got) & set(plain)
+    # the plain rule, step by step, on the plain model's logits
+    seq, want = list(prompt), []
+    for _ in range(8):
+        x = P.adjust_logits(P.forward(cfg, w, seq)[-1], [], logit_bias=banned)
+        want.append(int(torch.argmax(x)))
+        seq.append(want[-1])
+    assert got == want
+    forced = m.generate([prompt, prompt[:3]], SamplingParams(temperature=0.9, top_p=0.95, max_tokens=6, seed=3,
+                                                           logit_bias={17: 200.0}))
+    assert forced == [[17] * 6, [17] * 6]
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("D", "bfloat16")])
+def test_logprobs_come_back_with_the_tokens(dirs, name, dtype):
+    """Greedy and drawn requests side by side, some with log-probabilities and some without, with
+    and without steps launched ahead: the tokens are what they are without log-probabilities, and
+    every token's ln p and the listed alternatives are those of the plain rule on the plain
+    model's logits."""
+    from rllm_b200.sampling import SamplingParams
+    cfg, w = P.read_model_dir(dirs[name])
+    V = cfg["vocab_size"]
+    prompts = [tiny.random_prompt(n, V, 20 + n) for n in (9, 5, 14)]
+    sps = [SamplingParams(temperature=0.0, max_tokens=7, logprobs=True, top_logprobs=4),
+           SamplingParams(temperature=0.8, top_k=12, top_p=0.9, max_tokens=9, seed=5, logprobs=True, top_logprobs=2),
+           SamplingParams(temperature=0.7, max_tokens=8, seed=6)]
+    tol = 1e-3 if dtype == "float32" else 0.15
+    for ahead in (True, False):
+        m = llm(dirs[name], name, dtype, num_pages=32)
+        m.run_ahead = ahead
+        reqs = m.generate(prompts, sps, details=True)
+        bare = m.generate(prompts, [SamplingParams(**{**sp.__dict__, "logprobs": False, "top_logprobs": 0}) for sp in sps])
+        assert [r.output for r in reqs] == bare
+        assert reqs[2].logprobs == [] and [len(r.logprobs) for r in reqs[:2]] == [7, 9]
+        for r, prompt, sp in zip(reqs[:2], prompts, sps):
+            rows = P.forward(cfg, w, prompt + r.output[:-1])[len(prompt) - 1:]
+            for tok, (lp, top), x in zip(r.output, r.logprobs, rows):
+                want_lp, want_top = P.logprobs(x, sp.temperature, sp.top_k, tok, sp.top_logprobs)
+                assert abs(lp - want_lp) <= tol
+                assert len(top) == sp.top_logprobs and all(b <= a + 1e-6 for (_, a), (_, b) in zip(top, top[1:]))
+                if dtype == "float32":
+                    assert [t for t, _ in top] == [t for t, _ in want_top]
+                    assert all(abs(a[1] - b[1]) <= tol for a, b in zip(top, want_top))
+            if sp.greedy:
+                assert all(top[0][0] == tok for tok, (_, top) in zip(r.output, r.logprobs))
+
+
 def test_cli_run_and_batch(dirs, tmp_path):
     import os, subprocess, sys
     rllm = os.path.join(replay.ROOT, "bin", "rllm")

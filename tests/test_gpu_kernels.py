@@ -245,6 +245,45 @@ def test_sample_rows_have_their_own_parameters():
         assert p[got[r]] > 0 and lo - 2e-5 <= float(u[r]) <= float(cdf[got[r]]) + 2e-5
 
 
+@pytest.mark.parametrize("V", [200, 1000, 128256])
+def test_logprobs_of_the_chosen_token_and_of_the_most_probable(V):
+    """Rows with their own temperature (0 among them), top-k and chosen token; only some rows are
+    listed; a tie among the largest goes by rising index; top-k leaves fewer tokens than asked for."""
+    import math
+    R = 6
+    logits = rnd(R, V, seed=V + 1, scale=3.0)
+    logits[2, 7] = logits[2, 150] = logits[2].max() + 1.0        # two equal at the top
+    temp = torch.tensor([1.0, 0.0, 0.7, 1.5, 1.0, 0.9])
+    top_k = torch.tensor([0, 0, 0, 3, 50, 0], dtype=torch.int32)
+    chosen = torch.tensor([int(torch.argmax(logits[0])), int(torch.argmax(logits[1])), 150, 5, 11, V - 1], dtype=torch.int32)
+    chosen[3] = int(torch.topk(logits[3], 2).indices[1])         # inside its top-k of 3; row 4's token 11 is outside
+    rows = torch.tensor([0, 1, 2, 3, 4], dtype=torch.int32)
+    for n_top in (0, 5, 20):
+        lp, ids = ops().logprobs(logits.to(DEV), temp.to(DEV), top_k.to(DEV), chosen.to(DEV), rows.to(DEV), n_top)
+        assert lp.shape == (5, 1 + n_top) and ids.shape == (5, n_top)
+        lp, ids = lp.cpu(), ids.cpu()
+        for i, r in enumerate(rows.tolist()):
+            want_lp, want_top = P.logprobs(logits[r], float(temp[r]), int(top_k[r]), int(chosen[r]), n_top)
+            if want_lp == float("-inf"):
+                assert float(lp[i, 0]) == float("-inf")
+            else:
+                assert abs(float(lp[i, 0]) - want_lp) <= 1e-4
+            got = [(int(t), float(v)) for t, v in zip(ids[i], lp[i, 1:]) if int(t) >= 0]
+            assert [t for t, _ in got] == [t for t, _ in want_top], (r, n_top)
+            assert all(abs(a[1] - b[1]) <= 1e-4 for a, b in zip(got, want_top))
+            assert all(int(t) == -1 and float(v) == float("-inf")
+                       for t, v in zip(ids[i, len(got):], lp[i, 1 + len(got):]))
+        if n_top >= 5:
+            assert ids[2, :2].tolist() == [7, 150] and len([t for t in ids[3] if t >= 0]) == 3
+        assert float(lp[4, 0]) == float("-inf") or int(chosen[4]) in torch.topk(logits[4], 50).indices.tolist()
+    # probabilities of a whole small row add up to 1
+    small = rnd(1, 19, seed=3)
+    lp, ids = ops().logprobs(small.to(DEV), torch.ones(1, device=DEV), None, torch.zeros(1, dtype=torch.int32, device=DEV),
+                             torch.zeros(1, dtype=torch.int32, device=DEV), 19)
+    assert sorted(ids[0].tolist()) == list(range(19))
+    assert abs(sum(math.exp(v) for v in lp[0, 1:].tolist()) - 1.0) <= 1e-5
+
+
 def test_kernels_refuse_what_they_cannot_take():
     o = ops()
     with pytest.raises(o.KernelError):

@@ -86,3 +86,20 @@ def test_sampling_distribution_rules():
     assert torch.allclose(P.sample_probs(lg, 0.5), torch.tensor([16 / 22, 4 / 22, 1 / 22, 1 / 22]))
     p = torch.tensor([0.5, 0.25, 0.25])
     assert [P.sample_from_probs(p, u) for u in (0.0, 0.49, 0.5, 0.76, 0.9999999)] == [0, 0, 1, 2, 2]
+
+
+def test_plain_bias_and_logprobs():
+    import math
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(30, generator=g) * 2
+    lp, top = P.logprobs(x, 0.5, 0, 3, 30)
+    assert abs(sum(math.exp(v) for _, v in top) - 1.0) < 1e-9 and dict(top)[3] == lp
+    assert [t for t, _ in top] == sorted(range(30), key=lambda i: (-float(x[i]), i))
+    lp0, top0 = P.logprobs(x, 0.0, 0, 3, 2)                   # a greedy row: the raw logits' softmax
+    assert abs(lp0 - float(torch.log_softmax(x.double(), -1)[3])) < 1e-12 and len(top0) == 2
+    _, top_k = P.logprobs(x, 1.0, 4, int(torch.argmax(x)), 10)
+    assert len(top_k) == 4 and abs(sum(math.exp(v) for _, v in top_k) - 1.0) < 1e-9
+    assert P.logprobs(x, 1.0, 4, int(torch.argmin(x)), 0)[0] == float("-inf")
+    y = P.adjust_logits(x, [2, 2, 5], frequency_penalty=0.5, presence_penalty=1.0, logit_bias={5: 3.0, 99: 1.0})
+    want = x.clone(); want[2] -= 2.0; want[5] += 3.0 - 1.5
+    assert torch.allclose(y, want)

@@ -221,3 +221,30 @@ def test_a_step_is_planned_ahead_only_in_the_steady_state():
     s.add_request([2], SamplingParams(max_tokens=9))
     assert s.plan_ahead(plan) is None
     ex.cache.check()
+
+
+def test_logprobs_are_recorded_with_their_tokens():
+    """`advance` hands each sampled request its entry of the step's log-probabilities (keyed by the
+    request's place among the sampled ones), also when a request before it has ended meanwhile."""
+    s, ex = make(max_active=4, max_tokens_per_step=64)
+    a = s.add_request([1, 2, 3], SamplingParams(max_tokens=4, logprobs=True, top_logprobs=1))
+    b = s.add_request([4, 5], SamplingParams(max_tokens=4))
+    c = s.add_request([6], SamplingParams(max_tokens=4, logprobs=True))
+    plan, _ = s.schedule(ex)
+    ex.step(s.entries(plan))
+    s.abort(b, ex)
+    outs = s.advance(plan, [7, 8, 9], ex, {0: (-0.5, [(7, -0.5)]), 2: (-1.5, [])})
+    assert [(o.request_id, o.token, o.logprob, o.top_logprobs) for o in outs] == \
+        [(a, 7, -0.5, [(7, -0.5)]), (c, 9, -1.5, [])]
+    assert s.requests[a].logprobs == [(-0.5, [(7, -0.5)])] and s.requests[c].logprobs == [(-1.5, [])]
+    assert s.requests[b].logprobs == []
+
+
+def test_sampling_params_check_bias_and_logprobs():
+    sp = SamplingParams(logit_bias={9: -100.0, 3: 2})
+    assert sp.logit_bias == ((3, 2.0), (9, -100.0)) and hash(sp) is not None
+    assert SamplingParams(logit_bias=[(4, 1.0)]).logit_bias == ((4, 1.0),)
+    for bad in (dict(logit_bias=[(1, 1.0), (1, 2.0)]), dict(logit_bias={-1: 1.0}), dict(top_logprobs=3),
+                dict(logprobs=True, top_logprobs=21)):
+        with pytest.raises(ValueError):
+            SamplingParams(**bad)
