@@ -10,7 +10,7 @@ entry point (`LLM.add_request` / `LLM.step`), host token ids in, host token ids 
 step copying its inputs from pinned host memory and reading its tokens back. `prefill`: one
 2,048-token prompt in one step. `roofline`: bytes the decode step has to read (every weight
 once, and the cache of the live requests) over its time, against the measured copy
-bandwidth. `points`: decode at batch 1 and 64. Between timed steps nothing is flushed: one
+bandwidth. `points`: decode at batch 1 and 64 (`points_frac`: their roofline fractions). Between timed steps nothing is flushed: one
 step reads 2.47 GB of weights, twenty times the 126 MB L2.
 This engine runs on one GPU: for --gpus N > 1 it says so and exits with 2.
 """
@@ -287,11 +287,17 @@ def main():
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
         "points": {f"decode_b{B}": round(B / results[B][0] * 1e3, 1) for B in batches if B != a.batch},
+        # the same roofline fraction (bytes the step has to read / its time / the copy bandwidth) per point
+        "points_frac": {f"decode_b{B}": round((wbytes + B * results[B][2] * kv_bytes_per_token)
+                                              / (results[B][0] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+                        for B in batches if B != a.batch},
         "published": {"h100_nvl_b1_tok_s": 326, "note": "reference README, other hardware, batch 1"},
         "clocks": clocks,
     }
     if 1 in results:
         out["points"]["decode_b1"] = round(1 / results[1][0] * 1e3, 1)
+        out["points_frac"]["decode_b1"] = round((wbytes + results[1][2] * kv_bytes_per_token)
+                                                / (results[1][0] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
     print(json.dumps(out))
     return 0
 
