@@ -656,7 +656,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 // output tiles (token tiles fastest, so the CTAs of a wave share their weight tiles in L2 and a
 // weight byte comes from DRAM once) and keeps two accumulators in TMEM: while the epilogue warps
 // read tile i out of one, the MMA warp already fills the other with tile i + 1, so the tensor
-// cores do not wait for the epilogue. No ranges of K, no rotary or norm fusion here.
+// cores do not wait for the epilogue. No ranges of K and no norm in front here; the rotary epilogue
+// exists but is chosen only up to 128 tokens (beyond, the row-parallel rotation kernel is faster
+// than rotating in four epilogue warps).
 template <int BN, bool DUAL> struct PCfg {
   static constexpr int A_TILES = DUAL ? 2 : 1;
   static constexpr int A_BYTES = BM * BK * 2;
