@@ -34,7 +34,14 @@ LLAMA_1B = {   # BASELINE.json configs[2]
     "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
                      "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
 }
-FULL_LAYERS = 16
+# The other two sizes the reference's benchmarks name, for `--model 3b|8b` (not the default run)
+LLAMA_3B = dict(LLAMA_1B, hidden_size=3072, num_hidden_layers=28, num_attention_heads=24, num_key_value_heads=8,
+                head_dim=128, intermediate_size=8192)
+LLAMA_8B = dict(LLAMA_1B, hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+                head_dim=128, intermediate_size=14336, tie_word_embeddings=False,
+                rope_scaling=dict(LLAMA_1B["rope_scaling"], factor=8.0))
+MODELS = {"1b": ("llama-3.2-1b-shape", "Llama 3.2 1B", LLAMA_1B), "3b": ("llama-3.2-3b-shape", "Llama 3.2 3B", LLAMA_3B),
+          "8b": ("llama-3.1-8b-shape", "Llama 3.1 8B", LLAMA_8B)}
 CONTEXT = 4096
 PROMPT = 2048
 PAGE = 16
@@ -114,7 +121,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers where memory or time needs it")
+    ap.add_argument("--model", default="1b", choices=sorted(MODELS), help="layer sizes (default: the 1B shape)")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers where memory or time needs it")
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--phase", default="all", choices=["all", "prefill", "decode"],
                     help="run one part only (for profiling; the JSON line then lacks the other parts)")
@@ -138,7 +146,10 @@ def main():
     from rllm_b200.sampling import SamplingParams
 
     pk = peaks()
-    cfg = dict(LLAMA_1B, num_hidden_layers=a.layers)
+    model_name, model_title, full_cfg = MODELS[a.model]
+    full_layers = full_cfg["num_hidden_layers"]
+    a.layers = a.layers or full_layers
+    cfg = dict(full_cfg, num_hidden_layers=a.layers)
     batches = [a.batch] if a.no_points else sorted({1, a.batch, 64})
     pages = max(batches) * (CONTEXT // PAGE + 1) + 64
     llm = LLM(cfg, dtype="bfloat16", seed=0, page_size=PAGE, num_pages=pages, max_active=max(batches),
@@ -269,16 +280,17 @@ def main():
     clocks = sampler.stop(windows)
 
     out = {
-        "metric": "decode tok/s at batch 8 (Llama 3.2 1B, bf16, context 4096)" if a.batch == 8
-        else f"decode tok/s at batch {a.batch} (Llama 3.2 1B, bf16, context 4096)",
+        "metric": f"decode tok/s at batch {a.batch} ({model_title}, bf16, context {CONTEXT})",
         "value": round(a.batch / ms * 1e3, 1), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (random token ids, random weights N(0,0.02))",
         "impl": "ours",
-        "config": {"model": "llama-3.2-1b-shape", "layers": a.layers, "layers_full": FULL_LAYERS,
-                   "hidden": 2048, "heads": 32, "kv_heads": 8, "head_dim": 64, "intermediate": 8192,
-                   "vocab": 128256, "global_batch": a.batch, "seq_len": CONTEXT, "prompt_len": PROMPT,
-                   "kv_page": PAGE, "parallelism": "single-gpu", "l2": "step reads 2.5 GB > 126 MB L2, no flush",
+        "config": {"model": model_name, "layers": a.layers, "layers_full": full_layers,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": a.batch,
+                   "seq_len": CONTEXT, "prompt_len": PROMPT, "kv_page": PAGE, "parallelism": "single-gpu",
+                   "l2": f"step reads {wbytes / 1e9:.1f} GB > 126 MB L2, no flush",
                    "peaks": pk["source"]},
         "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": round(e2e_h2d[0]) if e2e_h2d else None,
                 "d2h_bytes_per_step": 4 * a.batch},
@@ -291,7 +303,7 @@ def main():
         "points_frac": {f"decode_b{B}": round((wbytes + B * results[B][2] * kv_bytes_per_token)
                                               / (results[B][0] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
                         for B in batches if B != a.batch},
-        "published": {"h100_nvl_b1_tok_s": 326, "note": "reference README, other hardware, batch 1"},
+        "published": {"h100_nvl_b1_tok_s": 326, "note": "reference README, other hardware, batch 1"} if a.model == "1b" else None,
         "clocks": clocks,
     }
     if 1 in results:
