@@ -46,6 +46,7 @@
 //
 // Every mbarrier wait is bounded; on a time-out the CTA records an error word, drains what it
 // has in flight, still meets its cluster's barriers, frees its TMEM and returns.
+#include <cstdlib>
 #include "common.cuh"
 #include "sm100.cuh"
 #include <mutex>
@@ -976,10 +977,19 @@ void plan(int epi, int T, int N, int K, int sm_count, bool allow_split, int* bn_
   int bn, splits = 1;
   const int kb = (K + BK - 1) / BK;
   if (allow_split && n_tiles * 2 <= sm_count) {
-    splits = sm_count / n_tiles;                              // one CTA per SM, as far as it goes
+    // One CTA per SM, as far as it goes; with a single token tile (up to 32 tokens) and a single
+    // weight tile (84 KB of shared memory a CTA) two per SM. More and shorter ranges win as long as
+    // the CTAs are resident together: at 8 ranges of a K of 2,048 a CTA's whole share of the weights
+    // (64 KB) is in flight before the previous kernel has ended (QKV at 8 tokens: 6.3 us with 6
+    // ranges, 5.9 us with 8). With two token tiles the doubled CTAs cost more than they save
+    // (64 tokens: 3 to 5 % of the decode step).
+    splits = ((!dual && T <= 32) ? 2 * sm_count : sm_count) / n_tiles;
     if (splits > kb / 2) splits = kb / 2;                     // at least two K blocks per range
     if (splits > MAX_CLUSTER) splits = MAX_CLUSTER;
     if (splits < 1) splits = 1;
+    // tuning knob of the microbenchmark: RLLM_B200_TC_SPLITS=n asks for n ranges where ranges are allowed
+    static const int forced = [] { const char* e = getenv("RLLM_B200_TC_SPLITS"); return e ? atoi(e) : 0; }();
+    if (forced > 0) splits = forced < kb / 2 ? (forced < MAX_CLUSTER ? forced : MAX_CLUSTER) : (kb / 2 > 0 ? kb / 2 : 1);
   }
   // A step of few tokens: token tiles of 16 or 32 (33 to 64 tokens: two tiles of 32 land their
   // parts faster than one of 64), and ranges of K until every SM has a CTA. Up to 128 tokens the
