@@ -122,7 +122,7 @@ def build_library(name: str, verbose_ptxas: bool = False) -> str:
         objs.append(obj)
         if not os.path.isfile(obj):
             jobs.append((s, obj))
-    so_tag = hashlib.sha256(" ".join(objs).encode()).hexdigest()[:12]
+    so_tag = hashlib.sha256(" ".join(os.path.basename(o) for o in objs).encode()).hexdigest()[:12]   # not the folder: a copied tree keeps its library
     so = os.path.join(libdir, f"librllm_b200_{name}.{so_tag}.so")
     if os.path.isfile(so) and not jobs:
         return so
