@@ -499,6 +499,22 @@ RLLM_API int rllm_add_at(float* logits, int R, int V, const int* rows, const int
 // where fewer than n_top tokens are kept the rest is (-inf, -1).
 constexpr int TOP_LOGPROBS_MAX = 20;
 
+// f(value, index) for every entry of a row, four a load where the row allows it (the passes below
+// wait for L2, not for arithmetic: independent wide loads are what shortens them)
+template <typename F>
+__device__ __forceinline__ void row_for_each(const float* __restrict__ x, int V, F f) {
+  const int tid = threadIdx.x;
+  if ((V & 3) == 0 && ((uintptr_t)x & 15) == 0) {
+#pragma unroll 2
+    for (int i = tid * 4; i < V; i += THREADS * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(x + i);
+      f(v.x, i); f(v.y, i + 1); f(v.z, i + 2); f(v.w, i + 3);
+    }
+  } else {
+    for (int i = tid; i < V; i += THREADS) f(x[i], i);
+  }
+}
+
 __global__ void __launch_bounds__(THREADS)
 logprobs_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
                 const int* __restrict__ top_k, const int* __restrict__ chosen, const int* __restrict__ rows,
@@ -523,17 +539,17 @@ logprobs_kernel(const float* __restrict__ logits, int V, const float* __restrict
     while (lo < hi) {
       const unsigned mid = lo + ((hi - lo) >> 1) + 1u;
       int c = 0;
-      for (int i = tid; i < V; i += THREADS) c += (f2key(x[i] * invT) >= mid);
+      row_for_each(x, V, [&](float xv, int) { c += (f2key(xv * invT) >= mid); });
       c = block_sum_i(c, redi);
       if (c >= k) lo = mid; else hi = mid - 1u;
     }
     thr = key2f(lo);
   }
   float mx = -INFINITY;
-  for (int i = tid; i < V; i += THREADS) { const float v = x[i] * invT; if (v >= thr) mx = fmaxf(mx, v); }
+  row_for_each(x, V, [&](float xv, int) { const float v = xv * invT; if (v >= thr) mx = fmaxf(mx, v); });
   mx = block_max(mx, redf);
   float sum = 0.f;
-  for (int i = tid; i < V; i += THREADS) { const float v = x[i] * invT; if (v >= thr) sum += expf(v - mx); }
+  row_for_each(x, V, [&](float xv, int) { const float v = xv * invT; if (v >= thr) sum += expf(v - mx); });
   sum = block_sum_f(sum, redf);
   const float lse = mx + logf(sum);
   float* lp_row = lp + (size_t)blockIdx.x * (1 + n_top);
@@ -547,10 +563,10 @@ logprobs_kernel(const float* __restrict__ logits, int V, const float* __restrict
   float last_v = INFINITY; int last_i = -1;
   for (int j = 0; j < n_top; ++j) {
     float best = -INFINITY; int bi = 0x7fffffff;
-    for (int i = tid; i < V; i += THREADS) {
-      const float v = x[i] * invT;
+    row_for_each(x, V, [&](float xv, int i) {
+      const float v = xv * invT;
       if (v >= thr && (v < last_v || (v == last_v && i > last_i))) argmax_take(best, bi, v, i);
-    }
+    });
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, best, o);
