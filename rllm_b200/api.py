@@ -38,7 +38,8 @@ class LLM:
         self.scheduler = Scheduler(self.engine.cache, max_active, max_tokens_per_step, max_chunk)
         self.sampler = Sampler(self.engine.backend)
         self._tokenizer = None
-        # a step that was launched ahead: (plan, its drawn tokens: device tensor, host copy, event)
+        # a step that was launched ahead: (plan, its drawn tokens: device tensor, host copy, event,
+        # and the host copies of the log-probabilities where a request asked for them)
         self._ahead = None
         self._pinned = []                        # host buffers the drawn tokens are copied into, in turn
         self.run_ahead = os.environ.get("RLLM_B200_NO_RUN_AHEAD") != "1"
@@ -55,7 +56,9 @@ class LLM:
         return self.scheduler.has_work()
 
     def _launch(self, plan, feed=None, ahead: int = 0):
-        """Run the plan's batch and draw its tokens; returns them on the device (or None).
+        """Run the plan's batch and draw its tokens. Returns None when nothing is sampled, else
+        (tokens on the device, their pinned host copy, the event after which that copy is
+        complete, log-probabilities on their way to the host or None).
         `ahead`: how many tokens each request is about to get that its `output` lacks."""
         logits = self.engine.step(self.scheduler.entries(plan), keep=False, feed=feed)
         sampled = [p.request for p in plan if p.samples]
