@@ -47,6 +47,13 @@ class LLM:
 
     # ---- the reference's engine loop
     def add_request(self, prompt_token_ids: list[int], params: SamplingParams | None = None) -> int:
+        """A request ends at the model's own end-of-sequence ids (config.json's `eos_token_id`)
+        unless its parameters name others or say `ignore_eos`, as the reference's engine stops
+        at its tokenizer's list (src/engine/mod.rs:694-699)."""
+        params = params or SamplingParams()
+        eos = getattr(self.engine.model.config, "eos_token_ids", ())
+        if eos and not params.eos_token_ids and not params.ignore_eos:
+            params = replace(params, eos_token_ids=tuple(eos))
         return self.scheduler.add_request(prompt_token_ids, params)
 
     def abort(self, request_id: int) -> bool:

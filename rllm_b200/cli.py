@@ -78,7 +78,11 @@ def _params(a):
 def _encode(llm, text: str | None, ids: str | None) -> list[int]:
     if ids is not None:
         return [int(x) for x in ids.replace(",", " ").split()]
-    return llm.tokenizer().encode(text).ids
+    # the text's tokens without the tokenizer's own special tokens, the model's BOS in front exactly
+    # once where it has one (src/model/tokenizer.rs:123-140)
+    toks = llm.tokenizer().encode(text, add_special_tokens=False).ids
+    bos = getattr(llm.engine.model.config, "bos_token_id", None)
+    return ([bos] if bos is not None else []) + toks
 
 
 def _show(llm, tokens: list[int], as_ids: bool) -> str:
@@ -97,6 +101,7 @@ def cmd_run(a) -> int:
     import torch
     rid = llm.add_request(prompt, _params(a))
     t0 = time.time(); first = None; n = 0
+    produced, shown = [], ""
     while llm.has_work():
         for out in llm.step():
             if out.token is None:
@@ -105,7 +110,16 @@ def cmd_run(a) -> int:
             if first is None:
                 torch.cuda.synchronize(); first = time.time()
             n += 1
-            sys.stdout.write((str(out.token) + " ") if as_ids else llm.tokenizer().decode([out.token]))
+            if as_ids:
+                sys.stdout.write(str(out.token) + " ")
+            else:
+                # the whole output decoded again, its new end printed: a character whose bytes are
+                # spread over several tokens appears when its last token has come
+                produced.append(out.token)
+                text = llm.tokenizer().decode(produced)
+                if not text.endswith("\ufffd") or out.finished:
+                    sys.stdout.write(text[len(shown):])
+                    shown = text
             sys.stdout.flush()
     torch.cuda.synchronize(); t1 = time.time()
     print()

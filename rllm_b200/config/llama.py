@@ -7,6 +7,10 @@ and `layer_norm_epsilon`. Where the reference silently defaults a missing
 `rope_theta` / eps to 0 we default to 10000 / 1e-5 instead. `sliding_window`
 with `layer_types` (src/model/config.rs:553-558, 970-985) is honoured when
 present, so one model may mix full and windowed attention layers.
+`bos_token_id` and `eos_token_id` (a number or a list) are read where config.json
+has them; without them a model with the Llama 3 vocabulary of 128,256 entries
+gets the ids the reference hard-codes for the family (src/model/tokenizer.rs:64-65:
+BOS 128000, stop on 128001 and 128009), any other model none.
 """
 from __future__ import annotations
 
@@ -77,6 +81,8 @@ class LlamaConfig(ModelConfig):
     attention_bias: bool = False
     sliding_window: int | None = None
     layer_types: tuple[str, ...] | None = None
+    bos_token_id: int | None = None          # put in front of a text prompt
+    eos_token_ids: tuple[int, ...] = ()      # a generation ends with any of these
     model_type: str = "llama"
     architectures: tuple[str, ...] = ("LlamaForCausalLM",)
     extra: dict = field(default_factory=dict, compare=False, hash=False)
@@ -145,7 +151,19 @@ class LlamaConfig(ModelConfig):
         theta = require_float(raw, "rope_theta", default=10000.0)
         if theta <= 0:
             raise ConfigError(f"rope_theta must be > 0, got {theta}")
-        known = {"hidden_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads",
+        bos, eos = raw.get("bos_token_id"), raw.get("eos_token_id")
+        if eos is None:
+            eos = []
+        elif isinstance(eos, int) and not isinstance(eos, bool):
+            eos = [eos]
+        if bos is None and not eos and "bos_token_id" not in raw and "eos_token_id" not in raw and V == 128256:
+            bos, eos = 128000, [128001, 128009]
+        if bos is not None and (isinstance(bos, bool) or not isinstance(bos, int) or not 0 <= bos < V):
+            raise ConfigError(f"bos_token_id must be a token id below vocab_size {V}, got {bos!r}")
+        if not isinstance(eos, (list, tuple)) or any(isinstance(t, bool) or not isinstance(t, int) or not 0 <= t < V
+                                                      for t in eos):
+            raise ConfigError(f"eos_token_id must be a token id or a list of them below vocab_size {V}, got {eos!r}")
+        known = {"bos_token_id", "eos_token_id", "hidden_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads",
                  "head_dim", "intermediate_size", "vocab_size", "max_position_embeddings",
                  "rope_theta", "rms_norm_eps", "norm_eps", "layer_norm_epsilon",
                  "tie_word_embeddings", "rope_scaling", "attention_bias", "sliding_window",
@@ -158,7 +176,7 @@ class LlamaConfig(ModelConfig):
             tie_word_embeddings=bool(raw.get("tie_word_embeddings", False)),
             rope_scaling=RopeScaling.from_dict(raw.get("rope_scaling")),
             attention_bias=bool(raw.get("attention_bias", False)),
-            sliding_window=sw, layer_types=lt,
+            sliding_window=sw, layer_types=lt, bos_token_id=bos, eos_token_ids=tuple(eos),
             model_type=raw.get("model_type", "llama"),
             architectures=tuple(raw.get("architectures") or ("LlamaForCausalLM",)),
             extra={k: v for k, v in raw.items() if k not in known},
@@ -181,4 +199,6 @@ class LlamaConfig(ModelConfig):
             d["sliding_window"] = self.sliding_window
         if self.layer_types is not None:
             d["layer_types"] = list(self.layer_types)
+        d["bos_token_id"] = self.bos_token_id
+        d["eos_token_id"] = list(self.eos_token_ids) if len(self.eos_token_ids) != 1 else self.eos_token_ids[0]
         return d

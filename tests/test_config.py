@@ -105,3 +105,26 @@ def test_model_is_built_from_the_configuration_layer_by_layer():
     assert model.head.tied_to is model.embedding
     specs = model.cache_specs()
     assert specs[0] == specs[2] != specs[1] == specs[3]
+
+
+def test_special_token_ids():
+    """bos_token_id / eos_token_id as config.json has them (a number or a list); a model with the
+    Llama 3 vocabulary and neither key gets the family's ids, any other model none; ids beyond
+    the vocabulary are refused; an explicit null survives the round trip."""
+    from rllm_b200.config import config_from_dict
+    base = dict(tiny.TINY_A)
+    _, c = config_from_dict(base)
+    assert c.bos_token_id is None and c.eos_token_ids == ()
+    _, c = config_from_dict(dict(base, bos_token_id=1, eos_token_id=2))
+    assert (c.bos_token_id, c.eos_token_ids) == (1, (2,))
+    _, c = config_from_dict(dict(base, eos_token_id=[3, 250]))
+    assert (c.bos_token_id, c.eos_token_ids) == (None, (3, 250))
+    _, c3 = config_from_dict(dict(base, vocab_size=128256))
+    assert (c3.bos_token_id, c3.eos_token_ids) == (128000, (128001, 128009))
+    _, again = config_from_dict(c.to_dict())
+    assert again.eos_token_ids == (3, 250) and again.bos_token_id is None
+    _, none = config_from_dict(dict(base, vocab_size=128256, bos_token_id=None, eos_token_id=None))
+    assert none.bos_token_id is None and none.eos_token_ids == ()
+    for bad in (dict(eos_token_id=256), dict(bos_token_id=-1), dict(eos_token_id="2"), dict(eos_token_id=[1, True])):
+        with pytest.raises(ConfigError):
+            config_from_dict(dict(base, **bad))

@@ -351,3 +351,33 @@ def test_cli_run_and_batch(dirs, tmp_path):
     r = subprocess.run([sys.executable, rllm, "run", "--model", dirs["A"], "--prompt-ids", "1 2",
                         "--kv-quant", "turbo4"], capture_output=True, text=True, timeout=600)
     assert r.returncode != 0 and "not built" in r.stderr
+
+
+def test_cli_text_prompt_gets_bos_and_stops_at_eos(dirs, tmp_path):
+    """`rllm run --prompt TEXT` with a tokenizer.json in the folder: the model's BOS goes in front
+    of the text's tokens once, the output ends with the model's end-of-sequence token (both from
+    config.json), and the text is streamed as it is decoded."""
+    import json, os, shutil, subprocess, sys
+    tk = pytest.importorskip("tokenizers")
+    cfg, w = P.read_model_dir(dirs["A"])
+    V = cfg["vocab_size"]
+    prompt = [1, 5, 17, 3]                                   # BOS = 1, then "w5 w17 w3"
+    want = P.greedy(cfg, w, prompt, 6)
+    stop = want.index(want[2])                               # the output ends where the third token first appears
+    d = str(tmp_path / "with_tokenizer")
+    shutil.copytree(dirs["A"], d)
+    with open(os.path.join(d, "config.json")) as f:
+        raw = json.load(f)
+    raw.update(bos_token_id=1, eos_token_id=want[stop])
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(raw, f)
+    tok = tk.Tokenizer(tk.models.WordLevel({f"w{i}": i for i in range(V)}, unk_token="w0"))
+    tok.pre_tokenizer = tk.pre_tokenizers.Whitespace()
+    tok.save(os.path.join(d, "tokenizer.json"))
+    rllm = os.path.join(replay.ROOT, "bin", "rllm")
+    r = subprocess.run([sys.executable, rllm, "run", "--model", d, "--prompt", "w5 w17 w3", "--max-tokens", "6",
+                        "--temperature", "0", "--dtype", "float32", "--kv-pages", "32"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    assert r.stdout.split() == [f"w{t}" for t in want[: stop + 1]]
+    assert f"prefill: {len(prompt)} tokens" in r.stderr
