@@ -248,3 +248,63 @@ def test_sampling_params_check_bias_and_logprobs():
                 dict(logprobs=True, top_logprobs=21)):
         with pytest.raises(ValueError):
             SamplingParams(**bad)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_traffic_keeps_the_budget_the_pages_and_the_order(seed):
+    """Random arrivals, prompt lengths, token limits, end tokens and aborts on a pool so small that
+    requests are preempted: every step stays within the token budget and the places, the pages
+    always suffice (the fake executor reserves like the real one and the cache proves its books),
+    nobody overtakes the head of the line, a preempted request goes on where it was, and
+    everybody ends with the tokens it should have."""
+    import random
+    r = random.Random(seed)
+    budget, chunk, places = r.choice([8, 17, 64]), r.choice([None, 5, 16]), r.choice([2, 3, 6])
+    s, ex = make(pages=r.choice([6, 9, 14]), page=4, max_active=places, max_tokens_per_step=budget, max_chunk=chunk)
+    pool = s.cache.groups[0].pool.num_pages
+    want, admitted_order, aborted, idle = {}, [], set(), 0
+    for step in range(5000):
+        if step < 250 and r.random() < 0.35:
+            n_prompt, n_new = r.randint(1, 30), r.randint(1, 12)
+            eos = (1000 + r.randint(1, n_new),) if r.random() < 0.3 else ()
+            rid = s.add_request(list(range(n_prompt)), SamplingParams(max_tokens=n_new, eos_token_ids=eos))
+            want[rid] = (n_prompt, n_new, eos)
+        if r.random() < 0.03 and want:
+            rid = r.choice(list(want))
+            if s.abort(rid, ex):
+                aborted.add(rid)
+        before = {q.request_id: len(q.output) for q in s.requests.values()}
+        was_running = {q.request_id for q in s.running}
+        plan, outs = run_step(s, ex)
+        idle = idle + 1 if not plan and not outs and s.has_work() else 0
+        assert idle < 3, "work is waiting and nothing runs"
+        assert sum(len(p.tokens) for p in plan) <= budget and len(s.running) <= places
+        assert len({p.request.request_id for p in plan}) == len(plan)
+        for p in plan:
+            rid = p.request.request_id
+            if chunk:
+                assert len(p.tokens) <= chunk
+            if rid not in was_running and p.request.preemptions == 0:
+                admitted_order.append(rid)
+            assert len(p.request.output) - before[rid] == (1 if p.samples else 0)
+        s.cache.check()
+        if not s.has_work() and step >= 250:
+            break
+    assert not s.has_work(), "requests were left over: the scheduler stalled"
+    assert admitted_order == sorted(admitted_order)          # first come, first admitted
+    assert s.cache.free_pages() == [pool]
+    for rid, (n_prompt, n_new, eos) in want.items():
+        q = s.requests[rid]
+        assert q.finished
+        if rid in aborted:
+            assert q.finish_reason == "aborted"
+            continue
+        if q.finish_reason == "out_of_pages":                # it could never fit, or outgrew the pool alone
+            assert (n_prompt + len(q.output)) // 4 + 1 > pool - 1 or n_prompt + n_new > (pool - 1) * 4
+            continue
+        assert q.output == [1000 + i for i in range(len(q.output))]     # nothing lost or repeated over preemptions
+        if eos and eos[0] < 1000 + n_new:
+            assert q.finish_reason == "eos" and q.output[-1] == eos[0]
+        else:
+            assert q.finish_reason == "max_tokens" and len(q.output) == n_new
+    assert s.preempted_total > 0 or pool > 9
