@@ -308,3 +308,15 @@ def test_random_traffic_keeps_the_budget_the_pages_and_the_order(seed):
         else:
             assert q.finish_reason == "max_tokens" and len(q.output) == n_new
     assert s.preempted_total > 0 or pool > 9
+
+
+def test_decode_graph_sizes_are_few_and_waste_little():
+    """A batch that shrinks request by request meets a short list of graph sizes: every size up to
+    8, then steps of 4, 8 and 16; a size serves itself, and the stand-in rows stay under a third."""
+    from rllm_b200.engine.graphs import padded_rows
+    sizes = sorted({padded_rows(s) for s in range(1, 257)})
+    assert sizes[:8] == list(range(1, 9)) and len(sizes) <= 32
+    for s in range(1, 257):
+        p = padded_rows(s)
+        assert p >= s and padded_rows(p) == p and (p - s) * 3 < p + 3
+    assert [padded_rows(s) for s in (9, 12, 13, 33, 64, 65, 200)] == [12, 12, 16, 40, 64, 80, 208]
