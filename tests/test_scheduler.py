@@ -320,3 +320,62 @@ def test_decode_graph_sizes_are_few_and_waste_little():
         p = padded_rows(s)
         assert p >= s and padded_rows(p) == p and (p - s) * 3 < p + 3
     assert [padded_rows(s) for s in (9, 12, 13, 33, 64, 65, 200)] == [12, 12, 16, 40, 64, 80, 208]
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_traffic_with_steps_planned_ahead_gives_the_same_outputs(seed):
+    """The loop of `LLM.step` (a step planned and run ahead whenever `plan_ahead` allows it, its
+    tokens recorded one call later) against the plain loop, on the same random traffic with end
+    tokens, limits and aborts: the same outputs and reasons, pages that always suffice, an empty
+    pool at the end. The token a request gets is a function of its id and its place, as with the
+    counter-based random numbers."""
+    import random
+
+    def token_of(req, ahead=0):
+        return (req.request_id * 7 + (len(req.output) + ahead) * 3) % 50
+
+    def traffic(s, ex, ahead_allowed):
+        r = random.Random(100 + seed)
+        ahead, aborted, planned_ahead = None, set(), 0
+        for step in range(3000):
+            if step < 200 and r.random() < 0.15:
+                sp = SamplingParams(max_tokens=r.randint(1, 25), eos_token_ids=(r.randrange(50),) if r.random() < 0.5 else ())
+                s.add_request(list(range(r.randint(1, 20))), sp)
+            if r.random() < 0.02 and s.requests:
+                rid = r.choice(list(s.requests))
+                if rid not in aborted and s.abort(rid, ex):
+                    aborted.add(rid)
+            if ahead is not None:
+                plan, tokens = ahead
+                ahead = None
+            else:
+                plan, _ = s.schedule(ex)
+                if not plan:
+                    if not s.has_work() and step >= 200:
+                        break
+                    continue
+                ex.step(s.entries(plan))
+                tokens = [token_of(p.request) for p in plan if p.samples]
+            if ahead_allowed:
+                nxt = s.plan_ahead(plan)
+                if nxt is not None:
+                    ex.step(s.entries(nxt))                 # runs before this step's tokens are recorded
+                    ahead = (nxt, [token_of(p.request, 1) for p in nxt])
+                    planned_ahead += 1
+            s.advance(plan, tokens, ex)
+            if ahead is not None and all(p.request.finished for p in ahead[0]):
+                ahead = None
+            s.cache.check()
+        assert not s.has_work() and s.cache.free_pages() == [s.cache.groups[0].pool.num_pages]
+        return {rid: (q.output, q.finish_reason) for rid, q in s.requests.items()}, planned_ahead
+
+    a, n_ahead = traffic(*make(pages=200, page=4, max_active=6, max_tokens_per_step=32), ahead_allowed=True)
+    b, _ = traffic(*make(pages=200, page=4, max_active=6, max_tokens_per_step=32), ahead_allowed=False)
+    assert n_ahead > 20
+    # an abort between a step ahead and its recording may cost the aborted request its last token;
+    # everybody else has exactly the same output
+    for rid in a:
+        if a[rid][1] == "aborted":
+            assert b[rid][1] == "aborted" and a[rid][0][: len(b[rid][0])] == b[rid][0][: len(a[rid][0])]
+        else:
+            assert a[rid] == b[rid], rid
