@@ -379,3 +379,23 @@ def test_random_traffic_with_steps_planned_ahead_gives_the_same_outputs(seed):
             assert b[rid][1] == "aborted" and a[rid][0][: len(b[rid][0])] == b[rid][0][: len(a[rid][0])]
         else:
             assert a[rid] == b[rid], rid
+
+
+def test_uniform_numbers_hang_on_seed_and_index_only():
+    """The draw of a request's n-th token: in [0, 1), 24 bits, the same for the same (seed, index),
+    spread evenly, and neighbouring seeds or indices give unrelated values."""
+    from rllm_b200.sampling.rng import uniform
+    us = [uniform(5, i) for i in range(4000)]
+    assert all(0.0 <= u < 1.0 and u * (1 << 24) == int(u * (1 << 24)) for u in us)
+    assert us == [uniform(5, i) for i in range(4000)] and len(set(us)) > 3990
+    assert abs(sum(us) / len(us) - 0.5) < 0.02
+    counts = [0] * 10
+    for u in us:
+        counts[int(u * 10)] += 1
+    assert min(counts) > 330 and max(counts) < 470
+    other = [uniform(6, i) for i in range(4000)]
+    mean = lambda v: sum(v) / len(v)
+    cov = mean([a * b for a, b in zip(us, other)]) - mean(us) * mean(other)
+    lag = mean([a * b for a, b in zip(us, us[1:])]) - mean(us[:-1]) * mean(us[1:])
+    assert abs(cov) < 0.01 and abs(lag) < 0.01
+    assert uniform(2 ** 63 + 11, 0) == uniform(2 ** 63 + 11, 0) and 0 <= uniform(-3, 7) < 1
