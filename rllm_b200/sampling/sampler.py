@@ -87,6 +87,8 @@ class Sampler:
         int32 for top-k), with the event that tells when its last reader has run."""
         if not self._ring or self._ring[0][0].shape[1] < R:
             cap = max(64, 1 << (R - 1).bit_length())
+            for _, _, done in self._ring:        # a kernel may still be reading the buffers that go
+                done.synchronize()
             self._ring = []
             for _ in range(4):
                 buf = torch.zeros((5, cap), dtype=torch.float32).pin_memory()
