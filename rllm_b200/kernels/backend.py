@@ -67,10 +67,14 @@ class Backend:
         """Take the norm into the product? Every CTA of the product then normalises its own slice of
         the rows, which pays while the weight has no more 128-row tiles than the GPU has SMs; a
         wider weight (the output head) gets the norm from its own kernel, once."""
-        return (isinstance(x, Normed) and x._tensor is None and self._sm100 is not None
+        if not (isinstance(x, Normed) and x._tensor is None and self._sm100 is not None
                 and os.environ.get("RLLM_B200_NO_NORM_FUSION") != "1"
-                and (w.shape[0] + 127) // 128 <= self._sm100.init(self.device).sm_count
-                and self._sm100.norm_supported(x.h, x.weight, w, x.rows))
+                and self._sm100.norm_supported(x.h, x.weight, w, x.rows)):
+            return False
+        # the kernel for steps of at most 8 tokens builds the normalised rows once per CTA whatever
+        # the width (a CTA walks many slabs of the weight)
+        return (w.shape[0] + 127) // 128 <= self._sm100.init(self.device).sm_count or \
+            self._sm100.stream_supported(ops.EPI_STORE_F32, True, x.shape[0], w.shape[0], w.shape[1])
 
     def gather_rows(self, x, rows):
         return ops.gather_rows(x, rows)

@@ -18,6 +18,11 @@ ops.register_signatures("sm100", {
     "rllm_tc_gemm_norm_max_tokens": [],
     "rllm_tc_gemm_qkv_rope": [_P, c_longlong, _P, c_longlong, _P, c_int, c_float, _P, _P, c_longlong, c_int, c_int,
                               _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P],
+    "rllm_stream_gemm_supported": [c_int, c_int, c_int, c_int, c_int, c_int],
+    "rllm_stream_gemm": [c_int, _P, c_longlong, _P, c_longlong, _P, _P, c_int, c_float, _P, _P, c_longlong, c_int,
+                         c_int, c_int, c_int, _P],
+    "rllm_stream_gemm_qkv_rope": [_P, c_longlong, _P, c_longlong, _P, c_int, c_float, _P, _P, c_longlong, c_int, c_int,
+                                  _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "rllm_attention_fa": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_float, c_int, c_int, _P, _P, _P],
     "rllm_attention_prefill_tc": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -62,6 +67,23 @@ def check_error(device) -> None:
                               f"its output is not valid")
 
 
+EPI_QKV_ROPE = 4
+STREAM = os.environ.get("RLLM_B200_NO_STREAM_GEMM") != "1"
+_stream_ok: dict[tuple, bool] = {}
+
+
+def stream_supported(epilogue: int, norm: bool, T: int, N: int, K: int, hd: int = 0) -> bool:
+    """Does the weight-streaming kernel for steps of at most 8 tokens take this product? (N: output
+    features, of one half with the SwiGLU epilogue.)"""
+    if not STREAM or T > 8:
+        return False
+    key = (epilogue, norm, T, N, K, hd)
+    ok = _stream_ok.get(key)
+    if ok is None:
+        ok = _stream_ok[key] = bool(ops._fn("sm100", "rllm_stream_gemm_supported")(epilogue, int(norm), T, N, K, hd))
+    return ok
+
+
 def gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2
             and x.stride(1) == 1 and w.is_contiguous() and x.shape[1] == w.shape[1]
@@ -93,6 +115,12 @@ def gemm(x: torch.Tensor, w: torch.Tensor, epilogue: int, out: torch.Tensor | No
         out = torch.empty((T, N), dtype=out_dtype, device=x.device)
     if out.dtype != out_dtype or out.shape != (T, N) or out.stride(1) != 1:
         raise ops.KernelError(f"tc gemm out must be [{T}, {N}] of {out_dtype}")
+    if split and stream_supported(epilogue, False, T, N, K):
+        rc = ops._fn("sm100", "rllm_stream_gemm")(
+            epilogue, x.data_ptr(), x.stride(0), None, 0, None, None, 0, 0.0, w.data_ptr(), out.data_ptr(),
+            out.stride(0), T, N, K, st.sm_count, ops._stream())
+        ops._check(rc, "stream_gemm")
+        return out
     rc = ops._fn("sm100", "rllm_tc_gemm")(
         epilogue, x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), T, N, K,
         int(split), st.err.data_ptr(), st.sm_count, ops._stream())
@@ -136,6 +164,12 @@ def gemm_norm(h: torch.Tensor, g: torch.Tensor, eps: float, w: torch.Tensor, epi
     N = w.shape[0] // 2 if epilogue == ops.EPI_SWIGLU else w.shape[0]
     out = torch.empty((T, N), dtype=torch.float32 if epilogue == ops.EPI_STORE_F32 else torch.bfloat16,
                       device=h.device)
+    if split and stream_supported(epilogue, True, T, N, K):
+        rc = ops._fn("sm100", "rllm_stream_gemm")(
+            epilogue, None, 0, h.data_ptr(), h.stride(0), ops._ptr(rows), g.data_ptr(), ops._dt(g, "norm weight"),
+            float(eps), w.data_ptr(), out.data_ptr(), out.stride(0), T, N, K, st.sm_count, ops._stream())
+        ops._check(rc, "stream_gemm_norm")
+        return out
     rc = ops._fn("sm100", "rllm_tc_gemm_norm")(
         epilogue, h.data_ptr(), h.stride(0), ops._ptr(rows), g.data_ptr(), ops._dt(g, "norm weight"), float(eps),
         w.data_ptr(), out.data_ptr(), out.stride(0), T, N, K, int(split), st.err.data_ptr(), st.sm_count,
@@ -156,16 +190,19 @@ def gemm_qkv_rope(x: torch.Tensor | None, w_qkv: torch.Tensor, positions: torch.
     `slots` (None: no write), all in the product's epilogue. Returns qkv [T, (nh + 2 nkv) * hd].
     `norm` = (h, g, eps) instead of x: RMSNorm of the float rows h in front, in the same kernel.
     `table`: `ops.rope_table` of these positions ([T, rot_dim / 2, 2]); else the angles are computed here."""
+    T, K = norm[0].shape if norm is not None else x.shape
+    # steps of at most 8 tokens: the weight-streaming kernel (any head size that is a multiple of 32)
+    streamed = split and rot_dim == hd and stream_supported(EPI_QKV_ROPE, norm is not None, T, (nh + 2 * nkv) * hd, K, hd)
     if norm is not None:
         h, g, eps = norm
-        if not norm_supported(h, g, w_qkv) or 128 % hd or (kcache is not None and kcache.dtype != torch.bfloat16):
+        if not norm_supported(h, g, w_qkv) or (128 % hd and not streamed) or \
+                (kcache is not None and kcache.dtype != torch.bfloat16):
             raise ops.KernelError("tc gemm with norm and rotary epilogue: sizes not supported")
-        T, K = h.shape
         dev = h.device
     else:
-        if not qkv_rope_supported(x, w_qkv, kcache, hd):
+        if not (gemm_supported(x, w_qkv) and (128 % hd == 0 or streamed)
+                and (kcache is None or kcache.dtype == torch.bfloat16)):
             raise ops.KernelError("tc gemm with rotary epilogue: bfloat16 operands and a head size dividing 128")
-        T, K = x.shape
         dev = x.device
     st = init(dev)
     N = (nh + 2 * nkv) * hd
@@ -189,6 +226,13 @@ def gemm_qkv_rope(x: torch.Tensor | None, w_qkv: torch.Tensor, positions: torch.
         xa = (None, 0, h.data_ptr(), h.stride(0), g.data_ptr(), ops._dt(g, "norm weight"), float(eps))
     else:
         xa = (x.data_ptr(), x.stride(0), None, 0, None, 0, 0.0)
+    if streamed:
+        rc = ops._fn("sm100", "rllm_stream_gemm_qkv_rope")(
+            *xa, w_qkv.data_ptr(), out.data_ptr(), out.stride(0), T, K, positions.data_ptr(),
+            inv_freq.data_ptr(), ops._ptr(table), ops._ptr(slots), ops._ptr(kcache) if slots is not None else None,
+            ops._ptr(vcache) if slots is not None else None, nh, nkv, hd, page_size, st.sm_count, ops._stream())
+        ops._check(rc, "stream_gemm_qkv_rope")
+        return out
     rc = ops._fn("sm100", "rllm_tc_gemm_qkv_rope")(
         *xa, w_qkv.data_ptr(), out.data_ptr(), out.stride(0), T, K, positions.data_ptr(),
         inv_freq.data_ptr(), ops._ptr(table), ops._ptr(slots), ops._ptr(kcache) if slots is not None else None,
