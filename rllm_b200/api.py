@@ -9,6 +9,7 @@ mirrors the reference's `InferenceEngine::step` loop (src/engine/mod.rs:82-117):
 from __future__ import annotations
 
 import os
+import warnings
 
 import torch
 from dataclasses import replace
@@ -44,6 +45,7 @@ class LLM:
         self._pinned = []                        # host buffers the drawn tokens are copied into, in turn
         self.run_ahead = os.environ.get("RLLM_B200_NO_RUN_AHEAD") != "1"
         self.steps_ahead = 0
+        self._warned_positions = False
 
     # ---- the reference's engine loop
     def add_request(self, prompt_token_ids: list[int], params: SamplingParams | None = None) -> int:
@@ -51,6 +53,19 @@ class LLM:
         unless its parameters name others or say `ignore_eos`, as the reference's engine stops
         at its tokenizer's list (src/engine/mod.rs:694-699)."""
         params = params or SamplingParams()
+        # positions the configuration does not allow are not run: a prompt that is too long is
+        # refused, a generation is cut where the positions end (finish reason "length")
+        limit = getattr(self.engine.model.config, "max_position_embeddings", None)
+        if limit is not None:
+            if len(prompt_token_ids) >= limit:
+                raise ValueError(f"the prompt has {len(prompt_token_ids)} tokens, the model's "
+                                 f"max_position_embeddings is {limit}")
+            if len(prompt_token_ids) + params.max_tokens > limit:
+                if not self._warned_positions:
+                    self._warned_positions = True
+                    warnings.warn(f"prompt + max_tokens exceeds max_position_embeddings {limit}: "
+                                  f"the generation is cut there", stacklevel=2)
+                params = replace(params, max_tokens=limit - len(prompt_token_ids))
         eos = getattr(self.engine.model.config, "eos_token_ids", ())
         if eos and not params.eos_token_ids and not params.ignore_eos:
             params = replace(params, eos_token_ids=tuple(eos))

@@ -66,6 +66,9 @@ def _load(a, max_active: int):
         llm.model_dir = a.model
     llm.warm_up()          # modules loaded, a first graph captured: the first request is not the slow one
     print(f"[rllm] model loaded in {time.time() - t0:.1f}s", file=sys.stderr)
+    if not getattr(llm.engine.model.config, "eos_token_ids", ()):
+        print("[rllm] the model folder names no end-of-sequence id (config.json / generation_config.json): "
+              "generations run to --max-tokens", file=sys.stderr)
     return llm
 
 

@@ -95,6 +95,19 @@ def load_config(model_dir: str) -> tuple[Architecture, ModelConfig]:
             raise ConfigError(f"{path}: not valid JSON ({e})") from e
     if not isinstance(raw, dict):
         raise ConfigError(f"{path}: top level must be an object")
+    # special token ids may stand in generation_config.json instead (checkpoints of the Llama 3
+    # family keep the list of end tokens there)
+    gen = os.path.join(model_dir, "generation_config.json")
+    if os.path.isfile(gen):
+        try:
+            with open(gen) as f:
+                extra = json.load(f)
+        except json.JSONDecodeError as e:
+            raise ConfigError(f"{gen}: not valid JSON ({e})") from e
+        if isinstance(extra, dict):
+            for key in ("bos_token_id", "eos_token_id"):
+                if raw.get(key) is None and extra.get(key) is not None:
+                    raw[key] = extra[key]
     return config_from_dict(raw)
 
 

@@ -7,10 +7,10 @@ and `layer_norm_epsilon`. Where the reference silently defaults a missing
 `rope_theta` / eps to 0 we default to 10000 / 1e-5 instead. `sliding_window`
 with `layer_types` (src/model/config.rs:553-558, 970-985) is honoured when
 present, so one model may mix full and windowed attention layers.
-`bos_token_id` and `eos_token_id` (a number or a list) are read where config.json
-has them; without them a model with the Llama 3 vocabulary of 128,256 entries
-gets the ids the reference hard-codes for the family (src/model/tokenizer.rs:64-65:
-BOS 128000, stop on 128001 and 128009), any other model none.
+`bos_token_id` and `eos_token_id` (a number or a list) are read where config.json has
+them (`load_config` takes them from a generation_config.json beside it when config.json
+has none); a model that names none has none. The reference hard-codes the Llama 3 ids in
+its tokenizer wrapper (src/model/tokenizer.rs:64-65); here no id stands in code.
 """
 from __future__ import annotations
 
@@ -156,8 +156,6 @@ class LlamaConfig(ModelConfig):
             eos = []
         elif isinstance(eos, int) and not isinstance(eos, bool):
             eos = [eos]
-        if bos is None and not eos and "bos_token_id" not in raw and "eos_token_id" not in raw and V == 128256:
-            bos, eos = 128000, [128001, 128009]
         if bos is not None and (isinstance(bos, bool) or not isinstance(bos, int) or not 0 <= bos < V):
             raise ConfigError(f"bos_token_id must be a token id below vocab_size {V}, got {bos!r}")
         if not isinstance(eos, (list, tuple)) or any(isinstance(t, bool) or not isinstance(t, int) or not 0 <= t < V

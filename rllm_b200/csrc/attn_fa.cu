@@ -63,6 +63,8 @@ struct FaParams {
   float scale_log2e;
   float* part_o;      // [(token * nh + head) * splits + z][HD]
   float* part_ml;     // [(token * nh + head) * splits + z][2]
+  long long part_rows;   // rows the two buffers above have: a row index beyond it (a cu_q that names more
+                         // tokens than the caller said) is skipped, never written
 };
 
 template <int HD, int NWARPS>
@@ -107,7 +109,7 @@ fa_paged_kernel(const FaParams p) {
 
   // this thread's two rows (A: quad, B: quad + 8 of the warp's 16)
   int rowA = tile * BM + warp * 16 + quad, rowB = rowA + 8;
-  const bool vA = rowA < rows_total, vB = rowB < rows_total;
+  bool vA = rowA < rows_total, vB = rowB < rows_total;
   const int tokA = vA ? rowA / G : 0, tokB = vB ? rowB / G : 0;
   const int headA = kvh * G + (vA ? rowA % G : 0), headB = kvh * G + (vB ? rowB % G : 0);
   const int posA = kv_len - q_len + tokA, posB = kv_len - q_len + tokB;
@@ -282,6 +284,8 @@ fa_paged_kernel(const FaParams p) {
   } else {
     const size_t ia = ((size_t)(q0 + tokA) * p.nh + headA) * p.splits + z;
     const size_t ib = ((size_t)(q0 + tokB) * p.nh + headB) * p.splits + z;
+    vA = vA && ia < (size_t)p.part_rows;
+    vB = vB && ib < (size_t)p.part_rows;
 #pragma unroll
     for (int dn = 0; dn < DTILES; ++dn) {
       const int d = dn * 8 + qi * 2;
@@ -323,11 +327,13 @@ template <int HD, int NWARPS>
 int launch_fa(const FaParams& p, int num_seqs, int max_rows, cudaStream_t s) {
   constexpr int BM = 16 * NWARPS;
   constexpr int SMEM = 4 * BN * HD * 2;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};             // the attribute belongs to a device's copy of the kernel
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return -5; }
+  if (!configured[dev]) {
     if (cudaFuncSetAttribute(fa_paged_kernel<HD, NWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              SMEM) != cudaSuccess) { cudaGetLastError(); return -5; }
-    configured = true;
+    configured[dev] = true;
   }
   dim3 grid((max_rows + BM - 1) / BM, p.nkv * p.splits, num_seqs);
   if (grid.y > 65535 || grid.z > 65535) return ERR_TOO_LARGE;
@@ -358,6 +364,7 @@ RLLM_API int rllm_attention_fa(const void* q, int q_stride, const void* kcache, 
   p.page_shift = -1;
   if ((page_size & (page_size - 1)) == 0) { p.page_shift = 0; while ((1 << p.page_shift) < page_size) ++p.page_shift; }
   p.part_o = part_o; p.part_ml = part_ml;
+  p.part_rows = (long long)num_tokens * nh * splits;
   cudaStream_t s = (cudaStream_t)stream;
   const int G = nh / nkv;
   const int max_rows = max_q_len * G;

@@ -21,6 +21,8 @@
 //    (at most RLLM_NOALLOC_PART_O_FLOATS) and num_tokens * nh * splits * 2 floats for the
 //    statistics (at most RLLM_NOALLOC_PART_ML_FLOATS). A larger problem is refused with
 //    ERR_TOO_LARGE (-4) before anything is launched. With splits == 1 no scratch is used.
+//  * cu_q[num_seqs] must equal num_tokens: the size check above is made from num_tokens. Rows that
+//    cu_q names beyond it are left out of the sum rather than written past the array.
 //  * The first call on each device looks up the array's device address
 //    (cudaGetSymbolAddress) with that device current, and remembers it. Make that first call
 //    outside any stream capture; `stream` must belong to the current device.

@@ -71,6 +71,7 @@ class Engine:
         self.steps_run = 0
         self.graph_steps = 0
         self.h2d_bytes = 0            # bytes of step metadata copied to the device so far
+        self._opened: list = []
         if use_graphs is None:
             use_graphs = os.environ.get("RLLM_B200_NO_GRAPHS") != "1"
         self.graphs = None
@@ -124,7 +125,8 @@ class Engine:
                                     f"{len(e.tokens)} tokens")
 
     def prepare(self, entries: list[Entry]):
-        """Reserve pages for every entry (all or nothing) and build the step's metadata."""
+        """Reserve pages for every entry (all or nothing). Returns the requests' holdings; the ids
+        of the requests this call opened are kept in `self._opened` until the step has run."""
         self._validate(entries)
         cache = self.cache
         opened, reserved = [], []
@@ -139,12 +141,20 @@ class Engine:
                 reserved.append(rc)
                 rcs.append(rc)
         except OutOfPages:
-            for rc in reserved:
-                cache.trim(rc)
-            for rid in opened:
-                cache.close(rid)
+            self._undo(reserved, opened)
             raise
+        self._opened = opened
         return rcs
+
+    def _undo(self, reserved, opened) -> None:
+        """A step that did not run to its end leaves every request as it was: reservations are
+        given back, requests it opened are closed."""
+        for rc in reserved:
+            if rc.handle >= 0:
+                self.cache.trim(rc)
+        for rid in opened:
+            if rid in self.cache.live:
+                self.cache.close(rid)
 
     def fill_meta(self, host: np.ndarray, lay: MetaLayout, entries: list[Entry], rcs) -> None:
         """Write the step's metadata into `host` (int32, `lay.total` long, preset to -1)."""
@@ -217,7 +227,8 @@ class Engine:
     def step(self, entries: list[Entry], keep: bool = True, feed: torch.Tensor | None = None) -> torch.Tensor | None:
         """Run one batch; returns float32 logits [wanted places, vocab] on the device, in
         the order of the entries and of each `want` (None if nothing is wanted).
-        Raises OutOfPages, leaving every request as it was, if the pages do not suffice.
+        Raises OutOfPages if the pages do not suffice; that, or any other error raised while the
+        batch runs, leaves every request as it was (nothing committed, reservations given back).
         `keep=False`: the caller reads the logits before the next step, so they may live
         in a buffer that the next step overwrites (saves a copy).
         `feed`: the entries' token ids as an int32 tensor on the device, one per entry (see
@@ -226,14 +237,19 @@ class Engine:
             raise StepError("token ids can be fed from the device only to a step that replays a graph")
         rcs = self.prepare(entries)
         logits = None
-        if self.graphs is not None and self.graphs.takes(entries, rcs):
-            logits = self.graphs.run(entries, rcs, keep, feed)
-            self.graph_steps += 1
-        else:
-            ctx, rows = self.build_context(entries, rcs)
-            h = self.model.forward(ctx, self.cache)
-            if rows.numel():
-                logits = self.model.logits(h, rows, ctx)
+        try:
+            if self.graphs is not None and self.graphs.takes(entries, rcs):
+                logits = self.graphs.run(entries, rcs, keep, feed)
+                self.graph_steps += 1
+            else:
+                ctx, rows = self.build_context(entries, rcs)
+                h = self.model.forward(ctx, self.cache)
+                if rows.numel():
+                    logits = self.model.logits(h, rows, ctx)
+        except BaseException:
+            # a refused size, a failed launch or capture: nothing is committed, the pages go back
+            self._undo(rcs, self._opened)
+            raise
         for e, rc in zip(entries, rcs):
             self.cache.commit(rc, rc.num_tokens + len(e.tokens))
         self.steps_run += 1

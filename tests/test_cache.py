@@ -208,3 +208,40 @@ def test_native_decode_metadata_rows_follow_their_holdings():
     assert fill([a, b2], [9, 9]) < 0
     L.rows_delete(rows)
     m.check()
+
+
+def test_a_step_that_fails_leaves_every_request_as_it_was():
+    """Whatever is raised while a step's batch runs (a refused size, a failed launch), nothing is
+    committed: reserved pages go back, and a request that the step opened is closed again."""
+    from rllm_b200.engine.step import Engine, Entry
+
+    class Backend:
+        device, fast = torch.device("cpu"), False
+
+    class Model:
+        vocab_size = 50
+
+        def parts(self):
+            return []
+
+    m = manager(pages=6, page=4, reqs=3)
+    eng = Engine(Model(), Backend(), m, use_graphs=False)
+    old = m.open("old")
+    m.reserve(old, 5)
+    m.commit(old, 5)
+    free, slots = m.free_pages(), m.slots.num_free
+
+    def boom(entries, rcs):
+        assert m.free_pages() != free            # the step had reserved its pages by then
+        raise RuntimeError("a kernel refused the size")
+
+    eng.build_context = boom
+    with pytest.raises(RuntimeError, match="refused"):
+        eng.step([Entry("old", [1, 2, 3, 4], [3]), Entry("new", [5, 6, 7, 8, 9], [])])
+    assert m.free_pages() == free and m.slots.num_free == slots
+    assert "new" not in m.live and old.num_tokens == 5
+    m.check()
+    with pytest.raises(OutOfPages):              # and the all-or-nothing rule as before
+        eng.step([Entry("old", [1] * 4, []), Entry("big", [2] * 40, [])])
+    assert m.free_pages() == free and "big" not in m.live
+    m.check()

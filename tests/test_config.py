@@ -108,9 +108,9 @@ def test_model_is_built_from_the_configuration_layer_by_layer():
 
 
 def test_special_token_ids():
-    """bos_token_id / eos_token_id as config.json has them (a number or a list); a model with the
-    Llama 3 vocabulary and neither key gets the family's ids, any other model none; ids beyond
-    the vocabulary are refused; an explicit null survives the round trip."""
+    """bos_token_id / eos_token_id as config.json has them (a number or a list); a model that names
+    none has none, whatever its vocabulary; ids beyond the vocabulary are refused; an explicit null
+    survives the round trip."""
     from rllm_b200.config import config_from_dict
     base = dict(tiny.TINY_A)
     _, c = config_from_dict(base)
@@ -120,7 +120,7 @@ def test_special_token_ids():
     _, c = config_from_dict(dict(base, eos_token_id=[3, 250]))
     assert (c.bos_token_id, c.eos_token_ids) == (None, (3, 250))
     _, c3 = config_from_dict(dict(base, vocab_size=128256))
-    assert (c3.bos_token_id, c3.eos_token_ids) == (128000, (128001, 128009))
+    assert (c3.bos_token_id, c3.eos_token_ids) == (None, ())
     _, again = config_from_dict(c.to_dict())
     assert again.eos_token_ids == (3, 250) and again.bos_token_id is None
     _, none = config_from_dict(dict(base, vocab_size=128256, bos_token_id=None, eos_token_id=None))
@@ -128,3 +128,17 @@ def test_special_token_ids():
     for bad in (dict(eos_token_id=256), dict(bos_token_id=-1), dict(eos_token_id="2"), dict(eos_token_id=[1, True])):
         with pytest.raises(ConfigError):
             config_from_dict(dict(base, **bad))
+
+
+def test_special_token_ids_from_generation_config(tmp_path):
+    """A folder whose config.json names no special ids takes them from generation_config.json
+    beside it; config.json's own win."""
+    import json
+    from rllm_b200.config import load_config
+    (tmp_path / "config.json").write_text(json.dumps(tiny.TINY_A))
+    (tmp_path / "generation_config.json").write_text(json.dumps({"bos_token_id": 5, "eos_token_id": [6, 7]}))
+    _, c = load_config(str(tmp_path))
+    assert (c.bos_token_id, c.eos_token_ids) == (5, (6, 7))
+    (tmp_path / "config.json").write_text(json.dumps(dict(tiny.TINY_A, eos_token_id=9)))
+    _, c = load_config(str(tmp_path))
+    assert (c.bos_token_id, c.eos_token_ids) == (5, (9,))

@@ -165,3 +165,68 @@ def test_long_prompt_whole_and_chosen_splits():
     assert sm100.attention_splits(8, 8, 4, 4096, 148) >= 8       # decode: cut until the GPU is full
     assert sm100.attention_splits(8, 8, 2048 * 4, 4096, 148) == 1  # prefill: tiles fill it already
     assert sm100.attention_splits(1, 8, 4, 100, 148) == 1          # too short to cut
+
+
+@pytest.mark.parametrize("kernel", ["fa", "decode", "tc"])
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("edge", ["in", "out"])
+@pytest.mark.parametrize("gave_back", [False, True])
+def test_window_edge_with_a_key_that_would_dominate(kernel, hd, edge, gave_back):
+    """The window's edge, made visible: the key at j = pos - window + 1 (the oldest the query may see)
+    is given a score that dominates, so the output must be its value; the key one further back gets
+    the same treatment and must leave no trace. Random scores would hide one key too many or too few
+    (it moves the output by about 1 / window). Single tokens for the decode kernels, and a portion
+    whose rows straddle the edge inside one key tile for the two prefill kernels; with `gave_back` the
+    pages that lie wholly before the window are gone from the block table (-1), as after the cache
+    manager has taken them back."""
+    from rllm_b200.kernels import sm100
+    nh, nkv, page, W = 8, 2, 8, 100
+    decode = kernel == "decode"
+    # (keys, rows of this step, row from the end whose query dominates)
+    seqs = [(300, 1, 0), (257, 1, 0)] if decode else [(400, 200, 89), (300, 1, 0), (700, 130, 5)]
+    lens, q_lens = [s[0] for s in seqs], [s[1] for s in seqs]
+    S = len(seqs)
+    kc, vc, bt, ks, vs = scattered_cache(S, lens, nkv, hd, page, torch.bfloat16, seed=hd + W)
+    g = torch.Generator().manual_seed(8)
+    T = sum(q_lens)
+    q = torch.randn(T, nh, hd, generator=g).to(torch.bfloat16)
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    marks = []
+    for s, (L, n, back) in enumerate(seqs):
+        pos = L - 1 - back
+        j = pos - W + 1 if edge == "in" else pos - W
+        ks[s][j] = 0
+        ks[s][j, :, 0] = 30.0
+        q[cu[s + 1] - 1 - back, :, 0] = 30.0
+        kc[int(bt[s, j // page]), :, j % page] = ks[s][j]
+        marks.append((cu[s + 1] - 1 - back, j))
+        if gave_back:
+            first_needed = max(0, (L - n) - W + 1)       # the oldest key the step's first row sees
+            bt[s, : first_needed // page] = -1
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    qd = q.reshape(T, nh * hd).to(DEV)
+    if kernel == "decode":
+        out = sm100.attention_decode(qd, kc.to(DEV), vc.to(DEV), i32(lens), bt.to(DEV), nh, hd ** -0.5, W, max(lens),
+                                     splits=2)
+    elif kernel == "tc":
+        out = sm100.attention_prefill_tc(qd, kc.to(DEV), vc.to(DEV), i32(cu), i32(lens), bt.to(DEV), max(q_lens), nh,
+                                         hd ** -0.5, W)
+    else:
+        out = sm100.attention_fa(qd, kc.to(DEV), vc.to(DEV), i32(cu), i32(lens), bt.to(DEV), T, max(q_lens), max(lens),
+                                 nh, hd ** -0.5, W, splits=1)
+    sm100.check_error(DEV)
+    for s, (L, n, back) in enumerate(seqs):
+        qf = torch.zeros(L, nh, hd); qf[L - n:] = q[cu[s]: cu[s + 1]].float()
+        ref = P.attention(qf, ks[s].float(), vs[s].float(), hd ** -0.5, W)[L - n:]
+        got = out[cu[s]: cu[s + 1]].float().cpu().view(n, nh, hd)
+        assert torch.isfinite(got).all()
+        assert rel(got, ref) <= TOL, f"sequence {s} (len {L}, q {n})"
+        row, j = marks[s]
+        mine = out[row].float().cpu().view(nh, hd)
+        vj = vs[s][j].float().repeat_interleave(nh // nkv, 0)
+        if edge == "in":
+            assert rel(mine, vj) <= TOL, f"sequence {s}: the oldest visible key was not seen"
+        else:
+            assert rel(mine, vj) > 0.1, f"sequence {s}: a key beyond the window was seen"

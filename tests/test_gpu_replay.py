@@ -12,11 +12,11 @@ import tiny
 
 pytestmark = pytest.mark.gpu
 
-# Largest error relative to the largest logit. 32-bit: only summation order differs
-# (measured 2e-6 or less on these models). bfloat16: weights are the same bfloat16
-# values in both, activations and cache are rounded to 8 bits of mantissa at every
-# layer boundary (measured up to 1.2e-2 on these models).
-TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+# Largest error at a position relative to that position's own largest logit. 32-bit: only
+# summation order differs (measured 1.3e-6 or less on these models). bfloat16: weights are the
+# same bfloat16 values in both, activations and cache are rounded to 8 bits of mantissa at
+# every layer boundary (measured up to 1.0e-2 on these models).
+TOL = {"float32": 2e-5, "bfloat16": 1.5e-2}
 
 # D and E have the head sizes of the tensor-core attention kernels; their long requests span
 # several key tiles, key ranges and pages, and a window's edge.
@@ -63,7 +63,7 @@ def test_family_matches_plain(model_dirs, plain, name, dtype, family):
     # a pool just large enough, so pages of finished requests are used again
     eng = engine_for(model_dirs[name], name, dtype, replay.max_live_tokens(steps, reqs))
     got = replay.run_in_process(eng, steps)
-    worst = replay.compare(got, plain[name], TOL[dtype], f"tiny-{name} {dtype} {family}")
+    worst = replay.compare(got, plain[name], TOL[dtype], f"tiny-{name} {dtype} {family}", per_position=True)
     assert all(n == eng.cache.groups[0].pool.num_pages for n in eng.cache.free_pages())
     print(f"tiny-{name} {dtype} {family}: worst relative error {worst:.2e}")
 
@@ -83,7 +83,8 @@ def test_family_with_the_tcgen05_prefill_attention(model_dirs, plain, name, fami
     steps = FAMILIES[family](reqs)
     eng = engine_for(model_dirs[name], name, "bfloat16", replay.max_live_tokens(steps, reqs))
     got = replay.run_in_process(eng, steps)
-    replay.compare(got, plain[name], TOL["bfloat16"], f"tiny-{name} bfloat16 {family} (tcgen05 attention)")
+    replay.compare(got, plain[name], TOL["bfloat16"], f"tiny-{name} bfloat16 {family} (tcgen05 attention)",
+                   per_position=True)
     if family in ("whole", "prefill_then_decode"):      # the other families' portions may all be under 128 rows
         assert calls, "the tcgen05 prefill kernel was not used"
 
@@ -114,7 +115,8 @@ def test_long_portions_beside_decode_tokens(model_dirs, plain, name, monkeypatch
     before = dict(used)
     got = replay.run_in_process(eng, steps)
     want = {k: v for k, v in plain[name].items() if k[0] in (a, b, c, d)}
-    replay.compare(got, want, TOL["bfloat16"], f"tiny-{name} bfloat16 portions beside decode tokens")
+    replay.compare(got, want, TOL["bfloat16"], f"tiny-{name} bfloat16 portions beside decode tokens",
+                   per_position=True)
     # steps 2 and 3 each went to both kernels, in every layer
     layers = tiny.TINY[name][0]["num_hidden_layers"]
     assert used["tc"] - before["tc"] >= 4 * layers and used["decode"] - before["decode"] >= 3 * layers
@@ -147,4 +149,4 @@ def test_trace_run_program(model_dirs, plain, tmp_path, dtype):
     got = replay.run_program(model_dirs[name], dtype, steps, str(tmp_path / "out"),
                              replay.max_live_tokens(steps, reqs), vocab,
                              extra_args=["--page-size", str(tiny.TINY[name][4])])
-    replay.compare(got, plain[name], TOL[dtype], f"trace_run {dtype}")
+    replay.compare(got, plain[name], TOL[dtype], f"trace_run {dtype}", per_position=True)
