@@ -171,7 +171,8 @@ class LLM:
         are loaded, their attributes set, the first decode graph is captured. The first real
         request then costs what every later one costs."""
         vocab = self.engine.vocab
-        n = max(1, min(prompt_len, self.scheduler.max_tokens_per_step,
+        limit = getattr(self.engine.model.config, "max_position_embeddings", None) or prompt_len + 8
+        n = max(1, min(prompt_len, self.scheduler.max_tokens_per_step, limit - 8,
                        (min(self.engine.cache.free_pages()) - 1) * self.engine.cache.page_size - 8))
         prompt = [(7 * i + 1) % vocab for i in range(n)]
         self.generate([prompt], SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))

@@ -350,6 +350,29 @@ RLLM_API int rllm_add_into(float* res, const void* delta, int dt, long long n, v
   return rc;
 }
 
+// y[t, n] += bias[n] in place, the sum formed in float (y and bias of one type, float or bf16):
+// the bias of a projection whose product ran without one (src/model/primitives.rs:60-83 adds it
+// the same way, after the product).
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ y, const T* __restrict__ bias, int rows, int N, long long ld) {
+  pdl_launch();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)rows * N) return;
+  const int n = (int)(i % N);
+  T* p = y + (size_t)(i / N) * ld + n;
+  *p = from_f32<T>(to_f32(*p) + to_f32(bias[n]));
+}
+RLLM_API int rllm_add_bias(void* y, const void* bias, int dt, int rows, int N, long long ld, void* stream) {
+  if (rows <= 0 || N <= 0) return 0;
+  const int threads = 256;
+  const unsigned blocks = (unsigned)(((size_t)rows * N + threads - 1) / threads);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dt == DT_F32) return launch_ex(add_bias_kernel<float>, dim3(blocks), dim3(threads), 0, s, 1, (float*)y, (const float*)bias, rows, N, ld);
+  if (dt == DT_BF16) return launch_ex(add_bias_kernel<bf16>, dim3(blocks), dim3(threads), 0, s, 1, (bf16*)y, (const bf16*)bias, rows, N, ld);
+  return ERR_BAD_DTYPE;
+}
+
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i]   (reference: elementwise.cu:36-49)
 template <typename T>
 __global__ void silu_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t n) {

@@ -90,8 +90,10 @@ class Backend:
         if bias is None and self._fused_norm(x, w):
             return self._sm100.gemm_norm(x.h, x.weight, x.eps, w, ops.EPI_STORE, rows=x.rows)
         x = x.tensor() if isinstance(x, Normed) else x
-        if bias is None and self._tc(x, w):
-            return self._sm100.gemm(x, w, ops.EPI_STORE)
+        if self._tc(x, w):
+            # a bias is added after the product (a small kernel): the product stays on the tensor cores
+            y = self._sm100.gemm(x, w, ops.EPI_STORE)
+            return y if bias is None else ops.add_bias(y, bias)
         return ops.gemm_simt(x, w, ops.EPI_STORE, bias=bias)
 
     def linear_f32(self, x, w):

@@ -37,6 +37,7 @@ _SIGS = {
         "rllm_gather_rows": [_P, _P, _P, c_int, c_int, _P],
         "rllm_step_meta": [_P, _P, c_int, _P, c_int, _P],
         "rllm_add_into": [_P, _P, c_int, c_longlong, _P],
+        "rllm_add_bias": [_P, _P, c_int, c_int, c_int, c_longlong, _P],
         "rllm_silu_gate": [_P, _P, c_int, c_int, c_int, _P],
         "rllm_gemm_simt": [c_int, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
         "rllm_paged_attention_simt": [c_int, _P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int,
@@ -208,6 +209,17 @@ def add_into(residual: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     _check(_fn("simt", "rllm_add_into")(residual.data_ptr(), delta.data_ptr(), _dt(delta, "delta"),
                                         residual.numel(), _stream()), "add_into")
     return residual
+
+
+def add_bias(y: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """y [T, N] += bias [N], in place; both float32 or both bfloat16."""
+    _cuda(y, "y"); _cuda(bias, "bias")
+    if y.dim() != 2 or y.stride(1) != 1 or bias.dtype != y.dtype or bias.shape != (y.shape[1],) \
+            or not bias.is_contiguous():
+        raise KernelError("add_bias takes y [T, N] with unit inner stride and a bias [N] of the same dtype")
+    _check(_fn("simt", "rllm_add_bias")(y.data_ptr(), bias.data_ptr(), _dt(y, "y"), y.shape[0], y.shape[1],
+                                        y.stride(0), _stream()), "add_bias")
+    return y
 
 
 def silu_gate(gu: torch.Tensor) -> torch.Tensor:

@@ -44,9 +44,10 @@ class GQAttention(Part):
                               Source("v_proj.weight", (KV, H)))),
               Param("w_o", (Source("o_proj.weight", (H, Q)),))]
         if self.bias:
-            ps.append(Param("b_qkv", (Source("q_proj.bias", (Q,), init="zeros"),
-                                      Source("k_proj.bias", (KV,), init="zeros"),
-                                      Source("v_proj.bias", (KV,), init="zeros"))))
+            # random-weights mode draws them like the matrices: a bias of zeros would hide a
+            # kernel that drops it
+            ps.append(Param("b_qkv", (Source("q_proj.bias", (Q,)), Source("k_proj.bias", (KV,)),
+                                      Source("v_proj.bias", (KV,)))))
         return ps
 
     def cache_spec(self):

@@ -166,6 +166,31 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
     return out
 
 
+def attention_tail(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
+                   window: int | None = None) -> torch.Tensor:
+    """The same formula for the last n positions only: q [n, nh, hd] are the queries at positions
+    L-n .. L-1 of a sequence whose keys and values k, v [L, nkv, hd] are all given. Equal to
+    `attention` over the whole sequence, cut to its last n rows, without the L x L scores (for
+    sequences of many thousand keys). src/gpu/cuda/shaders/attention.cu:328-388."""
+    n, nh, hd = q.shape
+    L, nkv = k.shape[0], k.shape[1]
+    g = nh // nkv
+    out = torch.empty_like(q)
+    qpos = torch.arange(L - n, L)
+    kpos = torch.arange(L)
+    mask = kpos[None, :] <= qpos[:, None]
+    if window:
+        mask &= kpos[None, :] > (qpos[:, None] - window)
+    for h in range(nh):
+        kh, vh = k[:, h // g], v[:, h // g]
+        s = (q[:, h] @ kh.t()) * scale
+        s = s.masked_fill(~mask, float("-inf"))
+        s = s - s.max(dim=-1, keepdim=True).values
+        e = torch.exp(s)
+        out[:, h] = (e / e.sum(dim=-1, keepdim=True)) @ vh
+    return out
+
+
 def swiglu(x: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, wd: torch.Tensor) -> torch.Tensor:
     """g = Wg x, u = Wu x, a = g/(1+exp(-g)) * u, y = Wd a.
     src/gpu/cuda/shaders/moe.cu:141-146; src/gpu/cuda/shaders/elementwise.cu:36-49;

@@ -94,6 +94,36 @@ def test_pages_running_out_preempts_and_output_is_unchanged(dirs):
     assert tight.engine.cache.free_pages() == [12]
 
 
+def test_preemption_and_temperature_in_bfloat16(dirs):
+    """The two tests above once on the serving path. bfloat16 rounds differently from step shape to
+    step shape, so outputs are not compared with each other but each with the plain implementation
+    on its own history: a greedy token must be the plain argmax or within the bfloat16 tolerance of
+    it, a drawn token's interval of the plain cumulative distribution must hold the request's
+    uniform number to within what that tolerance moves the distribution."""
+    from rllm_b200.sampling import SamplingParams, uniform
+    name = "B"
+    cfg, w = P.read_model_dir(dirs[name])
+    prompts = [tiny.random_prompt(n, cfg["vocab_size"], 31 + n) for n in (20, 22, 18)]
+    tight = llm(dirs[name], name, "bfloat16", num_pages=12)          # 96 positions for 3 x ~50
+    outs = tight.generate(prompts, SamplingParams(temperature=0.0, max_tokens=30))
+    assert tight.scheduler.preempted_total > 0
+    tight.engine.cache.check()
+    assert tight.engine.cache.free_pages() == [12]
+    for p, o in zip(prompts, outs):
+        assert len(o) == 30
+        lg = P.forward(cfg, w, p + o[:-1])[len(p) - 1:]
+        for i, tok in enumerate(o):
+            assert float(lg[i].max() - lg[i, tok]) <= 3e-2 * float(lg[i].abs().max()), (i, tok)
+    sps = [SamplingParams(temperature=0.8, max_tokens=12, seed=100 + i) for i in range(3)]
+    outs = llm(dirs[name], name, "bfloat16", num_pages=64, max_tokens_per_step=9, max_chunk=7).generate(prompts, sps)
+    for p, o, sp in zip(prompts, outs, sps):
+        for i, tok in enumerate(o):
+            cdf = torch.cumsum(P.sample_probs(P.forward(cfg, w, p + o[:i])[-1], 0.8).double(), 0)
+            u = uniform(sp.seed, i)
+            lo = float(cdf[tok - 1]) if tok else 0.0
+            assert lo - 2e-2 <= u <= float(cdf[tok]) + 2e-2, (i, tok, u)
+
+
 @pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 3e-2)])
 def test_long_decoding_and_first_tokens(dirs, dtype, tol):
     """250 tokens decoded one by one after a 3-token prompt (the window of model C passes

@@ -298,3 +298,18 @@ def test_kernels_refuse_what_they_cannot_take():
     z = torch.zeros(1, dtype=torch.int32, device=DEV)
     with pytest.raises(o.KernelError):
         o.paged_attention_simt(q, kc, kc, z, z, z.view(1, 1), 2, 1.0, None)
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_add_bias_in_place_on_a_strided_view(dtype):
+    from rllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(2)
+    big = torch.randn(9, 150, generator=g).to(DT[dtype])
+    b = torch.randn(70, generator=g).to(DT[dtype])
+    d = big.to(DEV)
+    ops.add_bias(d[:, 40:110], b.to(DEV))
+    want = big.clone()
+    want[:, 40:110] = (big[:, 40:110].float() + b.float()).to(DT[dtype])
+    assert torch.equal(d.cpu(), want)
+    with pytest.raises(ops.KernelError):
+        ops.add_bias(d[:, :70], b.float().to(DEV) if dtype != "float32" else b.to(torch.bfloat16).to(DEV))

@@ -21,7 +21,7 @@ TOL = {"float32": 2e-5, "bfloat16": 1.5e-2}
 # D and E have the head sizes of the tensor-core attention kernels; their long requests span
 # several key tiles, key ranges and pages, and a window's edge.
 LENGTHS = {"A": [5, 11, 17, 40, 70], "B": [3, 9, 24, 40, 97], "C": [6, 33, 58, 90, 121],
-           "D": [4, 70, 131, 300, 65], "E": [9, 150, 64, 257, 33]}
+           "D": [4, 70, 131, 300, 65], "E": [9, 150, 64, 257, 33], "F": [7, 90, 35, 140, 2]}
 
 
 def requests_for(name):

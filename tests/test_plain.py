@@ -103,3 +103,13 @@ def test_plain_bias_and_logprobs():
     y = P.adjust_logits(x, [2, 2, 5], frequency_penalty=0.5, presence_penalty=1.0, logit_bias={5: 3.0, 99: 1.0})
     want = x.clone(); want[2] -= 2.0; want[5] += 3.0 - 1.5
     assert torch.allclose(y, want)
+
+
+def test_attention_tail_is_the_whole_formula_cut_to_its_last_rows():
+    g = torch.Generator().manual_seed(3)
+    L, nh, nkv, hd = 45, 6, 2, 16
+    q, k, v = (torch.randn(L, h, hd, generator=g) for h in (nh, nkv, nkv))
+    for window in (None, 7, 100):
+        full = P.attention(q, k, v, 0.3, window)
+        for n in (1, 5, L):
+            assert torch.allclose(P.attention_tail(q[L - n:], k, v, 0.3, window), full[L - n:], atol=1e-6)

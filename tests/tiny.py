@@ -48,6 +48,13 @@ TINY_E = {  # head size 128, 4 heads on 1 kv head (group of 4), hidden 136 != he
     "rms_norm_eps": 2e-6, "tie_word_embeddings": True, "sliding_window": 80,
     "layer_types": ["full_attention", "sliding_attention"],
 }
+TINY_F = {  # biases on q, k, v (drawn non-zero); full multi-head attention (4 kv heads), head 64, hidden 128
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 128, "num_hidden_layers": 2, "num_attention_heads": 4,
+    "num_key_value_heads": 4, "head_dim": 64, "intermediate_size": 288, "vocab_size": 300,
+    "max_position_embeddings": 512, "rope_theta": 10000.0, "rope_scaling": None,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "attention_bias": True,
+}
 
 # name -> (config, seed, weight std, norm std, page size)
 TINY = {
@@ -56,6 +63,7 @@ TINY = {
     "C": (TINY_C, 2, 0.08, 0.2, 4),
     "D": (TINY_D, 3, 0.04, 0.1, 16),
     "E": (TINY_E, 4, 0.05, 0.0, 8),
+    "F": (TINY_F, 5, 0.06, 0.1, 16),
 }
 
 
