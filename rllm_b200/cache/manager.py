@@ -1,11 +1,13 @@
 """The cache manager: paged keys/values with a block table per request, one page pool per
 group of layers with equal needs, and slots of fixed-size per-request state.
 
-Layers are grouped by their `KVCacheSpec` (kv heads, head size, window). Each group has
-pages of its own: a group that keeps every key grows with the request, a group with a
-window gives pages back as soon as the window has passed them, and the pages of a request
-that ends return at once and are handed out again. State layers (`StateSpec`) get one slot
-per live request from a slot pool, zeroed when the request opens; Llama has none, the pool
+How a layer's need is served is looked up by the class of its spec (`parts.base.CacheKind`,
+`register_cache_kind`); the manager knows no spec class by name. Layers of a paged kind are
+grouped by equal specs (`KVCacheSpec`: kv heads, head size, window). Each group has pages of its
+own, and a pool of its own size: a group that keeps every key grows with the request, a group
+with a window gives pages back as soon as the window has passed them, and the pages of a request
+that ends return at once and are handed out again. Layers of a slot kind (`StateSpec`) get one
+slot per live request from a slot pool, zeroed when the request opens; Llama has none, the pool
 then has no tensors.
 
 The bookkeeping (pools, tables, state slots) is native: csrc/host_runtime.cpp.
@@ -23,18 +25,25 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
-from ..parts.base import KVCacheSpec, LayerCache, StateSpec
+from ..parts.base import LayerCache, cache_kind_of
 from .native import lib
 from .pages import CacheError, Holders, OutOfPages, PagePool
 
 
 @dataclass
 class CacheGroup:
-    spec: KVCacheSpec
+    spec: object
     layers: list[int]
     pool: PagePool
-    k: dict[int, torch.Tensor] = field(default_factory=dict)
-    v: dict[int, torch.Tensor] = field(default_factory=dict)
+    tensors: dict[int, dict[str, torch.Tensor]] = field(default_factory=dict)    # layer -> name -> tensor
+
+    @property
+    def k(self) -> dict[int, torch.Tensor]:
+        return {layer: t["k"] for layer, t in self.tensors.items() if "k" in t}
+
+    @property
+    def v(self) -> dict[int, torch.Tensor]:
+        return {layer: t["v"] for layer, t in self.tensors.items() if "v" in t}
 
 
 class RequestCache:
@@ -86,22 +95,30 @@ def pages_for(tokens: int, page_size: int) -> int:
 
 
 class CacheManager:
-    def __init__(self, specs: list, page_size: int, num_pages: int, max_requests: int,
+    def __init__(self, specs: list, page_size: int, num_pages, max_requests: int,
                  dtype: torch.dtype, device, allocate: bool = True):
+        """`num_pages`: pages of every group's pool, or a mapping spec -> pages for groups that
+        differ (a spec it does not name gets what its kind's `num_pages` makes of the largest)."""
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size, self.dtype, self.device = page_size, dtype, device
         self.max_requests = max_requests
         self.groups: list[CacheGroup] = []
         self.layer_group: dict[int, int] = {}
-        self.state_layers: dict[int, StateSpec] = {}
+        self.state_layers: dict[int, object] = {}
         self.state: dict[int, dict[str, torch.Tensor]] = {}
-        group_specs: list[KVCacheSpec] = []
+        group_specs: list = []
         group_layers: list[list[int]] = []
         for layer, spec in enumerate(specs):
-            if isinstance(spec, KVCacheSpec):
+            if spec is None:
+                continue
+            try:
+                kind = cache_kind_of(spec)
+            except TypeError as e:
+                raise TypeError(f"cache layer {layer}: {e}") from None
+            if kind.paged:
                 for gi, gs in enumerate(group_specs):
-                    if gs == spec:
+                    if type(gs) is type(spec) and gs == spec:
                         group_layers[gi].append(layer)
                         self.layer_group[layer] = gi
                         break
@@ -109,32 +126,33 @@ class CacheManager:
                     self.layer_group[layer] = len(group_specs)
                     group_specs.append(spec)
                     group_layers.append([layer])
-            elif isinstance(spec, StateSpec):
+            else:
                 self.state_layers[layer] = spec
-            elif spec is not None:
-                raise TypeError(f"cache layer {layer}: unknown spec {spec!r}")
+        by_spec = num_pages if isinstance(num_pages, dict) else {}
+        default = max(by_spec.values(), default=0) if isinstance(num_pages, dict) else int(num_pages)
+        pages_of = [int(by_spec[gs]) if gs in by_spec else int(cache_kind_of(gs).num_pages(gs, default))
+                    for gs in group_specs]
         # the native tables: one pool per group, the state slots, every holding
         self._L = lib()
         G = len(group_specs)
-        counts = (ctypes.c_int * max(G, 1))(*([num_pages] * G))
-        windows = (ctypes.c_int * max(G, 1))(*[(-1 if gs.window is None else gs.window) for gs in group_specs])
+        counts = (ctypes.c_int * max(G, 1))(*pages_of)
+        windows = (ctypes.c_int * max(G, 1))(*[(-1 if cache_kind_of(gs).window(gs) is None else cache_kind_of(gs).window(gs))
+                                               for gs in group_specs])
         self._ptr = self._L.cache_new(G, counts, windows, page_size, max_requests)
         if not self._ptr:
             raise ValueError("the native cache tables could not be made")
         self.holders = Holders()
         for gi, (gs, layers) in enumerate(zip(group_specs, group_layers)):
-            pool = PagePool(num_pages, _ptr=self._L.cache_pool(self._ptr, gi), _holders=self.holders, _owner=self)
+            pool = PagePool(pages_of[gi], _ptr=self._L.cache_pool(self._ptr, gi), _holders=self.holders, _owner=self)
             self.groups.append(CacheGroup(gs, layers, pool))
         self.slots = PagePool(max_requests, _ptr=self._L.cache_slots(self._ptr), _holders=self.holders, _owner=self)
         if allocate:
             for g in self.groups:
-                shape = (num_pages, g.spec.kv_heads, page_size, g.spec.head_dim)
+                kind = cache_kind_of(g.spec)
                 for layer in g.layers:
-                    g.k[layer] = torch.zeros(shape, dtype=dtype, device=device)
-                    g.v[layer] = torch.zeros(shape, dtype=dtype, device=device)
+                    g.tensors[layer] = kind.allocate(g.spec, g.pool.num_pages, page_size, dtype, device)
             for layer, spec in self.state_layers.items():
-                self.state[layer] = {name: torch.zeros((max_requests,) + tuple(shape), dtype=dt, device=device)
-                                     for name, shape, dt in spec.tensors}
+                self.state[layer] = cache_kind_of(spec).allocate(spec, max_requests, None, dtype, device)
         self.live: dict[object, RequestCache] = {}
 
     def __del__(self):
@@ -145,8 +163,9 @@ class CacheManager:
     # ------------------------------------------------------------ sizes
     @staticmethod
     def bytes_per_page(specs: list, page_size: int, dtype: torch.dtype) -> int:
-        per = torch.empty((), dtype=dtype).element_size()
-        return sum(2 * s.kv_heads * s.head_dim * page_size * per for s in specs if isinstance(s, KVCacheSpec))
+        """Bytes one page costs over all paged layers (each layer has the page in its own tensors)."""
+        return sum(cache_kind_of(s).page_bytes(s, page_size, dtype) for s in specs
+                   if s is not None and cache_kind_of(s).paged)
 
     def free_pages(self) -> list[int]:
         return [g.pool.num_free for g in self.groups]
@@ -238,11 +257,13 @@ class CacheManager:
 
     def layer_view(self, cache_layer: int, ctx, writes: bool = True) -> LayerCache:
         if cache_layer in self.state_layers:
-            return LayerCache(self.state_layers[cache_layer], state=self.state[cache_layer], writes=writes)
+            return LayerCache(self.state_layers[cache_layer], state=self.state[cache_layer], writes=writes,
+                              tensors=self.state[cache_layer])
         gi = self.layer_group[cache_layer]
         g, view = self.groups[gi], ctx.groups[gi]
-        return LayerCache(g.spec, self.page_size, g.k[cache_layer], g.v[cache_layer], view.slots,
-                          view.block_table, writes)
+        t = g.tensors[cache_layer]
+        return LayerCache(g.spec, self.page_size, t.get("k"), t.get("v"), view.slots, view.block_table, writes,
+                          tensors=t)
 
     # ------------------------------------------------------------ checks (tests, debug)
     def check(self) -> None:

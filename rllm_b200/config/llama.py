@@ -19,49 +19,52 @@ from typing import Any
 
 from .base import ConfigError, ModelConfig, require_float, require_int
 
-_ROPE_TYPES = ("default", "llama3", "linear")
-
-
 @dataclass(frozen=True)
 class RopeScaling:
+    """`rope_scaling` of config.json: the rule's name and its parameters. The names are those
+    registered in `parts.rope_rules` (built in: "llama3", "linear"); the typed fields are the
+    llama3 rule's, parameters of any other rule travel in `extra`."""
     rope_type: str = "default"
     factor: float = 1.0
     low_freq_factor: float = 1.0
     high_freq_factor: float = 4.0
     original_max_position_embeddings: int = 8192
+    extra: tuple = ()            # ((key, value), ...) of a registered rule's own keys
 
     @classmethod
     def from_dict(cls, raw: dict[str, Any] | None) -> "RopeScaling | None":
+        from ..parts.rope_rules import check_rope_rule
         if raw is None:
             return None
         if not isinstance(raw, dict):
             raise ConfigError(f"rope_scaling must be an object or null, got {raw!r}")
         rtype = raw.get("rope_type", raw.get("type", "default"))
-        if rtype not in _ROPE_TYPES:
-            raise ConfigError(f"rope_scaling.rope_type {rtype!r} is not supported "
-                              f"(supported: {list(_ROPE_TYPES)})")
         if rtype == "default":
             return None
-        factor = require_float(raw, "factor")
-        if factor <= 0:
-            raise ConfigError(f"rope_scaling.factor must be > 0, got {factor}")
+        params = {k: v for k, v in raw.items() if k not in ("rope_type", "type")}
+        try:
+            check_rope_rule(rtype, params)
+        except ValueError as e:
+            raise ConfigError(str(e)) from None
         if rtype == "linear":
-            return cls(rope_type="linear", factor=factor)
-        low = require_float(raw, "low_freq_factor", default=1.0)
-        high = require_float(raw, "high_freq_factor", default=4.0)
-        orig = require_int(raw, "original_max_position_embeddings")
-        if high <= low:
-            raise ConfigError("rope_scaling: high_freq_factor must exceed low_freq_factor "
-                              f"(got low={low}, high={high})")
-        return cls("llama3", factor, low, high, orig)
+            return cls(rope_type="linear", factor=float(params["factor"]))
+        if rtype == "llama3":
+            return cls("llama3", float(params["factor"]), float(params.get("low_freq_factor", 1.0)),
+                       float(params.get("high_freq_factor", 4.0)), int(params["original_max_position_embeddings"]))
+        try:
+            return cls(rope_type=rtype, factor=float(params.get("factor", 1.0)), extra=tuple(sorted(params.items())))
+        except TypeError:
+            raise ConfigError(f"rope_scaling of rule {rtype!r}: parameters must be plain values") from None
 
     def to_dict(self) -> dict[str, Any]:
         if self.rope_type == "linear":
             return {"rope_type": "linear", "factor": self.factor}
-        return {"rope_type": self.rope_type, "factor": self.factor,
-                "low_freq_factor": self.low_freq_factor,
-                "high_freq_factor": self.high_freq_factor,
-                "original_max_position_embeddings": self.original_max_position_embeddings}
+        if self.rope_type == "llama3":
+            return {"rope_type": self.rope_type, "factor": self.factor,
+                    "low_freq_factor": self.low_freq_factor,
+                    "high_freq_factor": self.high_freq_factor,
+                    "original_max_position_embeddings": self.original_max_position_embeddings}
+        return {"rope_type": self.rope_type, **dict(self.extra)}
 
 
 @dataclass(frozen=True)

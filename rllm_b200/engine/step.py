@@ -16,6 +16,7 @@ the cache are the same either way.
 """
 from __future__ import annotations
 
+import logging
 import os
 from dataclasses import dataclass, field
 
@@ -24,6 +25,9 @@ import torch
 
 from ..cache import CacheManager, OutOfPages
 from .context import GroupView, StepContext
+
+
+_log = logging.getLogger("rllm_b200")
 
 
 @dataclass
@@ -75,10 +79,16 @@ class Engine:
         if use_graphs is None:
             use_graphs = os.environ.get("RLLM_B200_NO_GRAPHS") != "1"
         self.graphs = None
-        if use_graphs and hasattr(model, "parts") and all(getattr(p, "graph_safe", False)
-                                                          for p in model.parts()):
-            from .graphs import DecodeGraphs
-            self.graphs = DecodeGraphs(self)
+        if use_graphs and hasattr(model, "parts"):
+            unsafe = sorted({type(p).__name__ for p in model.parts() if not getattr(p, "graph_safe", False)})
+            if unsafe:
+                # said once, when the engine is made: a part that reads the step on the host keeps the
+                # whole model's decode steps out of CUDA graphs (they then run launch by launch)
+                _log.warning("decode steps run without CUDA graphs: part(s) %s do not declare graph_safe",
+                             ", ".join(unsafe))
+            else:
+                from .graphs import DecodeGraphs
+                self.graphs = DecodeGraphs(self)
 
     # ------------------------------------------------------------------ requests
     def has(self, request_id) -> bool:

@@ -5,14 +5,13 @@ from __future__ import annotations
 
 from ..config.base import register_architecture
 from ..config.llama import LlamaConfig
-from ..parts import (Embedding, GQAttention, OutputHead, PreNormBlock, RMSNorm, RotaryEmbedding,
-                     SwiGLU)
+from ..parts import GQAttention, PreNormBlock, RMSNorm, RotaryEmbedding, SwiGLU, make_part
 from .model import LayerCall, Model
 
 
 def build_llama(cfg: LlamaConfig) -> Model:
     prefix = "model."
-    emb = Embedding(cfg.vocab_size, cfg.hidden_size)
+    emb = make_part("embedding", "table", vocab=cfg.vocab_size, hidden=cfg.hidden_size)
     emb.prefix = prefix
     blocks = []
     for i in range(cfg.num_hidden_layers):
@@ -27,8 +26,8 @@ def build_llama(cfg: LlamaConfig) -> Model:
         blocks.append(block)
     final_norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
     final_norm.prefix = prefix + "norm."
-    head = OutputHead(cfg.vocab_size, cfg.hidden_size, final_norm,
-                      tied_to=emb if cfg.tie_word_embeddings else None)
+    head = make_part("head", "linear", vocab=cfg.vocab_size, hidden=cfg.hidden_size, norm=final_norm,
+                     tied_to=emb if cfg.tie_word_embeddings else None)
     head.prefix = "lm_head."
     schedule = [LayerCall(i, i, True) for i in range(cfg.num_hidden_layers)]
     return Model(cfg, emb, blocks, schedule, head, prefix)

@@ -16,7 +16,7 @@ by layer, and so that code outside the package can add a kind.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any
+from typing import Any, Callable
 
 import torch
 
@@ -75,7 +75,9 @@ class Part:
     def children(self) -> list["Part"]:
         return []
 
-    def cache_spec(self) -> KVCacheSpec | StateSpec | None:
+    def cache_spec(self):
+        """A spec of a registered cache kind (`KVCacheSpec`, `StateSpec`, or a class of one's own,
+        see `register_cache_kind`), or None."""
         return None
 
     def finalize(self, device: torch.device, dtype: torch.dtype) -> None:
@@ -87,10 +89,67 @@ class Part:
             yield from c.walk()
 
 
+# ------------------------------------------------------------------ kinds of cache need
+
+@dataclass(frozen=True)
+class CacheKind:
+    """How the cache manager serves one class of cache spec.
+
+    `paged` kinds get pages: layers whose specs are equal form a group with a page pool and a block
+    table of its own; `allocate(spec, num_pages, page_size, dtype, device)` returns one layer's
+    tensors by name, each with the page as its first dimension. `window(spec)` is how many positions
+    a query looks back (None: all; pages that lie wholly before it go back to the pool);
+    `num_pages(spec, default)` the size of the group's pool; `page_bytes(spec, page_size, dtype)`
+    what one page of one layer costs (for sizing the pool from free memory).
+    Kinds that are not paged get a slot per live request:
+    `allocate(spec, max_requests, None, dtype, device)` returns tensors with the slot first; a
+    request's slot is zeroed when it opens."""
+    paged: bool
+    allocate: Callable[..., dict]
+    window: Callable[[Any], int | None] = lambda spec: None
+    num_pages: Callable[[Any, int], int] = lambda spec, default: default
+    page_bytes: Callable[[Any, int, torch.dtype], int] = lambda spec, page_size, dtype: 0
+
+
+_CACHE_KINDS: dict[type, CacheKind] = {}
+
+
+def register_cache_kind(spec_cls: type, kind: CacheKind) -> None:
+    """Tell the cache manager how to serve specs of class `spec_cls` (and its subclasses). A mixer
+    with a cache need of a new shape (a compressed latent per token, one tensor per page, pools of
+    another size) brings its spec class and this call; the manager itself stays as it is."""
+    _CACHE_KINDS[spec_cls] = kind
+
+
+def cache_kind_of(spec) -> CacheKind:
+    for cls in type(spec).__mro__:
+        if cls in _CACHE_KINDS:
+            return _CACHE_KINDS[cls]
+    raise TypeError(f"no cache kind is registered for {type(spec).__name__}; registered: "
+                    f"{sorted(c.__name__ for c in _CACHE_KINDS)}")
+
+
+def _kv_allocate(spec, num_pages, page_size, dtype, device):
+    shape = (num_pages, spec.kv_heads, page_size, spec.head_dim)
+    return {"k": torch.zeros(shape, dtype=dtype, device=device), "v": torch.zeros(shape, dtype=dtype, device=device)}
+
+
+def _state_allocate(spec, max_requests, _page_size, _dtype, device):
+    return {name: torch.zeros((max_requests,) + tuple(shape), dtype=dt, device=device)
+            for name, shape, dt in spec.tensors}
+
+
+register_cache_kind(KVCacheSpec, CacheKind(
+    paged=True, allocate=_kv_allocate, window=lambda spec: spec.window,
+    page_bytes=lambda spec, page_size, dtype: 2 * spec.kv_heads * spec.head_dim * page_size
+    * torch.empty((), dtype=dtype).element_size()))
+register_cache_kind(StateSpec, CacheKind(paged=False, allocate=_state_allocate))
+
+
 # ------------------------------------------------------------------ registry of part kinds
 
 _KINDS: dict[tuple[str, str], Any] = {}
-ROLES = ("mixer", "ffn", "norm", "position", "block")
+ROLES = ("mixer", "ffn", "norm", "position", "block", "embedding", "head")
 
 
 def register_part(role: str, name: str, factory) -> None:
@@ -117,11 +176,12 @@ def registered_parts(role: str) -> list[str]:
 class LayerCache:
     """What a mixer gets for its cache layer in one step.
 
-    KV layers: `k`, `v` [pages, kv_heads, page_size, head_dim]; `slots` [T] (page*page_size +
-    offset of each new token, -1 where the layer must not write); `block_table`
-    [sequences, pages] (-1 where a page was given back). State layers: `state[name]`
-    [slots, *shape]; the request's slot is `ctx.state_slots[seq]`."""
-    spec: KVCacheSpec | StateSpec
+    Paged layers: `tensors[name]` with the page first (keys and values: `k`, `v`
+    [pages, kv_heads, page_size, head_dim]); `slots` [T] (page*page_size + offset of each new
+    token, -1 where the layer must not write); `block_table` [sequences, pages] (-1 where a page was
+    given back). Slot layers: `state[name]` [slots, *shape]; the request's slot is
+    `ctx.state_slots[seq]`."""
+    spec: Any
     page_size: int = 0
     k: torch.Tensor | None = None
     v: torch.Tensor | None = None
@@ -129,3 +189,4 @@ class LayerCache:
     block_table: torch.Tensor | None = None
     writes: bool = True
     state: dict[str, torch.Tensor] = field(default_factory=dict)
+    tensors: dict[str, torch.Tensor] = field(default_factory=dict)

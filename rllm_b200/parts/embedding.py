@@ -5,7 +5,7 @@
 float32 and are computed only for the rows that were asked for."""
 from __future__ import annotations
 
-from .base import Param, Part, Source
+from .base import Param, Part, Source, register_part
 
 
 class Embedding(Part):
@@ -49,3 +49,7 @@ class OutputHead(Part):
         else:
             n = self.norm.forward(ctx.backend.gather_rows(h, rows), ctx)
         return ctx.backend.linear_f32(n, self.matrix())
+
+
+register_part("embedding", "table", Embedding)
+register_part("head", "linear", OutputHead)

@@ -2,41 +2,26 @@
 host in float64 and kept as float32; the rotation itself runs inside the kernel that
 also writes K and V to the cache.
 
-Plain rule f_i = theta^(-2i/d): src/gpu/cuda/shaders/rope.cu:62-66 of the reference.
-llama3 rule: the three bands of the reference's "yarn" kernel
-(src/gpu/cuda/shaders/rope.cu:233-251) with beta_fast = high_freq_factor and
-beta_slow = low_freq_factor. The reference parses `rope_scaling` for Llama
-(src/model/config.rs:724-746) but never applies it; here it is applied.
+Plain rule f_i = theta^(-2i/d): src/gpu/cuda/shaders/rope.cu:62-66 of the reference. A
+model's own rule (`rope_scaling.rope_type`) is looked up by name in `rope_rules`.
 """
 from __future__ import annotations
-
-import math
 
 import torch
 
 from .base import Part, register_part
+from .rope_rules import rope_rule
 
 
 def inverse_frequencies(rot_dim: int, theta: float, scaling=None) -> list[float]:
-    """The rot_dim/2 inverse frequencies in float64, scaling rule applied."""
-    out = []
-    for i in range(rot_dim // 2):
-        f = float(theta) ** (-2.0 * i / rot_dim)
-        if scaling is not None and scaling.rope_type == "llama3":
-            orig = float(scaling.original_max_position_embeddings)
-            wavelen = 2.0 * math.pi / f
-            if wavelen < orig / scaling.high_freq_factor:
-                pass
-            elif wavelen > orig / scaling.low_freq_factor:
-                f = f / scaling.factor
-            else:
-                s = (orig / wavelen - scaling.low_freq_factor) / \
-                    (scaling.high_freq_factor - scaling.low_freq_factor)
-                f = (1.0 - s) * f / scaling.factor + s * f
-        elif scaling is not None and scaling.rope_type == "linear":
-            f = f / scaling.factor
-        out.append(f)
-    return out
+    """The rot_dim/2 inverse frequencies in float64, the scaling rule applied. `scaling`: None, or
+    an object with `rope_type` and `to_dict()` (the rule's parameters)."""
+    freqs = [float(theta) ** (-2.0 * i / rot_dim) for i in range(rot_dim // 2)]
+    if scaling is not None and scaling.rope_type != "default":
+        freqs = list(rope_rule(scaling.rope_type)(freqs, scaling.to_dict()))
+        if len(freqs) != rot_dim // 2:
+            raise ValueError(f"rope rule {scaling.rope_type!r} returned {len(freqs)} frequencies for {rot_dim // 2}")
+    return freqs
 
 
 class RotaryEmbedding(Part):

@@ -245,3 +245,44 @@ def test_a_step_that_fails_leaves_every_request_as_it_was():
         eng.step([Entry("old", [1] * 4, []), Entry("big", [2] * 40, [])])
     assert m.free_pages() == free and "big" not in m.live
     m.check()
+
+
+def test_a_cache_kind_registered_from_outside_and_pools_of_different_size():
+    """The manager serves a spec class it has never heard of once a kind is registered for it: here
+    a paged kind with one tensor per page and a pool three pages larger than the others'. Its pages
+    go through the same tables and checks. A spec class with no kind is refused by name."""
+    from dataclasses import dataclass
+    from rllm_b200.parts import CacheKind, register_cache_kind
+
+    @dataclass(frozen=True)
+    class JointSpec:
+        width: int
+
+    @dataclass(frozen=True)
+    class Unknown:
+        x: int = 0
+
+    register_cache_kind(JointSpec, CacheKind(
+        paged=True,
+        allocate=lambda spec, pages, page, dtype, device: {"kv": torch.zeros(pages, page, spec.width, dtype=dtype, device=device)},
+        num_pages=lambda spec, default: default + 3,
+        page_bytes=lambda spec, page, dtype: page * spec.width * 4))
+    m = manager([FULL, JointSpec(6), FULL, JointSpec(6), JointSpec(10)], pages=8, page=4, allocate=True)
+    assert [g.layers for g in m.groups] == [[0, 2], [1, 3], [4]]
+    assert [g.pool.num_pages for g in m.groups] == [8, 11, 11] and m.free_pages() == [8, 11, 11]
+    assert m.groups[1].tensors[3]["kv"].shape == (11, 4, 6) and m.groups[2].tensors[4]["kv"].shape == (11, 4, 10)
+    assert CacheManager.bytes_per_page([FULL, JointSpec(6), None], 4, torch.float32) == 2 * 2 * 16 * 4 * 4 + 4 * 6 * 4
+    a = m.open("a")
+    m.reserve(a, 30)                         # 8 pages in every group: the small pool is empty then
+    m.commit(a, 30)
+    assert m.free_pages() == [0, 3, 3]
+    b = m.open("b")
+    with pytest.raises(OutOfPages):
+        m.reserve(b, 1)
+    m.check()
+    m.close("a"); m.close("b")
+    assert m.free_pages() == [8, 11, 11]
+    m2 = CacheManager([FULL, JointSpec(6)], 4, {FULL: 5, JointSpec(6): 9}, 2, torch.float32, "cpu", allocate=False)
+    assert [g.pool.num_pages for g in m2.groups] == [5, 9]
+    with pytest.raises(TypeError, match="Unknown"):
+        manager([FULL, Unknown()])

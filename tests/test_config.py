@@ -142,3 +142,29 @@ def test_special_token_ids_from_generation_config(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(dict(tiny.TINY_A, eos_token_id=9)))
     _, c = load_config(str(tmp_path))
     assert (c.bos_token_id, c.eos_token_ids) == (5, (9,))
+
+
+def test_a_rope_rule_registered_from_outside_is_accepted_by_name():
+    """`rope_scaling.rope_type` may be any registered rule: the configuration reader asks the
+    registry, runs the rule's own check of its parameters, and keeps them for the rotary part."""
+    from rllm_b200.config import config_from_dict
+    from rllm_b200.parts import inverse_frequencies, register_rope_rule, registered_rope_rules
+
+    def check(p):
+        if p.get("every", 0) < 1:
+            raise ValueError("rope_scaling.every must be >= 1")
+
+    register_rope_rule("toy_every", lambda f, p: [x / p["factor"] if i % p["every"] == 0 else x for i, x in enumerate(f)], check)
+    assert {"linear", "llama3", "toy_every"} <= set(registered_rope_rules())
+    raw = dict(tiny.TINY_A, rope_scaling={"rope_type": "toy_every", "factor": 4.0, "every": 2})
+    _, c = config_from_dict(raw)
+    assert c.rope_scaling.rope_type == "toy_every" and c.rope_scaling.to_dict() == raw["rope_scaling"]
+    _, again = config_from_dict(c.to_dict())
+    assert again.rope_scaling == c.rope_scaling
+    plain = inverse_frequencies(16, 10000.0)
+    got = inverse_frequencies(16, 10000.0, c.rope_scaling)
+    assert got == [x / 4.0 if i % 2 == 0 else x for i, x in enumerate(plain)]
+    with pytest.raises(ConfigError, match="every"):
+        config_from_dict(dict(tiny.TINY_A, rope_scaling={"rope_type": "toy_every", "factor": 4.0, "every": 0}))
+    with pytest.raises(ConfigError, match="toy_every"):            # the refusal lists what is registered
+        config_from_dict(dict(tiny.TINY_A, rope_scaling={"rope_type": "nonesuch", "factor": 2.0}))

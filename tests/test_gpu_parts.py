@@ -4,6 +4,7 @@ instead of rotating) that are registered, built into toy models beside the packa
 and stepped without a change to the package."""
 from dataclasses import dataclass
 
+import numpy as np
 import pytest
 import torch
 
@@ -490,3 +491,185 @@ def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
         assert eng.graphs is None                            # a part reads the step on the host: no graphs
         got = replay.run_in_process(eng, steps)
         replay.compare(got, want, 2e-5, f"routed toy {family.__name__}")
+
+
+# ------------------------------------------------------------------------------------------
+# a third kind of cache (one tensor per page, a pool of its own size) and a third rule for the
+# rotary frequencies, both registered here
+# ------------------------------------------------------------------------------------------
+
+@dataclass(frozen=True)
+class JointKVSpec:
+    """Keys and values of a token side by side in one tensor: [pages, page_size, 2 * width]."""
+    width: int
+
+
+def make_joint_toy():
+    from rllm_b200.config import ModelConfig, register_architecture
+    from rllm_b200.models import LayerCall, Model
+    from rllm_b200.parts import (CacheKind, GQAttention, Param, Part, PreNormBlock, RMSNorm, RotaryEmbedding,
+                                 Source, SwiGLU, make_part, register_cache_kind, register_part)
+
+    register_cache_kind(JointKVSpec, CacheKind(
+        paged=True,
+        allocate=lambda spec, pages, page, dtype, device: {"kv": torch.zeros(pages, page, 2 * spec.width, dtype=dtype, device=device)},
+        num_pages=lambda spec, default: default + 2))
+
+    class JointAttention(Part):
+        """One head, no position encoding; k and v of a token lie side by side in the layer's one
+        tensor. Plain torch over the block table (the step is read on the host: not graph safe)."""
+
+        def __init__(self, hidden, width):
+            self.hidden, self.width = hidden, width
+
+        def params(self):
+            H, W = self.hidden, self.width
+            return [Param("w_qkv", (Source("q_proj.weight", (W, H)), Source("k_proj.weight", (W, H)),
+                                    Source("v_proj.weight", (W, H)))),
+                    Param("w_o", (Source("o_proj.weight", (H, W)),))]
+
+        def cache_spec(self):
+            return JointKVSpec(self.width)
+
+        def forward(self, x, ctx, cache, residual):
+            be, W = ctx.backend, self.width
+            qkv = be.linear(x, self.w_qkv)
+            kv, ps = cache.tensors["kv"], cache.page_size
+            keep = cache.slots >= 0
+            kv[(cache.slots[keep] // ps).long(), (cache.slots[keep] % ps).long()] = qkv[keep, W:]
+            out = torch.empty(qkv.shape[0], W, dtype=torch.float32, device=qkv.device)
+            row = 0
+            for s, (n, L) in enumerate(zip(ctx.q_lens_host, ctx.kv_lens_host)):
+                pages = cache.block_table[s, : (L + ps - 1) // ps].long()
+                seq = kv[pages].reshape(-1, 2 * W)[:L].float()
+                sc = (qkv[row: row + n, :W].float() @ seq[:, :W].t()) * W ** -0.5
+                pos = torch.arange(L - n, L, device=sc.device)
+                sc = sc.masked_fill(torch.arange(L, device=sc.device)[None, :] > pos[:, None], float("-inf"))
+                out[row: row + n] = torch.softmax(sc, dim=-1) @ seq[:, W:]
+                row += n
+            be.linear_residual(out.to(qkv.dtype), self.w_o, residual)
+
+    register_part("mixer", "joint", JointAttention)
+
+    @dataclass(frozen=True)
+    class JointConfig(ModelConfig):
+        hidden: int
+        vocab: int
+        mixers: tuple
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["toy_hidden"], raw["toy_vocab"], tuple(raw["toy_mixers"]))
+
+    def build(cfg):
+        emb = make_part("embedding", "table", vocab=cfg.vocab, hidden=cfg.hidden); emb.prefix = "model."
+        blocks = []
+        for i, kind in enumerate(cfg.mixers):
+            mixer = make_part("mixer", "joint", hidden=cfg.hidden, width=24) if kind == "joint" \
+                else GQAttention(cfg.hidden, 2, 1, 16, RotaryEmbedding(16, 10000.0))
+            b = PreNormBlock(RMSNorm(cfg.hidden, 1e-5), mixer, RMSNorm(cfg.hidden, 1e-5), SwiGLU(cfg.hidden, 2 * cfg.hidden))
+            b.set_prefix(f"model.layers.{i}.")
+            blocks.append(b)
+        norm = RMSNorm(cfg.hidden, 1e-5); norm.prefix = "model.norm."
+        head = make_part("head", "linear", vocab=cfg.vocab, hidden=cfg.hidden, norm=norm, tied_to=emb); head.prefix = "lm_head."
+        return Model(cfg, emb, blocks, [LayerCall(i, i, True) for i in range(len(blocks))], head)
+
+    register_architecture("ToyJointForCausalLM", JointConfig, build, model_types=("toy_joint",))
+
+
+JOINT = {"architectures": ["ToyJointForCausalLM"], "toy_hidden": 56, "toy_vocab": 110,
+         "toy_mixers": ["joint", "attention", "joint"]}
+
+
+def joint_plain(w, ids, cfg=JOINT):
+    ids = torch.as_tensor(ids)
+    T = ids.numel()
+    pos = torch.arange(T)
+    f = P.rope_inv_freq(16, 10000.0, None)
+    h = P.embedding(w["model.embed_tokens.weight"], ids)
+    for i, kind in enumerate(cfg["toy_mixers"]):
+        p = f"model.layers.{i}."
+        n = P.rms_norm(h, w[p + "input_layernorm.weight"], 1e-5)
+        q, k, v = (P.linear(n, w[p + f"self_attn.{x}_proj.weight"]) for x in "qkv")
+        if kind == "joint":
+            a = P.attention(q.view(T, 1, 24), k.view(T, 1, 24), v.view(T, 1, 24), 24 ** -0.5).reshape(T, 24)
+        else:
+            a = P.attention(P.rope(q.view(T, 2, 16), pos, f), P.rope(k.view(T, 1, 16), pos, f), v.view(T, 1, 16),
+                            0.25).reshape(T, 32)
+        h = h + P.linear(a, w[p + "self_attn.o_proj.weight"])
+        n = P.rms_norm(h, w[p + "post_attention_layernorm.weight"], 1e-5)
+        h = h + P.swiglu(n, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    return P.linear(P.rms_norm(h, w["model.norm.weight"], 1e-5), w["model.embed_tokens.weight"])
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_a_third_cache_kind_from_outside_the_package(tmp_path, dtype, caplog):
+    """A mixer whose cache need is a class of its own (one tensor per page, a pool two pages larger
+    than the other group's), registered here with `register_cache_kind`: built, loaded and stepped in
+    every family beside ordinary attention layers, with pages used again in both pools. No file of
+    the package knows the class. The engine says once that the part keeps decode steps out of CUDA
+    graphs."""
+    import logging
+    from rllm_b200.config import registered_architectures
+    from rllm_b200.engine import load_engine
+    from rllm_b200.weights import write_random_model
+    if "ToyJointForCausalLM" not in registered_architectures():
+        make_joint_toy()
+    d = write_random_model(JOINT, 21, str(tmp_path / "joint"), std=0.12, norm_std=0.1)
+    _, w = P.read_model_dir(d)
+    reqs = {f"r{i}": tiny.random_prompt(n, 110, 80 + i) for i, n in enumerate([11, 37, 19, 52, 6])}
+    want = {}
+    for rid, toks in reqs.items():
+        lg = joint_plain(w, toks).numpy()
+        want.update({(rid, i): lg[i] for i in range(len(toks))})
+    for family in (replay.whole, replay.prefill_then_decode, replay.portions, replay.mixed):
+        steps = family(reqs)
+        with caplog.at_level(logging.WARNING, logger="rllm_b200"):
+            caplog.clear()
+            eng = load_engine(d, dtype=dtype, page_size=4, max_tokens=replay.max_live_tokens(steps, reqs),
+                              max_requests=4)
+        assert eng.graphs is None and any("JointAttention" in r.getMessage() for r in caplog.records)
+        assert [g.layers for g in eng.cache.groups] == [[0, 2], [1]]
+        sizes = [g.pool.num_pages for g in eng.cache.groups]
+        assert sizes[0] == sizes[1] + 2
+        got = replay.run_in_process(eng, steps)
+        replay.compare(got, want, {"float32": 2e-5, "bfloat16": 3e-2}[dtype], f"joint toy {dtype} {family.__name__}")
+        assert eng.cache.free_pages() == sizes
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_a_third_rope_rule_from_outside_the_package(tmp_path, dtype, monkeypatch):
+    """A Llama configuration whose `rope_scaling.rope_type` names a rule registered here: the
+    configuration reader takes the name, the rotary part applies the rule, and every family matches the
+    plain implementation run with the same frequencies."""
+    from rllm_b200.engine import load_engine
+    from rllm_b200.parts import register_rope_rule
+    from rllm_b200.weights import write_random_model
+    rule = lambda freqs, p: [f / p["factor"] if i % p["every"] == 0 else f for i, f in enumerate(freqs)]
+    register_rope_rule("toy_every", rule)
+    cfg = dict(tiny.TINY_D, rope_scaling={"rope_type": "toy_every", "factor": 5.0, "every": 3})
+    d = write_random_model(cfg, 31, str(tmp_path / "rule"), std=0.04, norm_std=0.1)
+    real = P.rope_inv_freq
+
+    def inv_freq(rot_dim, theta, scaling=None):
+        if scaling and scaling.get("rope_type") == "toy_every":
+            base = [float(theta) ** (-2.0 * i / rot_dim) for i in range(rot_dim // 2)]      # src/gpu/cuda/shaders/rope.cu:62-66
+            return torch.tensor(rule(base, scaling), dtype=torch.float64).float()
+        return real(rot_dim, theta, scaling)
+
+    monkeypatch.setattr(P, "rope_inv_freq", inv_freq)
+    pcfg, w = P.read_model_dir(d)
+    reqs = {f"r{i}": tiny.random_prompt(n, cfg["vocab_size"], 90 + i) for i, n in enumerate([5, 140, 66])}
+    want = {}
+    for rid, toks in reqs.items():
+        lg = P.forward(pcfg, w, toks).numpy()
+        want.update({(rid, i): lg[i] for i in range(len(toks))})
+    # the rule matters: without it the logits of the long request are visibly others
+    other = P.forward(dict(pcfg, rope_scaling=None), w, reqs["r1"]).numpy()
+    assert float(np.abs(other[-1] - want[("r1", 139)]).max()) > 1e-3
+    for family in (replay.whole, replay.prefill_then_decode, replay.mixed):
+        steps = family(reqs)
+        eng = load_engine(d, dtype=dtype, page_size=16, max_tokens=replay.max_live_tokens(steps, reqs), max_requests=4)
+        got = replay.run_in_process(eng, steps)
+        replay.compare(got, want, {"float32": 2e-5, "bfloat16": 1.5e-2}[dtype], f"rope rule {dtype} {family.__name__}",
+                       per_position=True)
