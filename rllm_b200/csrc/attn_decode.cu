@@ -39,21 +39,11 @@ namespace {
 // count for more than depth: at head size 64 six warps with two tiles each in flight beat four
 // with three (batch 8 x 4,096 keys: 15.1 against 16.1 us, batch 64: 86 against 96 us). At head
 // size 128 the kernel needs 186 registers a thread, and six warps would leave one CTA per SM.
-#ifndef ADEC_NW
-#define ADEC_NW 6
-#endif
-#ifndef ADEC_D
-#define ADEC_D 2                         // tiles in flight per warp
-#endif
-#ifndef ADEC_NW128
-#define ADEC_NW128 4
-#endif
-#ifndef ADEC_D128
-#define ADEC_D128 3
-#endif
-#ifndef ADEC_TILE_KB
-#define ADEC_TILE_KB 4                   // K (and V) bytes per tile, in KB
-#endif
+// warps per CTA and tiles in flight per warp, by head size (measured: six warps with two tiles each
+// beat four with three at head size 64; eight need a whole SM and lose), and the tile's size
+constexpr int ADEC_NW = 6, ADEC_D = 2;           // head size 64
+constexpr int ADEC_NW128 = 4, ADEC_D128 = 3;     // head size 128
+constexpr int ADEC_TILE_KB = 4;                  // K (and V) bytes per tile, in KB
 constexpr int MAX_CLUSTER = 8;
 
 struct DecParams {

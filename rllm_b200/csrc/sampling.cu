@@ -1,13 +1,16 @@
 // Token selection from float logits [R, V]: greedy argmax (lowest index wins a
 // tie) and the reference's sampling pipeline
 //   x/T -> top-k mask -> softmax -> min-p -> top-p -> inverse CDF in vocabulary order
-// (src/model/sampler.rs:361-499), one block per row, no scratch memory: the
-// probabilities are recomputed from the logits in every pass (V floats stay in L2).
+// (src/model/sampler.rs:361-499).
 //
-// Instead of sorting, top-k and top-p find their thresholds by bisection on
-// the bit pattern of a float: "the k-th largest logit" and "the largest
-// probability tau such that the mass of {p >= tau} reaches top_p". Ties at a
-// threshold are all kept, as in sampler.rs:397-403.
+// Argmax: the row is cut over a cluster of CTAs, rank 0 picks among the ranks' candidates through
+// distributed shared memory. Sampling: the row lies in the shared memory of a cluster of up to
+// 8 CTAs (one read of the logits). Instead of sorting, top-k and top-p find their thresholds on
+// the order-preserving bit pattern of a float ("the k-th largest logit", "the largest probability
+// tau such that the mass of {p >= tau} reaches top_p"), eight candidate thresholds a pass; prefix
+// sums over the cluster replace serial walks. Ties at a threshold are all kept, as in
+// sampler.rs:397-403. Rows too long for a cluster's shared memory run the one-block-per-row
+// kernels, which recompute the probabilities from the logits in every pass.
 #include "common.cuh"
 #include "sm100.cuh"
 #include <type_traits>

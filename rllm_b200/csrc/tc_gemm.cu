@@ -46,7 +46,6 @@
 //
 // Every mbarrier wait is bounded; on a time-out the CTA records an error word, drains what it
 // has in flight, still meets its cluster's barriers, frees its TMEM and returns.
-#include <cstdlib>
 #include "common.cuh"
 #include "sm100.cuh"
 #include <mutex>
@@ -65,15 +64,10 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;   // warp 0 TMA, warp 1 MMA + TMEM, warps 2..5 epilogue
 constexpr int THREADS_SMALL = 224;   // the small-tile kernel has a second MMA warp (6)
 constexpr int MAX_CLUSTER = 8;
-#ifndef SMALL_KB
-#define SMALL_KB 84
-#endif
-#ifndef SMALL_DUAL_KB
-#define SMALL_DUAL_KB 138
-#endif
-#ifndef NORM_MAX_TOKENS
-#define NORM_MAX_TOKENS 64
-#endif
+// shared memory of a small-tile CTA in KB: 84 + 138 (gate/up pair) = 222 KB, so that any two
+// small-tile kernels of a layer fit one SM together (measured: worth 20 % of a step of 9 to 64 tokens)
+constexpr int SMALL_KB = 84, SMALL_DUAL_KB = 138;
+constexpr int NORM_MAX_TOKENS = 64;
 constexpr int NORM_MAX_T = NORM_MAX_TOKENS;        // the fused-norm variants take steps of at most this many tokens
 
 // the most column slots a landing area needs. Tiles of 16: ranks * ceil(BN / ranks) over 1..8
@@ -971,7 +965,7 @@ int launch_bn(int bn, bool norm, const CUtensorMap& mw, const CUtensorMap& mx, c
   return ERR_BAD_SIZE;
 }
 
-void plan(int epi, int T, int N, int K, int sm_count, bool allow_split, int* bn_out, int* splits_out) {
+void plan(int epi, int T, int N, int K, int sm_count, int allow_split, int* bn_out, int* splits_out) {
   const bool dual = epi == EPI_SWIGLU;
   const int n_tiles = (N + BM - 1) / BM;
   int bn, splits = 1;
@@ -987,8 +981,8 @@ void plan(int epi, int T, int N, int K, int sm_count, bool allow_split, int* bn_
     if (splits > kb / 2) splits = kb / 2;                     // at least two K blocks per range
     if (splits > MAX_CLUSTER) splits = MAX_CLUSTER;
     if (splits < 1) splits = 1;
-    // tuning knob of the microbenchmark: RLLM_B200_TC_SPLITS=n asks for n ranges where ranges are allowed
-    static const int forced = [] { const char* e = getenv("RLLM_B200_TC_SPLITS"); return e ? atoi(e) : 0; }();
+    // allow_split > 1 asks for that many ranges where ranges are allowed (the microbenchmark's sweep)
+    const int forced = allow_split > 1 ? allow_split : 0;
     if (forced > 0) splits = forced < kb / 2 ? (forced < MAX_CLUSTER ? forced : MAX_CLUSTER) : (kb / 2 > 0 ? kb / 2 : 1);
   }
   // A step of few tokens: token tiles of 16 or 32 (33 to 64 tokens: two tiles of 32 land their
@@ -1029,7 +1023,7 @@ int run(int epi, const void* X, long long ldx, const NormArgs* norm, const void*
   int rc = get_encoder();
   if (rc) return rc;
   int bn, splits;
-  plan(epi, T, N, K, sm_count, allow_split != 0, &bn, &splits);
+  plan(epi, T, N, K, sm_count, allow_split, &bn, &splits);
   const bool dual = epi == EPI_SWIGLU;
   CUtensorMap mw, mx;
   if ((rc = cached_map(&mw, W, dual ? 2LL * N : N, K, K, BM))) return rc;
@@ -1068,13 +1062,14 @@ int run(int epi, const void* X, long long ldx, const NormArgs* norm, const void*
 // Token tile and ranges of K (= CTAs per cluster) the launcher would choose.
 RLLM_API int rllm_tc_gemm_plan(int epi, int T, int N, int K, int sm_count, int allow_split, int* bn_out,
                                int* splits_out) {
-  plan(epi, T, N, K, sm_count, allow_split != 0, bn_out, splits_out);
+  plan(epi, T, N, K, sm_count, allow_split, bn_out, splits_out);
   return 0;
 }
 
 // X: [T, K] bf16, row stride ldx; W: [N, K] bf16 contiguous ([2N, K] for SwiGLU: gate rows then up
 // rows); C: [T, N] with row stride ldc, bf16 (store, SwiGLU) or float (store-float, accumulate).
-// allow_split 0: one CTA per output tile whatever the size. Returns 0, or a negative refusal.
+// allow_split 0: one CTA per output tile whatever the size; 1: the launcher's choice of ranges of K;
+// n > 1: n ranges where ranges are allowed. Returns 0, or a negative refusal.
 RLLM_API int rllm_tc_gemm(int epi, const void* X, long long ldx, const void* W, void* Cout, long long ldc,
                           int T, int N, int K, int allow_split, int* err, int sm_count, void* stream) {
   if (epi < 0 || epi > 3 || !X) return ERR_BAD_SIZE;

@@ -28,7 +28,7 @@ CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 # bookkeeping of the cache manager (plain C++, no device code).
 LIBRARIES: dict[str, list[str]] = {
     "simt": ["simt_basic.cu", "simt_gemm.cu", "simt_attention.cu", "sampling.cu"],
-    "sm100": ["tc_gemm.cu", "stream_gemm.cu", "attn_fa.cu", "attn_decode.cu", "attn_prefill_tc.cu"],
+    "sm100": ["tc_gemm.cu", "stream_gemm.cu", "attn_fa.cu", "attn_decode.cu", "attn_prefill_tc.cu", "wait_probe.cu"],
     "host": ["host_runtime.cpp"],          # no CUDA: the cache manager's bookkeeping and metadata writer
 }
 

@@ -76,6 +76,7 @@ def cmd_gemm(a) -> None:
     rows = 2 * N if epi == ops.EPI_SWIGLU else N
     copies = max(1, min(a.copies, int(2e9 // (rows * K * 2)) or 1))
     ws = [torch.randn(rows, K, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    split = a.ranges if a.ranges > 1 else not a.no_split      # a number: that many ranges of K (tcgen05 small tiles)
     for T in a.tokens:
         out = torch.zeros(T, N, device=DEV, dtype=torch.float32) if epi == ops.EPI_ACCUM_F32 else None
         if a.norm:
@@ -84,8 +85,8 @@ def cmd_gemm(a) -> None:
             fns = [(lambda w=w: sm100.gemm_norm(h, g, 1e-5, w, epi)) for w in ws]
         else:
             x = torch.randn(T, K, device=DEV, dtype=torch.bfloat16)
-            fns = [(lambda w=w: sm100.gemm(x, w, epi, out=out, split=not a.no_split)) for w in ws]
-        bn, sp = sm100.plan(epi, T, N, K, split=not a.no_split)
+            fns = [(lambda w=w: sm100.gemm(x, w, epi, out=out, split=split)) for w in ws]
+        bn, sp = sm100.plan(epi, T, N, K, split=split)
         run(fns, a.plain, f"gemm {epi_name} T={T} N={N} K={K} tile={bn} ranges={sp}" + (" norm" if a.norm else ""),
             nbytes=rows * K * 2, flops=2.0 * T * rows * K)
     sm100.check_error(DEV)
@@ -174,6 +175,7 @@ def main(argv=None) -> int:
             p.add_argument("--tokens", type=ints, default=[1, 8, 64, 2048])
             p.add_argument("--norm", action="store_true", help="RMSNorm in front, in the same kernel")
             p.add_argument("--no-split", action="store_true")
+            p.add_argument("--ranges", type=int, default=0, help="ranges of K to force on the tcgen05 small-tile kernel")
         else:
             p.add_argument("--heads", type=int, default=32)
             p.add_argument("--kv-heads", type=int, default=8)

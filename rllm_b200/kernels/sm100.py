@@ -23,6 +23,7 @@ ops.register_signatures("sm100", {
                          c_int, c_int, c_int, _P],
     "rllm_stream_gemm_qkv_rope": [_P, c_longlong, _P, c_longlong, _P, c_int, c_float, _P, _P, c_longlong, c_int, c_int,
                                   _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "rllm_wait_probe": [_P, c_longlong, c_int, _P],
     "rllm_attention_fa": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_float, c_int, c_int, _P, _P, _P],
     "rllm_attention_prefill_tc": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -67,6 +68,15 @@ def check_error(device) -> None:
                               f"its output is not valid")
 
 
+def wait_probe(device, limit_cycles: int = 200000, arrive_first: bool = False) -> None:
+    """Launch the one-warp kernel that waits on an mbarrier nobody arrives at (unless `arrive_first`)
+    for at most `limit_cycles` cycles and records the time-out in the error word: the bounded wait
+    of the tcgen05 kernels, exercised where nothing else is in flight."""
+    st = init(device)
+    ops._check(ops._fn("sm100", "rllm_wait_probe")(st.err.data_ptr(), int(limit_cycles), int(arrive_first),
+                                                   ops._stream()), "wait_probe")
+
+
 EPI_QKV_ROPE = 4
 STREAM = os.environ.get("RLLM_B200_NO_STREAM_GEMM") != "1"
 _stream_ok: dict[tuple, bool] = {}
@@ -91,8 +101,9 @@ def gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and x.shape[0] > 0)
 
 
-def plan(epilogue: int, T: int, N: int, K: int, device="cuda:0", split: bool = True) -> tuple[int, int]:
-    """(token tile, ranges of K = CTAs per cluster) the launcher chooses for a problem."""
+def plan(epilogue: int, T: int, N: int, K: int, device="cuda:0", split: bool | int = True) -> tuple[int, int]:
+    """(token tile, ranges of K = CTAs per cluster) the tcgen05 launcher chooses for a problem.
+    `split`: False one CTA per tile, True its own choice, a number > 1 that many ranges."""
     st = init(device)
     bn, sp = c_int(), c_int()
     ops._fn("sm100", "rllm_tc_gemm_plan")(epilogue, T, N, K, st.sm_count, int(split), byref(bn), byref(sp))

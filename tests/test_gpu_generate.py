@@ -277,6 +277,37 @@ def test_the_step_loop_reports_a_kernel_that_gave_up(dirs):
     m.engine.check()                                         # read and cleared
 
 
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_gpu_goes_on(dirs):
+    """The kernels' own way out of a wait that never ends, for real: a one-warp kernel waits on an
+    mbarrier nobody arrives at, with a limit of 200,000 cycles (a tenth of a millisecond), gives up,
+    and records the failure in the device error word. The step loop raises at its next step, and
+    after the word is read the GPU works as before. (With an arrival first, the same kernel records
+    nothing.)"""
+    import time
+    from rllm_b200.kernels import ops, sm100
+    from rllm_b200.kernels.ops import KernelError
+    from rllm_b200.sampling import SamplingParams
+    m = llm(dirs["D"], "D", "bfloat16", num_pages=32)
+    m.add_request([1, 2, 3], SamplingParams(temperature=0.0, max_tokens=30))
+    m.step(); m.step()
+    sm100.wait_probe(m.engine.device, arrive_first=True)
+    torch.cuda.synchronize()
+    m.engine.check()                                         # the wait was met: nothing recorded
+    t0 = time.time()
+    sm100.wait_probe(m.engine.device, limit_cycles=200000)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 1.0                            # it gave up after its limit, not later
+    with pytest.raises(KernelError, match="role 9, detail 1"):
+        for _ in range(3):
+            m.step()
+    m.engine.check()                                         # read and cleared
+    x = torch.randn(8, 256, device="cuda:0").to(torch.bfloat16)
+    w = torch.randn(128, 256, device="cuda:0").to(torch.bfloat16)
+    got = sm100.gemm(x, w, ops.EPI_STORE_F32, split=False)   # a tcgen05 product afterwards
+    assert float((got - x.float() @ w.float().t()).abs().max()) <= 1e-3 * float(got.abs().max())
+    sm100.check_error("cuda:0")
+
+
 def test_sampling_params_defaults_follow_the_reference():
     from rllm_b200.sampling import SamplingParams
     sp = SamplingParams()
