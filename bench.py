@@ -10,8 +10,18 @@ entry point (`LLM.add_request` / `LLM.step`), host token ids in, host token ids 
 step copying its inputs from pinned host memory and reading its tokens back. `prefill`: one
 2,048-token prompt in one step. `roofline`: bytes the decode step has to read (every weight
 once, and the cache of the live requests) over its time, against the measured copy
-bandwidth. `points`: decode at batch 1 and 64 (`points_frac`: their roofline fractions). Between timed steps nothing is flushed: one
-step reads 2.47 GB of weights, twenty times the 126 MB L2.
+bandwidth. `points`: decode at batch 1 and 64 (`points_frac`: their roofline fractions);
+`e2e_points`: the same two through the entry point, with the share of the time the host was
+busy. Between timed steps nothing is flushed: one step reads 2.47 GB of weights, twenty times
+the 126 MB L2.
+
+`--workloads mixed_3b,continuous_8b` (or `all`) adds, under `workloads`, the two serving runs the
+larger model shapes are quoted for: 32 requests with prompts of 128 to 4,096 tokens and 256 decoded
+tokens each at the 3B shape; 64 requests that reach 8,192 tokens of context, prompts cut into
+portions of 512, at the 8B shape. Each goes through `LLM.add_request` / `LLM.step` (scheduler, mixed
+steps, graphs where a step is all decoding) and reports tokens a second, steps, mean step time,
+preemptions, the host's share, and the bytes and FLOPs the steps had to move and do against the
+measured peaks. They take some twenty seconds each and are off in the default run.
 This engine runs on one GPU: for --gpus N > 1 it says so and exits with 2.
 """
 import argparse
@@ -45,6 +55,9 @@ MODELS = {"1b": ("llama-3.2-1b-shape", "Llama 3.2 1B", LLAMA_1B), "3b": ("llama-
 CONTEXT = 4096
 PROMPT = 2048
 PAGE = 16
+# name -> (model, requests, shortest and longest prompt, decoded tokens each, portion, token budget a step)
+WORKLOADS = {"mixed_3b": ("3b", 32, 128, 4096, 256, None, 4096),
+             "continuous_8b": ("8b", 64, 8192 - 256, 8192 - 256, 256, 512, 2048)}
 
 
 def peaks():
@@ -124,6 +137,7 @@ def main():
     ap.add_argument("--model", default="1b", choices=sorted(MODELS), help="layer sizes (default: the 1B shape)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers where memory or time needs it")
     ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--workloads", default="", help="comma-separated: mixed_3b, continuous_8b, or all")
     ap.add_argument("--phase", default="all", choices=["all", "prefill", "decode"],
                     help="run one part only (for profiling; the JSON line then lacks the other parts)")
     ap.add_argument("--profile-range", action="store_true",
@@ -243,6 +257,7 @@ def main():
         sampler.stop(windows)
         return 0
     results = {B: decode_device(B) for B in batches}
+    graph_replays = eng.graph_steps
     ms, launches, ctx_mean = results[a.batch]
     step_bytes = wbytes + a.batch * ctx_mean * kv_bytes_per_token
     achieved = step_bytes / (ms * 1e-3) / 1e9
@@ -263,20 +278,90 @@ def main():
                     made[o.request_id] += 1
         torch.cuda.synchronize()
         h2d0 = eng.h2d_bytes
+        llm.stats.reset()
         w0 = time.time()
         n = 0
         for _ in range(K):
             n += sum(o.token is not None for o in llm.step())
         torch.cuda.synchronize()
         dt = time.time() - w0
-        e2e_h2d.append((eng.h2d_bytes - h2d0) / K)
+        e2e_h2d[B] = (eng.h2d_bytes - h2d0) / K
+        e2e_host[B] = llm.stats.host_share
+        e2e_plan[B] = (llm.stats.host_plan_s + llm.stats.host_record_s) / llm.stats.wall_s
         windows.append((w0, time.time()))
         assert n == B * K, "the batch changed size inside the timed steps"
         for r in rids:
             llm.abort(r)
+        while llm.has_work():
+            llm.step()
         return n / dt
-    e2e_h2d = []
+    e2e_h2d, e2e_host, e2e_plan = {}, {}, {}
     e2e_value = decode_e2e(a.batch) if a.phase == "all" else float("nan")
+    e2e_points = {B: decode_e2e(B) for B in batches if B != a.batch} if a.phase == "all" else {}
+
+    # ---------------------------------------------------------------- serving workloads (opt-in)
+    def linear_flops_per_token(c):
+        H, L, Q = c["hidden_size"], c["num_hidden_layers"], c["num_attention_heads"] * c["head_dim"]
+        KV, I = c["num_key_value_heads"] * c["head_dim"], c["intermediate_size"]
+        return 2 * L * (H * (Q + 2 * KV) + Q * H + 3 * H * I)
+
+    def run_workload(name):
+        mkey, n_req, lo, hi, n_new, chunk, budget = WORKLOADS[name]
+        wname, _, wcfg = MODELS[mkey]
+        rng = torch.Generator().manual_seed(1234)
+        lens = torch.randint(lo, hi + 1, (n_req,), generator=rng).tolist()
+        pages_w = sum((n + n_new) // PAGE + 2 for n in lens) + 64
+        wl = LLM(wcfg, dtype="bfloat16", seed=0, page_size=PAGE, num_pages=pages_w, max_active=n_req,
+                 max_tokens_per_step=budget, max_chunk=chunk)
+        wl.warm_up(min(2048, budget))
+        wb = weight_bytes(wl.engine.model)
+        kvb = sum(2 * sp.kv_heads * sp.head_dim * 2 for sp in wl.engine.model.cache_specs())
+        sp = SamplingParams(temperature=0.0, max_tokens=n_new, ignore_eos=True)
+        prompts = [torch.randint(0, wcfg["vocab_size"], (n,), generator=rng).tolist() for n in lens]
+        torch.cuda.synchronize()
+        wl.stats.reset()
+        graphs0 = wl.engine.graph_steps
+        w0 = time.time()
+        for pr in prompts:
+            wl.add_request(pr, sp)
+        done = 0
+        while wl.has_work():
+            done += sum(o.token is not None for o in wl.step())
+        torch.cuda.synchronize()
+        dt = time.time() - w0
+        windows.append((w0, time.time()))
+        st = wl.stats
+        assert done == n_req * n_new, f"{name}: {done} tokens drawn, {n_req * n_new} expected"
+        nbytes = st.steps * wb + st.kv_positions * kvb
+        flops = st.tokens * linear_flops_per_token(wcfg) + 4 * wcfg["num_hidden_layers"] * wcfg["num_attention_heads"] \
+            * wcfg["head_dim"] * st.attn_pairs + 2 * wcfg["hidden_size"] * wcfg["vocab_size"] * st.sampled
+        res = {"model": wname, "requests": n_req, "prompt_tokens": sum(lens), "decode_tokens": done,
+               "portion": chunk, "token_budget": budget,
+               "decode_tok_s": round(done / dt, 1), "all_tok_s": round(st.tokens / dt, 1), "seconds": round(dt, 3),
+               "steps": st.steps, "graph_steps": wl.engine.graph_steps - graphs0, "mean_step_ms": round(dt / st.steps * 1e3, 3),
+               "preemptions": st.preemptions, "host_share": round(st.host_share, 4),
+               "host_plan_share": round(st.host_plan_s / st.wall_s, 4), "host_launch_share": round(st.host_launch_s / st.wall_s, 4),
+               "host_record_share": round(st.host_record_s / st.wall_s, 4), "host_wait_share": round(st.wait_s / st.wall_s, 4),
+               "hbm_frac": round(nbytes / dt / 1e9 / pk["hbm_gbs"], 4),
+               "flop_frac": round(flops / dt / 1e12 / pk["bf16_tflops_sustained"], 4)}
+        res["bound"] = "hbm" if res["hbm_frac"] >= res["flop_frac"] else "tensor"
+        del wl
+        torch.cuda.empty_cache()
+        return res
+
+    wanted = [w for w in (sorted(WORKLOADS) if a.workloads == "all" else a.workloads.split(",")) if w]
+    for w in wanted:
+        if w not in WORKLOADS:
+            print(f"bench.py: unknown workload {w!r} (known: {sorted(WORKLOADS)})", file=sys.stderr)
+            return 2
+    workloads = {}
+    if wanted:
+        del llm, eng
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        for w in wanted:
+            workloads[w] = run_workload(w)
     clocks = sampler.stop(windows)
 
     out = {
@@ -292,9 +377,15 @@ def main():
                    "seq_len": CONTEXT, "prompt_len": PROMPT, "kv_page": PAGE, "parallelism": "single-gpu",
                    "l2": f"step reads {wbytes / 1e9:.1f} GB > 126 MB L2, no flush",
                    "peaks": pk["source"]},
-        "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": round(e2e_h2d[0]) if e2e_h2d else None,
-                "d2h_bytes_per_step": 4 * a.batch},
-        "gpu_launches": launches, "graph_replays": eng.graph_steps,
+        "e2e": {"value": round(e2e_value, 1), "unit": "tok/s",
+                "h2d_bytes_per_step": round(e2e_h2d[a.batch]) if a.batch in e2e_h2d else None,
+                "d2h_bytes_per_step": 4 * a.batch, "steps": K, "host_share": round(e2e_host.get(a.batch, float("nan")), 4),
+                "host_plan_record_share": round(e2e_plan.get(a.batch, float("nan")), 4)},
+        "e2e_points": {f"decode_b{B}": {"value": round(v, 1), "h2d_bytes_per_step": round(e2e_h2d[B]),
+                                        "d2h_bytes_per_step": 4 * B, "host_share": round(e2e_host[B], 4),
+                                        "host_plan_record_share": round(e2e_plan[B], 4)}
+                       for B, v in e2e_points.items()},
+        "gpu_launches": launches, "graph_replays": graph_replays,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
@@ -306,6 +397,8 @@ def main():
         "published": {"h100_nvl_b1_tok_s": 326, "note": "reference README, other hardware, batch 1"} if a.model == "1b" else None,
         "clocks": clocks,
     }
+    if workloads:
+        out["workloads"] = workloads
     if 1 in results:
         out["points"]["decode_b1"] = round(1 / results[1][0] * 1e3, 1)
         out["points_frac"]["decode_b1"] = round((wbytes + results[1][2] * kv_bytes_per_token)

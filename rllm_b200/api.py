@@ -11,12 +11,54 @@ from __future__ import annotations
 import os
 import warnings
 
+import time
+
 import torch
-from dataclasses import replace
+from dataclasses import dataclass, replace
 
 from .engine.factory import load_engine, parse_dtype, random_engine
 from .engine.scheduler import Scheduler, StepOutput
 from .sampling import Sampler, SamplingParams
+
+
+@dataclass
+class StepStats:
+    """What the steps of an `LLM` have run and where the host's time went, added up since the last
+    `reset()`. `host_*_s`: seconds the host spent planning (scheduler), launching (pages, metadata,
+    kernel launches, sampling launches) and recording results; `wait_s`: seconds it waited for a
+    step's tokens to arrive; `wall_s`: seconds inside `LLM.step`. With a step launched ahead the
+    host's work overlaps the device's, so `host_share` says how busy the host is, not how much it
+    delays the device. The reference logs tok/s per run (src/commands/run.rs:82-119); this is the
+    per-step account behind such a line."""
+    steps: int = 0
+    tokens: int = 0              # tokens run: prompt portions and decode tokens
+    prefill_tokens: int = 0      # of these, tokens of prompt portions
+    sampled: int = 0             # tokens drawn
+    h2d_bytes: int = 0           # step metadata copied to the device
+    kv_positions: int = 0        # sum over entries of the keys visible to the entry's last token
+    attn_pairs: int = 0          # (query, key) pairs scored
+    preemptions: int = 0
+    host_plan_s: float = 0.0
+    host_launch_s: float = 0.0
+    host_record_s: float = 0.0
+    wait_s: float = 0.0
+    wall_s: float = 0.0
+
+    def reset(self) -> None:
+        self.__init__()
+
+    @property
+    def host_share(self) -> float:
+        """Fraction of the time inside `LLM.step` that the host worked (did not wait for the device)."""
+        return (self.host_plan_s + self.host_launch_s + self.host_record_s) / self.wall_s if self.wall_s else 0.0
+
+    def line(self) -> str:
+        w = self.wall_s or 1e-30
+        return (f"{self.steps} steps, {self.tokens} tokens run ({self.prefill_tokens} of prompts), {self.sampled} drawn, "
+                f"{self.sampled / w:.1f} tok/s; per step {w / max(self.steps, 1) * 1e3:.3f} ms of which host "
+                f"{self.host_share:.1%} (plan {self.host_plan_s / w:.1%}, launch {self.host_launch_s / w:.1%}, "
+                f"record {self.host_record_s / w:.1%}), waiting {self.wait_s / w:.1%}; "
+                f"{self.h2d_bytes / max(self.steps, 1):.0f} B of metadata a step; {self.preemptions} preemptions")
 
 
 class LLM:
@@ -46,6 +88,8 @@ class LLM:
         self.run_ahead = os.environ.get("RLLM_B200_NO_RUN_AHEAD") != "1"
         self.steps_ahead = 0
         self._warned_positions = False
+        self.stats = StepStats()
+        self._since_report = 0
 
     # ---- the reference's engine loop
     def add_request(self, prompt_token_ids: list[int], params: SamplingParams | None = None) -> int:
@@ -82,7 +126,16 @@ class LLM:
         (tokens on the device, their pinned host copy, the event after which that copy is
         complete, log-probabilities on their way to the host or None).
         `ahead`: how many tokens each request is about to get that its `output` lacks."""
+        st = self.stats
+        for p in plan:
+            q, start = len(p.tokens), p.request.num_stored + ahead
+            st.tokens += q
+            st.prefill_tokens += q if q > 1 or not p.request.decoding else 0
+            st.kv_positions += start + q
+            st.attn_pairs += q * start + q * (q + 1) // 2
+        h2d0 = self.engine.h2d_bytes
         logits = self.engine.step(self.scheduler.entries(plan), keep=False, feed=feed)
+        st.h2d_bytes += self.engine.h2d_bytes - h2d0
         sampled = [p.request for p in plan if p.samples]
         if not sampled:
             return None
@@ -125,23 +178,40 @@ class LLM:
         output into the step's metadata on the device, so the GPU does not wait while the host
         reads the tokens, records them and plans. Each call still returns the tokens of exactly
         one step; a request that met its end token has one unused position computed for it."""
+        st, clock = self.stats, time.perf_counter
+        t_in = clock()
+        plan_s = launch_s = wait_s = 0.0
         failed: list[StepOutput] = []
         if self._ahead is not None:
             plan, drawn = self._ahead
             self._ahead = None
         else:
+            t0 = clock()
+            pre0 = self.scheduler.preempted_total
             plan, failed = self.scheduler.schedule(self.engine)
+            st.preemptions += self.scheduler.preempted_total - pre0
+            t1 = clock()
+            plan_s += t1 - t0
             if not plan:
+                st.host_plan_s += plan_s
+                st.wall_s += clock() - t_in
                 return failed
             drawn = self._launch(plan)
+            launch_s += clock() - t1
         if self.run_ahead and drawn is not None:
+            t0 = clock()
             nxt = self.scheduler.plan_ahead(plan)
+            t1 = clock()
+            plan_s += t1 - t0
             if nxt is not None and self.engine.takes_feed(self.scheduler.entries(nxt)):
                 self._ahead = (nxt, self._launch(nxt, feed=drawn[0], ahead=1))
                 self.steps_ahead += 1
+            launch_s += clock() - t1
         tokens, logprobs = [], None
         if drawn is not None:
+            t0 = clock()
             drawn[2].synchronize()               # this step's tokens only; the step ahead keeps running
+            wait_s = clock() - t0
             tokens = drawn[1].tolist()
             if drawn[3] is not None:
                 logprobs = self._logprobs(plan, *drawn[3])
@@ -151,6 +221,20 @@ class LLM:
         outs = failed + self.scheduler.advance(plan, tokens, self.engine, logprobs)
         if self._ahead is not None and all(p.request.finished for p in self._ahead[0]):
             self._ahead = None                   # nobody is left to take its tokens
+        wall = clock() - t_in
+        st.steps += 1
+        st.sampled += len(tokens)
+        st.host_plan_s += plan_s
+        st.host_launch_s += launch_s
+        st.wait_s += wait_s
+        st.wall_s += wall
+        st.host_record_s += wall - plan_s - launch_s - wait_s
+        prof = getattr(self.engine.backend, "report", None)
+        if prof is not None:                     # RLLM_B200_PROFILE=1: the per-operation table every 256 tokens drawn
+            self._since_report += len(tokens)
+            if self._since_report >= 256:
+                self._since_report = 0
+                prof()
         return outs
 
     @staticmethod

@@ -102,6 +102,7 @@ def cmd_run(a) -> int:
     prompt = _encode(llm, a.prompt, a.prompt_ids)
     as_ids = a.prompt_ids is not None
     import torch
+    llm.stats.reset()
     rid = llm.add_request(prompt, _params(a))
     t0 = time.time(); first = None; n = 0
     produced, shown = [], ""
@@ -130,6 +131,9 @@ def cmd_run(a) -> int:
         print(f"[rllm] prefill: {len(prompt)} tokens in {(first - t0) * 1e3:.1f} ms "
               f"({len(prompt) / max(first - t0, 1e-9):.1f} tok/s); generation: {n} tokens in "
               f"{(t1 - t0) * 1e3:.1f} ms ({n / max(t1 - t0, 1e-9):.1f} tok/s)", file=sys.stderr)
+    print(f"[rllm] {llm.stats.line()}", file=sys.stderr)
+    if hasattr(llm.engine.backend, "report"):
+        llm.engine.backend.report()              # RLLM_B200_PROFILE=1: what is left since the last table
     return 0
 
 

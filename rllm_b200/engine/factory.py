@@ -47,6 +47,10 @@ def make_engine(model, dtype, device="cuda:0", page_size: int = 16, num_pages: i
         else:
             num_pages = default_num_pages(model, page_size, dtype, device)
     cache = CacheManager(model.cache_specs(), page_size, num_pages, max_requests, dtype, device)
+    from ..kernels import profile
+    if profile.enabled():
+        # per-operation timing: every backend call bracketed by events, no graph replays
+        return Engine(model, profile.OpProfile(backend), cache, use_graphs=False)
     return Engine(model, backend, cache)
 
 
