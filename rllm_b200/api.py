@@ -146,7 +146,7 @@ class LLM:
         # step launched behind them on the main stream does not wait for a copy engine.
         if not self._pinned:
             n = max(self.scheduler.max_active, 1)
-            self._pinned = [torch.zeros(n + 2, dtype=torch.int32).pin_memory() for _ in range(2)]
+            self._pinned = [torch.zeros(n + 4, dtype=torch.int32).pin_memory() for _ in range(2)]
             self._copy_stream = torch.cuda.Stream(self.engine.device)
         self._pinned.reverse()
         buf = self._pinned[0]
@@ -158,7 +158,7 @@ class LLM:
         with torch.cuda.stream(self._copy_stream):
             self._copy_stream.wait_event(drawn_at)
             host.copy_(drawn, non_blocking=True)
-            buf[-2:].copy_(self.engine.error_words, non_blocking=True)      # and the device's error words with them
+            buf[-4:].copy_(self.engine.error_words, non_blocking=True)      # and the device's error words with them
             if lps is not None:                  # log-probabilities were asked for: they travel with the tokens
                 rows, lp, ids = lps
                 lp_host = (rows, torch.empty(lp.shape, dtype=lp.dtype).pin_memory(),
@@ -215,7 +215,7 @@ class LLM:
             tokens = drawn[1].tolist()
             if drawn[3] is not None:
                 logprobs = self._logprobs(plan, *drawn[3])
-            if self._pinned[0][-2] or self._pinned[0][-1] or self._pinned[1][-2] or self._pinned[1][-1]:
+            if self._pinned[0][-4:].any() or self._pinned[1][-4:].any():
                 self._ahead = None
                 self.engine.check()              # raises: a kernel gave up waiting, or a token id was out of range
         outs = failed + self.scheduler.advance(plan, tokens, self.engine, logprobs)

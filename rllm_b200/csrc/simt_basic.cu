@@ -373,6 +373,35 @@ RLLM_API int rllm_add_bias(void* y, const void* bias, int dt, int rows, int N, l
   return ERR_BAD_DTYPE;
 }
 
+// Checked runs: a step's block tables and cache slots are tested before any kernel uses them. An
+// entry outside [-1, num_pages) of a table, or a slot outside [-1, num_pages * page_size), is put to
+// -1, which every kernel reads as "no page here" / "do not write", so the access is skipped instead
+// of made; the error word gets 1 + the index of the first offender (first failure wins). This
+// stands in for a memory checker: a wrong table shows as an error naming the entry, not as a fault
+// or as silently wrong logits. (The reference checks its handles on the host only:
+// src/model/kv_cache.rs:864-875.)
+__global__ void check_meta_kernel(int* __restrict__ block_table, int n_table, int* __restrict__ slots, int n_slots,
+                                  int num_pages, int page_size, int* __restrict__ err) {
+  pdl_launch();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_table) {
+    const int v = block_table[i];
+    if (v < -1 || v >= num_pages) { block_table[i] = -1; atomicCAS(err, 0, 1 + i); }
+  } else if (i - n_table < n_slots) {
+    const int j = i - n_table, v = slots[j];
+    if (v < -1 || (long long)v >= (long long)num_pages * page_size) { slots[j] = -1; atomicCAS(err, 0, 0x40000000 | j); }
+  }
+}
+RLLM_API int rllm_check_meta(int* block_table, int n_table, int* slots, int n_slots, int num_pages, int page_size,
+                             int* err, void* stream) {
+  if (!err || num_pages < 0 || page_size <= 0) return ERR_BAD_SIZE;
+  const int n = (block_table ? n_table : 0) + (slots ? n_slots : 0);
+  if (n <= 0) return 0;
+  return launch_ex(check_meta_kernel, dim3((n + 255) / 256), dim3(256), 0, (cudaStream_t)stream, 1, block_table,
+                   block_table ? n_table : 0, slots, slots ? n_slots : 0, num_pages, page_size, err);
+}
+
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i]   (reference: elementwise.cu:36-49)
 template <typename T>
 __global__ void silu_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t n) {

@@ -77,6 +77,7 @@ class DecodeGraphs:
 
     def _forward(self, slot: _Slot) -> torch.Tensor:
         eng = self.engine
+        eng.check_meta(slot.ctx)
         h = eng.model.forward(slot.ctx, eng.cache)
         return eng.model.logits(h, slot.rows, slot.ctx)
 

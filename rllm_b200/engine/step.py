@@ -65,13 +65,17 @@ class Engine:
         self.model, self.backend, self.cache = model, backend, cache
         self.device = backend.device
         self.vocab = model.vocab_size
-        # two device words: [0] a kernel's bounded wait ran out, [1] a token id outside the table
+        # device words: [0] a kernel's bounded wait ran out, [1] a token id outside the table,
+        # [2] checked runs: a page number or cache slot outside the pool, [3] spare
         if backend.fast:
             from ..kernels import sm100
             self.error_words = sm100.init(self.device).err
         else:
-            self.error_words = torch.zeros(2, dtype=torch.int32, device=self.device)
+            self.error_words = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._err_flag = self.error_words[1:2]
+        # RLLM_B200_CHECKED=1: every step's block tables and slots are tested on the device before
+        # the model's kernels read them (one small kernel per cache group, also inside graphs)
+        self.checked = os.environ.get("RLLM_B200_CHECKED") == "1"
         self.steps_run = 0
         self.graph_steps = 0
         self.h2d_bytes = 0            # bytes of step metadata copied to the device so far
@@ -107,10 +111,14 @@ class Engine:
         """Read the device error words (one small copy): a token id outside the table, or a
         kernel whose bounded wait ran out. Callers that read results back anyway call this at
         the same time."""
-        wait, token = self.error_words.tolist()
+        wait, token, page = self.error_words.tolist()[:3]
         if token:
             self._err_flag.zero_()
             raise StepError("a token id outside the embedding table reached the device")
+        if page:
+            self.error_words[2:3].zero_()
+            what = f"slot of token {page & 0x3fffffff}" if page & 0x40000000 else f"block-table entry {page - 1}"
+            raise StepError(f"checked run: a {what} named a page outside the pool (the access was skipped)")
         if wait and self.backend.fast:
             from ..kernels import sm100
             sm100.check_error(self.device)
@@ -215,6 +223,15 @@ class Engine:
         ctx.extras["starts_host"] = list(starts)
         return ctx, lay.view(dev, 6, lay.n_rows)
 
+    def check_meta(self, ctx: StepContext) -> None:
+        """Checked runs: test (and make harmless) the step's tables and slots, group by group."""
+        if not self.checked:
+            return
+        from ..kernels import ops
+        for gi, view in ctx.groups.items():
+            ops.check_meta(view.block_table, view.slots, self.cache.groups[gi].pool.num_pages, view.page_size,
+                           self.error_words[2:3])
+
     def build_context(self, entries: list[Entry], rcs) -> tuple[StepContext, torch.Tensor]:
         G = len(self.cache.groups)
         q_lens = [len(e.tokens) for e in entries]
@@ -253,6 +270,7 @@ class Engine:
                 self.graph_steps += 1
             else:
                 ctx, rows = self.build_context(entries, rcs)
+                self.check_meta(ctx)
                 h = self.model.forward(ctx, self.cache)
                 if rows.numel():
                     logits = self.model.logits(h, rows, ctx)

@@ -38,6 +38,7 @@ _SIGS = {
         "rllm_step_meta": [_P, _P, c_int, _P, c_int, _P],
         "rllm_add_into": [_P, _P, c_int, c_longlong, _P],
         "rllm_add_bias": [_P, _P, c_int, c_int, c_int, c_longlong, _P],
+        "rllm_check_meta": [_P, c_int, _P, c_int, c_int, c_int, _P, _P],
         "rllm_silu_gate": [_P, _P, c_int, c_int, c_int, _P],
         "rllm_gemm_simt": [c_int, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
         "rllm_paged_attention_simt": [c_int, _P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int,
@@ -220,6 +221,18 @@ def add_bias(y: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
     _check(_fn("simt", "rllm_add_bias")(y.data_ptr(), bias.data_ptr(), _dt(y, "y"), y.shape[0], y.shape[1],
                                         y.stride(0), _stream()), "add_bias")
     return y
+
+
+def check_meta(block_table: torch.Tensor, slots: torch.Tensor, num_pages: int, page_size: int,
+               err: torch.Tensor) -> None:
+    """Checked runs: entries of a step's block table [S, P] outside [-1, num_pages) and slots outside
+    [-1, num_pages * page_size) are put to -1 (kernels then skip them) and `err` (one int32 on the
+    device) records the first offender: 1 + index into the table, or 0x40000000 | index of the slot."""
+    if block_table.dtype != torch.int32 or slots.dtype != torch.int32 or err.dtype != torch.int32 \
+            or not block_table.is_contiguous() or not slots.is_contiguous():
+        raise KernelError("check_meta takes contiguous int32 tensors")
+    _check(_fn("simt", "rllm_check_meta")(block_table.data_ptr(), block_table.numel(), slots.data_ptr(), slots.numel(),
+                                          int(num_pages), int(page_size), err.data_ptr(), _stream()), "check_meta")
 
 
 def silu_gate(gu: torch.Tensor) -> torch.Tensor:

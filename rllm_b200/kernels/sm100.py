@@ -36,9 +36,10 @@ ops.register_signatures("sm100", {
 class _State:
     def __init__(self, device):
         self.device = device
-        # word 0: set by a kernel whose bounded wait ran out; word 1: for the engine's own flag
-        # (a token id outside the table), so that one small copy brings both to the host
-        self.err = torch.zeros(2, dtype=torch.int32, device=device)
+        # word 0: set by a kernel whose bounded wait ran out; words 1 and 2: for the engine's own
+        # flags (a token id outside the table; in checked runs a page or slot outside the pool), so
+        # that one small copy brings them all to the host; word 3 spare
+        self.err = torch.zeros(4, dtype=torch.int32, device=device)
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
 
 

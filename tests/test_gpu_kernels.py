@@ -313,3 +313,18 @@ def test_add_bias_in_place_on_a_strided_view(dtype):
     assert torch.equal(d.cpu(), want)
     with pytest.raises(ops.KernelError):
         ops.add_bias(d[:, :70], b.float().to(DEV) if dtype != "float32" else b.to(torch.bfloat16).to(DEV))
+
+
+def test_check_meta_makes_bad_entries_harmless_and_names_the_first():
+    from rllm_b200.kernels import ops
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    table = i32([[0, 5, -1, 9], [3, 10, -2, 1]])                 # 10 pages: entries 10 and -2 are out
+    slots = i32([0, 159, 160, -1, -7])                            # 10 pages of 16: slots 160 and -7 are out
+    err = i32([0])
+    ops.check_meta(table, slots, 10, 16, err)
+    assert table.tolist() == [[0, 5, -1, 9], [3, -1, -1, 1]] and slots.tolist() == [0, 159, -1, -1, -1]
+    code = int(err.item())
+    assert code in (1 + 5, 1 + 6, 0x40000000 | 2, 0x40000000 | 4)           # one of the offenders, whichever came first
+    err.zero_()
+    ops.check_meta(table, slots, 10, 16, err)
+    assert int(err.item()) == 0

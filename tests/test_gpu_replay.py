@@ -150,3 +150,36 @@ def test_trace_run_program(model_dirs, plain, tmp_path, dtype):
                              replay.max_live_tokens(steps, reqs), vocab,
                              extra_args=["--page-size", str(tiny.TINY[name][4])])
     replay.compare(got, plain[name], TOL[dtype], f"trace_run {dtype}", per_position=True)
+
+
+@pytest.mark.parametrize("name", ["B", "D"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_checked_run(model_dirs, plain, name, dtype, monkeypatch):
+    """RLLM_B200_CHECKED=1: every step's block tables and cache slots are tested on the device before
+    a kernel reads them. The families run as always and nothing is reported; then a table entry that
+    names a page outside the pool is slipped in: the step runs to its end (the access is skipped, not
+    made), and the next check names the entry."""
+    from rllm_b200.engine import Entry
+    from rllm_b200.engine.step import Engine, StepError
+    monkeypatch.setenv("RLLM_B200_CHECKED", "1")
+    reqs = requests_for(name)
+    for family in ("prefill_then_decode", "mixed"):
+        steps = FAMILIES[family](reqs)
+        eng = engine_for(model_dirs[name], name, dtype, replay.max_live_tokens(steps, reqs))
+        assert eng.checked
+        got = replay.run_in_process(eng, steps)
+        replay.compare(got, plain[name], TOL[dtype], f"tiny-{name} {dtype} {family} (checked)", per_position=True)
+        eng.check()
+    real = Engine.fill_meta
+
+    def corrupt(self, host, lay, entries, rcs):
+        real(self, host, lay, entries, rcs)
+        host[int(lay.offs[8])] = self.cache.groups[0].pool.num_pages + 5       # first page of the first sequence
+    monkeypatch.setattr(Engine, "fill_meta", corrupt)
+    eng = engine_for(model_dirs[name], name, dtype, 256)
+    logits = eng.step([Entry("x", reqs["r3"][:20], [19])])
+    torch.cuda.synchronize()
+    assert logits.shape[0] == 1
+    with pytest.raises(StepError, match="block-table entry 0"):
+        eng.check()
+    eng.check()                                                              # read and cleared
