@@ -1,11 +1,14 @@
 """Plain, slow, whole-sequence Llama in float32 on the CPU: the tests' yardstick.
 
-It rests on the reference's formulas only. The reference's model code is Rust
-(no `cargo`/`rustc` on the build machine) and its kernels are device code, so
-none of it can be imported or compiled on the CPU here; there is no golden
-output of the reference to compare with. Every function below restates one
-formula and cites the reference file and lines it restates (paths relative to
-the reference project root).
+It restates the reference's formulas, each function citing the file and lines it restates (paths
+relative to the reference project root), and it is anchored on the reference's own code: the
+reference's host code is Rust (no `cargo`/`rustc` on the build machine) and cannot be imported or
+compiled on the CPU here, but its CUDA kernels compile as they are, and `tests/golden/` holds the
+logits of two tiny random models computed by those kernels (`tests/golden/make_golden.py`, run
+once on a GPU). `tests/test_plain.py::test_plain_against_the_reference_projects_own_kernels`
+compares this file with them (agreement to the reference's bfloat16 rounding, 5e-3 and 1e-2 of
+the largest logit; equal greedy tokens); the llama3 rule and attention across prompt portions,
+which the reference does not run, rest on the formulas alone.
 
 Deliberate differences from what the reference *does*, all argued from what
 it *states*:

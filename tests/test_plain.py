@@ -1,6 +1,9 @@
 """The plain implementation itself: closed-form cases in the manner of the reference's CPU
 kernel tests (src/gpu/cpu/mod.rs:2344-2631), and that no cache or batching hides in it."""
 import math
+import os
+
+import pytest
 
 import torch
 
@@ -113,3 +116,56 @@ def test_attention_tail_is_the_whole_formula_cut_to_its_last_rows():
         full = P.attention(q, k, v, 0.3, window)
         for n in (1, 5, L):
             assert torch.allclose(P.attention_tail(q[L - n:], k, v, 0.3, window), full[L - n:], atol=1e-6)
+
+
+@pytest.mark.parametrize("name", ["a", "g"])
+def test_plain_against_the_reference_projects_own_kernels(name, tmp_path):
+    """The outside anchor: tests/golden/golden_<name>.npz holds logits of a tiny random Llama computed
+    token by token by the reference project's own CUDA kernels (tests/golden/make_golden.py built and
+    ran them, unmodified). The plain implementation, whole sequence, must agree to the rounding the
+    reference's bfloat16 activations cost, and pick the same greedy token wherever the golden's best
+    two logits are clearly apart. A wrong rotary pairing, scale, mask or norm is off by far more."""
+    import hashlib
+    import json
+    import numpy as np
+    from rllm_b200.weights import write_random_model
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", f"golden_{name}.npz")
+    z = np.load(path)
+    cfg = json.loads(str(z["config"]))
+    d = write_random_model(cfg, int(z["seed"]), str(tmp_path / name), std=float(z["std"]), norm_std=float(z["norm_std"]))
+    with open(os.path.join(d, "model.safetensors"), "rb") as f:
+        digest = hashlib.sha256(f.read()).hexdigest()
+    assert digest == str(z["weights_sha256"]), "the random weights are no longer those the golden was made from: " \
+        "run tests/golden/make_golden.py again"
+    pcfg, w = P.read_model_dir(d)
+    ids = z["ids"].tolist()
+    got = P.forward(pcfg, w, ids).numpy()
+    want = z["logits"]
+    assert got.shape == want.shape
+    scale = float(np.abs(want).max())
+    err = float(np.abs(got - want).max()) / scale
+    assert err <= 3e-2, f"golden {name}: plain differs from the reference's kernels by {err:.3e} of the largest logit"
+    decided = agree = 0
+    for t in range(len(ids)):
+        top2 = np.partition(want[t], -2)[-2:]
+        if top2[1] - top2[0] > 6e-2 * scale:
+            decided += 1
+            agree += int(np.argmax(got[t]) == np.argmax(want[t]))
+    assert decided > 0 and agree == decided
+    # and the anchor bites: the other rotary pairing (neighbours instead of halves) is far outside
+    real = P.rope
+
+    def interleaved(x, positions, inv_freq):
+        T, nh, hd = x.shape
+        ang = positions[:, None].float() * inv_freq[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        a, b = x[..., 0::2], x[..., 1::2]
+        out = torch.empty_like(x)
+        out[..., 0::2], out[..., 1::2] = a * c - b * s, a * s + b * c
+        return out
+    P.rope = interleaved
+    try:
+        wrong = P.forward(pcfg, w, ids).numpy()
+    finally:
+        P.rope = real
+    assert float(np.abs(wrong - want).max()) / scale > 2 * err + 3e-2
