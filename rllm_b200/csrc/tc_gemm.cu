@@ -849,6 +849,188 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, C::TMEM_COLS); }
 }
 
+// ---------------------------------------------------------------------------- many tokens, two SMs a tile
+// The same persistent scheme on pairs of CTAs (a cluster of two, `tcgen05.mma.cta_group::2`): a tile is
+// 256 weight rows x BN tokens; each CTA of the pair loads its own 128 weight rows and its own half of
+// the token tile into its own shared memory (plain TMA loads, no multicast) and keeps its 128
+// accumulator rows in its own TMEM; the even CTA issues the MMAs, which read both CTAs' shared
+// memory. Per FLOP an SM takes in a third fewer operand bytes than alone (32 KB instead of 48 KB per
+// 64 of K at BN = 256), and operand bytes into the SM are what bounds the one-SM kernel above.
+// Hand-overs: a stage's bytes from both CTAs are counted by the even CTA's `full` barrier (the odd
+// CTA's loads name it by its cluster address); the even CTA's MMA thread commits to both CTAs' `empty`
+// and `acc_full` barriers; both CTAs' epilogue warps arrive at the even CTA's `acc_empty`. Both CTAs
+// allocate and free TMEM, and meet at a cluster barrier before they free it and leave, so that no
+// signal or MMA ever addresses a CTA that is gone. Every wait is bounded.
+template <int BN, bool DUAL> struct PairCfg {
+  static constexpr int A_TILES = DUAL ? 2 : 1;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = (BN / 2) * BK * 2;              // this CTA's half of the token tile
+  static constexpr int W_BYTES = A_TILES * A_BYTES;
+  static constexpr int STAGE_BYTES = W_BYTES + B_BYTES;
+  static constexpr int STAGES_RAW = 208 * 1024 / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES;
+  static constexpr int ACC_COLS = A_TILES * BN;
+  static constexpr int TMEM_COLS = 2 * ACC_COLS <= 64 ? 64 : 2 * ACC_COLS <= 128 ? 128 : 2 * ACC_COLS <= 256 ? 256 : 512;
+  static_assert(2 * ACC_COLS <= 512, "two accumulator sets must fit in TMEM");
+};
+constexpr long long PAIR_WAIT_CYCLES = 1000000000LL;             // about half a second
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                    const Params p) {
+  constexpr bool DUAL = (EPI == EPI_SWIGLU);
+  typedef PairCfg<BN, DUAL> C;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[C::STAGES];     // used in the even CTA: both CTAs' bytes of a stage
+  __shared__ __align__(8) uint64_t empty_bar[C::STAGES];    // in each CTA: the pair's MMAs have read the stage
+  __shared__ __align__(8) uint64_t acc_full[2];             // in each CTA: the accumulator set is complete
+  __shared__ __align__(8) uint64_t acc_empty[2];            // used in the even CTA: both CTAs have read the set out
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ int never_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t rank = cluster_rank();
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int t_tiles = (p.T + BN - 1) / BN, n_tiles = (p.N + 2 * BM - 1) / (2 * BM);
+  const int tiles = t_tiles * n_tiles;
+  const int n_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+    abort_flag = 0;
+    never_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) { prefetch_tensormap(&tmap_w); prefetch_tensormap(&tmap_x); }
+  if (warp == 1) { tmem_alloc_pair(&tmem_base_slot, C::TMEM_COLS); tmem_relinquish_pair(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  cluster_sync_all();          // the peer's barriers exist before anything is signalled there
+  pdl_launch();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (in both CTAs)
+    if (lane == 0) {
+      pdl_wait();
+      int it = 0, issued = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < tiles && ok; tile += n_pairs) {
+        const int t0 = (tile % t_tiles) * BN + (int)rank * (BN / 2);
+        const int n0 = (tile / t_tiles) * (2 * BM) + (int)rank * BM;
+        for (int kb = 0; kb < n_kb; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (uint32_t)(it / C::STAGES) & 1u;
+          if (it >= C::STAGES && !mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag, PAIR_WAIT_CYCLES)) {
+            abort_flag = 1; record_failure(p.err, 5, (int)rank); ok = false; break;
+          }
+          uint8_t* st = smem + (size_t)s * C::STAGE_BYTES;
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * C::STAGE_BYTES);
+          const uint32_t bar = map_to_rank(smem_u32(&full_bar[s]), 0);
+          const int k = kb * BK;
+          tma_load_2d_pair(st, &tmap_w, bar, k, n0);
+          if (DUAL) tma_load_2d_pair(st + C::A_BYTES, &tmap_w, bar, k, p.up_row0 + n0);
+          tma_load_2d_pair(st + C::W_BYTES, &tmap_x, bar, k, t0);
+          issued = it + 1;
+        }
+      }
+      (void)issued;
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (even CTA only)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, BN);
+      int it = 0, ti = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < tiles && ok; tile += n_pairs, ++ti) {
+        const int buf = ti & 1, use = ti >> 1;
+        if (use > 0 && !mbar_wait(&acc_empty[buf], (uint32_t)(use - 1) & 1u, &abort_flag, PAIR_WAIT_CYCLES)) {
+          abort_flag = 1; record_failure(p.err, 6); ok = false; break;
+        }
+        tc_fence_after();
+        const uint32_t acc_addr = tmem_base + (uint32_t)(buf * C::ACC_COLS);
+        for (int kb = 0; kb < n_kb; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (uint32_t)(it / C::STAGES) & 1u;
+          if (!mbar_wait(&full_bar[s], ph, &abort_flag, PAIR_WAIT_CYCLES)) { abort_flag = 1; record_failure(p.err, 2); ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
+          const uint64_t da = umma_desc_sw128(a_addr);
+          const uint64_t db = umma_desc_sw128(a_addr + C::W_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+            const uint64_t koff = (uint64_t)(k * UMMA_K * 2 / 16);
+            umma_bf16_pair(acc_addr, da + koff, db + koff, idesc, acc);
+            if (DUAL) umma_bf16_pair(acc_addr + BN, umma_desc_sw128(a_addr + C::A_BYTES) + koff, db + koff, idesc, acc);
+          }
+          umma_commit_pair_both(&empty_bar[s]);      // the stage is free, in both CTAs
+        }
+        if (ok) {
+          umma_commit_pair_both(&acc_full[buf]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps (2..5), in both CTAs
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t drained = map_to_rank(smem_u32(&acc_empty[0]), 0);        // the even CTA's acc_empty[0]
+    pdl_wait();
+    int ti = 0;
+    bool ok = true;
+    for (int tile = pair_id; tile < tiles && ok; tile += n_pairs, ++ti) {
+      const int t0 = (tile % t_tiles) * BN, n0 = (tile / t_tiles) * (2 * BM) + (int)rank * BM;
+      const int n = n0 + row;
+      const int buf = ti & 1, use = ti >> 1;
+      ok = mbar_wait(&acc_full[buf], (uint32_t)use & 1u, &abort_flag, PAIR_WAIT_CYCLES);
+      if (!ok) { abort_flag = 1; record_failure(p.err, 3, (int)rank); }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(buf * C::ACC_COLS);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (t0 + c0 >= p.T) break;
+        uint32_t g[16], u[16];
+        tmem_ld16(taddr + c0, g);
+        if (DUAL) tmem_ld16(taddr + BN + c0, u);
+        tmem_ld_wait();
+        if (n < p.N) {
+          if (EPI == EPI_ACCUM_F32) {
+            float* cp = (float*)p.C + (size_t)(t0 + c0) * p.ldc + n;
+            float r[16];
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) r[jj] = (t0 + c0 + jj < p.T) ? __ldcg(cp + (size_t)jj * p.ldc) : 0.f;
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj)
+              if (t0 + c0 + jj < p.T) cp[(size_t)jj * p.ldc] = r[jj] + __uint_as_float(g[jj]);
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) {
+              const int t = t0 + c0 + jj;
+              if (t < p.T) emit<EPI>(p, t, n, __uint_as_float(g[jj]), DUAL ? __uint_as_float(u[jj]) : 0.f);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(drained + (uint32_t)(buf * 8));   // this warp's quarter of this CTA's half is read out
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // both CTAs are done with each other's shared memory, barriers and TMEM
+  if (warp == 1) { tc_fence_after(); tmem_dealloc_pair(tmem_base, C::TMEM_COLS); }
+}
+
 // ------------------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -933,6 +1115,46 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const Params
   const int ctas = tiles < sm_count ? tiles : sm_count;
   return launch_ex(tc_gemm_persistent_kernel<BN, EPI>, dim3(ctas), dim3(THREADS), C::SMEM_BYTES, s, 1, mw, mx, p);
 }
+
+template <int BN, int EPI>
+int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int sm_count, cudaStream_t s) {
+  typedef PairCfg<BN, EPI == EPI_SWIGLU> C;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(tc_gemm_pair_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             C::SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return -5; }
+    configured = true;
+  }
+  const int tiles = ((p.T + BN - 1) / BN) * ((p.N + 2 * BM - 1) / (2 * BM));
+  const int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
+  // the two CTAs of a pair are neighbours along x: blocks 2i and 2i + 1
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = s;
+  cudaLaunchAttribute attrs[2];
+  int n = 0;
+  attrs[n].id = cudaLaunchAttributeClusterDimension;
+  attrs[n].val.clusterDim.x = 2; attrs[n].val.clusterDim.y = 1; attrs[n].val.clusterDim.z = 1;
+  ++n;
+  if (pdl_enabled()) {
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, tc_gemm_pair_kernel<BN, EPI>, mw, mx, p);
+  if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+  return 0;
+}
+
+// Whether pairs of CTAs take the products of long prompt portions (rllm_tc_gemm_set_pairs). Off unless asked
+// for: measured on a B200 (2,048 tokens, Llama 3.2 1B shapes) the pair kernel gives the same bits and is
+// level with the one-SM kernel on the q/k/v product and 4 to 12 % behind on the others; its MMA thread
+// waits for operands 40 to 70 % of the time although an SM takes in a third fewer bytes.
+bool g_pairs = false;
 
 template <int EPI>
 int launch_many(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int sm_count, cudaStream_t s) {
@@ -1027,8 +1249,11 @@ int run(int epi, const void* X, long long ldx, const NormArgs* norm, const void*
   const bool dual = epi == EPI_SWIGLU;
   CUtensorMap mw, mx;
   if ((rc = cached_map(&mw, W, dual ? 2LL * N : N, K, K, BM))) return rc;
+  // long portions: a tile of 256 weight rows x bn tokens on a pair of CTAs, each loading half of the token tile
+  const bool pair = g_pairs && !norm && epi != EPI_QKV_ROPE && sm_count >= 2 &&
+                    ((dual && bn == 128) || (!dual && bn == 256));
   if (norm) mx = mw;                                                 // not used by the kernel
-  else if ((rc = make_map(&mx, X, T, K, ldx, bn))) return rc;
+  else if ((rc = make_map(&mx, X, T, K, ldx, pair ? bn / 2 : bn))) return rc;
   Params p;
   p.C = Cout; p.ldc = (int)ldc; p.T = T; p.N = N; p.K = K; p.up_row0 = N; p.splits = splits; p.err = err;
   p.rope = rope ? *rope : RopeArgs{};
@@ -1037,6 +1262,14 @@ int run(int epi, const void* X, long long ldx, const NormArgs* norm, const void*
   if (grid.y > 65535) return ERR_TOO_LARGE;
   cudaStream_t s = (cudaStream_t)stream;
   const bool nm = norm != nullptr;
+  if (pair) {
+    switch (epi) {
+      case EPI_STORE: return launch_pair<256, EPI_STORE>(mw, mx, p, sm_count, s);
+      case EPI_STORE_F32: return launch_pair<256, EPI_STORE_F32>(mw, mx, p, sm_count, s);
+      case EPI_ACCUM_F32: return launch_pair<256, EPI_ACCUM_F32>(mw, mx, p, sm_count, s);
+      case EPI_SWIGLU: return launch_pair<128, EPI_SWIGLU>(mw, mx, p, sm_count, s);
+    }
+  }
   if (bn >= 64) {
     // many tokens: the persistent kernel with two accumulator sets
     switch (epi) {
@@ -1065,6 +1298,8 @@ RLLM_API int rllm_tc_gemm_plan(int epi, int T, int N, int K, int sm_count, int a
   plan(epi, T, N, K, sm_count, allow_split, bn_out, splits_out);
   return 0;
 }
+
+RLLM_API int rllm_tc_gemm_set_pairs(int on) { g_pairs = on != 0; return 0; }
 
 // X: [T, K] bf16, row stride ldx; W: [N, K] bf16 contiguous ([2N, K] for SwiGLU: gate rows then up
 // rows); C: [T, N] with row stride ldc, bf16 (store, SwiGLU) or float (store-float, accumulate).

@@ -12,6 +12,7 @@ from . import ops
 _P = c_void_p
 ops.register_signatures("sm100", {
     "rllm_tc_gemm": [c_int, _P, c_longlong, _P, _P, c_longlong, c_int, c_int, c_int, c_int, _P, c_int, _P],
+    "rllm_tc_gemm_set_pairs": [c_int],
     "rllm_tc_gemm_plan": [c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)],
     "rllm_tc_gemm_norm": [c_int, _P, c_longlong, _P, _P, c_int, c_float, _P, _P, c_longlong, c_int, c_int, c_int,
                           c_int, _P, c_int, _P],
@@ -93,6 +94,12 @@ def stream_supported(epilogue: int, norm: bool, T: int, N: int, K: int, hd: int 
     if ok is None:
         ok = _stream_ok[key] = bool(ops._fn("sm100", "rllm_stream_gemm_supported")(epilogue, int(norm), T, N, K, hd))
     return ok
+
+
+def set_pairs(on: bool) -> None:
+    """Products of long prompt portions on pairs of CTAs (`tcgen05.mma.cta_group::2`) or on single CTAs
+    (the default: measured level or faster)."""
+    ops._fn("sm100", "rllm_tc_gemm_set_pairs")(int(on))
 
 
 def gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:

@@ -115,6 +115,38 @@ def test_tc_gemm_takes_a_strided_view_and_refuses_misfits():
         sm100.gemm(rnd(4, 100).to(DEV), rnd(8, 100).to(DEV), ops.EPI_STORE)
 
 
+PAIR_SHAPES = [(2048, 3072, 2048), (2048, 2048, 8192), (1000, 2176, 520), (513, 384, 64), (4096, 8192, 2048), (1500, 200, 136)]
+
+
+@pytest.mark.parametrize("T,N,K", PAIR_SHAPES)
+def test_products_of_long_portions_on_cta_pairs(T, N, K):
+    """Tiles of 256 weight rows on pairs of CTAs (tcgen05.mma.cta_group::2): every epilogue against the
+    float product, widths and token counts that end inside a tile and inside a CTA's half of it, and
+    the same bits as the single-CTA kernel gives (same products, same order of K)."""
+    from rllm_b200.kernels import ops, sm100
+    x, w = rnd(T, K, seed=1), rnd(2 * N, K, seed=2, scale=K ** -0.5)
+    xd, wd = x.to(DEV), w.to(DEV)
+    w1 = wd[:N].contiguous()
+    ref = x.float() @ w[:N].float().t()
+    up = x.float() @ w[N:].float().t()
+    res = torch.randn(T, N, generator=torch.Generator().manual_seed(3))
+    outs = {}
+    for pairs in (True, False):
+        sm100.set_pairs(pairs)
+        try:
+            o = [sm100.gemm(xd, w1, ops.EPI_STORE), sm100.gemm(xd, w1, ops.EPI_STORE_F32),
+                 sm100.gemm(xd, w1, ops.EPI_ACCUM_F32, out=res.to(DEV).clone()), sm100.gemm(xd, wd, ops.EPI_SWIGLU)]
+            sm100.check_error(DEV)
+        finally:
+            sm100.set_pairs(False)
+        outs[pairs] = o
+    o = outs[True]
+    assert rel(o[0], ref) <= 6e-3 and rel(o[1], ref) <= 2e-5 and rel(o[2], res + ref) <= 2e-5
+    assert rel(o[3], ref / (1 + torch.exp(-ref)) * up) <= 6e-3
+    for a, b in zip(outs[True], outs[False]):
+        assert torch.equal(a, b)
+
+
 def test_the_streaming_kernel_takes_the_decode_products():
     """Which products of a decode step run the weight-streaming kernel: those of the three model
     shapes the benchmark runs, at 1 to 8 tokens; not 9 tokens, not a K that is no multiple of 32."""
