@@ -155,7 +155,7 @@ __device__ __forceinline__ void emit(const Params& p, int t, int n, float v, flo
   if (EPI == EPI_STORE) ((bf16*)p.C)[o] = __float2bfloat16_rn(v);
   else if (EPI == EPI_STORE_F32) ((float*)p.C)[o] = v;
   else if (EPI == EPI_ACCUM_F32) ((float*)p.C)[o] += v;
-  else if (EPI == EPI_SWIGLU) ((bf16*)p.C)[o] = __float2bfloat16_rn(v / (1.f + expf(-v)) * u);
+  else if (EPI == EPI_SWIGLU) ((bf16*)p.C)[o] = __float2bfloat16_rn(__fdividef(v, 1.f + __expf(-v)) * u);   // float, rounded once to bfloat16
 }
 
 // Rotary epilogue for one (token, output row n) whose pre-rotation value is v and whose pair
@@ -802,14 +802,13 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
         if (d < p.rope.rot_dim) prow = d < half ? row + half : row - half;
       }
       const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(buf * C::ACC_COLS);
+      if (ROPE) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        if (t0 + c0 >= p.T) break;
-        uint32_t g[16], u[16];
-        tmem_ld16(taddr + c0, g);
-        if (DUAL) tmem_ld16(taddr + BN + c0, u);
-        tmem_ld_wait();
-        if (ROPE) {
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          if (t0 + c0 >= p.T) break;
+          uint32_t g[16];
+          tmem_ld16(taddr + c0, g);
+          tmem_ld_wait();
           float* xb = xch + ((c0 >> 4) & 1) * 16 * BM;
 #pragma unroll
           for (int jj = 0; jj < 16; ++jj) xb[jj * BM + row] = __uint_as_float(g[jj]);
@@ -821,20 +820,43 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
               if (t < p.T) emit_rope(p, t, n, __uint_as_float(g[jj]), xb[jj * BM + prow]);
             }
           }
-        } else if (n < p.N) {
-          if (EPI == EPI_ACCUM_F32) {
-            float* cp = (float*)p.C + (size_t)(t0 + c0) * p.ldc + n;
-            float r[16];
-#pragma unroll
-            for (int jj = 0; jj < 16; ++jj) r[jj] = (t0 + c0 + jj < p.T) ? __ldcg(cp + (size_t)jj * p.ldc) : 0.f;
-#pragma unroll
-            for (int jj = 0; jj < 16; ++jj)
-              if (t0 + c0 + jj < p.T) cp[(size_t)jj * p.ldc] = r[jj] + __uint_as_float(g[jj]);
+        }
+      } else {
+        // The tile leaves TMEM 64 token columns at a time (32 of each half of a gate/up pair): a load from
+        // TMEM and the wait for it are a round trip of their own, and sixteen of them for a tile of 256
+        // columns were most of what the epilogue took. The residual values of the same columns are
+        // fetched while the accumulator values are on their way.
+        constexpr int CW = DUAL ? 32 : 64;
+        float* cbase = (float*)p.C + (size_t)t0 * p.ldc + n;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += CW) {
+          if (t0 + c0 >= p.T) break;
+          uint32_t g[CW], u[DUAL ? CW : 1];
+          float r[EPI == EPI_ACCUM_F32 ? CW : 1];
+          if (DUAL) {
+            tmem_ld32(taddr + c0, reinterpret_cast<uint32_t(&)[32]>(g));
+            tmem_ld32(taddr + BN + c0, reinterpret_cast<uint32_t(&)[32]>(u));
           } else {
+            tmem_ld64(taddr + c0, reinterpret_cast<uint32_t(&)[64]>(g));
+          }
+          if (EPI == EPI_ACCUM_F32 && n < p.N) {
+            const float* cp = cbase + (size_t)c0 * p.ldc;
 #pragma unroll
-            for (int jj = 0; jj < 16; ++jj) {
-              const int t = t0 + c0 + jj;
-              if (t < p.T) emit<EPI>(p, t, n, __uint_as_float(g[jj]), DUAL ? __uint_as_float(u[jj]) : 0.f);
+            for (int jj = 0; jj < CW; ++jj) r[jj] = (t0 + c0 + jj < p.T) ? __ldcg(cp + (size_t)jj * p.ldc) : 0.f;
+          }
+          tmem_ld_wait();
+          if (n < p.N) {
+            if (EPI == EPI_ACCUM_F32) {
+              float* cp = cbase + (size_t)c0 * p.ldc;
+#pragma unroll
+              for (int jj = 0; jj < CW; ++jj)
+                if (t0 + c0 + jj < p.T) cp[(size_t)jj * p.ldc] = r[jj] + __uint_as_float(g[jj]);
+            } else {
+#pragma unroll
+              for (int jj = 0; jj < CW; ++jj) {
+                const int t = t0 + c0 + jj;
+                if (t < p.T) emit<EPI>(p, t, n, __uint_as_float(g[jj]), DUAL ? __uint_as_float(u[jj]) : 0.f);
+              }
             }
           }
         }
@@ -995,25 +1017,36 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(buf * C::ACC_COLS);
+      // 64 token columns at a time, the residual values fetched while the accumulator's are on their way
+      // (as in tc_gemm_persistent_kernel)
+      constexpr int CW = DUAL ? 32 : 64;
+      float* cbase = (float*)p.C + (size_t)t0 * p.ldc + n;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
+      for (int c0 = 0; c0 < BN; c0 += CW) {
         if (t0 + c0 >= p.T) break;
-        uint32_t g[16], u[16];
-        tmem_ld16(taddr + c0, g);
-        if (DUAL) tmem_ld16(taddr + BN + c0, u);
+        uint32_t g[CW], u[DUAL ? CW : 1];
+        float r[EPI == EPI_ACCUM_F32 ? CW : 1];
+        if (DUAL) {
+          tmem_ld32(taddr + c0, reinterpret_cast<uint32_t(&)[32]>(g));
+          tmem_ld32(taddr + BN + c0, reinterpret_cast<uint32_t(&)[32]>(u));
+        } else {
+          tmem_ld64(taddr + c0, reinterpret_cast<uint32_t(&)[64]>(g));
+        }
+        if (EPI == EPI_ACCUM_F32 && n < p.N) {
+          const float* cp = cbase + (size_t)c0 * p.ldc;
+#pragma unroll
+          for (int jj = 0; jj < CW; ++jj) r[jj] = (t0 + c0 + jj < p.T) ? __ldcg(cp + (size_t)jj * p.ldc) : 0.f;
+        }
         tmem_ld_wait();
         if (n < p.N) {
           if (EPI == EPI_ACCUM_F32) {
-            float* cp = (float*)p.C + (size_t)(t0 + c0) * p.ldc + n;
-            float r[16];
+            float* cp = cbase + (size_t)c0 * p.ldc;
 #pragma unroll
-            for (int jj = 0; jj < 16; ++jj) r[jj] = (t0 + c0 + jj < p.T) ? __ldcg(cp + (size_t)jj * p.ldc) : 0.f;
-#pragma unroll
-            for (int jj = 0; jj < 16; ++jj)
+            for (int jj = 0; jj < CW; ++jj)
               if (t0 + c0 + jj < p.T) cp[(size_t)jj * p.ldc] = r[jj] + __uint_as_float(g[jj]);
           } else {
 #pragma unroll
-            for (int jj = 0; jj < 16; ++jj) {
+            for (int jj = 0; jj < CW; ++jj) {
               const int t = t0 + c0 + jj;
               if (t < p.T) emit<EPI>(p, t, n, __uint_as_float(g[jj]), DUAL ? __uint_as_float(u[jj]) : 0.f);
             }
