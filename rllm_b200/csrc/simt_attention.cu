@@ -75,11 +75,12 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, const T* __re
 
   for (int base = start; base <= pos; base += 32) {
     const int j = base + lane;
-    const bool valid = j <= pos;
+    bool valid = j <= pos;
     float s = -INFINITY;
     long long row = 0;       // element offset of this lane's key/value row
+    const int page = valid ? bt[j / page_size] : -1;
+    valid = valid && page >= 0;            // a table entry without a page (given back, or refused by a check): not read
     if (valid) {
-      const int page = bt[j / page_size];
       row = (((long long)page * nkv + kvh) * page_size + (j % page_size)) * hd;
       const V* kp = reinterpret_cast<const V*>(kcache + row);
       float dsum = 0.f;
@@ -105,7 +106,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, const T* __re
     }
     m = m_new;
   }
-  const float inv = 1.f / l;
+  const float inv = l > 0.f ? 1.f / l : 0.f;
   T* op = out + (size_t)t * out_stride + (size_t)h * hd;
 #pragma unroll
   for (int i = 0; i < NACC; ++i) {

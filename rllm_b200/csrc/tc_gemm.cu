@@ -63,6 +63,7 @@ constexpr int BK = 64;         // K per stage: 64 bf16 = one 128-byte swizzle ro
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;   // warp 0 TMA, warp 1 MMA + TMEM, warps 2..5 epilogue
 constexpr int THREADS_SMALL = 224;   // the small-tile kernel has a second MMA warp (6)
+constexpr int THREADS_MANY = 320;    // the persistent kernel has eight epilogue warps (2..9), two on each quarter of the rows
 constexpr int MAX_CLUSTER = 8;
 // shared memory of a small-tile CTA in KB: 84 + 138 (gate/up pair) = 222 KB, so that any two
 // small-tile kernels of a layer fit one SM together (measured: worth 20 % of a step of 9 to 64 tokens)
@@ -144,6 +145,7 @@ struct Params {
   int T, N, K;        // tokens, output features, inner size
   int up_row0;        // DUAL: first weight row of the "up" half
   int splits;         // CTAs per cluster = ranges of K
+  int bn;             // persistent kernel: tokens per tile (a multiple of 16, at most the template's BN)
   int* err;           // device error word (0 = fine)
   RopeArgs rope;
   NormArgs norm;      // NORM variants only
@@ -156,6 +158,15 @@ __device__ __forceinline__ void emit(const Params& p, int t, int n, float v, flo
   else if (EPI == EPI_STORE_F32) ((float*)p.C)[o] = v;
   else if (EPI == EPI_ACCUM_F32) ((float*)p.C)[o] += v;
   else if (EPI == EPI_SWIGLU) ((bf16*)p.C)[o] = __float2bfloat16_rn(__fdividef(v, 1.f + __expf(-v)) * u);   // float, rounded once to bfloat16
+}
+
+// (cos, sin) of a token's angle at one frequency, when the caller gave no table. Not inlined and returned
+// by value: sincosf's slow path, copied into an unrolled epilogue loop, is more code than the loop itself,
+// and results passed through memory would put the loop's arrays there too. The engine passes a table.
+__device__ __noinline__ float2 angle_of(const RopeArgs& r, int t, int i) {
+  float sn, cs;
+  sincosf((float)r.positions[t] * r.inv_freq[i], &sn, &cs);
+  return make_float2(cs, sn);
 }
 
 // Rotary epilogue for one (token, output row n) whose pre-rotation value is v and whose pair
@@ -195,6 +206,9 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 __device__ __forceinline__ void epilogue_warps_sync() {       // warps 2..5 only
   asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+__device__ __forceinline__ void epilogue8_sync() {            // the persistent kernel's warps 2..9
+  asm volatile("bar.sync 1, 256;" ::: "memory");
 }
 
 template <int BN, int EPI, bool NORM>
@@ -669,7 +683,7 @@ template <int BN, bool DUAL> struct PCfg {
 };
 
 template <int BN, int EPI>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS_MANY, 1)
 tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                           const Params p) {
   constexpr bool DUAL = (EPI == EPI_SWIGLU);
@@ -684,19 +698,22 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
   __shared__ int abort_flag;
   __shared__ int never_flag;
   // rotary epilogue: a row's pair partner lies 16+ rows away, in another warp's TMEM lanes; the
-  // epilogue warps pass 16 columns at a time through this buffer (two halves, used in turn)
-  __shared__ float xch[ROPE ? 2 * 16 * BM : 1];
+  // epilogue warps pass 32 columns at a time through this buffer
+  constexpr int XS = BM + 4;
+  __shared__ __align__(16) float xch[ROPE ? 32 * XS : 4];
+  __shared__ long long tok_off[ROPE ? BN : 1];
   __shared__ int epi_fail;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const int t_tiles = (p.T + BN - 1) / BN, n_tiles = (p.N + BM - 1) / BM;
+  const int bn = p.bn;                                   // tokens per tile: chosen by the host so that the tiles fill whole waves
+  const int t_tiles = (p.T + bn - 1) / bn, n_tiles = (p.N + BM - 1) / BM;
   const int tiles = t_tiles * n_tiles;
   const int n_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
     abort_flag = 0;
     never_flag = 0;
     epi_fail = 0;
@@ -718,7 +735,7 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
       int it = 0, issued = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-        const int t0 = (tile % t_tiles) * BN, n0 = (tile / t_tiles) * BM;
+        const int t0 = (tile % t_tiles) * bn, n0 = (tile / t_tiles) * BM;
         for (int kb = 0; kb < n_kb; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (uint32_t)(it / C::STAGES) & 1u;
@@ -726,7 +743,7 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
             abort_flag = 1; record_failure(p.err, 5); ok = false; break;
           }
           uint8_t* st = smem + (size_t)s * C::STAGE_BYTES;
-          mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
+          mbar_expect_tx(&full_bar[s], (uint32_t)(C::W_BYTES + bn * BK * 2));
           const int k = kb * BK;
           tma_load_2d(st, &tmap_w, &full_bar[s], k, n0);
           if (DUAL) tma_load_2d(st + C::A_BYTES, &tmap_w, &full_bar[s], k, p.up_row0 + n0);
@@ -742,7 +759,7 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      const uint32_t idesc = umma_idesc_bf16(BM, bn);
       int it = 0, ti = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++ti) {
@@ -777,72 +794,162 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue warps (2..5)
+    // ------------------------------------------------------------ epilogue warps (2..9): a warp reads the
+    // TMEM lanes of its quarter (warp % 4); the two warps of a quarter take half of the token columns
+    // each. One warp on a scheduler waits out every instruction's latency alone, so an epilogue's time
+    // goes with the instructions per warp, and the last tile's epilogue is not hidden by a mainloop.
     const int row = (warp & 3) * 32 + lane;
+    const int grp = (warp - 2) >> 2;
     pdl_wait();
     int ti = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++ti) {
-      const int t0 = (tile % t_tiles) * BN, n0 = (tile / t_tiles) * BM;
+      const int t0 = (tile % t_tiles) * bn, n0 = (tile / t_tiles) * BM;
       const int n = n0 + row;
       const int buf = ti & 1, use = ti >> 1;
       ok = mbar_wait(&acc_full[buf], (uint32_t)use & 1u, &abort_flag);
       if (!ok) { abort_flag = 1; record_failure(p.err, 3); }
       ok = __all_sync(0xffffffffu, ok);
-      if (ROPE) {                                        // the four warps leave together or not at all
+      if (ROPE) {                                        // the eight warps leave together or not at all
         if (!ok) epi_fail = 1;
-        epilogue_warps_sync();
+        epilogue8_sync();
         ok = epi_fail == 0;
       }
       if (!ok) break;
       tc_fence_after();
-      int prow = row;                                    // the pair partner of this row (same tile: heads do not straddle tiles)
-      if (ROPE) {
-        const int d = n % p.rope.hd, half = p.rope.rot_dim >> 1;
-        if (d < p.rope.rot_dim) prow = d < half ? row + half : row - half;
-      }
       const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(buf * C::ACC_COLS);
       if (ROPE) {
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 16) {
-          if (t0 + c0 >= p.T) break;
-          uint32_t g[16];
-          tmem_ld16(taddr + c0, g);
-          tmem_ld_wait();
-          float* xb = xch + ((c0 >> 4) & 1) * 16 * BM;
+        // Rotation needs a row's pair partner, which lies half a head away in another warp's TMEM lanes, and
+        // with one warp on each scheduler an epilogue is bound by the instructions it issues. So 32 token
+        // columns at a time go through shared memory ([token][row], rows padded by 4 against bank
+        // conflicts), and from there each of the 256 threads takes, for one token, two groups of 8
+        // neighbouring rows: values, partners and angles as 16-byte loads, the rotated result as one
+        // 16-byte store into C and one into the cache.
+        const RopeArgs& r = p.rope;
+        const int et = (warp - 2) * 32 + lane, tt = et >> 3, q8 = (et & 7) * 8;
+        const int half = r.rot_dim >> 1;
+        bool g_turn[2], g_low[2], g_live[2];
+        int g_fi[2], g_part[2];
+        bf16* g_cache[2];
 #pragma unroll
-          for (int jj = 0; jj < 16; ++jj) xb[jj * BM + row] = __uint_as_float(g[jj]);
-          epilogue_warps_sync();
-          if (n < p.N) {
+        for (int k = 0; k < 2; ++k) {
+          const int rb = q8 + 64 * k, nn = n0 + rb;
+          const int head = nn / r.hd, d = nn - head * r.hd;
+          g_live[k] = nn < p.N;
+          g_turn[k] = g_live[k] && head < r.nh + r.nkv && d < r.rot_dim;
+          g_low[k] = d < half;
+          g_fi[k] = g_low[k] ? d : d - half;
+          g_part[k] = g_turn[k] ? (g_low[k] ? rb + half : rb - half) : rb;
+          const bool is_k = head < r.nh + r.nkv;
+          g_cache[k] = (g_live[k] && head >= r.nh && r.slots != nullptr)
+              ? (is_k ? r.kcache : r.vcache) + (size_t)(head - r.nh - (is_k ? 0 : r.nkv)) * r.page_size * r.hd + d : nullptr;
+        }
+        // where each token of the tile starts in a cache (elements; -1: not written), once for all rows
+        if (r.slots != nullptr) {
+          for (int c = et; c < bn; c += 256) {
+            const int t = t0 + c;
+            const int slot = t < p.T ? r.slots[t] : -1;
+            tok_off[c] = slot >= 0 ? ((long long)(slot / r.page_size) * r.nkv * r.page_size + slot % r.page_size) * r.hd : -1ll;
+          }
+        }
+        // This thread's angles are asked for one chunk ahead, all at once: they come from L2, which is
+        // busy with the operands, and a chunk that waited for its own would wait about as long again
+        // as it works.
+        float4 ang[2][4], ang_next[2][4];
+        auto ask_angles = [&](int c0, float4 (&a)[2][4]) {
+          if (r.cos_sin == nullptr || t0 + c0 >= p.T) return;
+          const float2* trow = r.cos_sin + (size_t)min(t0 + c0 + tt, p.T - 1) * half;
 #pragma unroll
-            for (int jj = 0; jj < 16; ++jj) {
-              const int t = t0 + c0 + jj;
-              if (t < p.T) emit_rope(p, t, n, __uint_as_float(g[jj]), xb[jj * BM + prow]);
+          for (int k = 0; k < 2; ++k) {
+            if (g_turn[k]) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) a[k][i] = __ldg(reinterpret_cast<const float4*>(trow + g_fi[k]) + i);
             }
           }
+        };
+        ask_angles(0, ang_next);
+#pragma unroll 1
+        for (int c0 = 0; c0 < bn; c0 += 32) {
+          if (t0 + c0 >= p.T) break;
+#pragma unroll
+          for (int k = 0; k < 2; ++k)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ang[k][i] = ang_next[k][i];
+          if (c0 + 32 < bn) ask_angles(c0 + 32, ang_next);
+          {
+            uint32_t g[16];                               // 16 of the 32 columns from each warp of a quarter
+            tmem_ld16(taddr + c0 + 16 * grp, g);
+            tmem_ld_wait();
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) xch[(16 * grp + jj) * XS + row] = __uint_as_float(g[jj]);
+          }
+          epilogue8_sync();
+          const int t = t0 + c0 + tt;
+          if (t < p.T && c0 + tt < bn) {
+            const float* xr = xch + tt * XS;
+            const long long coff = r.slots != nullptr ? tok_off[c0 + tt] : -1ll;
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+              if (!g_live[k]) continue;
+              const float4 v0 = *reinterpret_cast<const float4*>(xr + q8 + 64 * k);
+              const float4 v1 = *reinterpret_cast<const float4*>(xr + q8 + 64 * k + 4);
+              float o[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+              if (g_turn[k]) {
+                const float4 w0 = *reinterpret_cast<const float4*>(xr + g_part[k]);
+                const float4 w1 = *reinterpret_cast<const float4*>(xr + g_part[k] + 4);
+                const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                float cs[8], sn[8];
+                if (r.cos_sin != nullptr) {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const float4 a = ang[k][i];
+                    cs[2 * i] = a.x; sn[2 * i] = a.y; cs[2 * i + 1] = a.z; sn[2 * i + 1] = a.w;
+                  }
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) { const float2 a = angle_of(r, t, g_fi[k] + i); cs[i] = a.x; sn[i] = a.y; }   // no table given
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = g_low[k] ? o[i] * cs[i] - w[i] * sn[i] : w[i] * sn[i] + o[i] * cs[i];
+              }
+              uint4 pk;
+              pk.x = pack_bf16x2(o[0], o[1]); pk.y = pack_bf16x2(o[2], o[3]);
+              pk.z = pack_bf16x2(o[4], o[5]); pk.w = pack_bf16x2(o[6], o[7]);
+              *reinterpret_cast<uint4*>((bf16*)p.C + (size_t)t * p.ldc + n0 + q8 + 64 * k) = pk;
+              if (g_cache[k] != nullptr && coff >= 0) *reinterpret_cast<uint4*>(g_cache[k] + coff) = pk;
+            }
+          }
+          epilogue8_sync();                               // all have read before the next 32 columns come in
         }
       } else {
         // The tile leaves TMEM 64 token columns at a time (32 of each half of a gate/up pair): a load from
         // TMEM and the wait for it are a round trip of their own, and sixteen of them for a tile of 256
         // columns were most of what the epilogue took. The residual values of the same columns are
         // fetched while the accumulator values are on their way.
-        constexpr int CW = DUAL ? 32 : 64;
+        // (with ten warps a thread has 168 registers: the residual's 64 beside the accumulator's 64 would spill)
+        constexpr int CW = (DUAL || BN < 128 || EPI == EPI_ACCUM_F32) ? 32 : 64;
         float* cbase = (float*)p.C + (size_t)t0 * p.ldc + n;
+        // the first warp of a quarter takes the columns up to `mid` (a multiple of 32), the second the rest;
+        // `lim`: columns of this warp that are tokens of the tile and of the step
+        const int mid = ((bn / 2 + 31) / 32) * 32;
+        const int c_begin = grp == 0 ? 0 : mid;
+        const int lim = min(grp == 0 ? mid : bn, p.T - t0);
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += CW) {
-          if (t0 + c0 >= p.T) break;
+        for (int c0 = c_begin; c0 < lim; c0 += CW) {
           uint32_t g[CW], u[DUAL ? CW : 1];
           float r[EPI == EPI_ACCUM_F32 ? CW : 1];
           if (DUAL) {
             tmem_ld32(taddr + c0, reinterpret_cast<uint32_t(&)[32]>(g));
             tmem_ld32(taddr + BN + c0, reinterpret_cast<uint32_t(&)[32]>(u));
+          } else if (CW == 32) {
+            tmem_ld32(taddr + c0, reinterpret_cast<uint32_t(&)[32]>(g));
           } else {
             tmem_ld64(taddr + c0, reinterpret_cast<uint32_t(&)[64]>(g));
           }
           if (EPI == EPI_ACCUM_F32 && n < p.N) {
             const float* cp = cbase + (size_t)c0 * p.ldc;
 #pragma unroll
-            for (int jj = 0; jj < CW; ++jj) r[jj] = (t0 + c0 + jj < p.T) ? __ldcg(cp + (size_t)jj * p.ldc) : 0.f;
+            for (int jj = 0; jj < CW; ++jj) r[jj] = (c0 + jj < lim) ? __ldcg(cp + (size_t)jj * p.ldc) : 0.f;
           }
           tmem_ld_wait();
           if (n < p.N) {
@@ -850,12 +957,16 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
               float* cp = cbase + (size_t)c0 * p.ldc;
 #pragma unroll
               for (int jj = 0; jj < CW; ++jj)
-                if (t0 + c0 + jj < p.T) cp[(size_t)jj * p.ldc] = r[jj] + __uint_as_float(g[jj]);
+                if (c0 + jj < lim) cp[(size_t)jj * p.ldc] = r[jj] + __uint_as_float(g[jj]);
+            } else if (EPI == EPI_STORE) {
+              bf16* cp = (bf16*)p.C + (size_t)(t0 + c0) * p.ldc + n;
+#pragma unroll
+              for (int jj = 0; jj < CW; ++jj, cp += p.ldc)
+                if (c0 + jj < lim) *cp = __float2bfloat16_rn(__uint_as_float(g[jj]));
             } else {
 #pragma unroll
               for (int jj = 0; jj < CW; ++jj) {
-                const int t = t0 + c0 + jj;
-                if (t < p.T) emit<EPI>(p, t, n, __uint_as_float(g[jj]), DUAL ? __uint_as_float(u[jj]) : 0.f);
+                if (c0 + jj < lim) emit<EPI>(p, t0 + c0 + jj, n, __uint_as_float(g[jj]), DUAL ? __uint_as_float(u[jj]) : 0.f);
               }
             }
           }
@@ -1144,9 +1255,10 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const Params
                              C::SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return -5; }
     configured = true;
   }
-  const int tiles = ((p.T + BN - 1) / BN) * ((p.N + BM - 1) / BM);
+  if (p.bn < 16 || p.bn > BN || p.bn % 16) return ERR_BAD_SIZE;
+  const int tiles = ((p.T + p.bn - 1) / p.bn) * ((p.N + BM - 1) / BM);
   const int ctas = tiles < sm_count ? tiles : sm_count;
-  return launch_ex(tc_gemm_persistent_kernel<BN, EPI>, dim3(ctas), dim3(THREADS), C::SMEM_BYTES, s, 1, mw, mx, p);
+  return launch_ex(tc_gemm_persistent_kernel<BN, EPI>, dim3(ctas), dim3(THREADS_MANY), C::SMEM_BYTES, s, 1, mw, mx, p);
 }
 
 template <int BN, int EPI>
@@ -1191,13 +1303,10 @@ bool g_pairs = false;
 
 template <int EPI>
 int launch_many(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int sm_count, cudaStream_t s) {
-  switch (bn) {
-    case 64: return launch_persistent<64, EPI>(mw, mx, p, sm_count, s);
-    case 128: return launch_persistent<128, EPI>(mw, mx, p, sm_count, s);
-    case 256:
-      if constexpr (EPI != EPI_SWIGLU) return launch_persistent<256, EPI>(mw, mx, p, sm_count, s);
-      break;
-  }
+  // the kernel's shared memory and accumulator sets are laid out for up to 64, 128 or 256 tokens a tile
+  if (bn <= 64) return launch_persistent<64, EPI>(mw, mx, p, sm_count, s);
+  if (bn <= 128) return launch_persistent<128, EPI>(mw, mx, p, sm_count, s);
+  if constexpr (EPI != EPI_SWIGLU) { if (bn <= 256) return launch_persistent<256, EPI>(mw, mx, p, sm_count, s); }
   return ERR_BAD_SIZE;
 }
 
@@ -1248,15 +1357,22 @@ void plan(int epi, int T, int N, int K, int sm_count, int allow_split, int* bn_o
     bn = T <= 16 ? 16 : 32;
     if (bn >= 32) while (splits & (splits - 1)) splits &= splits - 1;     // wider tiles: a power of two
   } else {
-    // more tokens: no ranges of K (a partial tile of 128+ columns costs more to merge than it
-    // saves); the widest token tile that still gives most SMs a CTA, else the narrowest
+    // More tokens: no ranges of K (a partial tile of 128+ columns costs more to merge than it saves), and
+    // the persistent kernel, whose tile takes any number of tokens in steps of 16. A CTA's time goes with
+    // its tiles x the operand rows a tile takes in per 64 of K (128 or 256 weight rows + the tokens): the
+    // width that makes this smallest fills whole waves (2,048 tokens x 24 weight tiles: 176 tokens a tile
+    // are 288 tiles, 1.95 waves of 148, where 256 are 192 tiles, 1.3 waves that cost 2); of equals the wider.
     splits = 1;
     const int widest = dual ? 128 : 256;
-    bn = 64;
-    for (int cand = widest; cand >= 128; cand /= 2) {
-      if (n_tiles * ((T + cand - 1) / cand) * 10 >= sm_count * 8) { bn = cand; break; }
+    const long long w_rows = dual ? 256 : 128;
+    long long best = -1;
+    bn = widest;
+    for (int cand = widest; cand >= 64; cand -= 16) {
+      const long long tiles = (long long)n_tiles * ((T + cand - 1) / cand);
+      const long long waves = (tiles + sm_count - 1) / sm_count;
+      const long long cost = waves * (w_rows + cand);
+      if (best < 0 || cost < best) { best = cost; bn = cand; }
     }
-    if (bn == 64 && T > 512) bn = 128;                        // long prompts on a narrow weight: fewer re-reads
   }
   *bn_out = bn;
   *splits_out = splits;
@@ -1283,12 +1399,12 @@ int run(int epi, const void* X, long long ldx, const NormArgs* norm, const void*
   CUtensorMap mw, mx;
   if ((rc = cached_map(&mw, W, dual ? 2LL * N : N, K, K, BM))) return rc;
   // long portions: a tile of 256 weight rows x bn tokens on a pair of CTAs, each loading half of the token tile
-  const bool pair = g_pairs && !norm && epi != EPI_QKV_ROPE && sm_count >= 2 &&
-                    ((dual && bn == 128) || (!dual && bn == 256));
+  const bool pair = g_pairs && !norm && epi != EPI_QKV_ROPE && sm_count >= 2 && bn >= 64 && T >= (dual ? 128 : 256);
+  if (pair) bn = dual ? 128 : 256;                                   // the pair kernel's tile is fixed
   if (norm) mx = mw;                                                 // not used by the kernel
   else if ((rc = make_map(&mx, X, T, K, ldx, pair ? bn / 2 : bn))) return rc;
   Params p;
-  p.C = Cout; p.ldc = (int)ldc; p.T = T; p.N = N; p.K = K; p.up_row0 = N; p.splits = splits; p.err = err;
+  p.C = Cout; p.ldc = (int)ldc; p.T = T; p.N = N; p.K = K; p.up_row0 = N; p.splits = splits; p.err = err; p.bn = bn;
   p.rope = rope ? *rope : RopeArgs{};
   p.norm = norm ? *norm : NormArgs{};
   dim3 grid((T + bn - 1) / bn, (N + BM - 1) / BM, splits);
@@ -1302,6 +1418,11 @@ int run(int epi, const void* X, long long ldx, const NormArgs* norm, const void*
       case EPI_ACCUM_F32: return launch_pair<256, EPI_ACCUM_F32>(mw, mx, p, sm_count, s);
       case EPI_SWIGLU: return launch_pair<128, EPI_SWIGLU>(mw, mx, p, sm_count, s);
     }
+  }
+  if (bn >= 64 && rope) {
+    // the persistent kernel's rotary epilogue moves groups of 8 neighbouring features as 16 bytes
+    if (rope->hd % 16 || rope->rot_dim % 16 || ldc % 8) return ERR_BAD_SIZE;
+    if (((uintptr_t)Cout | (uintptr_t)rope->kcache | (uintptr_t)rope->vcache | (uintptr_t)rope->cos_sin) & 15) return ERR_BAD_ALIGN;
   }
   if (bn >= 64) {
     // many tokens: the persistent kernel with two accumulator sets

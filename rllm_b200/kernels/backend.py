@@ -147,10 +147,8 @@ class Backend:
                                              kc, cache.v if writes else None, nh, nkv, hd, cache.page_size,
                                              rot_dim, norm=(x.h, x.weight, x.eps), table=table)
         x = x.tensor() if isinstance(x, Normed) else x
-        # the fused epilogue pays for decode and small mixed steps; for a long prompt portion the
-        # row-parallel rotation kernel is faster than rotating in the product's four epilogue warps
-        if bias is None and self._sm100 is not None and x.shape[0] <= 128 and \
-                self._sm100.qkv_rope_supported(x, w_qkv, cache.k if cache.writes else None, hd):
+        if bias is None and self._sm100 is not None and \
+                self._sm100.qkv_rope_supported(x, w_qkv, cache.k if cache.writes else None, hd, rot_dim):
             writes = cache.writes
             return self._sm100.gemm_qkv_rope(x, w_qkv, positions, inv_freq, cache.slots if writes else None,
                                              cache.k if writes else None, cache.v if writes else None,

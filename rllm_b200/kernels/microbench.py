@@ -26,6 +26,7 @@ DEV = "cuda:0"
 SHAPES = {   # name -> (output features, inner size, epilogue)
     "qkv": (3072, 2048, "store"), "o": (2048, 2048, "accum"), "gateup": (8192, 2048, "swiglu"),
     "down": (2048, 8192, "accum"), "head": (128256, 2048, "store_f32"),
+    "qkv-rope": (3072, 2048, "rope"),     # 32 + 2 x 8 heads of 64, rotated and written to a paged cache in the epilogue
 }
 EPI = {"store": ops.EPI_STORE, "store_f32": ops.EPI_STORE_F32, "accum": ops.EPI_ACCUM_F32,
        "swiglu": ops.EPI_SWIGLU}
@@ -72,6 +73,8 @@ def cmd_gemm(a) -> None:
         N, K, epi_name = SHAPES[a.shape]
     else:
         N, K, epi_name = a.n, a.k, a.epilogue
+    if epi_name == "rope":
+        return cmd_gemm_rope(a, N, K)
     epi = EPI[epi_name]
     rows = 2 * N if epi == ops.EPI_SWIGLU else N
     copies = max(1, min(a.copies, int(2e9 // (rows * K * 2)) or 1))
@@ -90,6 +93,29 @@ def cmd_gemm(a) -> None:
         bn, sp = sm100.plan(epi, T, N, K, split=split)
         run(fns, a.plain, f"gemm {epi_name} T={T} N={N} K={K} tile={bn} ranges={sp}" + (" norm" if a.norm else ""),
             nbytes=rows * K * 2, flops=2.0 * T * rows * K)
+    sm100.check_error(DEV)
+
+
+def cmd_gemm_rope(a, N: int, K: int) -> None:
+    """The q/k/v product with rotation and cache write in its epilogue (heads of 64, a quarter of them k and v each)."""
+    hd, page = 64, 16
+    nkv = N // hd // 6
+    nh = N // hd - 2 * nkv
+    copies = max(1, min(a.copies, int(2e9 // (N * K * 2)) or 1))
+    ws = [torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, hd, 2, device=DEV, dtype=torch.float32) / hd))).contiguous()
+    for T in a.tokens:
+        pages = (T + page - 1) // page
+        kc = torch.zeros(pages, nkv, page, hd, device=DEV, dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        pos = torch.arange(T, device=DEV, dtype=torch.int32)
+        slots = torch.arange(T, device=DEV, dtype=torch.int32)
+        table = ops.rope_table(pos, inv_freq, T)
+        x = torch.randn(T, K, device=DEV, dtype=torch.bfloat16)
+        fns = [(lambda w=w: sm100.gemm_qkv_rope(x, w, pos, inv_freq, slots, kc, vc, nh, nkv, hd, page, hd,
+                                                split=not a.no_split, table=table)) for w in ws]
+        run(fns, a.plain, f"gemm qkv+rope T={T} N={N} K={K} heads {nh}/{nkv} of {hd}", nbytes=N * K * 2,
+            flops=2.0 * T * N * K)
     sm100.check_error(DEV)
 
 

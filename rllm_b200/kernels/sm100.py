@@ -197,8 +197,14 @@ def gemm_norm(h: torch.Tensor, g: torch.Tensor, eps: float, w: torch.Tensor, epi
     return out
 
 
-def qkv_rope_supported(x: torch.Tensor, w: torch.Tensor, kcache, hd: int) -> bool:
-    return gemm_supported(x, w) and 128 % hd == 0 and (kcache is None or kcache.dtype == torch.bfloat16)
+def qkv_rope_supported(x: torch.Tensor, w: torch.Tensor, kcache, hd: int, rot_dim: int | None = None) -> bool:
+    """Rotation and cache write in the product's epilogue: heads that divide the 128 rows of a tile; from
+    65 tokens on (the kernel of long portions, which moves 8 neighbouring features at a time) head size
+    and rotated part in steps of 16."""
+    rot_dim = hd if rot_dim is None else rot_dim
+    long_ok = hd % 16 == 0 and rot_dim % 16 == 0
+    return gemm_supported(x, w) and 128 % hd == 0 and (x.shape[0] <= 64 or long_ok) and \
+        (kcache is None or kcache.dtype == torch.bfloat16)
 
 
 def gemm_qkv_rope(x: torch.Tensor | None, w_qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,

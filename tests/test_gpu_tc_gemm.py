@@ -175,8 +175,9 @@ def test_plan_splits_small_batches_only():
     assert sm100.plan(ops.EPI_ACCUM_F32, 129, 2048, 8192) == (64, 1)
     assert sm100.plan(ops.EPI_STORE, 128, 3072, 2048) == (64, 1)
     assert sm100.plan(ops.EPI_STORE, 8, 3072, 2048, split=False) == (16, 1)
-    assert sm100.plan(ops.EPI_STORE, 2048, 3072, 2048) == (256, 1)
-    assert sm100.plan(ops.EPI_ACCUM_F32, 2048, 2048, 8192) == (256, 1)
+    # long portions: the tile width that fills whole waves of 148 CTAs (288 tiles of 176 tokens; 144 of 240)
+    assert sm100.plan(ops.EPI_STORE, 2048, 3072, 2048) == (176, 1)
+    assert sm100.plan(ops.EPI_ACCUM_F32, 2048, 2048, 8192) == (240, 1)
     assert sm100.plan(ops.EPI_SWIGLU, 2048, 8192, 2048) == (128, 1)
     assert sm100.plan(ops.EPI_STORE_F32, 8, 128256, 2048) == (16, 1)
 
@@ -185,13 +186,14 @@ def test_plan_splits_small_batches_only():
 @pytest.mark.parametrize("T,K,nh,nkv,hd,page,rot", [
     (1, 64, 4, 2, 16, 16, None), (9, 96, 3, 1, 32, 8, None), (8, 2048, 32, 8, 64, 16, None),
     (70, 256, 5, 5, 64, 4, 32), (300, 128, 2, 1, 128, 16, None), (17, 512, 6, 2, 128, 32, 64),
-    (5, 3072, 24, 8, 128, 16, None), (8, 96, 3, 1, 32, 8, None), (3, 160, 2, 2, 96, 4, None), (1, 2048, 32, 8, 64, 16, None)])
+    (5, 3072, 24, 8, 128, 16, None), (8, 96, 3, 1, 32, 8, None), (3, 160, 2, 2, 96, 4, None), (1, 2048, 32, 8, 64, 16, None),
+    (600, 192, 6, 2, 64, 16, None), (1100, 256, 4, 2, 32, 8, 16), (257, 64, 3, 3, 16, 4, None)])
 def test_qkv_product_with_rotary_epilogue(T, K, nh, nkv, hd, page, rot, split):
     """q/k/v projection, rotation of q and k, and the cache write in one kernel, against the
     plain formulas: widths that are no multiple of the tile, head sizes 16 to 128, partial
     rotation, scattered slots, one token that must not be written."""
     import plain_llama as P
-    from rllm_b200.kernels import sm100
+    from rllm_b200.kernels import ops, sm100
     if 128 % hd and not split:
         pytest.skip("a head size that does not divide 128 runs in the kernel for steps of at most 8 tokens only")
     rot_dim = rot or hd
@@ -241,6 +243,15 @@ def test_qkv_product_with_rotary_epilogue(T, K, nh, nkv, hd, page, rot, split):
     out2 = sm100.gemm_qkv_rope(x.to(DEV), w.to(DEV), positions.to(DEV), inv_freq.to(DEV), None, None, None,
                                nh, nkv, hd, page, rot_dim, split=split)
     assert torch.equal(out2, out)
+    # the angles from a table made once for the step, as the engine passes them
+    table = ops.rope_table(positions.to(DEV), inv_freq.to(DEV), T)
+    kc4, vc4 = torch.zeros_like(kc), torch.zeros_like(vc)
+    out4 = sm100.gemm_qkv_rope(x.to(DEV), w.to(DEV), positions.to(DEV), inv_freq.to(DEV), slots.to(DEV), kc4, vc4,
+                               nh, nkv, hd, page, rot_dim, split=split, table=table)
+    sm100.check_error(DEV)
+    assert float((out4.float() - out.float()).abs().max()) <= scale * 2 ** -7      # a last place at most
+    assert float((kc4.float() - kc.float()).abs().max()) <= scale * 2 ** -7
+    assert torch.equal(vc4, vc)
     if T <= sm100.norm_max_tokens():
         # the same with RMSNorm in front, in the same kernel: h = x scaled per row, norm weight 1
         hrows = x.float() * torch.linspace(0.5, 3.0, T)[:, None]
