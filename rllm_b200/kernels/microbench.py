@@ -80,6 +80,7 @@ def cmd_gemm(a) -> None:
     copies = max(1, min(a.copies, int(2e9 // (rows * K * 2)) or 1))
     ws = [torch.randn(rows, K, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
     sm100.set_pairs(a.pairs)
+    sm100.set_token_rows(not a.weight_rows)
     split = a.ranges if a.ranges > 1 else not a.no_split      # a number: that many ranges of K (tcgen05 small tiles)
     for T in a.tokens:
         out = torch.zeros(T, N, device=DEV, dtype=torch.float32) if epi == ops.EPI_ACCUM_F32 else None
@@ -202,6 +203,8 @@ def main(argv=None) -> int:
             p.add_argument("--tokens", type=ints, default=[1, 8, 64, 2048])
             p.add_argument("--norm", action="store_true", help="RMSNorm in front, in the same kernel")
             p.add_argument("--no-split", action="store_true")
+            p.add_argument("--weight-rows", action="store_true",
+                           help="gate/up of long portions with the weight rows on the accumulator's rows (default: the tokens)")
             p.add_argument("--pairs", action="store_true", help="long portions on pairs of CTAs (tcgen05.mma.cta_group::2)")
             p.add_argument("--ranges", type=int, default=0, help="ranges of K to force on the tcgen05 small-tile kernel")
         else:

@@ -13,6 +13,7 @@ _P = c_void_p
 ops.register_signatures("sm100", {
     "rllm_tc_gemm": [c_int, _P, c_longlong, _P, _P, c_longlong, c_int, c_int, c_int, c_int, _P, c_int, _P],
     "rllm_tc_gemm_set_pairs": [c_int],
+    "rllm_tc_gemm_set_token_rows": [c_int],
     "rllm_tc_gemm_plan": [c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)],
     "rllm_tc_gemm_norm": [c_int, _P, c_longlong, _P, _P, c_int, c_float, _P, _P, c_longlong, c_int, c_int, c_int,
                           c_int, _P, c_int, _P],
@@ -100,6 +101,11 @@ def set_pairs(on: bool) -> None:
     """Products of long prompt portions on pairs of CTAs (`tcgen05.mma.cta_group::2`) or on single CTAs
     (the default: measured level or faster)."""
     ops._fn("sm100", "rllm_tc_gemm_set_pairs")(int(on))
+
+
+def set_token_rows(on: bool) -> None:
+    """Gate/up products of portions of 128 tokens and more with the tokens on the accumulator's rows."""
+    ops._fn("sm100", "rllm_tc_gemm_set_token_rows")(int(on))
 
 
 def gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
