@@ -859,6 +859,9 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
         // conflicts), and from there each of the 256 threads takes, for one token, two groups of 8
         // neighbouring rows: values, partners and angles as 16-byte loads, the rotated result as one
         // 16-byte store into C and one into the cache.
+        // (a row's place in the buffer has bit 2 flipped in the upper half of each 64 rows, so that the
+        // eight threads of a 16-byte read, 8 rows apart, meet 32 different banks)
+        auto xrow = [](int r_) { return r_ ^ (((r_ >> 5) & 1) << 2); };
         const RopeArgs& r = p.rope;
         const int et = (warp - 2) * 32 + lane, tt = et >> 3, q8 = (et & 7) * 8;
         const int half = r.rot_dim >> 1;
@@ -915,7 +918,7 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
             tmem_ld16(taddr + c0 + 16 * grp, g);
             tmem_ld_wait();
 #pragma unroll
-            for (int jj = 0; jj < 16; ++jj) xch[(16 * grp + jj) * XS + row] = __uint_as_float(g[jj]);
+            for (int jj = 0; jj < 16; ++jj) xch[(16 * grp + jj) * XS + xrow(row)] = __uint_as_float(g[jj]);
           }
           epilogue8_sync();
           const int t = t0 + c0 + tt;
@@ -925,12 +928,12 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
 #pragma unroll
             for (int k = 0; k < 2; ++k) {
               if (!g_live[k]) continue;
-              const float4 v0 = *reinterpret_cast<const float4*>(xr + q8 + 64 * k);
-              const float4 v1 = *reinterpret_cast<const float4*>(xr + q8 + 64 * k + 4);
+              const float4 v0 = *reinterpret_cast<const float4*>(xr + xrow(q8 + 64 * k));
+              const float4 v1 = *reinterpret_cast<const float4*>(xr + xrow(q8 + 64 * k + 4));
               float o[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
               if (g_turn[k]) {
-                const float4 w0 = *reinterpret_cast<const float4*>(xr + g_part[k]);
-                const float4 w1 = *reinterpret_cast<const float4*>(xr + g_part[k] + 4);
+                const float4 w0 = *reinterpret_cast<const float4*>(xr + xrow(g_part[k]));
+                const float4 w1 = *reinterpret_cast<const float4*>(xr + xrow(g_part[k] + 4));
                 const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
                 float cs[8], sn[8];
                 if (r.cos_sin != nullptr) {
