@@ -73,14 +73,14 @@ def cmd_gemm(a) -> None:
         N, K, epi_name = SHAPES[a.shape]
     else:
         N, K, epi_name = a.n, a.k, a.epilogue
+    sm100.set_pairs(a.pairs)
+    sm100.set_token_rows(not a.weight_rows)
     if epi_name == "rope":
         return cmd_gemm_rope(a, N, K)
     epi = EPI[epi_name]
     rows = 2 * N if epi == ops.EPI_SWIGLU else N
     copies = max(1, min(a.copies, int(2e9 // (rows * K * 2)) or 1))
     ws = [torch.randn(rows, K, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
-    sm100.set_pairs(a.pairs)
-    sm100.set_token_rows(not a.weight_rows)
     split = a.ranges if a.ranges > 1 else not a.no_split      # a number: that many ranges of K (tcgen05 small tiles)
     for T in a.tokens:
         out = torch.zeros(T, N, device=DEV, dtype=torch.float32) if epi == ops.EPI_ACCUM_F32 else None
