@@ -375,12 +375,8 @@ attn_decode_kernel(const DecParams p) {
 template <int HD>
 int launch_dec(const DecParams& p, int num_seqs, cudaStream_t s) {
   typedef DCfg<HD> C;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             C::smem_bytes(16)) != cudaSuccess) { cudaGetLastError(); return -5; }
-    configured = true;
-  }
+  static bool configured[64] = {};
+  if (allow_dynamic_smem(attn_decode_kernel<HD>, C::smem_bytes(16), configured)) return -5;
   dim3 grid(p.nkv, num_seqs, p.splits);
   if (grid.y > 65535) return ERR_TOO_LARGE;
   return launch_ex(attn_decode_kernel<HD>, grid, dim3(C::THREADS), C::smem_bytes(p.nh / p.nkv), s, p.splits, p);

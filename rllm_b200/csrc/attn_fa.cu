@@ -328,13 +328,7 @@ int launch_fa(const FaParams& p, int num_seqs, int max_rows, cudaStream_t s) {
   constexpr int BM = 16 * NWARPS;
   constexpr int SMEM = 4 * BN * HD * 2;
   static bool configured[64] = {};             // the attribute belongs to a device's copy of the kernel
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return -5; }
-  if (!configured[dev]) {
-    if (cudaFuncSetAttribute(fa_paged_kernel<HD, NWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             SMEM) != cudaSuccess) { cudaGetLastError(); return -5; }
-    configured[dev] = true;
-  }
+  if (allow_dynamic_smem(fa_paged_kernel<HD, NWARPS>, SMEM, configured)) return -5;
   dim3 grid((max_rows + BM - 1) / BM, p.nkv * p.splits, num_seqs);
   if (grid.y > 65535 || grid.z > 65535) return ERR_TOO_LARGE;
   return launch_ex(fa_paged_kernel<HD, NWARPS>, grid, dim3(NWARPS * 32), SMEM, s, 1, p);

@@ -584,12 +584,8 @@ int cache_map(CUtensorMap* out, const void* ptr, long long planes, int page_size
 
 template <int HD, bool TMA>
 int launch_pf(const CUtensorMap& mk, const CUtensorMap& mv, const PfParams& p, int ctas, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Shape<HD>::SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return -5; }
-    configured = true;
-  }
+  static bool configured[64] = {};
+  if (allow_dynamic_smem(attn_prefill_tc_kernel<HD, TMA>, Shape<HD>::SMEM_BYTES, configured)) return -5;
   return launch_ex(attn_prefill_tc_kernel<HD, TMA>, dim3(ctas), dim3(THREADS), Shape<HD>::SMEM_BYTES, s, 1, mk, mv, p);
 }
 

@@ -86,6 +86,23 @@ static inline bool pdl_enabled() {
   return v != 0;
 }
 
+// More than 48 KB of dynamic shared memory has to be allowed per kernel, and the permission belongs to a
+// device's copy of the kernel: `done` (one static array per kernel instantiation) remembers which devices
+// have it. Returns 0 or -5.
+template <typename K>
+static inline int allow_dynamic_smem(K kernel, int bytes, bool (&done)[64]) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return -5; }
+  if (!done[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+      cudaGetLastError();
+      return -5;
+    }
+    done[dev] = true;
+  }
+  return 0;
+}
+
 // Launch with the attributes this library uses: programmatic stream serialization, and a
 // thread-block cluster of (1, 1, cluster_z) when cluster_z > 1.
 template <typename... KArgs, typename... Args>

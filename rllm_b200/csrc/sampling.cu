@@ -635,12 +635,8 @@ RLLM_API int rllm_sample(const float* logits, int R, int V, const float* tempera
   while (splits < SAMPLE_SPLIT && (V + splits - 1) / splits > SAMPLE_SLICE_MAX / 2) splits *= 2;
   const int per = ((V + splits - 1) / splits + 3) & ~3;
   if (per <= SAMPLE_SLICE_MAX) {
-    static bool configured = false;
-    if (!configured) {
-      if (cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               SAMPLE_SLICE_MAX * 4) != cudaSuccess) { cudaGetLastError(); return -5; }
-      configured = true;
-    }
+    static bool configured[64] = {};
+    if (allow_dynamic_smem(sample_cluster_kernel, SAMPLE_SLICE_MAX * 4, configured)) return -5;
     return launch_ex(sample_cluster_kernel, dim3(R, 1, splits), dim3(THREADS), (size_t)per * 4, (cudaStream_t)stream,
                      splits, logits, V, temperature, top_k, top_p, min_p, uniform, out, splits, per);
   }

@@ -321,13 +321,7 @@ template <int EPI, bool NORM, int NCH>
 int launch(const Params& p, int ctas, cudaStream_t s) {
   typedef Cfg C;
   static bool configured[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return -5; }
-  if (!configured[dev]) {
-    if (cudaFuncSetAttribute(stream_gemm_kernel<EPI, NORM, NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             C::SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return -5; }
-    configured[dev] = true;
-  }
+  if (allow_dynamic_smem(stream_gemm_kernel<EPI, NORM, NCH>, C::SMEM_BYTES, configured)) return -5;
   return launch_ex(stream_gemm_kernel<EPI, NORM, NCH>, dim3(ctas), dim3(C::THREADS), C::SMEM_BYTES, s, 1, p);
 }
 

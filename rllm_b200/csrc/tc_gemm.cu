@@ -1274,24 +1274,16 @@ int cached_map(CUtensorMap* out, const void* ptr, long long rows, long long cols
 template <int BN, int EPI, bool NORM>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t s) {
   typedef Cfg<BN, EPI == EPI_SWIGLU> C;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(tc_gemm_kernel<BN, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             C::SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return -5; }
-    configured = true;
-  }
+  static bool configured[64] = {};
+  if (allow_dynamic_smem(tc_gemm_kernel<BN, EPI, NORM>, C::SMEM_BYTES, configured)) return -5;
   return launch_ex(tc_gemm_kernel<BN, EPI, NORM>, grid, dim3(THREADS_SMALL), C::SMEM_BYTES, s, p.splits, mw, mx, p);
 }
 
 template <int BN, int EPI, bool SWAP = false>
 int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int sm_count, cudaStream_t s) {
   typedef PCfg<BN, EPI == EPI_SWIGLU> C;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(tc_gemm_persistent_kernel<BN, EPI, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             C::SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return -5; }
-    configured = true;
-  }
+  static bool configured[64] = {};
+  if (allow_dynamic_smem(tc_gemm_persistent_kernel<BN, EPI, SWAP>, C::SMEM_BYTES, configured)) return -5;
   if (p.bn < 16 || p.bn > BN || p.bn % 16) return ERR_BAD_SIZE;
   const int tiles = ((p.T + p.bn - 1) / p.bn) * ((p.N + BM - 1) / BM);
   const int ctas = tiles < sm_count ? tiles : sm_count;
@@ -1301,12 +1293,8 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const Params
 template <int BN, int EPI>
 int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int sm_count, cudaStream_t s) {
   typedef PairCfg<BN, EPI == EPI_SWIGLU> C;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(tc_gemm_pair_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             C::SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return -5; }
-    configured = true;
-  }
+  static bool configured[64] = {};
+  if (allow_dynamic_smem(tc_gemm_pair_kernel<BN, EPI>, C::SMEM_BYTES, configured)) return -5;
   const int tiles = ((p.T + BN - 1) / BN) * ((p.N + 2 * BM - 1) / (2 * BM));
   const int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
   // the two CTAs of a pair are neighbours along x: blocks 2i and 2i + 1
