@@ -5,13 +5,17 @@
 // The weight tile is the MMA's A operand (M = 128 weight rows) and the token tile is its B
 // operand (N = BN tokens), so a decode step with a handful of tokens still fills the 128-row MMA
 // and streams every weight byte exactly once. Steps of up to 64 tokens (128 for a narrow weight)
-// run token tiles of 16 or 32 in the first kernel below; more tokens run tiles of 64 to 256 (128
-// with the gate/up pair) in the persistent kernel further down. The accumulator D[weight row (TMEM lane), token (TMEM column)] is read back
-// with tcgen05.ld by four epilogue warps, thread = weight row, and written as C[token][row].
+// run token tiles of 16 or 32 in the first kernel below; more tokens run in the persistent kernel
+// further down, whose token tile is any multiple of 16 up to 256 (128 with the gate/up pair),
+// chosen so that the tiles fill whole waves of CTAs. The accumulator D[weight row (TMEM lane),
+// token (TMEM column)] is read back with tcgen05.ld by the epilogue warps, thread = weight row, and
+// written as C[token][row]. Gate/up pairs of 128 tokens and more exchange the roles: tokens on the
+// accumulator's rows, the tile's 128 gate and 128 up weight rows one operand of 256 columns.
 //
 // One CTA = one 128 x BN output tile over a range of K: warp 0 issues TMA loads into a ring of
 // shared-memory stages, warp 1 issues the MMAs (one thread) and owns the TMEM allocation,
-// warps 2-5 run the epilogue. The small-tile kernel has a second MMA warp (6), see `Cfg::TWO`.
+// warps 2-5 run the epilogue (2-9 in the persistent kernel: one warp alone on a scheduler waits
+// out every instruction's latency). The small-tile kernel has a second MMA warp (6), see `Cfg::TWO`.
 //
 // Fused RMSNorm (NORM variants, steps of up to 64 tokens): X is not read by TMA. The input is the
 // float residual stream h and a norm weight g; warps 2-5 build the B operand themselves, stage
@@ -38,7 +42,8 @@
 //
 // Epilogues: store bf16 | store float (logits) | add into the float residual stream |
 // SwiGLU over a gate/up pair of weight tiles (two accumulators): out = silu(g) * u |
-// rotary position encoding of q and k heads with the write of k and v into the paged cache.
+// rotary position encoding of q and k heads with the write of k and v into the paged cache (in the
+// persistent kernel through shared memory, so that a thread moves 8 neighbouring features of a token).
 // Reference counterparts: gemm_bf16_tc (src/gpu/cuda/shaders/matmul_tc.cu:224-413, wmma),
 // matvec_bf16 (matmul.cu:49-77), fused_gate_up_swiglu_bf16 (moe.cu:86-147), rms_norm
 // (rms_norm.cu:78-115), rotary_embedding (rope.cu:62-77) and copy_to_paged_kv_cache
