@@ -44,7 +44,7 @@ namespace {
 constexpr int ADEC_NW = 6, ADEC_D = 2;           // head size 64
 constexpr int ADEC_NW128 = 4, ADEC_D128 = 3;     // head size 128
 constexpr int ADEC_TILE_KB = 4;                  // K (and V) bytes per tile, in KB
-constexpr int MAX_CLUSTER = 8;
+constexpr int MAX_CLUSTER = 16;       // ranges of a sequence's keys; more than 8 CTAs in a cluster need the kernel's own permission
 
 struct DecParams {
   const bf16* q; int q_stride;
@@ -377,6 +377,18 @@ int launch_dec(const DecParams& p, int num_seqs, cudaStream_t s) {
   typedef DCfg<HD> C;
   static bool configured[64] = {};
   if (allow_dynamic_smem(attn_decode_kernel<HD>, C::smem_bytes(16), configured)) return -5;
+  if (p.splits > 8) {
+    static bool wide[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return -5; }
+    if (!wide[dev]) {
+      if (cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+        cudaGetLastError();
+        return ERR_BAD_SIZE;
+      }
+      wide[dev] = true;
+    }
+  }
   dim3 grid(p.nkv, num_seqs, p.splits);
   if (grid.y > 65535) return ERR_TOO_LARGE;
   return launch_ex(attn_decode_kernel<HD>, grid, dim3(C::THREADS), C::smem_bytes(p.nh / p.nkv), s, p.splits, p);
@@ -386,7 +398,7 @@ int launch_dec(const DecParams& p, int num_seqs, cudaStream_t s) {
 
 // q: [S, ...] bf16, one row per sequence, stride q_stride, head h at h*hd; out likewise.
 // kcache / vcache: [num_pages][nkv][page_size][hd] bf16. kv_lens [S]: keys visible to each
-// sequence's token (its own included). splits: ranges of keys per sequence (1..8, one cluster).
+// sequence's token (its own included). splits: ranges of keys per sequence (1..16, one cluster).
 // `err` is not used (this kernel has no wait that can run out); it keeps the launchers alike.
 RLLM_API int rllm_attention_decode(const void* q, int q_stride, const void* kcache, const void* vcache,
                                    long long num_pages, void* out, int out_stride, const int* kv_lens,

@@ -346,17 +346,23 @@ def decode_supported(q: torch.Tensor, kcache: torch.Tensor, nh: int) -> bool:
 
 
 def decode_splits(num_seqs: int, nkv: int, max_kv_len: int, sm_count: int) -> int:
-    """Ranges the keys of a sequence are cut into (= CTAs per cluster, at most 8). Measured on a
-    B200: a CTA costs about as much as 1,150 keys before its first key, two CTAs fit an SM, and
-    CTAs beyond that wait for a free place; the number of ranges with the least
-    (rounds of CTAs over the places) x (1,150 + keys per range) is taken."""
+    """Ranges the keys of a sequence are cut into (= CTAs per cluster). Measured on a B200: a CTA
+    costs about as much as 1,150 keys before its first key and a range 30 more at the merge, two CTAs
+    fit an SM, and CTAs beyond that wait for a free place; the number of ranges with the least
+    (rounds of CTAs over the places) x (1,150 + keys per range) + 30 x ranges is taken. Up to 8
+    ranges any number; 12 and 16 (clusters beyond the portable size, for one or two long sequences:
+    16,384 keys of one sequence 13.3 us against 18.3 with 8) only while the CTAs leave a quarter of
+    the places free, since a large cluster needs its places inside one GPC (9 ranges of 4 sequences,
+    288 CTAs on 296 places: 16.7 us against 10.8 with 8)."""
     base = max(1, num_seqs * nkv)
     places = 2 * sm_count
     best, best_cost = 1, None
-    for s in range(1, 9):
+    for s in (1, 2, 3, 4, 5, 6, 7, 8, 12, 16):
         if s > 1 and max_kv_len // s < 64:
             break
-        cost = -(-base * s // places) * (1150 + max_kv_len / s)
+        if s > 8 and base * s * 4 > places * 3:
+            break
+        cost = -(-base * s // places) * (1150 + max_kv_len / s) + 30 * s
         if best_cost is None or cost < best_cost:
             best, best_cost = s, cost
     return best

@@ -81,7 +81,7 @@ def test_decode_with_split_keys(splits, nh, nkv, hd, page):
     run(nh, nkv, hd, page, 50, lens=[1, 63, 64, 65, 700, 129], q_lens=[1, 1, 1, 1, 1, 1], splits=splits)
 
 
-@pytest.mark.parametrize("splits", [1, 2, 3, 8])
+@pytest.mark.parametrize("splits", [1, 2, 3, 8, 12, 16])
 @pytest.mark.parametrize("nh,nkv,hd,page,window", [
     (32, 8, 64, 16, None), (8, 1, 128, 8, None), (3, 1, 64, 32, None), (16, 1, 64, 64, 100),
     (4, 4, 128, 16, 70), (12, 4, 64, 8, None), (6, 2, 128, 32, None), (6, 2, 64, 5, None), (2, 1, 128, 3, 40)])
