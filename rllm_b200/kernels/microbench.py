@@ -87,7 +87,7 @@ def cmd_gemm(a) -> None:
         if a.norm:
             h = torch.randn(T, K, device=DEV)
             g = torch.ones(K, device=DEV)
-            fns = [(lambda w=w: sm100.gemm_norm(h, g, 1e-5, w, epi)) for w in ws]
+            fns = [(lambda w=w: sm100.gemm_norm(h, g, 1e-5, w, epi, split=split)) for w in ws]
         else:
             x = torch.randn(T, K, device=DEV, dtype=torch.bfloat16)
             fns = [(lambda w=w: sm100.gemm(x, w, epi, out=out, split=split)) for w in ws]
