@@ -342,6 +342,7 @@ def main():
                "preemptions": st.preemptions, "host_share": round(st.host_share, 4),
                "host_plan_share": round(st.host_plan_s / st.wall_s, 4), "host_launch_share": round(st.host_launch_s / st.wall_s, 4),
                "host_record_share": round(st.host_record_s / st.wall_s, 4), "host_wait_share": round(st.wait_s / st.wall_s, 4),
+               "device_busy": round(st.device_s / st.wall_s, 4),
                "hbm_frac": round(nbytes / dt / 1e9 / pk["hbm_gbs"], 4),
                "flop_frac": round(flops / dt / 1e12 / pk["bf16_tflops_sustained"], 4)}
         res["bound"] = "hbm" if res["hbm_frac"] >= res["flop_frac"] else "tensor"

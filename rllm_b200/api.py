@@ -26,7 +26,8 @@ class StepStats:
     """What the steps of an `LLM` have run and where the host's time went, added up since the last
     `reset()`. `host_*_s`: seconds the host spent planning (scheduler), launching (pages, metadata,
     kernel launches, sampling launches) and recording results; `wait_s`: seconds it waited for a
-    step's tokens to arrive; `wall_s`: seconds inside `LLM.step`. With a step launched ahead the
+    step's tokens to arrive; `wall_s`: seconds inside `LLM.step`; `device_s`: seconds between the CUDA
+    events that bracket each step's launches on the stream (read once the step is over). With a step launched ahead the
     host's work overlaps the device's, so `host_share` says how busy the host is, not how much it
     delays the device. The reference logs tok/s per run (src/commands/run.rs:82-119); this is the
     per-step account behind such a line."""
@@ -43,6 +44,7 @@ class StepStats:
     host_record_s: float = 0.0
     wait_s: float = 0.0
     wall_s: float = 0.0
+    device_s: float = 0.0        # seconds the device worked on the steps (CUDA events around each step's launches)
 
     def reset(self) -> None:
         self.__init__()
@@ -57,7 +59,7 @@ class StepStats:
         return (f"{self.steps} steps, {self.tokens} tokens run ({self.prefill_tokens} of prompts), {self.sampled} drawn, "
                 f"{self.sampled / w:.1f} tok/s; per step {w / max(self.steps, 1) * 1e3:.3f} ms of which host "
                 f"{self.host_share:.1%} (plan {self.host_plan_s / w:.1%}, launch {self.host_launch_s / w:.1%}, "
-                f"record {self.host_record_s / w:.1%}), waiting {self.wait_s / w:.1%}; "
+                f"record {self.host_record_s / w:.1%}), waiting {self.wait_s / w:.1%}, device busy {self.device_s / w:.1%}; "
                 f"{self.h2d_bytes / max(self.steps, 1):.0f} B of metadata a step; {self.preemptions} preemptions")
 
 
@@ -85,6 +87,8 @@ class LLM:
         # and the host copies of the log-probabilities where a request asked for them)
         self._ahead = None
         self._pinned = []                        # host buffers the drawn tokens are copied into, in turn
+        self._timed = []                         # (begin, end) events of steps whose device time is not added up yet
+        self._free_events = []
         self.run_ahead = os.environ.get("RLLM_B200_NO_RUN_AHEAD") != "1"
         self.steps_ahead = 0
         self._warned_positions = False
@@ -134,10 +138,14 @@ class LLM:
             st.kv_positions += start + q
             st.attn_pairs += q * start + q * (q + 1) // 2
         h2d0 = self.engine.h2d_bytes
+        begin, end = self._event_pair()
+        begin.record()
         logits = self.engine.step(self.scheduler.entries(plan), keep=False, feed=feed)
         st.h2d_bytes += self.engine.h2d_bytes - h2d0
         sampled = [p.request for p in plan if p.samples]
         if not sampled:
+            end.record()
+            self._timed.append((begin, end))
             return None
         drawn, lps = self.sampler.draw(logits, [r.params for r in sampled], [r.seed for r in sampled],
                                        [len(r.output) + ahead for r in sampled], [r.output for r in sampled],
@@ -153,6 +161,8 @@ class LLM:
         host = buf[: drawn.numel()]
         drawn_at = torch.cuda.Event()
         drawn_at.record()
+        end.record()
+        self._timed.append((begin, end))
         arrived = torch.cuda.Event()
         lp_host = None
         with torch.cuda.stream(self._copy_stream):
@@ -169,6 +179,17 @@ class LLM:
                 ids.record_stream(self._copy_stream)
             arrived.record()
         return drawn, host, arrived, lp_host
+
+    def _event_pair(self):
+        return self._free_events.pop() if self._free_events else (torch.cuda.Event(enable_timing=True),
+                                                                  torch.cuda.Event(enable_timing=True))
+
+    def _settle_device_time(self) -> None:
+        """Adds up the device time of the steps that are over (their end events have passed)."""
+        while self._timed and self._timed[0][1].query():
+            begin, end = self._timed.pop(0)
+            self.stats.device_s += begin.elapsed_time(end) * 1e-3
+            self._free_events.append((begin, end))
 
     def step(self) -> list[StepOutput]:
         """One scheduler step: plan, run the batch, sample, finish and free.
@@ -218,6 +239,7 @@ class LLM:
             if self._pinned[0][-4:].any() or self._pinned[1][-4:].any():
                 self._ahead = None
                 self.engine.check()              # raises: a kernel gave up waiting, or a token id was out of range
+        self._settle_device_time()
         outs = failed + self.scheduler.advance(plan, tokens, self.engine, logprobs)
         if self._ahead is not None and all(p.request.finished for p in self._ahead[0]):
             self._ahead = None                   # nobody is left to take its tokens

@@ -178,6 +178,15 @@ def test_steps_launched_ahead_change_nothing(dirs, dtype):
                 assert m.abort(rids[3])
         m.engine.cache.check()
         assert m.engine.cache.free_pages() == [64]
+        # the account of the steps: every token run and drawn is counted, the device's time lies inside
+        # the time the steps took and is more than nothing
+        torch.cuda.synchronize()
+        m._settle_device_time()
+        st = m.stats
+        kept = sum(len(m.scheduler.requests[r].output) for r in rids)
+        assert st.steps == steps and kept <= st.sampled <= kept + 2 * len(rids)     # a token drawn ahead for a request that had ended is dropped
+        assert st.prefill_tokens == sum(len(p) for p in prompts) and st.tokens >= st.prefill_tokens + st.sampled - len(rids)
+        assert 0.0 < st.device_s <= st.wall_s * 1.05 and not m._timed
         return log, [m.scheduler.requests[r].output for r in rids], m.steps_ahead
 
     log0, out0, ahead0 = run(False)
