@@ -47,6 +47,88 @@ def test_tc_gemm_epilogues(T, N, K, split):
     assert torch.equal(again, out32)
 
 
+@pytest.mark.parametrize("seed", range(6))
+def test_products_of_random_sizes(seed):
+    """Portions of 65 to 900 tokens against weights of any height and depth the kernels take (steps of 8):
+    token tiles of every width the launcher may choose, partial tiles on every edge, an output with a
+    row stride of its own, with and without the kernel that puts the tokens on the accumulator's rows."""
+    import random
+    from rllm_b200.kernels import ops, sm100
+    r = random.Random(seed)
+    for _ in range(4):
+        T, N, K = r.randint(65, 900), 8 * r.randint(1, 90), 8 * r.randint(1, 80)
+        x, w = rnd(T, K, seed=seed + 1), rnd(2 * N, K, seed=seed + 2, scale=K ** -0.5)
+        xd, wd = x.to(DEV), w.to(DEV)
+        w1 = wd[:N].contiguous()
+        ref = x.float() @ w[:N].float().t()
+        up = x.float() @ w[N:].float().t()
+        tag = f"T={T} N={N} K={K} plan={sm100.plan(ops.EPI_STORE, T, N, K)}"
+        assert rel(sm100.gemm(xd, w1, ops.EPI_STORE), ref) <= 6e-3, tag
+        assert rel(sm100.gemm(xd, w1, ops.EPI_STORE_F32), ref) <= 2e-5, tag
+        # the residual as a view into a wider buffer: the untouched columns stay as they were
+        wide = torch.randn(T, N + 24, generator=torch.Generator().manual_seed(seed)).to(DEV)
+        keep = wide.clone()
+        res = wide[:, 8: 8 + N]
+        got = sm100.gemm(xd, w1, ops.EPI_ACCUM_F32, out=res)
+        assert rel(got, keep[:, 8: 8 + N].cpu() + ref) <= 2e-5, tag
+        assert torch.equal(wide[:, :8], keep[:, :8]) and torch.equal(wide[:, 8 + N:], keep[:, 8 + N:]), tag
+        want = ref / (1 + torch.exp(-ref)) * up
+        for rows_on in (True, False):
+            sm100.set_token_rows(rows_on)
+            try:
+                assert rel(sm100.gemm(xd, wd, ops.EPI_SWIGLU), want) <= 6e-3, tag + f" token rows {rows_on}"
+            finally:
+                sm100.set_token_rows(True)
+        sm100.check_error(DEV)
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_rotary_epilogue_of_random_sizes(seed):
+    """Long portions through the product with rotation and cache write, at random head counts, head sizes
+    of 16 to 128, page sizes and depths, against the plain formulas; scattered slots, some tokens unwritten."""
+    import random
+    import plain_llama as P
+    from rllm_b200.kernels import ops, sm100
+    r = random.Random(100 + seed)
+    for _ in range(3):
+        hd = r.choice([16, 32, 64, 128])
+        nkv = r.randint(1, 4)
+        nh = nkv * r.randint(1, 4)
+        T, K, page = r.randint(65, 700), 8 * r.randint(2, 60), r.choice([4, 8, 16, 32])
+        N = (nh + 2 * nkv) * hd
+        x, w = rnd(T, K, seed=seed + 1), rnd(N, K, seed=seed + 2, scale=K ** -0.5)
+        g = torch.Generator().manual_seed(seed)
+        positions = torch.randint(0, 9000, (T,), generator=g, dtype=torch.int32)
+        inv_freq = P.rope_inv_freq(hd, 500000.0, None)
+        pages = (T + page - 1) // page + 2
+        slots = torch.randperm(pages * page, generator=g)[:T].to(torch.int32)
+        slots[r.randrange(T)] = -1
+        kc = torch.zeros(pages, nkv, page, hd, dtype=torch.bfloat16, device=DEV)
+        vc = torch.zeros_like(kc)
+        table = ops.rope_table(positions.to(DEV), inv_freq.to(DEV), T)
+        out = sm100.gemm_qkv_rope(x.to(DEV), w.to(DEV), positions.to(DEV), inv_freq.to(DEV), slots.to(DEV), kc, vc,
+                                  nh, nkv, hd, page, hd, table=table)
+        sm100.check_error(DEV)
+        ref = x.float() @ w.float().t()
+        q = P.rope(ref[:, : nh * hd].view(T, nh, hd), positions, inv_freq)
+        k = P.rope(ref[:, nh * hd: (nh + nkv) * hd].view(T, nkv, hd), positions, inv_freq)
+        v = ref[:, (nh + nkv) * hd:].view(T, nkv, hd)
+        scale = float(ref.abs().max())
+        tag = f"T={T} K={K} heads {nh}/{nkv} of {hd}, pages of {page}"
+        got = out.float().cpu()
+        assert float((got[:, : nh * hd].view(T, nh, hd) - q).abs().max()) <= 6e-3 * scale, tag
+        assert float((got[:, nh * hd: (nh + nkv) * hd].view(T, nkv, hd) - k).abs().max()) <= 6e-3 * scale, tag
+        assert float((got[:, (nh + nkv) * hd:].view(T, nkv, hd) - v).abs().max()) <= 6e-3 * scale, tag
+        kcc, vcc = kc.float().cpu(), vc.float().cpu()
+        want_k, want_v = torch.zeros_like(kcc), torch.zeros_like(vcc)
+        for t in range(T):
+            if slots[t] >= 0:
+                want_k[int(slots[t]) // page, :, int(slots[t]) % page] = k[t]
+                want_v[int(slots[t]) // page, :, int(slots[t]) % page] = v[t]
+        assert float((kcc - want_k).abs().max()) <= 6e-3 * scale and float((vcc - want_v).abs().max()) <= 6e-3 * scale, tag
+        assert float(kcc[want_k == 0].abs().sum()) == 0.0, tag            # nothing beside the written slots
+
+
 NORM_SHAPES = [(1, 128, 64), (8, 384, 200), (16, 100, 72), (17, 3072, 2048), (33, 640, 520), (64, 2048, 2048),
                (5, 128256, 256), (8, 2048, 8192), (64, 256, 1000),
                (3, 2048, 2048), (8, 8192, 2048), (8, 3072, 3072), (6, 256, 4096), (2, 48, 96), (4, 128256, 2048)]
