@@ -110,7 +110,9 @@ template <int HD> struct DCfg {
   static constexpr int smem_bytes(int G) { return 1024 + RING_BYTES + merge_floats(G) * 4; }
 };
 
-template <int HD>
+// MAXC: the most ranges (CTAs of a cluster) this instantiation merges, 8 or 16: the merge holds that many
+// addresses and maxima a thread
+template <int HD, int MAXC>
 // (head size 64: 168 registers a thread; six warps twice per SM leave 170)
 __global__ void __launch_bounds__(DCfg<HD>::THREADS)
 attn_decode_kernel(const DecParams p) {
@@ -334,9 +336,9 @@ attn_decode_kernel(const DecParams p) {
     __syncwarp();
     cluster_sync_all();
     {
-      uint32_t bo[MAX_CLUSTER], bm[MAX_CLUSTER], bl[MAX_CLUSTER];
+      uint32_t bo[MAXC], bm[MAXC], bl[MAXC];
 #pragma unroll
-      for (int s = 0; s < MAX_CLUSTER; ++s) {
+      for (int s = 0; s < MAXC; ++s) {
         const uint32_t rk = s < p.splits ? (uint32_t)s : 0u;
         bo[s] = map_to_rank(smem_u32(c_o), rk);
         bm[s] = map_to_rank(smem_u32(c_m), rk);
@@ -346,16 +348,16 @@ attn_decode_kernel(const DecParams p) {
       for (int idx = threadIdx.x; idx < G * HD; idx += THREADS) {
         const int r = idx / HD, d = idx % HD;
         if (r % p.splits != rank) continue;
-        float ms[MAX_CLUSTER];
+        float ms[MAXC];
         float M = -INFINITY;
 #pragma unroll
-        for (int s = 0; s < MAX_CLUSTER; ++s) {
+        for (int s = 0; s < MAXC; ++s) {
           ms[s] = s < p.splits ? ld_cluster_f32(bm[s] + (uint32_t)r * 4) : -INFINITY;
           M = fmaxf(M, ms[s]);
         }
         float L = 0.f, O = 0.f;
 #pragma unroll
-        for (int s = 0; s < MAX_CLUSTER; ++s) {
+        for (int s = 0; s < MAXC; ++s) {
           if (s < p.splits && ms[s] != -INFINITY) {
             const float f = exp2f(ms[s] - M);
             L += ld_cluster_f32(bl[s] + (uint32_t)r * 4) * f;
@@ -372,17 +374,18 @@ attn_decode_kernel(const DecParams p) {
 }
 
 // ------------------------------------------------------------------------------------ host side
-template <int HD>
-int launch_dec(const DecParams& p, int num_seqs, cudaStream_t s) {
+template <int HD, int MAXC>
+int launch_dec_c(const DecParams& p, int num_seqs, cudaStream_t s) {
   typedef DCfg<HD> C;
   static bool configured[64] = {};
-  if (allow_dynamic_smem(attn_decode_kernel<HD>, C::smem_bytes(16), configured)) return -5;
-  if (p.splits > 8) {
+  if (allow_dynamic_smem(attn_decode_kernel<HD, MAXC>, C::smem_bytes(16), configured)) return -5;
+  if (MAXC > 8) {
+    // more than 8 CTAs in a cluster need the kernel's own permission, per device
     static bool wide[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return -5; }
     if (!wide[dev]) {
-      if (cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+      if (cudaFuncSetAttribute(attn_decode_kernel<HD, MAXC>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
         cudaGetLastError();
         return ERR_BAD_SIZE;
       }
@@ -391,7 +394,12 @@ int launch_dec(const DecParams& p, int num_seqs, cudaStream_t s) {
   }
   dim3 grid(p.nkv, num_seqs, p.splits);
   if (grid.y > 65535) return ERR_TOO_LARGE;
-  return launch_ex(attn_decode_kernel<HD>, grid, dim3(C::THREADS), C::smem_bytes(p.nh / p.nkv), s, p.splits, p);
+  return launch_ex(attn_decode_kernel<HD, MAXC>, grid, dim3(C::THREADS), C::smem_bytes(p.nh / p.nkv), s, p.splits, p);
+}
+
+template <int HD>
+int launch_dec(const DecParams& p, int num_seqs, cudaStream_t s) {
+  return p.splits <= 8 ? launch_dec_c<HD, 8>(p, num_seqs, s) : launch_dec_c<HD, 16>(p, num_seqs, s);
 }
 
 }  // namespace
