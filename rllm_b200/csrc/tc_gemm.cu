@@ -1389,7 +1389,10 @@ void plan(int epi, int T, int N, int K, int sm_count, int allow_split, int* bn_o
   // A step of few tokens: token tiles of 16 or 32 (33 to 64 tokens: two tiles of 32 land their
   // parts faster than one of 64), and ranges of K until every SM has a CTA. Up to 128 tokens the
   // same holds for a narrow weight that would give the persistent kernel under a quarter of the SMs.
-  const bool few = T <= 64 || (T <= 128 && splits > 1 && n_tiles * ((T + 63) / 64) * 4 <= sm_count);
+  // (33 to 64 tokens against a weight of many tiles, the output head: one token tile of 64 in the persistent
+  // kernel reads the weight once, two tiles of 32 read it twice)
+  const bool wide_head = T > 32 && T <= 64 && n_tiles >= 4 * sm_count;
+  const bool few = (T <= 64 && !wide_head) || (T <= 128 && splits > 1 && n_tiles * ((T + 63) / 64) * 4 <= sm_count);
   if (few) {
     bn = T <= 16 ? 16 : 32;
     if (bn >= 32) while (splits & (splits - 1)) splits &= splits - 1;     // wider tiles: a power of two
