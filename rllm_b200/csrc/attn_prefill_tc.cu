@@ -174,7 +174,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     for (int i = 0; i < KVS; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
     for (int i = 0; i < SB; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4); }
     for (int i = 0; i < RT; ++i) { mbar_init(&p_full[i], 4); mbar_init(&pv_full[i], 1); }
-    mbar_init(&q_full, RT);
+    mbar_init(&q_full, TMA ? 4 * RT : RT);             // TMA: one arrival per softmax warp, which brings its own rows of Q
     fence_barrier_init();
   }
   __syncthreads();
@@ -302,17 +302,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
           tma_load_3d(v_s + dst, &tmap_v, &kv_full[s], at * 64, off, page * p.nkv + kvh);
         }
       }
-    } else if (warp - 1 < RT) {
-      // warps 1 and 2: the Q rows of one row tile each, meanwhile
-      if (n_t[warp - 1] > 0) {
-        load_q((warp - 1) * PM, PM);
-        cp_async_commit();
-        cp_async_wait<0>();
-        fence_proxy_async();
-        __syncwarp();
-      }
-      if (lane == 0) mbar_arrive(&q_full);
-      if (warp == 2 && lane == 0 && n_steps > 0) {
+    } else if (warp == 2) {
+      // (Q comes from the softmax warps, each thread its own row: one warp fetching a row tile spent 5 us
+      // of every item on the addresses of its 1,024 copies)
+      if (lane == 0 && n_steps > 0) {
         // ... and warp 2 then issues the S products, as far ahead as accumulators are free
         bool ok = true;
         if (!mbar_wait(&q_full, 0u, &abort_flag)) { abort_flag = 1; record_failure(p.err, 27, 0); ok = false; }
@@ -398,6 +391,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     const int tok = valid ? row / G : 0, head = kvh * G + (valid ? row % G : 0);
     const int pos = kv_len - q_len + tok;
     const int lo = p.window > 0 ? pos - p.window + 1 : 0;
+    if (TMA) {
+      // this thread's own row of Q into the A-operand layout (rows beyond the sequence zero), while the
+      // first K and V tiles are on their way
+      const bf16* src = p.q + (size_t)(q0 + tok) * p.q_stride + (size_t)head * HD;
+      const uint32_t drow = q_s + (uint32_t)(g * C::Q_BYTES + r * 128);
+#pragma unroll
+      for (int a = 0; a < C::HA; ++a)
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch)
+          cp_async16z(drow + (uint32_t)(a * C::ATOM_ROWS) + (uint32_t)((ch ^ (r & 7)) << 4), src + a * 64 + ch * 8, valid);
+      cp_async_commit();
+      cp_async_wait<0>();
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&q_full);
+    }
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     const uint32_t pv_addr = lane_addr + C::O_COL + (uint32_t)g * HD;
     const uint32_t prow = p_s + (uint32_t)g * C::P_BYTES + (uint32_t)(r * 128);
@@ -517,6 +526,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
       }
       tc_fence_before();
     }
+  } else if (TMA) {
+    if (lane == 0) mbar_arrive(&q_full);                  // a row tile beyond the sequence's rows: nothing to bring
   }
   }
   }   // items
