@@ -52,6 +52,7 @@ struct DecParams {
   bf16* out; int out_stride;
   const int* kv_lens; const int* block_table; int bt_stride;
   int nh, nkv, page_size, window, splits;
+  int page_shift;       // log2(page_size), or -1 when it is no power of two
   float scale_log2e;
 };
 
@@ -155,6 +156,9 @@ attn_decode_kernel(const DecParams p) {
   const int last_held = pos / p.page_size;
   const int pos_page = bt[last_held];
   const uint32_t ring = smem_u32(smem) + (uint32_t)(warp * D) * C::STAGE_BYTES;   // this warp's stages
+  const int lane_r = lane / CPR, lane_ch = lane % CPR;      // this lane's first key row of a tile and its 16 bytes of a row
+  const size_t page_stride = (size_t)p.nkv * p.page_size * HD;
+  const size_t lane_off = (size_t)kvh * p.page_size * HD + lane_ch * 8;
   bool waited = false;
 
   // Starts the copies of this warp's tile `i` (the (i / NW)-th of the warp) and closes a copy
@@ -164,16 +168,23 @@ attn_decode_kernel(const DecParams p) {
       if (tb + i == last_tile && !waited) { pdl_wait(); waited = true; }
       const uint32_t st = ring + (uint32_t)((i / NW) % D) * C::STAGE_BYTES;
       const int j0 = (tb + i) * TILE;
+      // A lane copies the same 16 bytes of every (32 / CPR)-th key row. What its addresses share is
+      // worked out once per kernel (lane_off, page_stride), and a key's page and place in it are a shift
+      // and a mask where the page size is a power of two: the addresses of a tile's 16 copies were some 400
+      // instructions a lane, as long as the copies took to arrive.
 #pragma unroll
       for (int c = 0; c < CHUNKS; ++c) {
-        const int id = lane + 32 * c;
-        const int r = id / CPR, ch = id % CPR;
+        const int r = lane_r + (32 / CPR) * c;
         const int j = j0 + r;
-        const int pg_idx = j / p.page_size;
+        // (measured: at head size 128 the divisions are the faster code, 27.3 against 28.4 us for 8 sequences
+        // of 4,096 keys; at 64 the shifts, 80.5 against 85.2 us for 64 sequences)
+        const bool shifts = HD == 64 && p.page_shift >= 0;
+        const int pg_idx = shifts ? (j >> p.page_shift) : j / p.page_size;
+        const int off = shifts ? (j & (p.page_size - 1)) : j % p.page_size;
         int page = pg_idx <= last_held ? __ldg(bt + pg_idx) : -1;
         if (page < 0) page = pos_page;
-        const size_t src = (((size_t)page * p.nkv + kvh) * p.page_size + j % p.page_size) * HD + ch * 8;
-        const uint32_t dst = st + tile_off<TILE>(r, ch);
+        const size_t src = (size_t)page * page_stride + lane_off + (size_t)(off * HD);
+        const uint32_t dst = st + tile_off<TILE>(r, lane_ch);
         cp_async16(dst, p.kcache + src);
         cp_async16(dst + C::KV_BYTES, p.vcache + src);
       }
@@ -423,6 +434,8 @@ RLLM_API int rllm_attention_decode(const void* q, int q_stride, const void* kcac
   p.out = (bf16*)out; p.out_stride = out_stride;
   p.kv_lens = kv_lens; p.block_table = block_table; p.bt_stride = bt_stride; p.nh = nh; p.nkv = nkv;
   p.page_size = page_size; p.window = window; p.splits = splits; p.scale_log2e = scale * 1.4426950408889634f;
+  p.page_shift = -1;
+  for (int sft = 0; sft < 31; ++sft) if ((1 << sft) == page_size) p.page_shift = sft;
   cudaStream_t s = (cudaStream_t)stream;
   return hd == 64 ? launch_dec<64>(p, num_seqs, s) : launch_dec<128>(p, num_seqs, s);
 }
