@@ -101,6 +101,11 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Where token column `col` of row `row` lies within the row's 8 floats of a warp's partial sums: rows four
+// apart would meet the same bank, so the column index is flipped by an even number that differs for them (a
+// pair of columns 2t, 2t + 1 stays a pair).
+__device__ __forceinline__ int red_col(int row, int col) { return col ^ (((row >> 2) & 3) << 1); }
+
 // first weight row of a job's tile
 template <int EPI>
 __device__ __forceinline__ int tile_row0(const Params& p, int job, int tile) {
@@ -253,9 +258,11 @@ stream_gemm_kernel(const Params p) {
             for (int kb = 0; kb < 4; ++kb) bcur[kb] = bnext[kb];
           }
         }
+        // (a row's 8 token columns are stored with their index flipped by the row's group of four, red_col:
+        // the epilogue's threads, 16 rows of one token side by side, then meet 16 different banks)
         float* r = red + ((size_t)((jb * 2 + tile) * WARPS + warp)) * (16 * NT);
-        *reinterpret_cast<float2*>(r + g * NT + 2 * t) = make_float2(acc[0], acc[1]);
-        *reinterpret_cast<float2*>(r + (g + 8) * NT + 2 * t) = make_float2(acc[2], acc[3]);
+        *reinterpret_cast<float2*>(r + g * NT + red_col(g, 2 * t)) = make_float2(acc[0], acc[1]);
+        *reinterpret_cast<float2*>(r + (g + 8) * NT + red_col(g + 8, 2 * t)) = make_float2(acc[2], acc[3]);
       }
     }
     __syncthreads();
@@ -266,8 +273,8 @@ stream_gemm_kernel(const Params p) {
       float s0 = 0.f, s1 = 0.f;
 #pragma unroll
       for (int w = 0; w < WARPS; ++w) {
-        s0 += red[(size_t)((jb * 2) * WARPS + w) * (16 * NT) + r * NT + tok];
-        if (TILES == 2) s1 += red[(size_t)((jb * 2 + 1) * WARPS + w) * (16 * NT) + r * NT + tok];
+        s0 += red[(size_t)((jb * 2) * WARPS + w) * (16 * NT) + r * NT + red_col(r, tok)];
+        if (TILES == 2) s1 += red[(size_t)((jb * 2 + 1) * WARPS + w) * (16 * NT) + r * NT + red_col(r, tok)];
       }
       if (NORM) {
         float sq = 0.f;
