@@ -351,16 +351,18 @@ def decode_splits(num_seqs: int, nkv: int, max_kv_len: int, sm_count: int) -> in
     fit an SM, and CTAs beyond that wait for a free place; the number of ranges with the least
     (rounds of CTAs over the places) x (1,150 + keys per range) + 30 x ranges is taken. Up to 8
     ranges any number; 12 and 16 (clusters beyond the portable size, for one or two long sequences:
-    16,384 keys of one sequence 13.3 us against 18.3 with 8) only while the CTAs leave a quarter of
-    the places free, since a large cluster needs its places inside one GPC (9 ranges of 4 sequences,
-    288 CTAs on 296 places: 16.7 us against 10.8 with 8)."""
+    16,384 keys of one sequence 13.3 us against 18.3 with 8) only from 16,384 keys on and while the CTAs
+    leave a quarter of the places free: a large cluster needs its places inside one GPC (9 ranges of 4
+    sequences, 288 CTAs on 296 places: 16.7 us against 10.8 with 8), and inside a decode step, behind a
+    kernel whose CTAs fill whole SMs, it starts later than a small one (4,096 keys: 6.3 us against 6.9
+    alone, but the step at batch 1 0.621 ms against 0.615, at batch 2 0.692 against 0.642)."""
     base = max(1, num_seqs * nkv)
     places = 2 * sm_count
     best, best_cost = 1, None
     for s in (1, 2, 3, 4, 5, 6, 7, 8, 12, 16):
         if s > 1 and max_kv_len // s < 64:
             break
-        if s > 8 and base * s * 4 > places * 3:
+        if s > 8 and (base * s * 4 > places * 3 or max_kv_len < 16384):
             break
         cost = -(-base * s // places) * (1150 + max_kv_len / s) + 30 * s
         if best_cost is None or cost < best_cost:
