@@ -164,7 +164,8 @@ def main():
     full_layers = full_cfg["num_hidden_layers"]
     a.layers = a.layers or full_layers
     cfg = dict(full_cfg, num_hidden_layers=a.layers)
-    batches = [a.batch] if a.no_points else sorted({1, a.batch, 64})
+    # the headline batch is measured first, right after the prefill, the other two points after it
+    batches = [a.batch] if a.no_points else [a.batch] + [b for b in (1, 64) if b != a.batch]
     pages = max(batches) * (CONTEXT // PAGE + 1) + 64
     llm = LLM(cfg, dtype="bfloat16", seed=0, page_size=PAGE, num_pages=pages, max_active=max(batches),
               max_tokens_per_step=8192)
