@@ -1366,7 +1366,8 @@ int launch_bn(int bn, bool norm, const CUtensorMap& mw, const CUtensorMap& mx, c
 // 99 us against 110.
 bool g_token_rows = true;
 
-void plan(int epi, int T, int N, int K, int sm_count, int allow_split, int* bn_out, int* splits_out) {
+void plan(int epi, int T, int N, int K, int sm_count, int allow_split, int* bn_out, int* splits_out,
+          bool* few_out = nullptr) {
   const bool dual = epi == EPI_SWIGLU;
   const int n_tiles = (N + BM - 1) / BM;
   int bn, splits = 1;
@@ -1387,7 +1388,9 @@ void plan(int epi, int T, int N, int K, int sm_count, int allow_split, int* bn_o
     if (forced > 0) splits = forced < kb / 2 ? (forced < MAX_CLUSTER ? forced : MAX_CLUSTER) : (kb / 2 > 0 ? kb / 2 : 1);
   }
   // A step of few tokens: token tiles of 16 or 32 (33 to 64 tokens: two tiles of 32 land their
-  // parts faster than one of 64), and ranges of K until every SM has a CTA. Up to 128 tokens the
+  // parts faster than one of 64, which reads the weights once but has three stages and one issuing
+  // thread: at 64 tokens gate/up 21.8 against 19.2 us, down 16.2 against 12.3, O 10.5 against 7.3),
+  // and ranges of K until every SM has a CTA. Up to 128 tokens the
   // same holds for a narrow weight that would give the persistent kernel under a quarter of the SMs.
   // (33 to 64 tokens against a weight of many tiles, the output head: one token tile of 64 in the persistent
   // kernel reads the weight once, two tiles of 32 read it twice)
@@ -1417,6 +1420,7 @@ void plan(int epi, int T, int N, int K, int sm_count, int allow_split, int* bn_o
   }
   *bn_out = bn;
   *splits_out = splits;
+  if (few_out) *few_out = few;
 }
 
 // X null: the fused-norm variants (norm must be given, T <= NORM_MAX_T).
@@ -1435,12 +1439,15 @@ int run(int epi, const void* X, long long ldx, const NormArgs* norm, const void*
   int rc = get_encoder();
   if (rc) return rc;
   int bn, splits;
-  plan(epi, T, N, K, sm_count, allow_split, &bn, &splits);
+  bool few;
+  plan(epi, T, N, K, sm_count, allow_split, &bn, &splits, &few);
+  const bool many = !few;            // the persistent kernel (no ranges of K, no norm in front)
+  if (many && norm) return ERR_BAD_SIZE;
   const bool dual = epi == EPI_SWIGLU;
   CUtensorMap mw, mx;
   if ((rc = cached_map(&mw, W, dual ? 2LL * N : N, K, K, BM))) return rc;
   // long portions: a tile of 256 weight rows x bn tokens on a pair of CTAs, each loading half of the token tile
-  const bool pair = g_pairs && !norm && epi != EPI_QKV_ROPE && sm_count >= 2 && bn >= 64 && T >= (dual ? 128 : 256);
+  const bool pair = g_pairs && !norm && epi != EPI_QKV_ROPE && sm_count >= 2 && many && T >= (dual ? 128 : 256);
   if (pair) bn = dual ? 128 : 256;                                   // the pair kernel's tile is fixed
   if (norm) mx = mw;                                                 // not used by the kernel
   else if ((rc = make_map(&mx, X, T, K, ldx, pair ? bn / 2 : bn))) return rc;
@@ -1460,14 +1467,14 @@ int run(int epi, const void* X, long long ldx, const NormArgs* norm, const void*
       case EPI_SWIGLU: return launch_pair<128, EPI_SWIGLU>(mw, mx, p, sm_count, s);
     }
   }
-  if (bn >= 64 && rope) {
+  if (many && rope) {
     // the persistent kernel's rotary epilogue moves groups of 8 neighbouring features as 16 bytes
     if (rope->hd % 16 || rope->rot_dim % 16 || ldc % 8) return ERR_BAD_SIZE;
     if (((uintptr_t)Cout | (uintptr_t)rope->kcache | (uintptr_t)rope->vcache | (uintptr_t)rope->cos_sin) & 15) return ERR_BAD_ALIGN;
   }
-  if (bn >= 64 && dual && g_token_rows && T >= 128 && N % 8 == 0 && ldc % 8 == 0 && !((uintptr_t)Cout & 15))
+  if (many && dual && g_token_rows && T >= 128 && N % 8 == 0 && ldc % 8 == 0 && !((uintptr_t)Cout & 15))
     return launch_persistent<128, EPI_SWIGLU, true>(mw, mx, p, sm_count, s);
-  if (bn >= 64) {
+  if (many) {
     // many tokens: the persistent kernel with two accumulator sets
     switch (epi) {
       case EPI_STORE: return launch_many<EPI_STORE>(bn, mw, mx, p, sm_count, s);

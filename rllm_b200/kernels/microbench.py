@@ -112,11 +112,17 @@ def cmd_gemm_rope(a, N: int, K: int) -> None:
         pos = torch.arange(T, device=DEV, dtype=torch.int32)
         slots = torch.arange(T, device=DEV, dtype=torch.int32)
         table = ops.rope_table(pos, inv_freq, T)
-        x = torch.randn(T, K, device=DEV, dtype=torch.bfloat16)
+        split = a.ranges if a.ranges > 1 else not a.no_split
+        if a.norm:
+            h = torch.randn(T, K, device=DEV)
+            g = torch.ones(K, device=DEV)
+            x, norm = None, (h, g, 1e-5)
+        else:
+            x, norm = torch.randn(T, K, device=DEV, dtype=torch.bfloat16), None
         fns = [(lambda w=w: sm100.gemm_qkv_rope(x, w, pos, inv_freq, slots, kc, vc, nh, nkv, hd, page, hd,
-                                                split=not a.no_split, table=table)) for w in ws]
-        run(fns, a.plain, f"gemm qkv+rope T={T} N={N} K={K} heads {nh}/{nkv} of {hd}", nbytes=N * K * 2,
-            flops=2.0 * T * N * K)
+                                                split=split, table=table, norm=norm)) for w in ws]
+        run(fns, a.plain, f"gemm qkv+rope T={T} N={N} K={K} heads {nh}/{nkv} of {hd}" + (" norm" if a.norm else "")
+            + (f" ranges asked {a.ranges}" if a.ranges > 1 else ""), nbytes=N * K * 2, flops=2.0 * T * N * K)
     sm100.check_error(DEV)
 
 
