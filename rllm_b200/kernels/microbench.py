@@ -129,12 +129,19 @@ def cmd_gemm_rope(a, N: int, K: int) -> None:
 def cmd_attn_decode(a) -> None:
     nh, nkv, hd, page = a.heads, a.kv_heads, a.head_dim, a.page
     pages_per = (a.context + page - 1) // page
-    npages = a.batch * pages_per
+    used = a.batch * pages_per
+    npages = max(used, a.pool_pages)          # a pool larger than what the sequences hold spreads their pages
     per_copy = npages * nkv * page * hd * 2 * 2
     copies = max(1, min(a.copies, int(4e9 // per_copy) or 1))
     caches = [(torch.randn(npages, nkv, page, hd, device=DEV, dtype=torch.bfloat16),
                torch.randn(npages, nkv, page, hd, device=DEV, dtype=torch.bfloat16)) for _ in range(copies)]
-    bt = torch.randperm(npages, device=DEV).to(torch.int32).view(a.batch, pages_per).contiguous()
+    if a.page_order == "random":              # a sequence's pages anywhere in the pool
+        order = torch.randperm(npages, device=DEV)[:used]
+    elif a.page_order == "reversed":          # each sequence a run of neighbouring pages, falling
+        order = torch.arange(used - 1, -1, -1, device=DEV)
+    else:                                     # each sequence a run of neighbouring pages, rising
+        order = torch.arange(used, device=DEV)
+    bt = order.to(torch.int32).view(a.batch, pages_per).contiguous()
     lens = torch.full((a.batch,), a.context, dtype=torch.int32, device=DEV)
     q = torch.randn(a.batch, nh * hd, device=DEV, dtype=torch.bfloat16)
     out = torch.empty_like(q)
@@ -143,7 +150,8 @@ def cmd_attn_decode(a) -> None:
     for sp in (a.splits or [auto]):
         fns = [(lambda kc=kc, vc=vc: sm100.attention_decode(q, kc, vc, lens, bt, nh, hd ** -0.5, None, a.context,
                                                             splits=sp, out=out)) for kc, vc in caches]
-        run(fns, a.plain, f"attn-decode B={a.batch} ctx={a.context} hd={hd} page={page} ranges={sp} (auto {auto})",
+        run(fns, a.plain, f"attn-decode B={a.batch} ctx={a.context} hd={hd} page={page} pages {a.page_order} of {npages} "
+            f"ranges={sp} (auto {auto})",
             nbytes=nbytes)
 
 
@@ -222,6 +230,8 @@ def main(argv=None) -> int:
                 p.add_argument("--batch", type=int, default=8)
                 p.add_argument("--context", type=int, default=3000)
                 p.add_argument("--splits", type=ints, default=None)
+                p.add_argument("--page-order", choices=["random", "rising", "reversed"], default="random")
+                p.add_argument("--pool-pages", type=int, default=0, help="pages of the pool (at least what the sequences hold)")
             else:
                 p.add_argument("--tokens", type=ints, default=[2048])
                 p.add_argument("--kernel", choices=["tc", "fa"], default="tc",
