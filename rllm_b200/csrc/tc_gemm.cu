@@ -251,7 +251,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   const int kb_end = (int)((long long)(rank + 1) * kb_total / p.splits);
   const int n_kb = kb_end - kb_begin;
   const bool two_sets = C::TWO && n_kb >= 2;       // else the second accumulator set is never written
-  // float [ranks][slots per rank][ACCS][BM]: partial columns pushed here by every rank
+  // partial columns pushed here by every rank: float [ranks][slots per rank][ACCS][BM] (tiles of 16),
+  // float4 [ranks][ACCS][groups of four columns per rank][BM] (wider tiles)
   float* land = reinterpret_cast<float*>(C::DEDICATED ? smem + C::RING_BYTES : smem);
 
   if (threadIdx.x == 0) {
@@ -538,12 +539,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           for (int q = 0; q < 4; ++q) {
             const int c = c0 + 4 * q;
             if (c < ncols) {
+              // [rank][accumulator][group of four columns][row] x 16 bytes: the rows of a warp lie side
+              // by side, so neither these stores nor the owner's loads meet in a bank
               const int owner = c / cpr, slot = c % cpr;
-              const uint32_t off = (uint32_t)((((rank * ACCS) * BM + row) * cpr + slot) * 4);
+              const uint32_t off = (uint32_t)(((((rank * ACCS) * (cpr >> 2) + (slot >> 2)) * BM) + row) * 16);
               const uint32_t dst = (clustered ? map_to_rank(land_cta, (uint32_t)owner) : land_cta) + off;
               st_cluster_v4(dst, __uint_as_float(g[4 * q]), __uint_as_float(g[4 * q + 1]),
                             __uint_as_float(g[4 * q + 2]), __uint_as_float(g[4 * q + 3]));
-              if (DUAL) st_cluster_v4(dst + (uint32_t)(BM * cpr * 4), __uint_as_float(u[4 * q]),
+              if (DUAL) st_cluster_v4(dst + (uint32_t)((cpr >> 2) * BM * 16), __uint_as_float(u[4 * q]),
                                       __uint_as_float(u[4 * q + 1]), __uint_as_float(u[4 * q + 2]),
                                       __uint_as_float(u[4 * q + 3]));
             }
@@ -596,15 +599,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 #pragma unroll
           for (int s = 0; s < MAX_CLUSTER; ++s) {              // rank order
             if (s < p.splits) {
-              const float* base = land + (size_t)(s * ACCS) * BM * cpr + slot;
-              const float4 vg = *reinterpret_cast<const float4*>(base + (size_t)row * cpr);
+              const float4* base = reinterpret_cast<const float4*>(land) + (size_t)((s * ACCS) * (cpr >> 2) + (slot >> 2)) * BM;
+              const float4 vg = base[row];
               g[0] += vg.x; g[1] += vg.y; g[2] += vg.z; g[3] += vg.w;
               if (DUAL) {
-                const float4 vu = *reinterpret_cast<const float4*>(base + (size_t)(BM + row) * cpr);
+                const float4 vu = base[(size_t)(cpr >> 2) * BM + row];
                 u[0] += vu.x; u[1] += vu.y; u[2] += vu.z; u[3] += vu.w;
               }
               if (ROPE) {
-                const float4 vw = *reinterpret_cast<const float4*>(base + (size_t)prow * cpr);
+                const float4 vw = base[prow];
                 w[0] += vw.x; w[1] += vw.y; w[2] += vw.z; w[3] += vw.w;
               }
               if (NORM) {
