@@ -1392,7 +1392,7 @@ void plan(int epi, int T, int N, int K, int sm_count, int allow_split, int* bn_o
   }
   // A step of few tokens: token tiles of 16 or 32 (33 to 64 tokens: two tiles of 32 land their
   // parts faster than one of 64, which reads the weights once but has three stages and one issuing
-  // thread: at 64 tokens gate/up 21.8 against 19.2 us, down 16.2 against 12.3, O 10.5 against 7.3),
+  // thread: at 64 tokens gate/up 20.8 against 19.3 us, down 13.7 against 12.2, O 8.3 against 7.3),
   // and ranges of K until every SM has a CTA. Up to 128 tokens the
   // same holds for a narrow weight that would give the persistent kernel under a quarter of the SMs.
   // (33 to 64 tokens against a weight of many tiles, the output head: one token tile of 64 in the persistent
