@@ -676,28 +676,31 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 // cores do not wait for the epilogue. No ranges of K and no norm in front here; the rotary epilogue
 // exists but is chosen only up to 128 tokens (beyond, the row-parallel rotation kernel is faster
 // than rotating in four epilogue warps).
-template <int BN, bool DUAL> struct PCfg {
+// WR: weight rows of a tile per accumulator. 128, or 64 for the kernel with the tokens on the accumulator's
+// rows when the 128-row tiles would leave most SMs without one (few tokens).
+template <int BN, bool DUAL, int WR = BM> struct PCfg {
   static constexpr int A_TILES = DUAL ? 2 : 1;
-  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int A_BYTES = WR * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int W_BYTES = A_TILES * A_BYTES;
   static constexpr int STAGE_BYTES = W_BYTES + B_BYTES;
   static constexpr int STAGES_RAW = 208 * 1024 / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES;
-  static constexpr int ACC_COLS = A_TILES * BN;                 // one accumulator set
+  static constexpr int ACC_COLS = WR == BM ? A_TILES * BN : A_TILES * WR;   // one accumulator set (WR < 128: tokens on the rows)
   static constexpr int TMEM_COLS = 2 * ACC_COLS <= 64 ? 64 : 2 * ACC_COLS <= 128 ? 128 : 2 * ACC_COLS <= 256 ? 256 : 512;
   static_assert(2 * ACC_COLS <= 512, "two accumulator sets must fit in TMEM");
 };
 
-template <int BN, int EPI, bool SWAP>
+template <int BN, int EPI, bool SWAP, int WR = BM>
 __global__ void __launch_bounds__(THREADS_MANY, 1)
 tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                           const Params p) {
   constexpr bool DUAL = (EPI == EPI_SWIGLU);
   constexpr bool ROPE = (EPI == EPI_QKV_ROPE);
-  static_assert(!SWAP || (DUAL && BN == 128), "tokens on the accumulator's rows: gate/up pairs, 128 tokens x 128 features a tile");
-  typedef PCfg<BN, DUAL> C;
+  static_assert(!SWAP || (DUAL && BN == 128), "tokens on the accumulator's rows: gate/up pairs, 128 tokens x 128 or 64 features a tile");
+  static_assert(WR == BM || (SWAP && WR == 64), "tiles of 64 weight rows only with the tokens on the accumulator's rows");
+  typedef PCfg<BN, DUAL, WR> C;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[C::STAGES];
   __shared__ __align__(8) uint64_t empty_bar[C::STAGES];
@@ -716,7 +719,7 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int bn = p.bn;                                   // tokens per tile: chosen by the host so that the tiles fill whole waves
-  const int t_tiles = (p.T + bn - 1) / bn, n_tiles = (p.N + BM - 1) / BM;
+  const int t_tiles = (p.T + bn - 1) / bn, n_tiles = (p.N + WR - 1) / WR;
   const int tiles = t_tiles * n_tiles;
   const int n_kb = (p.K + BK - 1) / BK;
 
@@ -744,7 +747,7 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
       int it = 0, issued = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-        const int t0 = (tile % t_tiles) * bn, n0 = (tile / t_tiles) * BM;
+        const int t0 = (tile % t_tiles) * bn, n0 = (tile / t_tiles) * WR;
         for (int kb = 0; kb < n_kb; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (uint32_t)(it / C::STAGES) & 1u;
@@ -768,9 +771,9 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      // SWAP: the 128 tokens are the rows and the tile's 128 gate and 128 up weight rows, which lie one
-      // after the other in a stage, the 256 columns of one product
-      const uint32_t idesc = SWAP ? umma_idesc_bf16(BM, 2 * BM) : umma_idesc_bf16(BM, bn);
+      // SWAP: the 128 tokens are the rows and the tile's 128 (64) gate and 128 (64) up weight rows, which
+      // lie one after the other in a stage, the 256 (128) columns of one product
+      const uint32_t idesc = SWAP ? umma_idesc_bf16(BM, 2 * WR) : umma_idesc_bf16(BM, bn);
       int it = 0, ti = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++ti) {
@@ -816,7 +819,7 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
     int ti = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++ti) {
-      const int t0 = (tile % t_tiles) * bn, n0 = (tile / t_tiles) * BM;
+      const int t0 = (tile % t_tiles) * bn, n0 = (tile / t_tiles) * WR;
       const int n = n0 + row;
       const int buf = ti & 1, use = ti >> 1;
       ok = mbar_wait(&acc_full[buf], (uint32_t)use & 1u, &abort_flag);
@@ -831,17 +834,17 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(buf * C::ACC_COLS);
       if (SWAP) {
-        // this thread's row is a token; its gate values are columns 0..127, its up values 128..255. The
-        // first warp of a quarter takes features 0..63, the second 64..127, 32 at a time, and writes
-        // them as 16-byte pieces of the token's output row.
+        // this thread's row is a token; its gate values are columns 0..WR-1, its up values WR..2 WR-1. The
+        // first warp of a quarter takes the lower half of the features, the second the upper, 32 at a
+        // time, and writes them as 16-byte pieces of the token's output row.
         const int t = t0 + row;
         bf16* crow = (bf16*)p.C + (size_t)t * p.ldc + n0;
 #pragma unroll 1
-        for (int c0 = grp * 64; c0 < grp * 64 + 64; c0 += 32) {
+        for (int c0 = grp * (WR / 2); c0 < grp * (WR / 2) + WR / 2; c0 += 32) {
           if (n0 + c0 >= p.N) break;
           uint32_t g[32], u[32];
           tmem_ld32(taddr + c0, g);
-          tmem_ld32(taddr + BM + c0, u);
+          tmem_ld32(taddr + WR + c0, u);
           tmem_ld_wait();
           if (t < p.T) {
 #pragma unroll
@@ -1287,15 +1290,15 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 g
   return launch_ex(tc_gemm_kernel<BN, EPI, NORM>, grid, dim3(THREADS_SMALL), C::SMEM_BYTES, s, p.splits, mw, mx, p);
 }
 
-template <int BN, int EPI, bool SWAP = false>
+template <int BN, int EPI, bool SWAP = false, int WR = BM>
 int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int sm_count, cudaStream_t s) {
-  typedef PCfg<BN, EPI == EPI_SWIGLU> C;
+  typedef PCfg<BN, EPI == EPI_SWIGLU, WR> C;
   static bool configured[64] = {};
-  if (allow_dynamic_smem(tc_gemm_persistent_kernel<BN, EPI, SWAP>, C::SMEM_BYTES, configured)) return -5;
+  if (allow_dynamic_smem(tc_gemm_persistent_kernel<BN, EPI, SWAP, WR>, C::SMEM_BYTES, configured)) return -5;
   if (p.bn < 16 || p.bn > BN || p.bn % 16) return ERR_BAD_SIZE;
-  const int tiles = ((p.T + p.bn - 1) / p.bn) * ((p.N + BM - 1) / BM);
+  const int tiles = ((p.T + p.bn - 1) / p.bn) * ((p.N + WR - 1) / WR);
   const int ctas = tiles < sm_count ? tiles : sm_count;
-  return launch_ex(tc_gemm_persistent_kernel<BN, EPI, SWAP>, dim3(ctas), dim3(THREADS_MANY), C::SMEM_BYTES, s, 1, mw, mx, p);
+  return launch_ex(tc_gemm_persistent_kernel<BN, EPI, SWAP, WR>, dim3(ctas), dim3(THREADS_MANY), C::SMEM_BYTES, s, 1, mw, mx, p);
 }
 
 template <int BN, int EPI>
@@ -1362,7 +1365,7 @@ int launch_bn(int bn, bool norm, const CUtensorMap& mw, const CUtensorMap& mx, c
   return ERR_BAD_SIZE;
 }
 
-// Whether gate/up products of portions of 128 tokens and more put the tokens on the accumulator's rows
+// Whether gate/up products of portions of more than 64 tokens put the tokens on the accumulator's rows
 // (rllm_tc_gemm_set_token_rows): a tile is then 128 tokens x (128 gate + 128 up weight rows) and one product
 // of 256 columns per 16 of K, where weight rows on the accumulator's rows need two of 128 columns, which
 // read as many bytes of shared memory per cycle as it delivers. Same bits; 2,048 tokens, 2 x 8,192 x 2,048:
@@ -1370,7 +1373,7 @@ int launch_bn(int bn, bool norm, const CUtensorMap& mw, const CUtensorMap& mx, c
 bool g_token_rows = true;
 
 void plan(int epi, int T, int N, int K, int sm_count, int allow_split, int* bn_out, int* splits_out,
-          bool* few_out = nullptr) {
+          bool* few_out = nullptr, bool norm = false) {
   const bool dual = epi == EPI_SWIGLU;
   const int n_tiles = (N + BM - 1) / BM;
   int bn, splits = 1;
@@ -1398,7 +1401,10 @@ void plan(int epi, int T, int N, int K, int sm_count, int allow_split, int* bn_o
   // (33 to 64 tokens against a weight of many tiles, the output head: one token tile of 64 in the persistent
   // kernel reads the weight once, two tiles of 32 read it twice)
   const bool wide_head = T > 32 && T <= 64 && n_tiles >= 4 * sm_count;
-  const bool few = (T <= 64 && !wide_head) || (T <= 128 && splits > 1 && n_tiles * ((T + 63) / 64) * 4 <= sm_count);
+  // (33 to 64 tokens against a gate/up pair: the kernel with the tokens on the accumulator's rows, which has
+  // no ranges of K to merge and no norm in front, unless the norm is asked for in the same kernel)
+  const bool rows_kernel = dual && g_token_rows && !norm && T > 32;
+  const bool few = (T <= 64 && !wide_head && !rows_kernel) || (T <= 128 && splits > 1 && n_tiles * ((T + 63) / 64) * 4 <= sm_count);
   if (few) {
     bn = T <= 16 ? 16 : 32;
     if (bn >= 32) while (splits & (splits - 1)) splits &= splits - 1;     // wider tiles: a power of two
@@ -1419,7 +1425,9 @@ void plan(int epi, int T, int N, int K, int sm_count, int allow_split, int* bn_o
       const long long cost = waves * (w_rows + cand);
       if (best < 0 || cost < best) { best = cost; bn = cand; }
     }
-    if (dual && g_token_rows && T >= 128) bn = 128;           // tokens on the accumulator's rows: 128 a tile
+    // tokens on the accumulator's rows: 128 a tile, also where fewer tokens leave rows empty (96 tokens:
+    // 17.8 us against 19.1 with 96 tokens beside the weight rows)
+    if (dual && g_token_rows) bn = 128;
   }
   *bn_out = bn;
   *splits_out = splits;
@@ -1443,7 +1451,7 @@ int run(int epi, const void* X, long long ldx, const NormArgs* norm, const void*
   if (rc) return rc;
   int bn, splits;
   bool few;
-  plan(epi, T, N, K, sm_count, allow_split, &bn, &splits, &few);
+  plan(epi, T, N, K, sm_count, allow_split, &bn, &splits, &few, norm != nullptr);
   const bool many = !few;            // the persistent kernel (no ranges of K, no norm in front)
   if (many && norm) return ERR_BAD_SIZE;
   const bool dual = epi == EPI_SWIGLU;
@@ -1475,8 +1483,16 @@ int run(int epi, const void* X, long long ldx, const NormArgs* norm, const void*
     if (rope->hd % 16 || rope->rot_dim % 16 || ldc % 8) return ERR_BAD_SIZE;
     if (((uintptr_t)Cout | (uintptr_t)rope->kcache | (uintptr_t)rope->vcache | (uintptr_t)rope->cos_sin) & 15) return ERR_BAD_ALIGN;
   }
-  if (many && dual && g_token_rows && T >= 128 && N % 8 == 0 && ldc % 8 == 0 && !((uintptr_t)Cout & 15))
+  if (many && dual && g_token_rows && N % 8 == 0 && ldc % 8 == 0 && !((uintptr_t)Cout & 15)) {
+    // tiles of 64 gate and 64 up rows where tiles of 128 would leave half of the SMs without one
+    const long long tiles128 = (long long)((T + bn - 1) / bn) * ((N + BM - 1) / BM);
+    if (tiles128 * 2 <= sm_count + sm_count / 8) {
+      CUtensorMap mw64;
+      if ((rc = cached_map(&mw64, W, 2LL * N, K, K, 64))) return rc;
+      return launch_persistent<128, EPI_SWIGLU, true, 64>(mw64, mx, p, sm_count, s);
+    }
     return launch_persistent<128, EPI_SWIGLU, true>(mw, mx, p, sm_count, s);
+  }
   if (many) {
     // many tokens: the persistent kernel with two accumulator sets
     switch (epi) {

@@ -104,7 +104,7 @@ def set_pairs(on: bool) -> None:
 
 
 def set_token_rows(on: bool) -> None:
-    """Gate/up products of portions of 128 tokens and more with the tokens on the accumulator's rows."""
+    """Gate/up products of portions of more than 64 tokens with the tokens on the accumulator's rows."""
     ops._fn("sm100", "rllm_tc_gemm_set_token_rows")(int(on))
 
 

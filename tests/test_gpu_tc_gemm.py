@@ -18,6 +18,8 @@ def rel(a, b):
 
 SHAPES = [(1, 128, 64), (8, 384, 200), (16, 100, 72), (17, 3072, 2048), (64, 2048, 2048), (100, 640, 520),
           (128, 256, 8192), (65, 2048, 4096), (96, 200, 1024), (300, 1000, 264), (1, 128256, 256), (8, 2048, 8192), (600, 512, 1024),
+          # gate/up with the tokens on the accumulator's rows: tiles of 128 weight rows (many tiles) and of 64 (few)
+          (900, 1536, 192), (40, 1000, 264),
           # steps of at most 8 tokens with K a multiple of 32 and N of 16 run the weight-streaming kernel
           # (one to four chunks of K per warp held in registers, or more, fetched chunk by chunk)
           (1, 48, 96), (3, 2048, 2048), (8, 8192, 2048), (8, 2048, 3072), (5, 3072, 4096), (8, 4096, 14336),
@@ -55,8 +57,9 @@ def test_products_of_random_sizes(seed):
     import random
     from rllm_b200.kernels import ops, sm100
     r = random.Random(seed)
-    for _ in range(4):
-        T, N, K = r.randint(65, 900), 8 * r.randint(1, 90), 8 * r.randint(1, 80)
+    for i in range(4):
+        # the first of each seed under 128 tokens: one partial tile of the kernel with the tokens on the rows
+        T, N, K = r.randint(65, 127 if i == 0 else 900), 8 * r.randint(1, 90), 8 * r.randint(1, 80)
         x, w = rnd(T, K, seed=seed + 1), rnd(2 * N, K, seed=seed + 2, scale=K ** -0.5)
         xd, wd = x.to(DEV), w.to(DEV)
         w1 = wd[:N].contiguous()
@@ -261,6 +264,9 @@ def test_plan_splits_small_batches_only():
     assert sm100.plan(ops.EPI_STORE, 2048, 3072, 2048) == (176, 1)
     assert sm100.plan(ops.EPI_ACCUM_F32, 2048, 2048, 8192) == (240, 1)
     assert sm100.plan(ops.EPI_SWIGLU, 2048, 8192, 2048) == (128, 1)
+    assert sm100.plan(ops.EPI_SWIGLU, 96, 8192, 2048) == (128, 1)        # tokens on the accumulator's rows from 65 on
+    assert sm100.plan(ops.EPI_SWIGLU, 64, 8192, 2048) == (128, 1)        # and from 33 on where no norm is in front
+    assert sm100.plan(ops.EPI_SWIGLU, 32, 8192, 2048) == (32, 2)
     assert sm100.plan(ops.EPI_STORE_F32, 8, 128256, 2048) == (16, 1)
 
 
