@@ -275,7 +275,10 @@ def test_plan_splits_small_batches_only():
     (1, 64, 4, 2, 16, 16, None), (9, 96, 3, 1, 32, 8, None), (8, 2048, 32, 8, 64, 16, None),
     (70, 256, 5, 5, 64, 4, 32), (300, 128, 2, 1, 128, 16, None), (17, 512, 6, 2, 128, 32, 64),
     (5, 3072, 24, 8, 128, 16, None), (8, 96, 3, 1, 32, 8, None), (3, 160, 2, 2, 96, 4, None), (1, 2048, 32, 8, 64, 16, None),
-    (600, 192, 6, 2, 64, 16, None), (1100, 256, 4, 2, 32, 8, 16), (257, 64, 3, 3, 16, 4, None)])
+    (600, 192, 6, 2, 64, 16, None), (1100, 256, 4, 2, 32, 8, 16), (257, 64, 3, 3, 16, 4, None),
+    # 33 to 128 tokens against wide weights
+    (64, 256, 32, 8, 64, 16, None), (100, 128, 12, 4, 128, 16, None), (40, 192, 30, 10, 64, 8, None),
+    (33, 72, 40, 20, 32, 4, None), (128, 64, 24, 8, 64, 16, None)])
 def test_qkv_product_with_rotary_epilogue(T, K, nh, nkv, hd, page, rot, split):
     """q/k/v projection, rotation of q and k, and the cache write in one kernel, against the
     plain formulas: widths that are no multiple of the tile, head sizes 16 to 128, partial
