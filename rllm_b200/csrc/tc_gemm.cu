@@ -9,8 +9,10 @@
 // further down, whose token tile is any multiple of 16 up to 256 (128 with the gate/up pair),
 // chosen so that the tiles fill whole waves of CTAs. The accumulator D[weight row (TMEM lane),
 // token (TMEM column)] is read back with tcgen05.ld by the epilogue warps, thread = weight row, and
-// written as C[token][row]. Gate/up pairs of 128 tokens and more exchange the roles: tokens on the
-// accumulator's rows, the tile's 128 gate and 128 up weight rows one operand of 256 columns.
+// written as C[token][row]. Gate/up pairs of 33 tokens and more (with no norm in front) exchange the
+// roles: tokens on the accumulator's rows, the tile's 128 gate and 128 up weight rows one operand of
+// 256 columns; 64 + 64 rows where tiles of 128 would leave most SMs without one (up to 128 tokens
+// against 8,192 features).
 //
 // One CTA = one 128 x BN output tile over a range of K: warp 0 issues TMA loads into a ring of
 // shared-memory stages, warp 1 issues the MMAs (one thread) and owns the TMEM allocation,
